@@ -1,0 +1,162 @@
+"""The CPU oracle against the known-answer fixtures of CUV's own tests (tests/golden/make_golden.py)
+and against float64 dense computations for the cases the reference never tests."""
+import numpy as np
+import pytest
+
+from oracle import host_oracle as ho
+
+
+def F(a):
+    return np.asfortranarray(a, dtype=np.float32)
+
+
+def test_dia_to_dense_matches_reference_fixture(golden):
+    g = golden
+    A = ho.DiaHost(int(g["diamat_h"]), int(g["diamat_w"]), g["diamat_offsets"], int(g["diamat_stride"]), 1,
+                   g["diamat_vals"])
+    assert np.array_equal(A.to_dense(), g["diamat_dense"])        # src/tests/dia_mat.cpp:111-119
+    A = ho.DiaHost(int(g["spmv_h"]), int(g["spmv_w"]), g["spmv_offsets"], int(g["spmv_stride"]), 1, g["spmv_vals"])
+    assert np.array_equal(A.to_dense(), g["spmv_dense"])
+    for i in range(A.h):
+        for j in range(A.w):
+            c = A.cell_index(i, j)
+            assert (c < 0) == (abs(j - i) > 3)
+            if c >= 0:
+                assert A.vals[c] == g["spmv_dense"][i, j]
+
+
+def _spmv_fixture(g):
+    A = ho.DiaHost(int(g["spmv_h"]), int(g["spmv_w"]), g["spmv_offsets"], int(g["spmv_stride"]),
+                   int(g["spmv_rf"]), g["spmv_vals"])
+    return A, F(g["spmv_B"]), F(g["spmv_C"])
+
+
+def test_prod_trans_defaults_matches_reference_fixture(golden):
+    A, B, C = _spmv_fixture(golden)                                  # src/tests/spmv.cpp:103-115
+    out = F(np.full_like(B, np.nan))                                 # factC == 0: old contents must not matter
+    ho.prod(out, A, C, "t")
+    assert np.array_equal(out.astype(np.float64), golden["spmv_expect_t_1_0"])   # integers < 2^24: exact
+
+
+def test_prod_n_2_13_matches_reference_fixture(golden):
+    A, B, C = _spmv_fixture(golden)                                  # src/tests/spmv.cpp:116-136
+    ho.prod(C, A, B, "n", 2.0, 1.3)
+    np.testing.assert_allclose(C, golden["spmv_expect_n_2_13"], rtol=1e-6)
+
+
+def test_prod_t_2_13_matches_reference_fixture(golden):
+    A, B, C = _spmv_fixture(golden)                                  # src/tests/spmv.cpp:137-143
+    ho.prod(B, A, C, "t", 2.0, 1.3)
+    np.testing.assert_allclose(B, golden["spmv_expect_t_2_13"], rtol=1e-6)
+
+
+@pytest.mark.parametrize("literal", [False, True])
+def test_dd2dia_matches_reference_fixture(golden, literal):
+    g = golden                                                        # src/tests/densedense_to_dia.cpp:139-197
+    C = ho.DiaHost(int(g["dd2dia_h"]), int(g["dd2dia_w"]), g["dd2dia_offsets"], int(g["dd2dia_stride"]),
+                   int(g["dd2dia_rf"]))
+    ho.densedense_to_dia(C, F(g["dd2dia_A"]), F(g["dd2dia_B"]), literal_host=literal)
+    assert np.array_equal(C.vals.astype(np.float64), g["dd2dia_expect"])          # exact integers
+    assert np.array_equal(C.valid_mask().reshape(-1), g["dd2dia_mask"])
+
+
+def test_dd2dia_padding_untouched_and_factors():
+    rng = np.random.default_rng(5)
+    h, w, rf, nb = 24, 11, 2, 9
+    offs = np.array([3, -2, 0, 7, -11], dtype=np.int32)
+    C = ho.DiaHost(h, w, offs, 32, rf, rng.standard_normal(5 * 32).astype(np.float32))
+    old = C.vals.copy()
+    X, H = F(rng.standard_normal((h, nb))), F(rng.standard_normal((w, nb)))
+    ho.densedense_to_dia(C, X, H, 0.25, 0.5)
+    m = C.valid_mask().reshape(-1)
+    assert np.array_equal(C.vals[~m], old[~m])
+    dense = X.astype(np.float64) @ H.astype(np.float64).T
+    for s, k in enumerate(offs.tolist()):
+        for i in range(h):
+            j = i // rf + k
+            if 0 <= j < w:
+                assert m[s * 32 + i]
+                np.testing.assert_allclose(C.vals[s * 32 + i], 0.5 * old[s * 32 + i] + 0.25 * dense[i, j],
+                                           rtol=2e-5, atol=2e-6)
+            else:
+                assert not m[s * 32 + i]
+
+
+@pytest.mark.parametrize("rf", [1, 2, 4])
+@pytest.mark.parametrize("trans", ["n", "t"])
+def test_prod_row_fact_vs_float64_dense(rf, trans):
+    """Not pinned by any reference test (prod with row_fact > 1 is host-only code the reference never
+    exercises): checked against a float64 dense product of the dia->dense conversion."""
+    rng = np.random.default_rng(10 * rf + (trans == "t"))
+    w, nb = 13, 5
+    h = rf * 10
+    offs = np.array([-9, 4, 0, -1, 12, 2], dtype=np.int32)          # user order, unsorted
+    A = ho.DiaHost(h, w, offs, h + 3, rf, rng.standard_normal(6 * (h + 3)).astype(np.float32))
+    A.vals[~A.valid_mask().reshape(-1)] = np.nan                     # padding must never be read
+    D = A.to_dense().astype(np.float64)
+    if trans == "n":
+        B, C = F(rng.standard_normal((w, nb))), F(rng.standard_normal((h, nb)))
+        ref = 0.5 * C.astype(np.float64) + 1.5 * (D @ B)
+    else:
+        B, C = F(rng.standard_normal((h, nb))), F(rng.standard_normal((w, nb)))
+        ref = 0.5 * C.astype(np.float64) + 1.5 * (D.T @ B)
+    ho.prod(C, A, B, trans, 1.5, 0.5)
+    np.testing.assert_allclose(C, ref, rtol=1e-5, atol=1e-5)
+
+
+def test_prod_threads_bit_identical():
+    rng = np.random.default_rng(3)
+    h = w = 257
+    offs = np.sort(rng.choice(np.arange(-200, 201), 17, replace=False)).astype(np.int32)
+    A = ho.DiaHost(h, w, offs, h, 1, rng.uniform(-1, 1, 17 * h).astype(np.float32))
+    B = F(rng.uniform(-1, 1, (w, 33)))
+    C1, C2 = F(np.zeros((h, 33))), F(np.zeros((h, 33)))
+    ho.prod(C1, A, B, nthreads=1)
+    ho.prod(C2, A, B, nthreads=5)
+    assert np.array_equal(C1, C2)
+
+
+NAMES = {ho.RF_ADD: "add", ho.RF_MAX: "max", ho.RF_MIN: "min", ho.RF_ARGMAX: "argmax", ho.RF_ARGMIN: "argmin",
+         ho.RF_LOGADDEXP: "logaddexp", ho.RF_ADD_SQUARED: "addsq"}
+
+
+@pytest.mark.parametrize("rf", sorted(NAMES))
+@pytest.mark.parametrize("over_strided", [True, False])
+def test_reduce_matches_reference_fixture(golden, rf, over_strided):
+    src = F(golden["reduce_src"])                                    # src/tests/matrix_op.cpp:858-924
+    dst = np.full(270, np.nan, dtype=np.float32)
+    ho.reduce(dst, src, over_strided, rf, nthreads=3)
+    want = golden["reduce_%s_over_%s" % (NAMES[rf], "cols" if over_strided else "rows")]
+    if rf in (ho.RF_ARGMAX, ho.RF_ARGMIN):
+        assert np.array_equal(dst.astype(np.int64), want)
+    else:
+        np.testing.assert_allclose(dst, want, rtol=1e-5)
+
+
+def test_reduce_factors_mean_mult():
+    rng = np.random.default_rng(9)
+    src = F(rng.uniform(0.5, 1.5, (37, 21)))
+    old = rng.standard_normal(37).astype(np.float32)
+    dst = old.copy()
+    ho.reduce_to_col(dst, src, ho.RF_ADD, 0.25, 0.5)
+    np.testing.assert_allclose(dst, 0.5 * old + 0.25 * src.astype(np.float64).sum(1), rtol=1e-5)
+    dst = np.zeros(21, dtype=np.float32)
+    ho.reduce_to_row(dst, src, ho.RF_MEAN)
+    np.testing.assert_allclose(dst, src.astype(np.float64).mean(0), rtol=1e-5)
+    ho.reduce_to_row(dst, src, ho.RF_MULT)
+    np.testing.assert_allclose(dst, src.astype(np.float64).prod(0), rtol=1e-4)
+    ho.reduce_to_row(dst, src, ho.RF_ADDEXP)
+    np.testing.assert_allclose(dst, np.exp(src.astype(np.float64)).sum(0), rtol=1e-4)
+    with pytest.raises(RuntimeError):
+        ho.reduce_to_row(dst, src, ho.RF_MEAN, 2.0, 0.0)
+
+
+def test_bias_sigmoid_sample():
+    rng = np.random.default_rng(2)
+    a = F(rng.standard_normal((19, 7)))
+    b = rng.standard_normal(19).astype(np.float32)
+    u = F(rng.uniform(0, 1, (19, 7)))
+    p = 1.0 / (1.0 + np.exp(-(a.astype(np.float64) + b[:, None])))
+    s = ho.bias_sigmoid_sample(a, b, u)
+    np.testing.assert_allclose(a, p, rtol=1e-6)
+    assert np.array_equal(s, (a > u).astype(np.float32))
