@@ -1,0 +1,244 @@
+"""B200 implementation of CUV's DIA sparse hot path - Python mirror of the reference interface.
+
+The names follow CUV's disabled Python export of the same routines
+(``src/cuv_python/export_dia_mat.cpp:212-235``): ``dev_dia_matrix_f``, ``dev_block_descriptor_f``,
+``prod``, ``densedense_to_dia``, ``reduce_to_col`` / ``reduce_to_row``.  Every call goes through the C ABI
+of ``libcuvdia.so`` (``include/cuvdia.h``); torch only provides device memory and streams.
+
+Dense matrices are CUV's ``tensor<float, dev_memory_space, column_major>``: here a 2-D CUDA torch tensor of
+logical shape ``(rows, cols)`` whose rows are contiguous (``stride(0) == 1``); make one with
+:func:`colmajor_empty` or :func:`to_device`.
+"""
+import ctypes
+
+import numpy as np
+
+from . import _capi
+from ._capi import (CuvDiaError, MODE_EXACT, MODE_FAST, RF_ADD, RF_MEAN, RF_ADD_SQUARED, RF_MAX, RF_ARGMAX,
+                    RF_ARGMIN, RF_MIN, RF_MULT, RF_LOGADDEXP, RF_ADDEXP)
+
+__all__ = ["dev_dia_matrix_f", "dev_block_descriptor_f", "prod", "spmv", "densedense_to_dia", "reduce_to_col",
+           "reduce_to_row", "bias_sigmoid_sample", "axpby", "colmajor_empty", "to_device", "to_host",
+           "launch_count", "CuvDiaError", "MODE_EXACT", "MODE_FAST"]
+
+
+def _torch():
+    import torch
+    return torch
+
+
+def _stream():
+    return ctypes.c_void_p(_torch().cuda.current_stream().cuda_stream)
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def launch_count():
+    """Kernels launched by the library so far in this process."""
+    return int(_capi.lib().cuvdia_launch_count())
+
+
+# ---- dense column-major helpers ---------------------------------------------------------------------
+
+def colmajor_empty(rows, cols, device="cuda"):
+    torch = _torch()
+    return torch.empty((cols, rows), dtype=torch.float32, device=device).t()
+
+
+def to_device(a, device="cuda"):
+    """numpy (any layout) -> column-major CUDA matrix, or 1-D vector."""
+    torch = _torch()
+    a = np.asarray(a, dtype=np.float32)
+    if a.ndim == 1:
+        return torch.from_numpy(np.ascontiguousarray(a)).to(device)
+    return torch.from_numpy(np.ascontiguousarray(a.T)).to(device).t()
+
+
+def to_host(t):
+    """CUDA matrix -> float32 Fortran-ordered numpy array (or 1-D array)."""
+    if t.dim() == 1:
+        return t.detach().cpu().numpy()
+    return np.asfortranarray(t.detach().cpu().numpy())
+
+
+def _check_colmajor(t, name):
+    torch = _torch()
+    if not (isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == torch.float32 and t.dim() == 2):
+        raise CuvDiaError(_capi.ERR_INVALID, name + " must be a 2-D float32 CUDA tensor")
+    if t.shape[0] > 1 and t.stride(0) != 1:
+        raise CuvDiaError(_capi.ERR_INVALID, name + " must be column-major (stride(0) == 1)")
+    ld = t.stride(1) if t.shape[1] > 1 else t.shape[0]
+    if ld < t.shape[0]:
+        raise CuvDiaError(_capi.ERR_INVALID, name + " has overlapping columns")
+    return int(ld)
+
+
+# ---- dia_matrix<float, dev_memory_space> -------------------------------------------------------------------
+
+class dev_dia_matrix_f:
+    """``dia_matrix<float, dev_memory_space>`` (basics/dia_matrix.hpp:57-276): ``num_dia`` diagonals of
+    ``stride`` floats stored back to back in ``vec``; cell (i, j) lives at ``vec[slot(j - i//rf)*stride + i]``;
+    ``offsets`` keeps the caller's order.  Owns a plan (device offsets + kernel metadata)."""
+
+    def __init__(self, h, w, offsets, stride=None, row_fact=1, device="cuda"):
+        torch = _torch()
+        self.h, self.w, self.row_fact = int(h), int(w), int(row_fact)
+        self.offsets = np.ascontiguousarray(offsets, dtype=np.int32).reshape(-1)
+        self.num_dia = int(self.offsets.size)
+        self.stride = int(stride) if stride is not None else max(self.h, self.w)
+        self._plan = ctypes.c_void_p()
+        with torch.cuda.device(torch.device(device)):
+            _capi.check(_capi.lib().cuvdia_plan_create(
+                ctypes.byref(self._plan), self.h, self.w, self.num_dia, self.stride, self.row_fact,
+                self.offsets.ctypes.data_as(ctypes.POINTER(ctypes.c_int))))
+        self.vec = torch.empty(self.num_dia * self.stride, dtype=torch.float32, device=device)   # uninitialised, as CUV
+        band, nnz = ctypes.c_int(), ctypes.c_longlong()
+        _capi.check(_capi.lib().cuvdia_plan_info(self._plan, ctypes.byref(band), ctypes.byref(nnz)))
+        self.is_band, self.nnz = bool(band.value), int(nnz.value)
+
+    def __del__(self):
+        plan, self._plan = getattr(self, "_plan", None), None
+        if plan:
+            try:
+                _capi.lib().cuvdia_plan_destroy(plan)
+            except Exception:
+                pass
+
+    def __len__(self):
+        return self.h * self.w
+
+    @property
+    def shape(self):
+        return (self.h, self.w)
+
+    def dia(self, k):
+        """View on the storage of diagonal number ``k`` (dia_matrix.hpp:199-217)."""
+        slot = int(np.nonzero(self.offsets == k)[0][-1])
+        return self.vec[slot * self.stride:(slot + 1) * self.stride]
+
+    def has(self, i, j):
+        return bool(np.any(self.offsets == j - i // self.row_fact))
+
+    def __call__(self, i, j):
+        hit = np.nonzero(self.offsets == j - i // self.row_fact)[0]
+        return float(self.vec[int(hit[-1]) * self.stride + i]) if hit.size else 0.0
+
+    def set(self, i, j, val):
+        hit = np.nonzero(self.offsets == j - i // self.row_fact)[0]
+        if hit.size:
+            self.vec[int(hit[-1]) * self.stride + i] = val
+
+    def set_vec(self, vals):
+        """Copy host values (num_dia*stride floats) into the matrix: the host->device ``convert``
+        (convert/convert.cu:71-90)."""
+        v = np.ascontiguousarray(vals, dtype=np.float32).reshape(-1)
+        if v.size != self.num_dia * self.stride:
+            raise CuvDiaError(_capi.ERR_INVALID, "vals.size == num_dia*stride")
+        self.vec.copy_(_torch().from_numpy(v))
+        return self
+
+
+class dev_block_descriptor_f:
+    """``dev_block_descriptor<float>`` (matrix_ops/densedense_to_sparse.hpp:72-105).  CUV precomputes a
+    list of 16x16 tiles here; this implementation needs no tile list, so the descriptor only refers
+    to the matrix's plan.  It stays in the interface so calling code is unchanged."""
+
+    def __init__(self, mat):
+        self._mat = mat
+
+    def __len__(self):
+        # number of 16x16 tiles a stored diagonal crosses is what CUV reports; not needed here
+        return 0
+
+
+# ---- operations --------------------------------------------------------------------------------------
+
+def prod(C, A, B, transA="n", transB="n", factAB=1.0, factC=0.0, mode=MODE_EXACT):
+    """C = factC*C + factAB*op(A)*B (matrix_ops/matrix_ops.hpp:118-119, matrix_ops/spmv.cu:221-247)."""
+    ldc, ldb = _check_colmajor(C, "C"), _check_colmajor(B, "B")
+    if C.shape[1] != B.shape[1]:
+        raise CuvDiaError(_capi.ERR_INVALID, "dst.shape()[1] == B.shape()[1]")
+    rows_b, rows_c = (A.h, A.w) if transA == "t" else (A.w, A.h)
+    if transA in ("n", "t") and (B.shape[0] != rows_b or C.shape[0] != rows_c):
+        raise CuvDiaError(_capi.ERR_INVALID, "operand heights match the matrix (spmv.cu:159-160,180-181)")
+    _capi.check(_capi.lib().cuvdia_prod_f32(A._plan, _ptr(A.vec), _ptr(B), ldb, _ptr(C), ldc, int(C.shape[1]),
+                                            transA.encode(), transB.encode(), factAB, factC, mode, _stream()))
+    return C
+
+
+def spmv(dst, A, v, transA="n", factAv=1.0, factC=0.0, mode=MODE_EXACT):
+    """dst = factC*dst + factAv*op(A)*v for one or several vectors packed column-major in 1-D tensors
+    (matrix_ops/matrix_ops.hpp:277-278, spmv.cu:248-253)."""
+    rows_b, rows_c = (A.h, A.w) if transA == "t" else (A.w, A.h)
+    if v.numel() % rows_b or dst.numel() // rows_c != v.numel() // rows_b or dst.numel() % rows_c:
+        raise CuvDiaError(_capi.ERR_INVALID, "vector sizes are multiples of the matrix dimensions")
+    n = v.numel() // rows_b
+    _capi.check(_capi.lib().cuvdia_prod_f32(A._plan, _ptr(A.vec), _ptr(v), rows_b, _ptr(dst), rows_c, n,
+                                            transA.encode(), b"n", factAv, factC, mode, _stream()))
+    return dst
+
+
+def densedense_to_dia(C, Cbd, A, B, factAB=1.0, factC=0.0):
+    """C_dia = factC*C_dia + factAB*(A*B^T on the stored diagonals)
+    (matrix_ops/densedense_to_sparse.hpp:123-130)."""
+    lda, ldb = _check_colmajor(A, "A"), _check_colmajor(B, "B")
+    if C.w != B.shape[0] or C.h != A.shape[0] or A.shape[1] != B.shape[1]:
+        raise CuvDiaError(_capi.ERR_INVALID, "dst.w()==B.shape()[0] && dst.h()==A.shape()[0] && "
+                                             "A.shape()[1]==B.shape()[1]")
+    _capi.check(_capi.lib().cuvdia_dd2dia_f32(C._plan, _ptr(C.vec), _ptr(A), lda, _ptr(B), ldb, int(A.shape[1]),
+                                              factAB, factC, _stream()))
+    return C
+
+
+def _reduce(dst, src, over_first_axis_kept, rf, factNew, factOld):
+    torch = _torch()
+    if not (src.is_cuda and src.dtype == torch.float32 and src.dim() == 2 and src.is_cuda and dst.is_cuda):
+        raise CuvDiaError(_capi.ERR_INVALID, "src must be a 2-D float32 CUDA tensor")
+    if src.stride(0) == 1 and (src.shape[1] == 1 or src.stride(1) == src.shape[0]):      # column-major
+        n_contig, n_strided, keep_contig = src.shape[0], src.shape[1], over_first_axis_kept
+    elif src.stride(1) == 1 and (src.shape[0] == 1 or src.stride(0) == src.shape[1]):    # row-major
+        n_contig, n_strided, keep_contig = src.shape[1], src.shape[0], not over_first_axis_kept
+    else:
+        raise CuvDiaError(_capi.ERR_INVALID, "src must be densely packed")
+    if dst.numel() != (n_contig if keep_contig else n_strided) or not dst.is_contiguous():
+        raise CuvDiaError(_capi.ERR_INVALID, "main_dim == v.size()")
+    _capi.check(_capi.lib().cuvdia_reduce_f32(_ptr(dst), _ptr(src), n_contig, n_strided, 1 if keep_contig else 0,
+                                              rf, factNew, factOld, _stream()))
+    return dst
+
+
+def reduce_to_col(dst, src, rf=RF_ADD, factNew=1.0, factOld=0.0):
+    """dst[i] = factOld*dst[i] + factNew*rf_j(src[i, j]); dst.size == src.shape[0]
+    (matrix_ops/matrix_ops.hpp:211-212, matrix_ops_reduce.cu:348-362)."""
+    return _reduce(dst, src, True, rf, factNew, factOld)
+
+
+def reduce_to_row(dst, src, rf=RF_ADD, factNew=1.0, factOld=0.0):
+    """dst[j] = factOld*dst[j] + factNew*rf_i(src[i, j]); dst.size == src.shape[1]
+    (matrix_ops/matrix_ops.hpp:227-228, matrix_ops_reduce.cu:364-379)."""
+    return _reduce(dst, src, False, rf, factNew, factOld)
+
+
+def bias_sigmoid_sample(act, bias=None, u=None, sample=None):
+    """act <- sigmoid(act + bias[:, None]); sample <- (act > u) as 0/1 floats when ``u`` is given
+    (matrix_plus_col + SF_SIGM + rnd_binarize's compare, examples/rbm/base.py:52-54,93-106)."""
+    ld = _check_colmajor(act, "act")
+    ldu = lds = 0
+    if u is not None:
+        ldu = _check_colmajor(u, "u")
+        if sample is None:
+            sample = colmajor_empty(act.shape[0], act.shape[1], act.device)
+        lds = _check_colmajor(sample, "sample")
+    _capi.check(_capi.lib().cuvdia_bias_sigmoid_sample_f32(_ptr(act), ld, _ptr(bias), _ptr(u), ldu, _ptr(sample),
+                                                           lds, int(act.shape[0]), int(act.shape[1]), _stream()))
+    return sample
+
+
+def axpby(dst, x, y, a, b):
+    """dst = a*x + b*y (apply_binary_functor BF_AXPBY, tensor_ops/tensor_ops.hpp:530-655)."""
+    if not (dst.numel() == x.numel() == y.numel()):
+        raise CuvDiaError(_capi.ERR_INVALID, "sizes match")
+    _capi.check(_capi.lib().cuvdia_axpby_f32(_ptr(dst), _ptr(x), _ptr(y), a, b, dst.numel(), _stream()))
+    return dst

@@ -1,0 +1,220 @@
+// extern "C" layer of libcuvdia.so: argument checks (CUV's cuvAssert preconditions turned into
+// error codes), the plan object, error strings and the per-stream workspace.
+#include <algorithm>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <set>
+
+#include "cuvdia_internal.cuh"
+
+namespace cuvdia {
+
+static thread_local std::string t_last_error;
+std::atomic<unsigned long long> g_launches{0};
+
+void set_last_error(const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    t_last_error = buf;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+    set_last_error("%s: %s", what, cudaGetErrorString(e));
+    return e == cudaErrorMemoryAllocation ? CUVDIA_ERR_NOMEM : CUVDIA_ERR_CUDA;
+}
+
+int check_launch(const char* kernel) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, kernel);
+    return CUVDIA_OK;
+}
+
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (!cached[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+struct Workspace { void* ptr = nullptr; size_t bytes = 0; };
+static std::mutex g_ws_mutex;
+static std::map<std::pair<int, cudaStream_t>, Workspace> g_ws;
+
+int get_workspace(cudaStream_t stream, size_t bytes, void** ptr) {
+    int dev = 0;
+    CUVDIA_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(g_ws_mutex);
+    Workspace& ws = g_ws[std::make_pair(dev, stream)];
+    if (ws.bytes < bytes) {
+        if (ws.ptr) {
+            // the old buffer may still be in use by work queued on this stream
+            CUVDIA_CUDA(cudaStreamSynchronize(stream));
+            CUVDIA_CUDA(cudaFree(ws.ptr));
+            ws.ptr = nullptr; ws.bytes = 0;
+        }
+        size_t want = std::max(bytes, (size_t)1 << 20);
+        CUVDIA_CUDA(cudaMalloc(&ws.ptr, want));
+        ws.bytes = want;
+    }
+    *ptr = ws.ptr;
+    return CUVDIA_OK;
+}
+
+}  // namespace cuvdia
+
+using namespace cuvdia;
+
+extern "C" {
+
+const char* cuvdia_error_string(int code) {
+    switch (code) {
+        case CUVDIA_OK: return "success";
+        case CUVDIA_ERR_INVALID: return "precondition failed (invalid argument)";
+        case CUVDIA_ERR_CUDA: return "CUDA runtime error";
+        case CUVDIA_ERR_UNSUPPORTED: return "not supported";
+        case CUVDIA_ERR_NOMEM: return "out of memory";
+        default: return "unknown cuvdia error code";
+    }
+}
+
+const char* cuvdia_last_error_message(void) { return t_last_error.c_str(); }
+
+unsigned long long cuvdia_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int cuvdia_plan_create(cuvdia_plan** out, int h, int w, int num_dia, int stride, int row_fact,
+                       const int* offsets_host) {
+    CUVDIA_REQUIRE(out != nullptr);
+    *out = nullptr;
+    CUVDIA_REQUIRE(h > 0 && w > 0);
+    CUVDIA_REQUIRE(num_dia > 0);
+    CUVDIA_REQUIRE(row_fact > 0);                       // basics/dia_matrix.hpp:106
+    CUVDIA_REQUIRE(stride >= h);                        // cells are indexed by row (dia_matrix.hpp:234,242)
+    CUVDIA_REQUIRE(offsets_host != nullptr);
+    CUVDIA_REQUIRE((long long)num_dia * (long long)stride <= 2147483647LL);   // basics/tensor.hpp:209-213
+    std::set<int> seen;
+    for (int k = 0; k < num_dia; k++) {
+        if (!seen.insert(offsets_host[k]).second) {
+            set_last_error("offsets must be distinct (offset %d appears twice)", offsets_host[k]);
+            return CUVDIA_ERR_INVALID;
+        }
+    }
+    cuvdia_plan* p = new (std::nothrow) cuvdia_plan();
+    if (!p) { set_last_error("host allocation failed"); return CUVDIA_ERR_NOMEM; }
+    p->h = h; p->w = w; p->nd = num_dia; p->stride = stride; p->rf = row_fact;
+    p->offsets.assign(offsets_host, offsets_host + num_dia);
+    p->d_offsets = nullptr; p->scratch = nullptr; p->scratch_floats = 0;
+    p->is_band = true;
+    for (int k = 1; k < num_dia; k++) if (p->offsets[k] != p->offsets[0] + k) { p->is_band = false; break; }
+    p->band_lo = p->offsets[0];
+    p->off_min = *std::min_element(p->offsets.begin(), p->offsets.end());
+    p->off_max = *std::max_element(p->offsets.begin(), p->offsets.end());
+    p->nnz = 0;
+    for (int k = 0; k < num_dia; k++) {                 // matrix_ops/spmv.cu:185-189
+        long long o = p->offsets[k];
+        long long rs = (long long)row_fact * std::max(0LL, -o), js = std::max(0LL, o);
+        long long n = std::min((long long)h - rs, (long long)row_fact * ((long long)w - js));
+        if (n > 0) p->nnz += n;
+    }
+    cudaError_t e = cudaGetDevice(&p->device);
+    if (e == cudaSuccess) e = cudaMalloc(&p->d_offsets, sizeof(int) * (size_t)num_dia);
+    if (e == cudaSuccess)
+        e = cudaMemcpy(p->d_offsets, p->offsets.data(), sizeof(int) * (size_t)num_dia, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        if (p->d_offsets) cudaFree(p->d_offsets);
+        delete p;
+        return cuda_fail(e, "cuvdia_plan_create");
+    }
+    *out = p;
+    return CUVDIA_OK;
+}
+
+int cuvdia_plan_destroy(cuvdia_plan* p) {
+    if (!p) return CUVDIA_OK;
+    if (p->d_offsets) cudaFree(p->d_offsets);
+    if (p->scratch) cudaFree(p->scratch);
+    delete p;
+    return CUVDIA_OK;
+}
+
+int cuvdia_plan_info(const cuvdia_plan* p, int* is_band, long long* nnz) {
+    CUVDIA_REQUIRE(p != nullptr);
+    if (is_band) *is_band = p->is_band ? 1 : 0;
+    if (nnz) *nnz = p->nnz;
+    return CUVDIA_OK;
+}
+
+const int* cuvdia_plan_offsets_device(const cuvdia_plan* p) { return p ? p->d_offsets : nullptr; }
+
+int cuvdia_prod_f32(const cuvdia_plan* p, const float* A_vals, const float* B, int ldb, float* C, int ldc,
+                    int ncols, char transA, char transB, float factAB, float factC, int mode, void* stream) {
+    CUVDIA_REQUIRE(p != nullptr);
+    CUVDIA_REQUIRE(transB == 'n');                       // matrix_ops/spmv.cu:213,231
+    CUVDIA_REQUIRE(transA == 'n' || transA == 't');      // make_spmv_header.pl:121-123
+    CUVDIA_REQUIRE(C != nullptr);                        // spmv.cu:233
+    CUVDIA_REQUIRE(A_vals != nullptr);                   // spmv.cu:234
+    CUVDIA_REQUIRE(B != nullptr);                        // spmv.cu:235
+    CUVDIA_REQUIRE(ncols >= 0);
+    CUVDIA_REQUIRE(mode == CUVDIA_MODE_EXACT || mode == CUVDIA_MODE_FAST);
+    const bool trans = transA == 't';
+    const int rows_b = trans ? p->h : p->w, rows_c = trans ? p->w : p->h;
+    CUVDIA_REQUIRE(ldb >= rows_b);                       // spmv.cu:159,180 (operand heights)
+    CUVDIA_REQUIRE(ldc >= rows_c);                       // spmv.cu:160,181,236-240
+    if (ncols == 0) return CUVDIA_OK;
+    return launch_prod(p, A_vals, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, (cudaStream_t)stream);
+}
+
+int cuvdia_dd2dia_f32(cuvdia_plan* p, float* C_vals, const float* A, int lda, const float* B, int ldb, int ncols,
+                      float factAB, float factC, void* stream) {
+    CUVDIA_REQUIRE(p != nullptr);
+    CUVDIA_REQUIRE(C_vals != nullptr);
+    CUVDIA_REQUIRE(A != nullptr && B != nullptr);
+    CUVDIA_REQUIRE(ncols >= 0);
+    CUVDIA_REQUIRE(lda >= p->h);                         // densedense_to_sparse.cu:215,277
+    CUVDIA_REQUIRE(ldb >= p->w);                         // densedense_to_sparse.cu:214,276
+    CUVDIA_REQUIRE(p->h % p->rf == 0);                   // densedense_to_sparse.cu:244-249 overruns otherwise
+    return launch_dd2dia(p, C_vals, A, lda, B, ldb, ncols, factAB, factC, (cudaStream_t)stream);
+}
+
+int cuvdia_reduce_f32(float* dst, const float* src, long long n_contig, long long n_strided, int over_strided,
+                      int functor, float factNew, float factOld, void* stream) {
+    CUVDIA_REQUIRE(dst != nullptr);
+    CUVDIA_REQUIRE(src != nullptr);                      // matrix_ops_reduce.cu:160,192
+    CUVDIA_REQUIRE(n_contig > 0 && n_strided > 0);
+    CUVDIA_REQUIRE(n_contig * n_strided <= 2147483647LL);
+    CUVDIA_REQUIRE(functor >= CUVDIA_RF_ADD && functor <= CUVDIA_RF_ADDEXP);
+    if (functor == CUVDIA_RF_MEAN) {                     // matrix_ops_reduce.cu:309-310
+        CUVDIA_REQUIRE(factNew == 1.f);
+        CUVDIA_REQUIRE(factOld == 0.f);
+    }
+    return launch_reduce(dst, src, n_contig, n_strided, over_strided != 0, functor, factNew, factOld,
+                         (cudaStream_t)stream);
+}
+
+int cuvdia_bias_sigmoid_sample_f32(float* act, int ld, const float* bias, const float* u, int ldu, float* sample,
+                                   int lds, int units, int ncols, void* stream) {
+    CUVDIA_REQUIRE(act != nullptr);
+    CUVDIA_REQUIRE(units > 0 && ncols >= 0);
+    CUVDIA_REQUIRE(ld >= units);
+    CUVDIA_REQUIRE((u == nullptr) == (sample == nullptr));
+    if (u) { CUVDIA_REQUIRE(ldu >= units); CUVDIA_REQUIRE(lds >= units); }
+    if (ncols == 0) return CUVDIA_OK;
+    return launch_bias_sigmoid_sample(act, ld, bias, u, ldu, sample, lds, units, ncols, (cudaStream_t)stream);
+}
+
+int cuvdia_axpby_f32(float* dst, const float* x, const float* y, float a, float b, long long n, void* stream) {
+    CUVDIA_REQUIRE(dst != nullptr && x != nullptr && y != nullptr);
+    CUVDIA_REQUIRE(n >= 0);
+    if (n == 0) return CUVDIA_OK;
+    return launch_axpby(dst, x, y, a, b, n, (cudaStream_t)stream);
+}
+
+}  // extern "C"

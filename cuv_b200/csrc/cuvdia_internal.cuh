@@ -1,0 +1,75 @@
+// Internal declarations shared by the translation units of libcuvdia.so.
+#pragma once
+#include <cuda_runtime.h>
+#include <atomic>
+#include <cstdarg>
+#include <algorithm>
+#include <cstdint>
+#include <cstdio>
+#include <string>
+#include <vector>
+
+#include "cuvdia.h"
+
+namespace cuvdia {
+
+// ---- error plumbing ---------------------------------------------------------------------------
+void set_last_error(const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);
+
+#define CUVDIA_REQUIRE(cond)                                                           \
+    do {                                                                               \
+        if (!(cond)) { ::cuvdia::set_last_error("%s", #cond); return CUVDIA_ERR_INVALID; } \
+    } while (0)
+
+#define CUVDIA_CUDA(call)                                                              \
+    do {                                                                               \
+        cudaError_t e__ = (call);                                                      \
+        if (e__ != cudaSuccess) return ::cuvdia::cuda_fail(e__, #call);                \
+    } while (0)
+
+extern std::atomic<unsigned long long> g_launches;
+inline void count_launch(unsigned n = 1) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+// Checks the launch that was just issued (configuration errors surface here, not at the next sync).
+int check_launch(const char* kernel);
+
+// ---- per-(device, stream) workspace for kernels that have no plan (reductions) -------------------
+// Grows on demand with cudaMalloc; contents are undefined between calls.
+int get_workspace(cudaStream_t stream, size_t bytes, void** ptr);
+
+int sm_count();
+
+}  // namespace cuvdia
+
+// ---- plan ------------------------------------------------------------------------------------------
+struct cuvdia_plan {
+    int h, w, nd, stride, rf;
+    int device;
+    std::vector<int> offsets;   // storage (user) order
+    int* d_offsets;             // device copy, storage order
+    bool is_band;               // offsets[k] == offsets[0] + k
+    int band_lo;                // offsets[0] when is_band
+    int off_min, off_max;
+    long long nnz;
+    // scratch for densedense_to_dia's batch split (floats); allocated on first need
+    float* scratch;
+    size_t scratch_floats;
+};
+
+namespace cuvdia {
+// kernels' host-side launchers (each returns a CUVDIA_* code)
+int launch_prod(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
+                bool trans, float factAB, float factC, int mode, cudaStream_t st);
+int launch_dd2dia(cuvdia_plan* p, float* Cv, const float* A, int lda, const float* B, int ldb, int ncols,
+                  float factAB, float factC, cudaStream_t st);
+int launch_prod_generic(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
+                        bool trans, float factAB, float factC, int mode, cudaStream_t st);
+int launch_dd2dia_generic(cuvdia_plan* p, float* Cv, const float* A, int lda, const float* B, int ldb, int ncols,
+                          float factAB, float factC, cudaStream_t st);
+int ensure_plan_scratch(cuvdia_plan* p, size_t floats, cudaStream_t st);
+int launch_reduce(float* dst, const float* src, long long n_contig, long long n_strided, bool over_strided,
+                  int functor, float factNew, float factOld, cudaStream_t st);
+int launch_bias_sigmoid_sample(float* act, int ld, const float* bias, const float* u, int ldu, float* sample,
+                               int lds, int units, int ncols, cudaStream_t st);
+int launch_axpby(float* dst, const float* x, const float* y, float a, float b, long long n, cudaStream_t st);
+}  // namespace cuvdia

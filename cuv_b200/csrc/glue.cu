@@ -1,0 +1,72 @@
+// Element-wise glue of the RBM step: bias add + logistic + compare-to-uniform in one pass over a
+// column-major activation matrix, and the AXPBY update of apply_binary_functor.
+#include "cuvdia_internal.cuh"
+
+namespace cuvdia {
+
+__device__ __forceinline__ float sigm(float x) { return 1.f / (1.f + expf(-x)); }   // tensor_ops/functors.hpp:122
+
+template <bool VEC>
+__global__ void __launch_bounds__(256)
+bias_sigmoid_sample_kernel(float* __restrict__ act, int ld, const float* __restrict__ bias,
+                           const float* __restrict__ u, int ldu, float* __restrict__ sample, int lds,
+                           int units, int ncols) {
+    const int per_col = VEC ? units / 4 : units;
+    const long long total = (long long)per_col * ncols;
+    for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total;
+         t += (long long)gridDim.x * blockDim.x) {
+        const int col = (int)(t / per_col);
+        const int i = (int)(t - (long long)col * per_col) * (VEC ? 4 : 1);
+        if (VEC) {
+            float4 a = *reinterpret_cast<float4*>(act + (size_t)col * ld + i);
+            if (bias) {
+                const float4 b = __ldg(reinterpret_cast<const float4*>(bias + i));
+                a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+            }
+            a.x = sigm(a.x); a.y = sigm(a.y); a.z = sigm(a.z); a.w = sigm(a.w);
+            *reinterpret_cast<float4*>(act + (size_t)col * ld + i) = a;
+            if (sample) {
+                const float4 r = __ldg(reinterpret_cast<const float4*>(u + (size_t)col * ldu + i));
+                float4 s;
+                s.x = a.x > r.x ? 1.f : 0.f; s.y = a.y > r.y ? 1.f : 0.f;       // random/random.cu:86-91
+                s.z = a.z > r.z ? 1.f : 0.f; s.w = a.w > r.w ? 1.f : 0.f;
+                *reinterpret_cast<float4*>(sample + (size_t)col * lds + i) = s;
+            }
+        } else {
+            float a = act[(size_t)col * ld + i];
+            if (bias) a += bias[i];
+            a = sigm(a);
+            act[(size_t)col * ld + i] = a;
+            if (sample) sample[(size_t)col * lds + i] = a > u[(size_t)col * ldu + i] ? 1.f : 0.f;
+        }
+    }
+}
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+int launch_bias_sigmoid_sample(float* act, int ld, const float* bias, const float* u, int ldu, float* sample,
+                               int lds, int units, int ncols, cudaStream_t st) {
+    bool vec = units % 4 == 0 && ld % 4 == 0 && aligned16(act) && (!bias || aligned16(bias));
+    if (u) vec = vec && ldu % 4 == 0 && lds % 4 == 0 && aligned16(u) && aligned16(sample);
+    const long long total = (long long)(vec ? units / 4 : units) * ncols;
+    const int blocks = (int)std::min<long long>((total + 255) / 256, 16LL * sm_count());
+    if (vec) bias_sigmoid_sample_kernel<true><<<blocks, 256, 0, st>>>(act, ld, bias, u, ldu, sample, lds, units, ncols);
+    else     bias_sigmoid_sample_kernel<false><<<blocks, 256, 0, st>>>(act, ld, bias, u, ldu, sample, lds, units, ncols);
+    count_launch();
+    return check_launch("bias_sigmoid_sample_kernel");
+}
+
+__global__ void __launch_bounds__(256)
+axpby_kernel(float* dst, const float* x, const float* y, float a, float b, long long n) {
+    for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < n; t += (long long)gridDim.x * blockDim.x)
+        dst[t] = a * x[t] + b * y[t];                                           // tensor_ops/functors.hpp:412-433
+}
+
+int launch_axpby(float* dst, const float* x, const float* y, float a, float b, long long n, cudaStream_t st) {
+    const int blocks = (int)std::min<long long>((n + 255) / 256, 16LL * sm_count());
+    axpby_kernel<<<blocks, 256, 0, st>>>(dst, x, y, a, b, n);
+    count_launch();
+    return check_launch("axpby_kernel");
+}
+
+}  // namespace cuvdia

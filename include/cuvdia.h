@@ -1,0 +1,162 @@
+/*
+ * cuvdia.h - C ABI of the B200 (sm_100a) implementation of CUV's DIA sparse hot path.
+ *
+ * Every entry point below replaces one device_memory_space routine of CUV; the comment on each
+ * names the reference interface (file:line within the CUV source tree) whose FFI it is.  CUV's
+ * C++ templates (include/cuv/...) forward their dev_memory_space specialisations to these calls.
+ *
+ * Conventions
+ *  - All matrix pointers are DEVICE pointers to fp32, column-major, with a leading dimension in
+ *    elements.  `offsets_host` is a HOST pointer.  `stream` is a cudaStream_t passed as void*;
+ *    NULL means the legacy default stream.  Calls are stream-ordered and do not synchronise
+ *    (CUV's blocking behaviour is restored by the C++ wrappers, which synchronise afterwards).
+ *  - Every function returns 0 on success or a CUVDIA_ERR_* code; cuvdia_error_string() names the
+ *    code and cuvdia_last_error_message() gives the failed precondition of the calling thread's
+ *    last failing call (the text CUV's cuvAssert would have thrown).  Preconditions are checked
+ *    before anything is launched.
+ *  - There is no CPU fallback: without a CUDA device every compute call fails with
+ *    CUVDIA_ERR_CUDA.
+ */
+#ifndef CUVDIA_H
+#define CUVDIA_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define CUVDIA_API __attribute__((visibility("default")))
+#else
+#define CUVDIA_API
+#endif
+
+#define CUVDIA_OK               0
+#define CUVDIA_ERR_INVALID      1   /* a precondition (CUV: cuvAssert) failed                      */
+#define CUVDIA_ERR_CUDA         2   /* a CUDA runtime call failed (CUV: cuvSafeCall/checkCudaError) */
+#define CUVDIA_ERR_UNSUPPORTED  3   /* valid in CUV's interface but not implemented here            */
+#define CUVDIA_ERR_NOMEM        4   /* device or host allocation failed                             */
+
+/* Arithmetic of prod.  EXACT evaluates every output in the order of CUV's host code
+ * (matrix_ops/spmv.cu:153-198): separate multiply and add, diagonals in storage order, and is
+ * bit-identical to it.  FAST fuses multiply and add (one rounding per term, same order). */
+#define CUVDIA_MODE_EXACT 0
+#define CUVDIA_MODE_FAST  1
+
+/* Reduce functors: the values of enum cuv::reduce_functor, matrix_ops/matrix_ops.hpp:185-196. */
+#define CUVDIA_RF_ADD          0
+#define CUVDIA_RF_MEAN         1
+#define CUVDIA_RF_ADD_SQUARED  2
+#define CUVDIA_RF_MAX          3
+#define CUVDIA_RF_ARGMAX       4
+#define CUVDIA_RF_ARGMIN       5
+#define CUVDIA_RF_MIN          6
+#define CUVDIA_RF_MULT         7
+#define CUVDIA_RF_LOGADDEXP    8
+#define CUVDIA_RF_ADDEXP       9
+
+CUVDIA_API const char* cuvdia_error_string(int code);
+CUVDIA_API const char* cuvdia_last_error_message(void);
+
+/* Number of kernels this library has launched in this process (all threads), for harnesses that
+ * must prove the CUDA path ran. */
+CUVDIA_API unsigned long long cuvdia_launch_count(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * Plan: the structure of one DIA matrix (shape, diagonals, row factor) with the device-side
+ * metadata and scratch the kernels need.  It replaces the internals of
+ * cuv::dev_block_descriptor (matrix_ops/densedense_to_sparse.hpp:72-105, ctor
+ * densedense_to_sparse.cu:123-171) and the per-call offset handling of spmv_dia_device
+ * (matrix_ops/spmv.cu:89-101); like the block descriptor it can be reused for every matrix with
+ * the same layout.  It never owns or reads matrix values.
+ *
+ * h, w        matrix height and width             (basics/matrix.hpp:49-106)
+ * num_dia     number of stored diagonals          (basics/dia_matrix.hpp:76,146)
+ * stride      floats per stored diagonal, >= h    (basics/dia_matrix.hpp:77,129-133; cells are
+ *             indexed by the ROW of the matrix: value(i,j) = vals[slot*stride + i], :228-243)
+ * row_fact    "steepness": diagonal k holds the cells (i, i/row_fact + k)   (:81,230)
+ * offsets_host  num_dia diagonal numbers in the caller's order; the order is the storage order
+ *             and is never changed (basics/dia_matrix.hpp:156-185).  Must be distinct.
+ * The plan is bound to the CUDA device that is current when it is created.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct cuvdia_plan cuvdia_plan;
+
+CUVDIA_API int cuvdia_plan_create(cuvdia_plan** plan, int h, int w, int num_dia, int stride, int row_fact,
+                       const int* offsets_host);
+CUVDIA_API int cuvdia_plan_destroy(cuvdia_plan* plan);
+
+/* Structure queries.  is_band: 1 when offsets are consecutive ascending integers in storage
+ * order (the banded kernels apply).  nnz: number of matrix cells the stored diagonals cover
+ * (sum over diagonals of N as in matrix_ops/spmv.cu:185-189). */
+CUVDIA_API int cuvdia_plan_info(const cuvdia_plan* plan, int* is_band, long long* nnz);
+
+/* Device pointer to the plan's copy of the offsets (int32, storage order), e.g. to initialise a
+ * dia_matrix<float,dev_memory_space>::get_offsets() tensor. */
+CUVDIA_API const int* cuvdia_plan_offsets_device(const cuvdia_plan* plan);
+
+/* ---------------------------------------------------------------------------------------------
+ * C = factC*C + factAB*op(A)*B with A in DIA format.
+ * Replaces cuv::prod(tensor&, const dia_matrix<float,dev_memory_space>&, const tensor&, char,
+ * char, const float&, const float&)  (matrix_ops/matrix_ops.hpp:118-119; device specialisation
+ * matrix_ops/spmv.cu:221-247 and the generated dispatch it calls) and cuv::spmv
+ * (matrix_ops/matrix_ops.hpp:277-278, spmv.cu:248-253), for any row_fact >= 1.
+ *
+ * transA 'n': B is w x ncols, C is h x ncols.   transA 't': B is h x ncols, C is w x ncols.
+ * factC == 0 means C is overwritten and never read (spmv.cu:153-154).  Cells of A_vals outside
+ * the range each diagonal covers are never read.  B and C must not overlap.
+ * Errors (CUVDIA_ERR_INVALID), mirroring spmv.cu:211-214,229-240: transA not 'n'/'t', transB
+ * not 'n', null pointers, ldb/ldc smaller than the row counts, ncols < 0.
+ * ------------------------------------------------------------------------------------------- */
+CUVDIA_API int cuvdia_prod_f32(const cuvdia_plan* plan, const float* A_vals,
+                    const float* B, int ldb, float* C, int ldc, int ncols,
+                    char transA, char transB, float factAB, float factC, int mode, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * C_dia = factC*C_dia + factAB*(A*B^T restricted to the stored diagonals).
+ * Replaces cuv::densedense_to_dia(dia_matrix<float,dev_memory_space>&, const
+ * dev_block_descriptor<float>&, const tensor&, const tensor&, const float&, const float&)
+ * (matrix_ops/densedense_to_sparse.hpp:123-130; launcher densedense_to_sparse.cu:253-296, kernel
+ * :51-120).  A is h x ncols, B is w x ncols.  factC == 0: C_dia cells are overwritten, not read;
+ * cells outside each diagonal's range are neither read nor written (:104-119).  The sum over the
+ * batch is evaluated in a fixed order, so repeated calls give identical bits.
+ * Requires h % row_fact == 0 (the reference's host loop overruns otherwise, :244-249).
+ * May allocate plan-owned scratch on first use (not during stream capture).
+ * ------------------------------------------------------------------------------------------- */
+CUVDIA_API int cuvdia_dd2dia_f32(cuvdia_plan* plan, float* C_vals, const float* A, int lda,
+                      const float* B, int ldb, int ncols, float factAB, float factC, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * dst = factOld*dst + factNew*functor(src) along one axis of a matrix.
+ * Replaces cuv::reduce_to_col / cuv::reduce_to_row (matrix_ops/matrix_ops.hpp:211-212,227-228;
+ * layout dispatch matrix_ops_reduce.cu:348-379, device launchers :155-215, kernels :39-147).
+ * src is n_strided lines of n_contig contiguous floats (a column-major n_contig x n_strided
+ * matrix, or a row-major n_strided x n_contig one).
+ *   over_strided != 0: reduce across lines; dst has n_contig entries
+ *       (reduce_to_col of a column-major matrix, reduce_to_row of a row-major one);
+ *   over_strided == 0: reduce along each line; dst has n_strided entries.
+ * factOld == 0: dst is not read (:95-99,139-144).  ARGMAX/ARGMIN store the index as float and
+ * ignore the factors; MEAN requires factNew == 1 and factOld == 0 (:308-313).
+ * Uses a library-owned per-stream workspace that may be allocated on first use.
+ * ------------------------------------------------------------------------------------------- */
+CUVDIA_API int cuvdia_reduce_f32(float* dst, const float* src, long long n_contig, long long n_strided,
+                      int over_strided, int functor, float factNew, float factOld, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Element-wise glue of the RBM step on a column-major [units x ncols] activation matrix:
+ *   act <- sigmoid(act + bias[unit])      (bias may be NULL)
+ *   sample <- act > u ? 1 : 0             (sample and u may both be NULL)
+ * Replaces the sequence matrix_plus_col (matrix_ops/matrix_ops.hpp:306-307), apply_scalar_functor
+ * SF_SIGM (tensor_ops/functors.hpp:122) and rnd_binarize's compare (random/random.cu:86-91) that
+ * examples/rbm/base.py:52-54,93-106 issues after each prod.
+ * ------------------------------------------------------------------------------------------- */
+CUVDIA_API int cuvdia_bias_sigmoid_sample_f32(float* act, int ld, const float* bias, const float* u, int ldu,
+                                   float* sample, int lds, int units, int ncols, void* stream);
+
+/* dst = a*x + b*y element-wise over n floats (apply_binary_functor BF_AXPBY,
+ * tensor_ops/tensor_ops.hpp:530-655, tensor_ops/functors.hpp:412-433); dst may alias x or y. */
+CUVDIA_API int cuvdia_axpby_f32(float* dst, const float* x, const float* y, float a, float b, long long n,
+                     void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CUVDIA_H */

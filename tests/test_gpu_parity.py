@@ -1,0 +1,320 @@
+"""GPU parity: every C-ABI routine against the CPU oracle on identical seeded inputs.
+
+prod in EXACT mode must be bit-identical to the oracle; prod in FAST mode within 1e-5 of the sum of
+|terms| (fused multiply-add rounds once per term); densedense_to_dia and additive reductions within
+1e-4*sqrt(batch/128) relative; index-valued and min/max reductions exactly."""
+import numpy as np
+import pytest
+
+from oracle import host_oracle as ho
+from tests.helpers import F, assert_bits_equal, make_dia, scattered_offsets, to_dev_dia
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def cb():
+    import torch
+    assert torch.cuda.is_available()
+    import cuv_b200
+    return cuv_b200
+
+
+def run_prod(cb, A, B, C0, trans, fab, fc, mode):
+    D = to_dev_dia(A)
+    Bd, Cd = cb.to_device(B), cb.to_device(C0)
+    before = cb.launch_count()
+    cb.prod(Cd, D, Bd, trans, "n", fab, fc, mode)
+    assert cb.launch_count() > before
+    return cb.to_host(Cd)
+
+
+def prod_case(cb, rng, h, w, offsets, rf, ncols, trans, fab, fc, stride=None):
+    A = make_dia(rng, h, w, offsets, rf, stride)
+    rb, rc = (h, w) if trans == "t" else (w, h)
+    B = F(rng.uniform(-1, 1, (rb, ncols)))
+    C0 = F(rng.uniform(-1, 1, (rc, ncols)))
+    if fc == 0:
+        C0[:] = np.nan                                   # factC == 0: C must never be read
+    want = C0.copy(order="F")
+    ho.prod(want, A, B, trans, fab, fc, nthreads=4)
+    got = run_prod(cb, A, B, C0, trans, fab, fc, cb.MODE_EXACT)
+    assert_bits_equal(got, want, "exact prod %s h=%d w=%d rf=%d nd=%d" % (trans, h, w, rf, len(offsets)))
+    fast = run_prod(cb, A, B, C0, trans, fab, fc, cb.MODE_FAST)
+    # bound: one rounding difference per term
+    Aabs = ho.DiaHost(h, w, A.offsets, A.stride, rf, np.abs(np.nan_to_num(A.vals)))
+    mag = F(np.abs(np.nan_to_num(C0)) * abs(fc))
+    ho.prod(mag, Aabs, F(np.abs(B)), trans, abs(fab), 1.0, nthreads=4)
+    assert np.all(np.abs(fast.astype(np.float64) - want) <= 1e-5 * mag + 1e-30)
+    return got
+
+
+def test_reference_fixture_spmv(cb, golden):
+    g = golden                                           # src/tests/spmv.cpp:103-129
+    A = ho.DiaHost(int(g["spmv_h"]), int(g["spmv_w"]), g["spmv_offsets"], int(g["spmv_stride"]), 1, g["spmv_vals"])
+    B, C = F(g["spmv_B"]), F(g["spmv_C"])
+    got = run_prod(cb, A, C, F(np.full_like(B, np.nan)), "t", 1.0, 0.0, cb.MODE_EXACT)
+    assert np.array_equal(got.astype(np.float64), g["spmv_expect_t_1_0"])
+    got = run_prod(cb, A, B, C, "n", 2.0, 1.3, cb.MODE_EXACT)
+    np.testing.assert_allclose(got, g["spmv_expect_n_2_13"], rtol=1e-6)
+    want = C.copy(order="F"); ho.prod(want, A, B, "n", 2.0, 1.3)
+    assert_bits_equal(got, want)
+
+
+@pytest.mark.parametrize("trans", ["n", "t"])
+@pytest.mark.parametrize("rf", [1, 2, 4])
+def test_prod_scattered_small(cb, trans, rf):
+    rng = np.random.default_rng(100 + rf + 10 * (trans == "t"))
+    w = 150
+    h = 57 * rf
+    offs = scattered_offsets(rng, 9, -(h // rf) + 1, w - 1, sort=False)   # user order, includes extreme diagonals
+    prod_case(cb, rng, h, w, offs, rf, 13, trans, 1.5, 0.5, stride=h + 5)
+    prod_case(cb, rng, h, w, offs, rf, 1, trans, 1.0, 0.0)
+
+
+@pytest.mark.parametrize("trans", ["n", "t"])
+@pytest.mark.parametrize("rf", [1, 2, 4])
+@pytest.mark.parametrize("lo,nd", [(-8, 16), (-5, 11), (3, 40), (-70, 33)])
+def test_prod_band_small(cb, trans, rf, lo, nd):
+    rng = np.random.default_rng(7 * nd + rf + 1000 * (trans == "t"))
+    w = 200
+    h = 64 * rf
+    offs = np.arange(lo, lo + nd, dtype=np.int32)
+    prod_case(cb, rng, h, w, offs, rf, 24, trans, 1.0, 0.0)
+    prod_case(cb, rng, h, w, offs, rf, 37, trans, 0.75, 2.0, stride=h + 12)
+
+
+@pytest.mark.parametrize("trans", ["n", "t"])
+def test_prod_band_ragged_sizes(cb, trans):
+    rng = np.random.default_rng(31 + (trans == "t"))
+    for h, w, ncols in [(257, 301, 65), (130, 97, 3), (1000, 1000, 129)]:
+        offs = np.arange(-17, 23, dtype=np.int32)
+        prod_case(cb, rng, h, w, offs, 1, ncols, trans, 1.0, 0.5)
+
+
+def test_prod_config0_shape(cb):
+    """BASELINE config 0: 4096x4096, 64 sorted scattered diagonals, batch 128, factors 1/0."""
+    rng = np.random.Generator(np.random.PCG64(1000))
+    offs = scattered_offsets(rng, 64, -2047, 2047)
+    prod_case(cb, rng, 4096, 4096, offs, 1, 128, "n", 1.0, 0.0)
+
+
+def test_prod_config1_shape_reduced(cb):
+    """BASELINE config 1 pattern (transposed, rf 4, band centred on 0, factC 0.5) at a quarter of the rows."""
+    rng = np.random.Generator(np.random.PCG64(1001))
+    offs = np.arange(-128, 128, dtype=np.int32)
+    prod_case(cb, rng, 4096, 1024, offs, 4, 96, "t", 1.0, 0.5)
+
+
+def test_prod_band_medium_both_ways(cb):
+    """RBM-like band (config 3 pattern) at 2048 units, batch 160: up ('n') and down ('t')."""
+    rng = np.random.Generator(np.random.PCG64(1003))
+    offs = np.arange(-64, 64, dtype=np.int32)
+    prod_case(cb, rng, 2048, 2048, offs, 1, 160, "n", 1.0, 0.0)
+    prod_case(cb, rng, 2048, 2048, offs, 1, 160, "t", 1.0, 0.0)
+
+
+def test_spmv_packed_vectors(cb):
+    rng = np.random.default_rng(77)
+    A = make_dia(rng, 64, 48, np.array([0, -3, 5], dtype=np.int32))
+    v = rng.uniform(-1, 1, 48 * 3).astype(np.float32)
+    D = to_dev_dia(A)
+    dst = cb.to_device(np.zeros(64 * 3, dtype=np.float32))
+    cb.spmv(dst, D, cb.to_device(v), "n", 2.0, 0.0)
+    want = F(np.zeros((64, 3)))
+    ho.prod(want, A, F(v.reshape(48, 3, order="F")), "n", 2.0, 0.0)
+    assert_bits_equal(cb.to_host(dst).reshape(64, 3, order="F"), want)
+
+
+def test_prod_preconditions(cb):
+    rng = np.random.default_rng(1)
+    A = make_dia(rng, 32, 16, np.arange(-3, 4, dtype=np.int32))
+    D = to_dev_dia(A)
+    B, C = cb.colmajor_empty(16, 6), cb.colmajor_empty(32, 6)
+    with pytest.raises(cb.CuvDiaError, match="transB == 'n'"):
+        cb.prod(C, D, B, "n", "t")
+    with pytest.raises(cb.CuvDiaError):
+        cb.prod(C, D, B, "x", "n")
+    with pytest.raises(cb.CuvDiaError):
+        cb.prod(C, D, cb.colmajor_empty(16, 5))
+    with pytest.raises(cb.CuvDiaError):
+        cb.prod(B, D, C, "n")                         # heights swapped
+    with pytest.raises(cb.CuvDiaError, match="distinct"):
+        cb.dev_dia_matrix_f(8, 8, [0, 1, 1])
+    with pytest.raises(cb.CuvDiaError, match="row_fact > 0"):
+        cb.dev_dia_matrix_f(8, 8, [0], row_fact=0)
+
+
+# ---- densedense_to_dia -------------------------------------------------------------------------------
+
+def dd_case(cb, rng, h, w, offsets, rf, ncols, fab, fc, stride=None, dist="rbm"):
+    C = make_dia(rng, h, w, offsets, rf, stride)
+    if dist == "rbm":
+        X = F((rng.uniform(0, 1, (h, ncols)) < 0.5).astype(np.float32))
+        H = F(1.0 / (1.0 + np.exp(-rng.standard_normal((w, ncols)))))
+    else:
+        X, H = F(rng.uniform(0, 1, (h, ncols))), F(rng.uniform(0, 1, (w, ncols)))
+    want = ho.DiaHost(h, w, C.offsets, C.stride, rf, C.vals.copy())
+    if fc == 0:
+        C.vals[C.valid_mask().reshape(-1)] = np.nan      # old values must not be read
+    ho.densedense_to_dia(want, X, H, fab, fc, nthreads=4)
+    D = to_dev_dia(C)
+    Xd, Hd = cb.to_device(X), cb.to_device(H)
+    bd = cb.dev_block_descriptor_f(D)
+    cb.densedense_to_dia(D, bd, Xd, Hd, fab, fc)
+    got = D.vec.cpu().numpy()
+    m = C.valid_mask().reshape(-1)
+    assert_bits_equal(got[~m], C.vals[~m], "cells outside the diagonals' ranges must be untouched")
+    tol = 1e-4 * np.sqrt(max(ncols, 128) / 128.0)
+    np.testing.assert_allclose(got[m], want.vals[m], rtol=tol, atol=tol * 1e-3)
+    D2 = to_dev_dia(C)
+    cb.densedense_to_dia(D2, bd, Xd, Hd, fab, fc)
+    assert_bits_equal(D2.vec.cpu().numpy()[m], got[m], "run-to-run reproducibility")
+
+
+def test_reference_fixture_dd2dia(cb, golden):
+    g = golden                                           # src/tests/densedense_to_dia.cpp:109-137,166-197
+    h, w, rf, S = int(g["dd2dia_h"]), int(g["dd2dia_w"]), int(g["dd2dia_rf"]), int(g["dd2dia_stride"])
+    D = cb.dev_dia_matrix_f(h, w, g["dd2dia_offsets"], S, rf)
+    D.vec.zero_()
+    cb.densedense_to_dia(D, cb.dev_block_descriptor_f(D), cb.to_device(g["dd2dia_A"]), cb.to_device(g["dd2dia_B"]))
+    assert np.array_equal(D.vec.cpu().numpy().astype(np.float64), g["dd2dia_expect"])
+
+
+@pytest.mark.parametrize("rf", [1, 2, 4])
+def test_dd2dia_scattered_small(cb, rf):
+    rng = np.random.default_rng(200 + rf)
+    w, h = 150, 60 * rf
+    offs = scattered_offsets(rng, 11, -(h // rf) + 1, w - 1, sort=False)
+    dd_case(cb, rng, h, w, offs, rf, 48, 1.0, 0.0, stride=h + 4)
+    dd_case(cb, rng, h, w, offs, rf, 200, 0.01, 0.9, dist="uniform")
+    dd_case(cb, rng, h, w, offs, rf, 1, -0.5, 1.0)
+
+
+@pytest.mark.parametrize("rf", [1, 2, 4])
+@pytest.mark.parametrize("lo,nd", [(-8, 16), (-5, 11), (3, 40), (-70, 133)])
+def test_dd2dia_band_small(cb, rf, lo, nd):
+    rng = np.random.default_rng(300 + rf + nd)
+    w, h = 200, 64 * rf
+    offs = np.arange(lo, lo + nd, dtype=np.int32)
+    dd_case(cb, rng, h, w, offs, rf, 96, 1.0, 0.0)
+    dd_case(cb, rng, h, w, offs, rf, 130, 0.01, 0.9, stride=h + 8)
+
+
+def test_dd2dia_config2_shape(cb):
+    """BASELINE config 2: 4096x4096, 128 sorted scattered diagonals, batch 1024, 0.01 / 0.9."""
+    rng = np.random.Generator(np.random.PCG64(1002))
+    offs = scattered_offsets(rng, 128, -2047, 2047)
+    dd_case(cb, rng, 4096, 4096, offs, 1, 1024, 0.01, 0.9)
+
+
+def test_dd2dia_band_medium(cb):
+    rng = np.random.Generator(np.random.PCG64(1013))
+    dd_case(cb, rng, 2048, 2048, np.arange(-64, 64, dtype=np.int32), 1, 256, 1.0 / 256, 0.0)
+    dd_case(cb, rng, 1000, 1100, np.arange(-30, 45, dtype=np.int32), 1, 77, 1.0, 1.0)
+
+
+def test_dd2dia_preconditions(cb):
+    D = cb.dev_dia_matrix_f(30, 16, [0, 1], row_fact=4)           # 30 % 4 != 0
+    with pytest.raises(cb.CuvDiaError, match="rf == 0"):
+        cb.densedense_to_dia(D, None, cb.colmajor_empty(30, 4), cb.colmajor_empty(16, 4))
+    D = cb.dev_dia_matrix_f(32, 16, [0, 1])
+    with pytest.raises(cb.CuvDiaError):
+        cb.densedense_to_dia(D, None, cb.colmajor_empty(32, 4), cb.colmajor_empty(16, 5))
+
+
+# ---- reductions ----------------------------------------------------------------------------------------
+
+ALL_RF = [ho.RF_ADD, ho.RF_MEAN, ho.RF_ADD_SQUARED, ho.RF_MAX, ho.RF_ARGMAX, ho.RF_ARGMIN, ho.RF_MIN, ho.RF_MULT,
+          ho.RF_LOGADDEXP, ho.RF_ADDEXP]
+
+
+def reduce_case(cb, rng, rows, cols, to_col, rf, fnew=1.0, fold=0.0, row_major=False):
+    import torch
+    lo = 0.5 if rf == ho.RF_MULT else -1.0
+    src = F(rng.uniform(lo, 1.5, (rows, cols)))
+    n_out = rows if to_col else cols
+    old = rng.standard_normal(n_out).astype(np.float32)
+    want = old.copy() if fold != 0 else np.full(n_out, np.nan, dtype=np.float32)
+    (ho.reduce_to_col if to_col else ho.reduce_to_row)(want, src, rf, fnew, fold, nthreads=4)
+    dsrc = torch.from_numpy(np.ascontiguousarray(src)).cuda() if row_major else cb.to_device(src)
+    dst = cb.to_device(old if fold != 0 else np.full(n_out, np.nan, dtype=np.float32))
+    (cb.reduce_to_col if to_col else cb.reduce_to_row)(dst, dsrc, rf, fnew, fold)
+    got = dst.cpu().numpy()
+    if rf in (ho.RF_MAX, ho.RF_MIN, ho.RF_ARGMAX, ho.RF_ARGMIN):
+        assert np.array_equal(got, want)
+    else:
+        n_red = cols if to_col else rows
+        tol = 1e-4 * np.sqrt(max(n_red, 128) / 128.0)
+        np.testing.assert_allclose(got, want, rtol=tol, atol=tol * 1e-2)
+
+
+@pytest.mark.parametrize("rf", ALL_RF)
+@pytest.mark.parametrize("to_col", [True, False])
+@pytest.mark.parametrize("row_major", [False, True])
+def test_reduce_reference_sweep(cb, rf, to_col, row_major):
+    """The shape of the reference's sweep (src/tests/matrix_op.cpp:858-924): 270x270, both axes, both layouts."""
+    rng = np.random.default_rng(rf * 4 + to_col * 2 + row_major)
+    reduce_case(cb, rng, 270, 270, to_col, rf, row_major=row_major)
+
+
+@pytest.mark.parametrize("to_col", [True, False])
+def test_reduce_shapes_and_factors(cb, to_col):
+    rng = np.random.default_rng(55 + to_col)
+    for rows, cols in [(1, 1), (1, 300), (300, 1), (4096, 96), (96, 4096), (33, 70001), (70001, 33), (2048, 2048)]:
+        reduce_case(cb, rng, rows, cols, to_col, ho.RF_ADD, 0.25, 0.5)
+        reduce_case(cb, rng, rows, cols, to_col, ho.RF_ARGMAX)
+    reduce_case(cb, rng, 16384, 256, to_col, ho.RF_ADD, 1.0 / 256, 1.0)
+
+
+def test_reduce_ties_take_first_index(cb):
+    import torch
+    src = np.zeros((64, 5000), dtype=np.float32, order="F")
+    src[:, 17] = 3.0; src[:, 4000] = 3.0
+    dst = torch.empty(64, device="cuda")
+    cb.reduce_to_col(dst, cb.to_device(src), ho.RF_ARGMAX)
+    assert np.array_equal(dst.cpu().numpy(), np.full(64, 17.0, dtype=np.float32))
+    srcT = np.asfortranarray(src.T)
+    dst = torch.empty(64, device="cuda")
+    cb.reduce_to_row(dst, cb.to_device(srcT), ho.RF_ARGMAX)
+    assert np.array_equal(dst.cpu().numpy(), np.full(64, 17.0, dtype=np.float32))
+
+
+def test_reduce_preconditions(cb):
+    import torch
+    src = cb.colmajor_empty(8, 4)
+    with pytest.raises(cb.CuvDiaError):
+        cb.reduce_to_col(torch.empty(4, device="cuda"), src)
+    with pytest.raises(cb.CuvDiaError, match="factNew == 1"):
+        cb.reduce_to_col(torch.empty(8, device="cuda"), src, ho.RF_MEAN, 2.0, 0.0)
+
+
+# ---- glue ------------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("units,ncols", [(64, 8), (37, 5), (4096, 33)])
+def test_bias_sigmoid_sample(cb, units, ncols):
+    rng = np.random.default_rng(units)
+    a = F(rng.standard_normal((units, ncols)) * 3)
+    b = rng.standard_normal(units).astype(np.float32)
+    p = a.copy(order="F")
+    ho.bias_sigmoid_sample(p, b, None)
+    u = F(rng.uniform(0, 1, (units, ncols)))
+    near = np.abs(p - u) < 1e-4                         # keep the compare away from ties (expf differs by ulps)
+    u[near] = np.where(p[near] > 0.5, 0.0, 1.0)
+    s_want = (p > u).astype(np.float32)
+    ad = cb.to_device(a)
+    sd = cb.bias_sigmoid_sample(ad, cb.to_device(b), cb.to_device(u))
+    np.testing.assert_allclose(cb.to_host(ad), p, rtol=1e-5)
+    assert np.array_equal(cb.to_host(sd), s_want)
+    ad = cb.to_device(a)
+    assert cb.bias_sigmoid_sample(ad) is None
+    q = a.copy(order="F"); ho.bias_sigmoid_sample(q, None, None)
+    np.testing.assert_allclose(cb.to_host(ad), q, rtol=1e-5)
+
+
+def test_axpby(cb):
+    rng = np.random.default_rng(4)
+    x, y = rng.standard_normal(1001).astype(np.float32), rng.standard_normal(1001).astype(np.float32)
+    xd, yd = cb.to_device(x), cb.to_device(y)
+    cb.axpby(xd, xd, yd, 0.9, -0.01)
+    assert_bits_equal(xd.cpu().numpy(), np.float32(0.9) * x + np.float32(-0.01) * y)
