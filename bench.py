@@ -1,0 +1,437 @@
+#!/usr/bin/env python
+"""Benchmark of the DIA sparse hot path on B200.
+
+Default workload (``--case rbm_cfg4``): the sparse-RBM CD-1 step of BASELINE config 4 - visible and
+hidden layers of 65536 units, a banded DIA weight matrix with 1024 diagonals (row_fact 1), global
+batch 8192 whose columns are sharded over the ranks (strong scaling); per step: prod up, prod down
+(transposed), prod up again for the negative phase, two densedense_to_dia, four bias reductions,
+the element-wise glue, and with more than one rank an NCCL all-reduce of the gradient diagonals
+and bias gradients.  Inputs are synthetic with the configuration's shapes and distributions.
+
+``python bench.py --gpus N --steps K --warmup W`` prints ONE JSON line (rank 0).  Launched under
+``torch.distributed.run`` for N > 1.  ``--impl reference`` times the CPU oracle (the restatement of
+CUV's host code) on all host cores on a bounded batch slice of the same workload.
+
+Other cases (single routines, used for profiling and for the per-configuration table):
+``--case prod_n|prod_t|dd2dia|reduce|glue`` on the band shape given by --units/--num-dia/--batch, and
+``--case cfg0|cfg1|cfg2|rbm_cfg3`` for the other BASELINE configurations.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "DIA prod / densedense_to_dia effective HBM GB/s and % of roofline at 1/2/4/8 B200"
+CASES = {
+    "rbm_cfg4": dict(units=65536, num_dia=1024, batch=8192),
+    "rbm_cfg3": dict(units=16384, num_dia=512, batch=1024),
+}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.path = index, None, "/tmp/cuvdia_clocks_%d_%d.csv" % (os.getpid(), index)
+
+    def start(self):
+        try:
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=self.out, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        sm, smax, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            p = [x.strip() for x in line.split(",")]
+            if len(p) < 8:
+                continue
+            try:
+                sm.append(float(p[0])); smax.append(float(p[1])); power.append(float(p[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, p[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        try:
+            os.remove(self.path)
+        except OSError:
+            pass
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        # samples under load: the upper half by power draw
+        cut = statistics.median(power)
+        loaded = [s for s, w in zip(sm, power) if w >= cut] or sm
+        return {"sm_mhz": statistics.median(loaded), "sm_max_mhz": max(smax), "reasons": sorted(reasons),
+                "samples": len(sm), "power_w_max": max(power)}
+
+
+def band_offsets(nd):
+    import numpy as np
+    return np.arange(-(nd // 2), nd - nd // 2, dtype=np.int32)
+
+
+def event_ms(pairs):
+    return [a.elapsed_time(b) for a, b in pairs]
+
+
+# ---------------------------------------------------------------------------------------------------
+# CPU arm: the oracle on the host cores, on a bounded batch slice
+# ---------------------------------------------------------------------------------------------------
+
+def cpu_rbm(units, nd, batch, sample_cols, steps, warmup):
+    """Times the CPU oracle's CD-1 step on ``sample_cols`` batch columns of the workload, with all host
+    threads; returns (seconds per step on the slice, threads)."""
+    from oracle import rbm_oracle
+    threads = os.cpu_count() or 1
+    W, V0, U_h, U_v = rbm_oracle.make_inputs(1004, units, units, band_offsets(nd), sample_cols, nthreads=threads)
+    ts = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        rbm_oracle.cd1_step(W, V0, U_h, U_v, batch_global=batch, nthreads=threads)
+        if i >= warmup:
+            ts.append(time.perf_counter() - t0)
+    return sum(ts) / len(ts), threads, W.nnz()
+
+
+def run_reference(args, cfg):
+    from cuv_b200 import rbm
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    units, nd, batch = cfg["units"], cfg["num_dia"], cfg["batch"]
+    sample = min(batch, args.cpu_sample_cols)
+    t, threads, nnz = cpu_rbm(units, nd, batch, sample, max(1, args.steps), max(0, min(args.warmup, 1)))
+    work = rbm.algorithmic_work(units, units, nd, nnz, batch)
+    t_full = t * (batch / float(sample))
+    value = work["bytes"] / t_full / 1e9
+    sample_txt = ("CD-1 step of the CPU oracle on the first %d of %d batch columns (same matrix), %d threads; "
+                  "time scaled linearly to the full batch" % (sample, batch, threads))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_full * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(args.case, cfg), "units": units, "num_dia": nd, "row_fact": 1,
+                   "global_batch": batch, "l2": "inputs larger than L2"},
+        "gflops": work["flops"] / t_full / 1e9,
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample_txt},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_name(case, cfg):
+    if case == "rbm_cfg4":
+        return ("BASELINE config 4: sparse RBM CD-1 step, visible=hidden=%d, DIA weights num_dia=%d row_fact=1 "
+                "band centred on 0, global batch %d sharded by columns" % (cfg["units"], cfg["num_dia"], cfg["batch"]))
+    if case == "rbm_cfg3":
+        return ("BASELINE config 3: sparse RBM CD-1 step, visible=hidden=%d, num_dia=%d, batch %d"
+                % (cfg["units"], cfg["num_dia"], cfg["batch"]))
+    return "%s on a %dx%d band with %d diagonals, batch %d" % (case, cfg["units"], cfg["units"], cfg["num_dia"],
+                                                              cfg["batch"])
+
+
+# ---------------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------------
+
+def run_ours(args, cfg):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import cuv_b200 as cb
+    from cuv_b200 import rbm
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the DIA path has no CPU fallback "
+                         "(use --impl reference for the CPU oracle)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    units, nd, batch = cfg["units"], cfg["num_dia"], cfg["batch"]
+    assert batch % world == 0
+    nb = batch // world
+    mode = cb.MODE_FAST if args.mode == "fast" else cb.MODE_EXACT
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1004)                      # identical weights on every rank
+    W = cb.dev_dia_matrix_f(units, units, band_offsets(nd), units, 1, device=dev)
+    W.vec.normal_(0.0, 0.01, generator=gen)
+    gen.manual_seed(2000 + rank)               # rank-specific batch columns
+    V0 = cb.colmajor_empty(units, nb, dev)
+    tmp = torch.rand((nb, units), device=dev, generator=gen)
+    V0.t().copy_((tmp < 0.3).float())
+    U_h, U_v = cb.colmajor_empty(units, nb, dev), cb.colmajor_empty(units, nb, dev)
+    U_h.t().copy_(torch.rand((nb, units), device=dev, generator=gen))
+    U_v.t().copy_(torch.rand((nb, units), device=dev, generator=gen))
+    del tmp
+    step = rbm.SparseRBMStep(W, nb, batch, mode, dev)
+    work = rbm.algorithmic_work(units, units, nd, W.nnz, nb)
+
+    def one_step():
+        step.step(V0, U_h, U_v)
+        if world > 1:
+            step.allreduce()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident timing ----
+    for _ in range(args.warmup):
+        one_step()
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    step.timers = {}
+    launches0 = cb.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        one_step()
+    e1.record()
+    barrier()
+    launches = cb.launch_count() - launches0
+    clocks = sampler.stop()
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    ms_step = ms_total / args.steps
+    op_ms = {k: statistics.mean(event_ms(v)) for k, v in step.timers.items()}
+    step.timers = None
+
+    # ---- end to end: host buffers in, results out, every step ----
+    e2e = None
+    if not args.no_e2e:
+        hV0 = torch.empty((nb, units), dtype=torch.float32, pin_memory=True)
+        hUh, hUv = torch.empty_like(hV0, pin_memory=True), torch.empty_like(hV0, pin_memory=True)
+        hV0.copy_(V0.t()); hUh.copy_(U_h.t()); hUv.copy_(U_v.t())
+        hG = torch.empty(step.G.vec.numel(), dtype=torch.float32, pin_memory=True) if rank == 0 else None
+        hb = torch.empty(step.bias_grad.numel(), dtype=torch.float32, pin_memory=True) if rank == 0 else None
+
+        def e2e_step():
+            V0.t().copy_(hV0, non_blocking=True)
+            U_h.t().copy_(hUh, non_blocking=True)
+            U_v.t().copy_(hUv, non_blocking=True)
+            one_step()
+            if rank == 0:
+                hG.copy_(step.G.vec, non_blocking=True)
+                hb.copy_(step.bias_grad, non_blocking=True)
+
+        e2e_step()
+        barrier()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        for _ in range(args.steps):
+            e2e_step()
+        a1.record()
+        barrier()
+        e2e_ms = max_over_ranks(a0.elapsed_time(a1)) / args.steps
+        e2e = {"value": world * work["bytes"] / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+               "h2d_bytes_per_step": int(world * 3 * units * nb * 4),
+               "d2h_bytes_per_step": int((step.G.vec.numel() + step.bias_grad.numel()) * 4),
+               "ms_per_step": e2e_ms}
+
+    status = 0
+    if rank == 0:
+        import ctypes
+        st = ctypes.c_int()
+        cb._capi.check(cb._capi.lib().cuvdia_plan_status(W._plan, ctypes.byref(st)))
+        status = st.value
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_src = load_peaks()
+    fp32_fused = cb.fp32_peak_tflops(True)
+    fp32_split = cb.fp32_peak_tflops(False)
+    # dominant kernel: the banded prod (3 of the 5 large launches per step)
+    prod_ms = (2 * op_ms["prod_n"] + op_ms["prod_t"]) / 3.0
+    prod_bytes = (2 * work["per_call_bytes"]["prod_n"] + work["per_call_bytes"]["prod_t"]) / 3.0
+    prod_flops = work["per_call_flops"]["prod_n"]
+    achieved = prod_bytes / (prod_ms * 1e-3) / 1e9
+    fp32_peak = fp32_fused if args.mode == "fast" else fp32_split
+    per_op = {}
+    for k, ms in op_ms.items():
+        per_op[k] = {"ms": ms, "gbs": work["per_call_bytes"][k] / (ms * 1e-3) / 1e9}
+        if k in work["per_call_flops"]:
+            per_op[k]["tflops"] = work["per_call_flops"][k] / (ms * 1e-3) / 1e12
+    line = {
+        "metric": METRIC, "value": world * work["bytes"] / (ms_step * 1e-3) / 1e9, "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(args.case, cfg), "units": units, "num_dia": nd, "row_fact": 1,
+                   "global_batch": batch, "batch_per_gpu": nb, "parallelism": "batch columns x%d" % world,
+                   "prod_arithmetic": args.mode, "l2": "inputs larger than L2 (each activation matrix %.0f MB)"
+                   % (units * nb * 4 / 1e6)},
+        "gflops": world * work["flops"] / (ms_step * 1e-3) / 1e9,
+        "roofline": {"bound": "hbm", "kernel": "prod_band_kernel", "achieved": achieved, "peak": peak,
+                     "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                     "ms_per_launch": prod_ms,
+                     "binding": "fp32 issue (no tensor cores on this path): %.1f TFLOP/s achieved of %.1f measured "
+                                "%s peak = %.2f" % (prod_flops / (prod_ms * 1e-3) / 1e12, fp32_peak,
+                                                    "fused" if args.mode == "fast" else "mul+add",
+                                                    prod_flops / (prod_ms * 1e-3) / 1e12 / fp32_peak)},
+        "fp32": {"achieved_tflops": prod_flops / (prod_ms * 1e-3) / 1e12, "peak_fused_tflops": fp32_fused,
+                 "peak_mul_add_tflops": fp32_split, "frac": prod_flops / (prod_ms * 1e-3) / 1e12 / fp32_peak},
+        "per_op": per_op, "clocks": clocks, "gpu_launches": int(launches), "plan_status": status,
+    }
+    if e2e:
+        line["e2e"] = e2e
+    if world == 1 and not args.no_cpu:
+        sample = min(batch, args.cpu_sample_cols)
+        t, threads, _ = cpu_rbm(units, nd, batch, sample, 1, 0)
+        t_full = t * (batch / float(sample))
+        line["cpu_baseline"] = {
+            "value": work["bytes"] / t_full / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": "CD-1 step of the CPU oracle on the first %d of %d batch columns, %d threads, %.1f s; "
+                      "time scaled linearly to the full batch" % (sample, batch, threads, t)}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_single(args, cfg):
+    """One routine on one GPU (profiling and per-configuration figures)."""
+    import numpy as np
+    import torch
+    import cuv_b200 as cb
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the DIA path has no CPU fallback")
+    torch.cuda.set_device(0)
+    mode = cb.MODE_FAST if args.mode == "fast" else cb.MODE_EXACT
+    rng = np.random.Generator(np.random.PCG64(1000))
+    case = args.case
+    if case == "cfg0":
+        h = w = 4096; nb = 128; rf = 1
+        offs = np.sort(rng.choice(np.arange(-2047, 2048), 64, replace=False)).astype(np.int32); op = "prod_n"
+    elif case == "cfg1":
+        h, w, nb, rf = 16384, 4096, 512, 4
+        offs = np.arange(-128, 128, dtype=np.int32); op = "prod_t"
+    elif case == "cfg2":
+        h = w = 4096; nb = 1024; rf = 1
+        offs = np.sort(rng.choice(np.arange(-2047, 2048), 128, replace=False)).astype(np.int32); op = "dd2dia"
+    else:
+        h = w = cfg["units"]; nb = cfg["batch"]; rf = 1
+        offs = band_offsets(cfg["num_dia"]); op = case
+    A = cb.dev_dia_matrix_f(h, w, offs, h, rf)
+    A.vec.uniform_(-1, 1)
+    X, Y = cb.colmajor_empty(h, nb), cb.colmajor_empty(w, nb)
+    X.uniform_(-1, 1); Y.uniform_(-1, 1)
+    vec = torch.empty(h, device="cuda")
+    nnz, nd = A.nnz, offs.size
+    if op == "prod_n":
+        fc = 0.0
+        fn = lambda: cb.prod(X, A, Y, "n", "n", 1.0, fc, mode)
+        byts, flops = 4 * (nnz + nd + w * nb + h * nb), 2.0 * nnz * nb
+    elif op == "prod_t":
+        fc = 0.5 if case == "cfg1" else 0.0
+        fn = lambda: cb.prod(Y, A, X, "t", "n", 1.0, fc, mode)
+        byts, flops = 4 * (nnz + nd + h * nb + w * nb * (2 if fc else 1)), 2.0 * nnz * nb
+    elif op == "dd2dia":
+        fa, fc = (0.01, 0.9) if case == "cfg2" else (1.0 / nb, 0.0)
+        fn = lambda: cb.densedense_to_dia(A, None, X, Y, fa, fc)
+        byts, flops = 4 * (h * nb + w * nb + nd + nnz * (2 if fc else 1)), 2.0 * nnz * nb
+    elif op == "reduce":
+        fn = lambda: cb.reduce_to_col(vec, X, cb.RF_ADD, 1.0, 0.0)
+        byts, flops = 4 * (h * nb + h), float(h * nb)
+    elif op == "glue":
+        S = cb.colmajor_empty(h, nb)
+        fn = lambda: cb.bias_sigmoid_sample(X, vec, Y[:h] if w >= h else X, S)
+        byts, flops = 16 * h * nb, 4.0 * h * nb
+    else:
+        raise SystemExit("unknown case " + case)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if args.flush_l2 else None
+    for _ in range(args.warmup):
+        fn()
+    torch.cuda.synchronize()
+    l0 = cb.launch_count()
+    ts = []
+    for _ in range(args.steps):
+        if flush is not None:
+            flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); fn(); b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    ms = statistics.median(ts)
+    peak, peak_src = load_peaks()
+    print(json.dumps({"case": case, "op": op, "h": h, "w": w, "num_dia": int(nd), "row_fact": rf, "batch": nb,
+                      "mode": args.mode, "ms": ms, "ms_min": min(ts), "gbs": byts / (ms * 1e-3) / 1e9,
+                      "hbm_frac": byts / (ms * 1e-3) / 1e9 / peak, "tflops": flops / (ms * 1e-3) / 1e12,
+                      "l2_flushed": bool(args.flush_l2), "gpu_launches": int(cb.launch_count() - l0)}), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--mode", default="exact", choices=["exact", "fast"])
+    ap.add_argument("--case", default="rbm_cfg4")
+    ap.add_argument("--units", type=int)
+    ap.add_argument("--num-dia", type=int)
+    ap.add_argument("--batch", type=int)
+    ap.add_argument("--cpu-sample-cols", type=int, default=64)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--flush-l2", action="store_true")
+    args = ap.parse_args()
+    cfg = dict(CASES.get(args.case, CASES["rbm_cfg3"]))
+    for k, v in (("units", args.units), ("num_dia", args.num_dia), ("batch", args.batch)):
+        if v:
+            cfg[k] = v
+    if args.impl == "reference":
+        return run_reference(args, cfg)
+    if args.case.startswith("rbm"):
+        return run_ours(args, cfg)
+    return run_single(args, cfg)
+
+
+if __name__ == "__main__":
+    main()

@@ -35,6 +35,13 @@ def _ptr(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else None
 
 
+def fp32_peak_tflops(fused=True):
+    """Measured FP32 ceiling of the current device in TFLOP/s (multiply-add = 2 flops)."""
+    out = ctypes.c_float()
+    _capi.check(_capi.lib().cuvdia_fp32_peak_tflops(1 if fused else 0, ctypes.byref(out)))
+    return float(out.value)
+
+
 def launch_count():
     """Kernels launched by the library so far in this process."""
     return int(_capi.lib().cuvdia_launch_count())

@@ -111,7 +111,7 @@ int cuvdia_plan_create(cuvdia_plan** out, int h, int w, int num_dia, int stride,
     if (!p) { set_last_error("host allocation failed"); return CUVDIA_ERR_NOMEM; }
     p->h = h; p->w = w; p->nd = num_dia; p->stride = stride; p->rf = row_fact;
     p->offsets.assign(offsets_host, offsets_host + num_dia);
-    p->d_offsets = nullptr; p->scratch = nullptr; p->scratch_floats = 0;
+    p->d_offsets = nullptr; p->scratch = nullptr; p->scratch_floats = 0; p->d_status = nullptr;
     p->is_band = true;
     for (int k = 1; k < num_dia; k++) if (p->offsets[k] != p->offsets[0] + k) { p->is_band = false; break; }
     p->band_lo = p->offsets[0];
@@ -128,8 +128,11 @@ int cuvdia_plan_create(cuvdia_plan** out, int h, int w, int num_dia, int stride,
     if (e == cudaSuccess) e = cudaMalloc(&p->d_offsets, sizeof(int) * (size_t)num_dia);
     if (e == cudaSuccess)
         e = cudaMemcpy(p->d_offsets, p->offsets.data(), sizeof(int) * (size_t)num_dia, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMalloc(&p->d_status, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(p->d_status, 0, sizeof(int));
     if (e != cudaSuccess) {
         if (p->d_offsets) cudaFree(p->d_offsets);
+        if (p->d_status) cudaFree(p->d_status);
         delete p;
         return cuda_fail(e, "cuvdia_plan_create");
     }
@@ -141,6 +144,7 @@ int cuvdia_plan_destroy(cuvdia_plan* p) {
     if (!p) return CUVDIA_OK;
     if (p->d_offsets) cudaFree(p->d_offsets);
     if (p->scratch) cudaFree(p->scratch);
+    if (p->d_status) cudaFree(p->d_status);
     delete p;
     return CUVDIA_OK;
 }
@@ -149,6 +153,12 @@ int cuvdia_plan_info(const cuvdia_plan* p, int* is_band, long long* nnz) {
     CUVDIA_REQUIRE(p != nullptr);
     if (is_band) *is_band = p->is_band ? 1 : 0;
     if (nnz) *nnz = p->nnz;
+    return CUVDIA_OK;
+}
+
+int cuvdia_plan_status(const cuvdia_plan* p, int* status) {
+    CUVDIA_REQUIRE(p != nullptr && status != nullptr);
+    CUVDIA_CUDA(cudaMemcpy(status, p->d_status, sizeof(int), cudaMemcpyDeviceToHost));
     return CUVDIA_OK;
 }
 

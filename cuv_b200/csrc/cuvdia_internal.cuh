@@ -54,6 +54,8 @@ struct cuvdia_plan {
     // scratch for densedense_to_dia's batch split (floats); allocated on first need
     float* scratch;
     size_t scratch_floats;
+    // device word set non-zero by a kernel whose bounded wait on a TMA barrier gave up
+    int* d_status;
 };
 
 namespace cuvdia {
@@ -67,6 +69,9 @@ int launch_prod_generic(const cuvdia_plan* p, const float* A, const float* B, in
 int launch_dd2dia_generic(cuvdia_plan* p, float* Cv, const float* A, int lda, const float* B, int ldb, int ncols,
                           float factAB, float factC, cudaStream_t st);
 int ensure_plan_scratch(cuvdia_plan* p, size_t floats, cudaStream_t st);
+bool prod_band_applicable(const cuvdia_plan* p, const float* A, const float* B, int ldb, int ncols);
+int launch_prod_band(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
+                     bool trans, float factAB, float factC, int mode, cudaStream_t st);
 int launch_reduce(float* dst, const float* src, long long n_contig, long long n_strided, bool over_strided,
                   int functor, float factNew, float factOld, cudaStream_t st);
 int launch_bias_sigmoid_sample(float* act, int ld, const float* bias, const float* u, int ldu, float* sample,

@@ -1,0 +1,323 @@
+// prod with a banded DIA operand (consecutive ascending diagonals, row_fact 1): the tiled kernel.
+//
+// With offsets lo, lo+1, ..., lo+nd-1 the product is a 1-D stencil with spatially varying
+// coefficients,   'n':  C[i,b] = sum_k A[k][i]       * B[i+lo+k, b]
+//                 't':  C[j,b] = sum_k A[k][j-lo-k]  * B[j-lo-k, b].
+// A block computes a 128 x 128 tile of C (256 threads, 8 rows x 8 columns each) and walks the band
+// in chunks of 32 steps.  Per chunk one thread issues two TMA tile loads (cp.async.bulk.tensor,
+// no multicast) into a double-buffered stage: the slice of the diagonal band and the window of B
+// rows the chunk touches, for all 128 batch columns (B's columns are contiguous runs of rows, so
+// the window is a 2-D box of the column-major operand).  Out-of-range rows/diagonals arrive as
+// zeros.  The band slice is then re-laid in shared memory ("skewed") so that the 8 coefficients a
+// thread needs in one step are contiguous; in the same pass they are multiplied by factAB and
+// cells whose matrix column/row falls outside the matrix are zeroed, so padding cells of the
+// diagonal storage never contribute (they may hold NaN).  In the main loop a step costs two
+// 128-bit loads of coefficients and a quarter of eight 128-bit loads of B for 64 multiply-adds,
+// with no register shuffling: stepping index q = (row in thread) + (diagonal) for 'n', and
+// q = (diagonal) - (row in thread) for 't', makes every thread row read the same B row in a step.
+// Per output the terms are still added in diagonal storage order, so the EXACT mode (separate
+// multiply and add) reproduces CUV's host loop (matrix_ops/spmv.cu:161-198) bit for bit, except
+// that skipped cells are added as +0 (a -0 accumulator becomes +0) and a non-finite B value next
+// to the band edge meets a zeroed coefficient.  A is read from HBM once per 128 batch columns and
+// stays in L2 across column tiles; the kernel is bound by FP32 issue, not by memory.
+#include <cuda.h>
+
+#include "cuvdia_internal.cuh"
+
+namespace cuvdia {
+
+namespace pb {
+constexpr int TM = 128;          // output rows per block
+constexpr int TN = 128;          // batch columns per block
+constexpr int KC = 32;           // steps per chunk
+constexpr int NRAW = KC + 7;     // diagonals a chunk touches
+constexpr int WR = 156;          // rows of the B window (>= KC + 120, = 4 * odd: conflict-free 128-bit loads)
+constexpr int THREADS = 256;
+constexpr int RAW_FLOATS_N = TM * NRAW;     // 'n': band slice is TM rows wide
+constexpr int RAW_FLOATS_T = WR * NRAW;     // 't': band slice is as wide as the B window
+constexpr int BS_FLOATS = WR * TN;
+constexpr int AS_FLOATS = KC * TM;
+__host__ __device__ constexpr size_t align128(size_t x) { return (x + 127) / 128 * 128; }
+template <bool TRANS> __host__ __device__ constexpr size_t raw_bytes() { return align128(sizeof(float) * (TRANS ? RAW_FLOATS_T : RAW_FLOATS_N)); }
+__host__ __device__ constexpr size_t bs_bytes() { return align128(sizeof(float) * BS_FLOATS); }
+template <bool TRANS> __host__ __device__ constexpr size_t smem_bytes() {
+    return 2 * raw_bytes<TRANS>() + 2 * bs_bytes() + sizeof(float) * AS_FLOATS + 64 /*barriers*/ + 128 /*alignment slack*/;
+}
+constexpr unsigned SPIN_LIMIT = 1u << 26;   // bounded wait on a TMA completion barrier
+}  // namespace pb
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Returns false if the barrier did not complete within the spin limit.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+    const unsigned addr = smem_u32(bar);
+    for (unsigned it = 0; it < pb::SPIN_LIMIT; it++) {
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+
+template <bool EXACT>
+__device__ __forceinline__ void mac(float& acc, float a, float b) {
+    if (EXACT) acc = __fadd_rn(acc, __fmul_rn(a, b));
+    else acc = fmaf(a, b, acc);
+}
+
+struct BandParams {
+    int h, w, nd, lo;         // matrix shape, number of diagonals, first offset
+    int rows_out;             // h ('n') or w ('t')
+    int ncols, ldc;
+    int rem;                  // lo mod 4 (non-negative): shift that keeps TMA x coordinates 16-byte aligned
+    int nchunks;
+    float fa, fc;
+    int vec_c;                // C allows 128-bit accesses
+    float* C;
+    int* status;              // set to 1 if a TMA wait gave up
+};
+
+template <bool TRANS, bool EXACT>
+__global__ void __launch_bounds__(pb::THREADS, 1)
+prod_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                 const BandParams P) {
+    using namespace pb;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+    auto raw = [&](int s) { return reinterpret_cast<float*>(base + s * raw_bytes<TRANS>()); };
+    auto Bs = [&](int s) { return reinterpret_cast<float*>(base + 2 * raw_bytes<TRANS>() + s * bs_bytes()); };
+    float* As = reinterpret_cast<float*>(base + 2 * raw_bytes<TRANS>() + 2 * bs_bytes());
+    unsigned long long* full = reinterpret_cast<unsigned long long*>(As + AS_FLOATS);
+
+    const int tid = threadIdx.x;
+    const int t0 = blockIdx.x * TM;               // first output row of the tile
+    const int n0 = blockIdx.y * TN;               // first batch column of the tile
+    const int lane = tid & 31, warp = tid >> 5;
+    const int rg = lane >> 4, cg = lane & 15;
+    const int r0 = (warp * 2 + rg) * 8;           // this thread's 8 output rows: t0 + r0 .. t0 + r0 + 7
+    // this thread's 8 columns: n0 + cg + 16*c
+
+    constexpr unsigned TX_BYTES = sizeof(float) * ((TRANS ? RAW_FLOATS_T : RAW_FLOATS_N) + BS_FLOATS);
+
+    // Chunk c covers steps q in [c*KC, (c+1)*KC).
+    //  'n': q = j + k + rem           (j = row within the thread's 8, k = diagonal index)
+    //       band slice rows k from c*KC - rem - 7, matrix rows from t0;
+    //       B window starts at matrix row t0 + lo - rem + c*KC; a thread reads window row r0 + qq.
+    //  't': q = k - j + 7 + rem
+    //       band slice rows k from c*KC - rem - 7, matrix rows = the B window's rows;
+    //       B window starts at matrix row t0 - lo + rem + 8 - (c+1)*KC; a thread reads window row r0 + KC-1 - qq.
+    auto issue = [&](int c, int s) {
+        const int y0 = c * KC - P.rem - 7;
+        const int xb = TRANS ? (t0 - P.lo + P.rem + 8 - (c + 1) * KC) : (t0 + P.lo - P.rem + c * KC);
+        mbar_expect_tx(&full[s], TX_BYTES);
+        tma_load_2d(raw(s), &mapA, TRANS ? xb : t0, y0, &full[s]);
+        tma_load_2d(Bs(s), &mapB, xb, n0, &full[s]);
+    };
+
+    if (tid == 0) {
+        mbar_init(&full[0], 1);
+        mbar_init(&full[1], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (tid == 0) {
+        issue(0, 0);
+        if (P.nchunks > 1) issue(1, 1);
+    }
+
+    float acc[8][8];
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+#pragma unroll
+        for (int c = 0; c < 8; c++) acc[j][c] = 0.f;
+    if (P.fc != 0.f) {
+#pragma unroll
+        for (int c = 0; c < 8; c++) {
+            const int col = n0 + cg + 16 * c;
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const int row = t0 + r0 + j;
+                if (col < P.ncols && row < P.rows_out) acc[j][c] = __fmul_rn(P.C[(size_t)col * P.ldc + row], P.fc);
+            }
+        }
+    }
+
+    for (int c = 0; c < P.nchunks; c++) {
+        const int s = c & 1;
+        if (!mbar_wait(&full[s], (c >> 1) & 1)) {
+            if (P.status) *P.status = 1;
+            return;
+        }
+        // ---- skew pass: As[qq][r] = factAB * A[k][matrix row], zero where the cell is outside the matrix ----
+        {
+            const int r = tid & (TM - 1);
+            const int j = r & 7;
+            const float* rw = raw(s);
+            const int y0 = c * KC - P.rem - 7;
+#pragma unroll 4
+            for (int qq = tid >> 7; qq < KC; qq += THREADS / TM) {
+                float v;
+                bool ok;
+                if (!TRANS) {
+                    const int rr = qq - j + 7;                      // row of the slice (diagonal k = y0 + rr)
+                    const int k = y0 + rr;
+                    const int jb = t0 + r + P.lo + k;               // matrix column of the cell
+                    ok = k >= 0 && k < P.nd && jb >= 0 && jb < P.w;
+                    v = rw[rr * TM + r];
+                } else {
+                    const int rr = qq + j;
+                    const int k = y0 + rr;
+                    const int wr = (r - j) + KC - 1 - qq;           // window row = matrix row - window start
+                    const int i = t0 - P.lo + P.rem + 8 - (c + 1) * KC + wr;
+                    ok = k >= 0 && k < P.nd && i >= 0 && i < P.h;
+                    v = rw[rr * WR + wr];
+                }
+                if (P.fa != 1.f) v = __fmul_rn(P.fa, v);
+                As[qq * TM + r] = ok ? v : 0.f;
+            }
+        }
+        __syncthreads();
+        // ---- main loop ----
+        const float* bsp = Bs(s) + (size_t)cg * WR + (TRANS ? (r0 + KC - 4) : r0);
+        const float* asp = As + r0;
+#pragma unroll 2
+        for (int g = 0; g < KC / 4; g++) {
+            float4 bw[8];
+#pragma unroll
+            for (int cc = 0; cc < 8; cc++)
+                bw[cc] = *reinterpret_cast<const float4*>(bsp + (size_t)cc * 16 * WR + (TRANS ? -4 * g : 4 * g));
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const float4 a0 = *reinterpret_cast<const float4*>(asp + (4 * g + u) * TM);
+                const float4 a1 = *reinterpret_cast<const float4*>(asp + (4 * g + u) * TM + 4);
+                const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+                for (int cc = 0; cc < 8; cc++) {
+                    float b;
+                    if (!TRANS) b = u == 0 ? bw[cc].x : u == 1 ? bw[cc].y : u == 2 ? bw[cc].z : bw[cc].w;
+                    else        b = u == 0 ? bw[cc].w : u == 1 ? bw[cc].z : u == 2 ? bw[cc].y : bw[cc].x;
+#pragma unroll
+                    for (int j = 0; j < 8; j++) mac<EXACT>(acc[j][cc], a[j], b);
+                }
+            }
+        }
+        __syncthreads();                 // everyone is done with stage s and with As
+        if (tid == 0 && c + 2 < P.nchunks) issue(c + 2, s);
+    }
+
+    // ---- store ----
+#pragma unroll
+    for (int cc = 0; cc < 8; cc++) {
+        const int col = n0 + cg + 16 * cc;
+        if (col >= P.ncols) continue;
+        float* cp = P.C + (size_t)col * P.ldc + t0 + r0;
+        if (P.vec_c && t0 + r0 + 8 <= P.rows_out) {
+            *reinterpret_cast<float4*>(cp) = make_float4(acc[0][cc], acc[1][cc], acc[2][cc], acc[3][cc]);
+            *reinterpret_cast<float4*>(cp + 4) = make_float4(acc[4][cc], acc[5][cc], acc[6][cc], acc[7][cc]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                if (t0 + r0 + j < P.rows_out) cp[j] = acc[j][cc];
+        }
+    }
+}
+
+// ---- host side ----------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// 2-D fp32 tensor map: dim0 (contiguous) x dim1 with a pitch in elements, box0 x box1 tile, zero fill.
+int make_map_2d(CUtensorMap* m, const float* base, long long dim0, long long dim1, long long pitch, int box0, int box1) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) { set_last_error("cuTensorMapEncodeTiled is not available from the driver"); return CUVDIA_ERR_CUDA; }
+    cuuint64_t dims[2] = {(cuuint64_t)dim0, (cuuint64_t)dim1};
+    cuuint64_t strides[1] = {(cuuint64_t)pitch * sizeof(float)};
+    cuuint32_t box[2] = {(cuuint32_t)box0, (cuuint32_t)box1};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_last_error("cuTensorMapEncodeTiled failed with code %d", (int)r); return CUVDIA_ERR_CUDA; }
+    return CUVDIA_OK;
+}
+
+static inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+bool prod_band_applicable(const cuvdia_plan* p, const float* A, const float* B, int ldb, int ncols) {
+    (void)ncols;
+    return p->is_band && p->rf == 1 && al16(A) && al16(B) && p->stride % 4 == 0 && ldb % 4 == 0 &&
+           get_encode() != nullptr;
+}
+
+template <bool TRANS, bool EXACT>
+static int launch_band_t(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
+                         float fa, float fc, cudaStream_t st) {
+    using namespace pb;
+    CUtensorMap mapA, mapB;
+    int rc = make_map_2d(&mapA, A, p->h, p->nd, p->stride, TRANS ? WR : TM, NRAW);
+    if (rc) return rc;
+    rc = make_map_2d(&mapB, B, TRANS ? p->h : p->w, ncols, ldb, WR, TN);
+    if (rc) return rc;
+    BandParams P;
+    P.h = p->h; P.w = p->w; P.nd = p->nd; P.lo = p->band_lo;
+    P.rows_out = TRANS ? p->w : p->h;
+    P.ncols = ncols; P.ldc = ldc;
+    P.rem = ((p->band_lo % 4) + 4) % 4;
+    P.nchunks = (p->nd + P.rem + 7 + KC - 1) / KC;
+    P.fa = fa; P.fc = fc;
+    P.vec_c = (al16(C) && ldc % 4 == 0) ? 1 : 0;
+    P.C = C; P.status = p->d_status;
+    static bool attr_done[2][2] = {{false, false}, {false, false}};
+    if (!attr_done[TRANS][EXACT]) {
+        CUVDIA_CUDA(cudaFuncSetAttribute(prod_band_kernel<TRANS, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem_bytes<TRANS>()));
+        attr_done[TRANS][EXACT] = true;
+    }
+    const int gx = (P.rows_out + TM - 1) / TM, gy = (ncols + TN - 1) / TN;
+    if (gy > 65535) { set_last_error("too many batch columns for the banded kernel"); return CUVDIA_ERR_UNSUPPORTED; }
+    prod_band_kernel<TRANS, EXACT><<<dim3(gx, gy), THREADS, smem_bytes<TRANS>(), st>>>(mapA, mapB, P);
+    count_launch();
+    return check_launch("prod_band_kernel");
+}
+
+int launch_prod_band(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
+                     bool trans, float fa, float fc, int mode, cudaStream_t st) {
+    const bool exact = mode == CUVDIA_MODE_EXACT;
+    if (trans) return exact ? launch_band_t<true, true>(p, A, B, ldb, C, ldc, ncols, fa, fc, st)
+                            : launch_band_t<true, false>(p, A, B, ldb, C, ldc, ncols, fa, fc, st);
+    return exact ? launch_band_t<false, true>(p, A, B, ldb, C, ldc, ncols, fa, fc, st)
+                 : launch_band_t<false, false>(p, A, B, ldb, C, ldc, ncols, fa, fc, st);
+}
+
+}  // namespace cuvdia

@@ -1,0 +1,115 @@
+"""The sparse-RBM contrastive-divergence (CD-1) step that calls the DIA path.
+
+Call order and scaling follow CUV's RBM trainer (examples/rbm/base.py:223-258 with one Gibbs step;
+upPass/downPass :48-54, gradient accumulation :76-83), with the dense weight products replaced by
+their DIA forms.  W is hidden x visible, so the up pass is ``prod(..., 'n')`` and the down pass the
+transposed product:
+
+    H0p = sigm(W V0 + c)      H0 = H0p > U_h          prod 'n'  + bias/sigmoid/compare
+    V1p = sigm(W^T H0 + b)    V1 = V1p > U_v          prod 't'  + bias/sigmoid/compare
+    H1p = sigm(W V1 + c)                              prod 'n'  + bias/sigmoid
+    G   =  (1/B) (H0p V0^T)|dia                       densedense_to_dia(factAB= 1/B, factC=0)
+    G   = -(1/B) (H1p V1^T)|dia + G                   densedense_to_dia(factAB=-1/B, factC=1)
+    gc  = (1/B)(sum_b H0p - sum_b H1p)                reduce_to_col x2 (second accumulates)
+    gb  = (1/B)(sum_b V0  - sum_b V1)                 reduce_to_col x2
+
+The uniform numbers U_h, U_v are inputs, so a step is deterministic.  With several ranks every rank
+holds the batch columns ``[r*B/P, (r+1)*B/P)`` and its own copy of W; B in the factors is the global
+batch, so the per-rank G, gc, gb are partial sums that one all-reduce completes.
+"""
+import cuv_b200 as cb
+
+
+class SparseRBMStep:
+    def __init__(self, W, batch_local, batch_global=None, mode=cb.MODE_EXACT, device="cuda"):
+        import torch
+        self.W = W
+        self.hid, self.vis = W.h, W.w
+        self.nb = int(batch_local)
+        self.B = int(batch_global if batch_global is not None else batch_local)
+        self.mode = mode
+        self.dev = device
+        E = cb.colmajor_empty
+        self.H0p, self.H0 = E(self.hid, self.nb, device), E(self.hid, self.nb, device)
+        self.V1p, self.V1 = E(self.vis, self.nb, device), E(self.vis, self.nb, device)
+        self.H1p = E(self.hid, self.nb, device)
+        # gradient with W's layout; padding cells are never written, keep them at zero
+        self.G = cb.dev_dia_matrix_f(W.h, W.w, W.offsets, W.stride, W.row_fact, device=device)
+        self.G.vec.zero_()
+        self.Gbd = cb.dev_block_descriptor_f(self.G)
+        # gc and gb share one buffer so that a single collective covers both
+        self.bias_grad = torch.zeros(self.hid + self.vis, dtype=torch.float32, device=device)
+        self.gc, self.gb = self.bias_grad[:self.hid], self.bias_grad[self.hid:]
+        self.b_vis = torch.zeros(self.vis, dtype=torch.float32, device=device)
+        self.c_hid = torch.zeros(self.hid, dtype=torch.float32, device=device)
+        self.timers = None        # optional dict name -> list of (start_event, end_event)
+
+    def _timed(self, name, fn):
+        if self.timers is None:
+            return fn()
+        import torch
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        r = fn()
+        e1.record()
+        self.timers.setdefault(name, []).append((e0, e1))
+        return r
+
+    def step(self, V0, U_h, U_v):
+        """One CD-1 gradient evaluation on this rank's batch columns; results in G.vec, gc, gb
+        (partial sums when batch_global > batch_local)."""
+        W, inv = self.W, 1.0 / self.B
+        t = self._timed
+        t("prod_n", lambda: cb.prod(self.H0p, W, V0, "n", "n", 1.0, 0.0, self.mode))
+        t("glue", lambda: cb.bias_sigmoid_sample(self.H0p, self.c_hid, U_h, self.H0))
+        t("prod_t", lambda: cb.prod(self.V1p, W, self.H0, "t", "n", 1.0, 0.0, self.mode))
+        t("glue", lambda: cb.bias_sigmoid_sample(self.V1p, self.b_vis, U_v, self.V1))
+        t("prod_n", lambda: cb.prod(self.H1p, W, self.V1, "n", "n", 1.0, 0.0, self.mode))
+        t("glue", lambda: cb.bias_sigmoid_sample(self.H1p, self.c_hid))
+        t("dd2dia", lambda: cb.densedense_to_dia(self.G, self.Gbd, self.H0p, V0, inv, 0.0))
+        t("dd2dia", lambda: cb.densedense_to_dia(self.G, self.Gbd, self.H1p, self.V1, -inv, 1.0))
+        t("reduce", lambda: cb.reduce_to_col(self.gc, self.H0p, cb.RF_ADD, inv, 0.0))
+        t("reduce", lambda: cb.reduce_to_col(self.gc, self.H1p, cb.RF_ADD, -inv, 1.0))
+        t("reduce", lambda: cb.reduce_to_col(self.gb, V0, cb.RF_ADD, inv, 0.0))
+        t("reduce", lambda: cb.reduce_to_col(self.gb, self.V1, cb.RF_ADD, -inv, 1.0))
+
+    def allreduce(self, group=None):
+        """Sum the partial gradients over the ranks (NCCL over NVLink): the diagonals of G and the
+        two bias gradients."""
+        allreduce_gradients(self.G.vec, self.bias_grad, group)
+
+
+def shard_columns(batch_global, world, rank):
+    """Batch columns [c0, c1) that ``rank`` of ``world`` owns; the dense operands are column-major,
+    so a shard is one contiguous block of memory."""
+    if batch_global % world:
+        raise ValueError("the global batch must divide evenly over the ranks")
+    nb = batch_global // world
+    return rank * nb, (rank + 1) * nb
+
+
+def allreduce_gradients(g_vec, bias_grad, group=None):
+    """In-place sum over the ranks of the per-rank partial gradients (every rank computed its
+    partials with the GLOBAL batch in the 1/B factor, so the sum is the full-batch gradient)."""
+    import torch.distributed as dist
+    dist.all_reduce(g_vec, op=dist.ReduceOp.SUM, group=group)
+    dist.all_reduce(bias_grad, op=dist.ReduceOp.SUM, group=group)
+
+
+def algorithmic_work(h, w, nd, nnz, nb):
+    """Bytes and flops of one step on ``nb`` batch columns, each operand counted once per routine
+    (prod: A values + offsets + B + C; densedense_to_dia: both dense operands + offsets + the
+    diagonals once or twice; reduction: the matrix + the output once or twice)."""
+    prod_n = 4 * (nnz + nd + w * nb + h * nb)
+    prod_t = 4 * (nnz + nd + h * nb + w * nb)
+    dd0 = 4 * (h * nb + w * nb + nd + nnz)
+    dd1 = 4 * (h * nb + w * nb + nd + 2 * nnz)
+    red = lambda n, acc: 4 * (n * nb + n * (2 if acc else 1))
+    glue_s, glue_n = 4 * 4, 4 * 2        # bytes per element: act r/w + u + sample, or act r/w
+    byts = {"prod_n": prod_n, "prod_t": prod_t, "dd2dia": (dd0 + dd1) / 2.0,
+            "reduce": (red(h, 0) + red(h, 1) + red(w, 0) + red(w, 1)) / 4.0,
+            "glue": (glue_s * h * nb + glue_s * w * nb + glue_n * h * nb) / 3.0}
+    total_bytes = 2 * prod_n + prod_t + dd0 + dd1 + red(h, 0) + red(h, 1) + red(w, 0) + red(w, 1)
+    flops = 5 * 2.0 * nnz * nb
+    return {"bytes": float(total_bytes), "flops": flops, "per_call_bytes": byts,
+            "per_call_flops": {"prod_n": 2.0 * nnz * nb, "prod_t": 2.0 * nnz * nb, "dd2dia": 2.0 * nnz * nb}}

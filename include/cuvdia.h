@@ -89,6 +89,12 @@ CUVDIA_API int cuvdia_plan_destroy(cuvdia_plan* plan);
  * (sum over diagonals of N as in matrix_ops/spmv.cu:185-189). */
 CUVDIA_API int cuvdia_plan_info(const cuvdia_plan* plan, int* is_band, long long* nnz);
 
+/* Device-side health word of the plan, copied to *status (blocking: waits for the device).  0 = no
+ * kernel of this plan ever gave up a bounded wait on an asynchronous copy; non-zero = one did and
+ * its output is incomplete.  Waits inside the kernels are bounded so that a fault in the copy
+ * engine cannot hang the GPU. */
+CUVDIA_API int cuvdia_plan_status(const cuvdia_plan* plan, int* status);
+
 /* Device pointer to the plan's copy of the offsets (int32, storage order), e.g. to initialise a
  * dia_matrix<float,dev_memory_space>::get_offsets() tensor. */
 CUVDIA_API const int* cuvdia_plan_offsets_device(const cuvdia_plan* plan);
@@ -155,6 +161,12 @@ CUVDIA_API int cuvdia_bias_sigmoid_sample_f32(float* act, int ld, const float* b
  * tensor_ops/tensor_ops.hpp:530-655, tensor_ops/functors.hpp:412-433); dst may alias x or y. */
 CUVDIA_API int cuvdia_axpby_f32(float* dst, const float* x, const float* y, float a, float b, long long n,
                      void* stream);
+
+/* Benchmark aid, no counterpart in CUV: measures the device's FP32 ceiling with a register-resident
+ * loop and returns it in TFLOP/s counting a multiply-add as 2 flops.  fused != 0: one fused
+ * multiply-add per step (the FAST arithmetic); fused == 0: a separate multiply and add per step
+ * (the EXACT arithmetic, half the rate).  Blocking; allocates and frees 4 bytes. */
+CUVDIA_API int cuvdia_fp32_peak_tflops(int fused, float* tflops);
 
 #ifdef __cplusplus
 }

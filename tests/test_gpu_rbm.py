@@ -1,0 +1,64 @@
+"""The sparse-RBM CD-1 step on the GPU against the CPU oracle's step (same seeded inputs)."""
+import numpy as np
+import pytest
+
+from oracle import host_oracle as ho
+from oracle import rbm_oracle
+from tests.helpers import assert_bits_equal
+
+pytestmark = pytest.mark.gpu
+
+
+def run_gpu_step(cb, W, V0, U_h, U_v, batch_global=None, mode=None):
+    from cuv_b200 import rbm
+    Wd = cb.dev_dia_matrix_f(W.h, W.w, W.offsets, W.stride, W.rf).set_vec(W.vals)
+    st = rbm.SparseRBMStep(Wd, V0.shape[1], batch_global, cb.MODE_EXACT if mode is None else mode)
+    st.step(cb.to_device(V0), cb.to_device(U_h), cb.to_device(U_v))
+    return st
+
+
+@pytest.mark.parametrize("units,nd,nb", [(1024, 32, 96), (2048, 128, 160)])
+def test_cd1_step_matches_oracle(units, nd, nb):
+    import cuv_b200 as cb
+    offs = np.arange(-nd // 2, nd // 2, dtype=np.int32)
+    W, V0, U_h, U_v = rbm_oracle.make_inputs(1003, units, units, offs, nb, w_std=0.05)
+    ref = rbm_oracle.cd1_step(W, V0, U_h, U_v, nthreads=8)
+    st = run_gpu_step(cb, W, V0, U_h, U_v)
+    np.testing.assert_allclose(cb.to_host(st.H0p), ref["H0p"], rtol=1e-5)           # activations: rel 1e-5
+    assert np.array_equal(cb.to_host(st.H0), ref["H0"])                              # samples identical
+    np.testing.assert_allclose(cb.to_host(st.V1p), ref["V1p"], rtol=1e-5)
+    assert np.array_equal(cb.to_host(st.V1), ref["V1"])
+    np.testing.assert_allclose(cb.to_host(st.H1p), ref["H1p"], rtol=1e-5)
+    # gradients are differences of two batch sums: compare against the size of the summands
+    tol = 1e-4 * np.sqrt(max(nb, 128) / 128.0)
+    m = ref["G"].valid_mask().reshape(-1)
+    got = st.G.vec.cpu().numpy()
+    scale = np.zeros_like(got)
+    pos = ho.DiaHost(W.h, W.w, W.offsets, W.stride, 1)
+    ho.densedense_to_dia(pos, ref["H0p"], V0, 1.0 / nb, 0.0, nthreads=8)
+    scale = np.abs(pos.vals) + 1e-6
+    assert np.all(np.abs(got[m] - ref["G"].vals[m]) <= tol * scale[m])
+    assert np.all(got[~m] == 0)
+    np.testing.assert_allclose(st.gc.cpu().numpy(), ref["gc"], rtol=0, atol=tol)
+    np.testing.assert_allclose(st.gb.cpu().numpy(), ref["gb"], rtol=0, atol=tol)
+
+
+def test_sharded_partials_sum_to_full_batch():
+    """Two column shards computed with the global batch in the factors add up to the unsharded step
+    (what the all-reduce does across ranks), here on one GPU."""
+    import cuv_b200 as cb
+    from cuv_b200 import rbm
+    units, nd, B = 1024, 64, 128
+    offs = np.arange(-nd // 2, nd // 2, dtype=np.int32)
+    W, V0, U_h, U_v = rbm_oracle.make_inputs(1004, units, units, offs, B, w_std=0.05)
+    full = run_gpu_step(cb, W, V0, U_h, U_v)
+    parts = []
+    for r in range(2):
+        c0, c1 = rbm.shard_columns(B, 2, r)
+        sl = lambda a: np.asfortranarray(a[:, c0:c1])
+        parts.append(run_gpu_step(cb, W, sl(V0), sl(U_h), sl(U_v), batch_global=B))
+    G = parts[0].G.vec + parts[1].G.vec
+    bias = parts[0].bias_grad + parts[1].bias_grad
+    np.testing.assert_allclose(G.cpu().numpy(), full.G.vec.cpu().numpy(), rtol=0, atol=2e-6)
+    np.testing.assert_allclose(bias.cpu().numpy(), full.bias_grad.cpu().numpy(), rtol=0, atol=2e-6)
+    assert_bits_equal(cb.to_host(parts[1].H0p), np.asfortranarray(cb.to_host(full.H0p)[:, 64:]))
