@@ -35,10 +35,11 @@ def _ptr(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else None
 
 
-def fp32_peak_tflops(fused=True):
-    """Measured FP32 ceiling of the current device in TFLOP/s (multiply-add = 2 flops)."""
+def fp32_peak_tflops(fused=True, packed=False):
+    """Measured FP32 ceiling of the current device in TFLOP/s (multiply-add = 2 flops), with scalar or
+    packed-pair (f32x2) instructions."""
     out = ctypes.c_float()
-    _capi.check(_capi.lib().cuvdia_fp32_peak_tflops(1 if fused else 0, ctypes.byref(out)))
+    _capi.check(_capi.lib().cuvdia_fp32_peak_tflops((1 if fused else 0) + (2 if packed else 0), ctypes.byref(out)))
     return float(out.value)
 
 

@@ -1,0 +1,221 @@
+// densedense_to_dia for a banded pattern (consecutive ascending diagonals, row_fact 1).
+//
+//   G[k][i] = factC*G[k][i] + factAB * sum_b A[i,b] * B[i+lo+k, b],   k = 0..nd-1
+//
+// is the product A*B^T restricted to a band, so it is computed as dense 128 x 128 tiles of A*B^T
+// that cover the band: block (ti, t, z) owns rows i0 = 128*ti of A, rows j0 = i0 + lo - rem + 128*t
+// of B and the z-th share of the batch.  Both operands are column-major, so a tile of 128 rows x 32
+// batch columns is one TMA box (cp.async.bulk.tensor, no multicast) and lands in shared memory as
+// [batch column][row]: exactly the layout an outer-product inner loop wants - per batch column a
+// thread reads 8 values of each operand with four 128-bit loads and issues 32 packed fused
+// multiply-adds (f32x2) into its 8 x 8 accumulators.  Three stages are kept in flight and two blocks
+// share an SM.  Rows/columns outside the operands arrive as zeros.  At the end every accumulator
+// that lies on a stored diagonal inside the matrix is written to its DIA cell (cells outside the
+// diagonals' ranges are never touched, matrix_ops/densedense_to_sparse.cu:104-119); with a batch
+// split the partial tiles go to plan-owned scratch and dd2dia_combine_kernel adds them in split
+// order.  The two triangular end tiles of each row block compute products the band does not need;
+// that is the price of the dense formulation (128/nd of the work).
+#include <cuda.h>
+
+#include "cuvdia_internal.cuh"
+
+namespace cuvdia {
+
+int make_map_2d(CUtensorMap* m, const float* base, long long dim0, long long dim1, long long pitch, int box0, int box1);
+__global__ void dd2dia_combine_kernel(float* __restrict__ Cv, const int* __restrict__ offs, int nd, int h, int w,
+                                      int S, int rf, float fa, float fc, int nsplit,
+                                      const float* __restrict__ partial);
+
+namespace db {
+constexpr int TI = 128, TJ = 128, KB = 32, STAGES = 3, THREADS = 256;
+constexpr int TILE_FLOATS = TI * KB;                 // one operand tile of one stage
+constexpr size_t SMEM = sizeof(float) * 2 * TILE_FLOATS * STAGES + 64;
+constexpr unsigned SPIN_LIMIT = 1u << 26;
+}  // namespace db
+
+__device__ __forceinline__ unsigned dsmem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool dmbar_wait(unsigned long long* bar, unsigned parity) {
+    const unsigned addr = dsmem_u32(bar);
+    for (unsigned it = 0; it < db::SPIN_LIMIT; it++) {
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+struct DdBandParams {
+    int h, w, nd, lo, S, ncols;
+    int rem;            // lo mod 4 (non-negative): keeps the TMA row coordinate of B 16-byte aligned
+    int nsplit;
+    float fa, fc;
+    float* G;
+    float* partial;     // [nsplit][nd*S] when nsplit > 1
+    int* status;
+};
+
+__global__ void __launch_bounds__(db::THREADS, 2)
+dd2dia_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                   const DdBandParams P) {
+    using namespace db;
+    extern __shared__ __align__(1024) float smem_f[];
+    float* const Xs0 = smem_f;                                  // [STAGES][KB][TI]
+    float* const Hs0 = smem_f + STAGES * TILE_FLOATS;           // [STAGES][KB][TJ]
+    unsigned long long* const full = reinterpret_cast<unsigned long long*>(smem_f + 2 * STAGES * TILE_FLOATS);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int R = warp * 2 + (lane >> 4);        // row group 0..15: rows 4R..4R+3 and 64+4R..64+4R+3 of the tile
+    const int cg = lane & 15;                    // column group: columns 4cg..4cg+3 and 64+4cg..64+4cg+3
+    const int i0 = blockIdx.x * TI;
+    const int j0 = i0 + P.lo - P.rem + (int)blockIdx.y * TJ;
+    const int z = blockIdx.z;
+    const int nch_all = (P.ncols + KB - 1) / KB;
+    const int ch0 = (int)((long long)nch_all * z / P.nsplit), ch1 = (int)((long long)nch_all * (z + 1) / P.nsplit);
+    const int nch = ch1 - ch0;
+
+    constexpr unsigned TX_BYTES = sizeof(float) * 2 * TILE_FLOATS;
+    auto issue = [&](int c) {
+        const int s = c % STAGES;
+        const unsigned bar = dsmem_u32(&full[s]);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(TX_BYTES) : "memory");
+        asm volatile(
+            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+            ::"r"(dsmem_u32(Xs0 + s * TILE_FLOATS)), "l"(&mapA), "r"(i0), "r"((ch0 + c) * KB), "r"(bar) : "memory");
+        asm volatile(
+            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+            ::"r"(dsmem_u32(Hs0 + s * TILE_FLOATS)), "l"(&mapB), "r"(j0), "r"((ch0 + c) * KB), "r"(bar) : "memory");
+    };
+
+    if (tid == 0) {
+#pragma unroll
+        for (int s = 0; s < STAGES; s++)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(dsmem_u32(&full[s])));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (tid == 0)
+        for (int c = 0; c < STAGES && c < nch; c++) issue(c);
+
+    // acc[ii][jp]: row ii of the thread's 8, columns (2jp, 2jp+1) as a packed pair
+    float2 acc[8][4];
+#pragma unroll
+    for (int ii = 0; ii < 8; ii++)
+#pragma unroll
+        for (int jp = 0; jp < 4; jp++) acc[ii][jp] = make_float2(0.f, 0.f);
+
+    for (int c = 0; c < nch; c++) {
+        const int s = c % STAGES;
+        if (!dmbar_wait(&full[s], (c / STAGES) & 1)) {
+            if (P.status) *P.status = 2;
+            return;
+        }
+        const float* xs = Xs0 + s * TILE_FLOATS + 4 * R;
+        const float* hs = Hs0 + s * TILE_FLOATS + 4 * cg;
+#pragma unroll 8
+        for (int b = 0; b < KB; b++) {
+            const float4 x0 = *reinterpret_cast<const float4*>(xs + b * TI);
+            const float4 x1 = *reinterpret_cast<const float4*>(xs + b * TI + 64);
+            const float4 h0 = *reinterpret_cast<const float4*>(hs + b * TJ);
+            const float4 h1 = *reinterpret_cast<const float4*>(hs + b * TJ + 64);
+            const float x[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+            const float2 hp[4] = {make_float2(h0.x, h0.y), make_float2(h0.z, h0.w), make_float2(h1.x, h1.y),
+                                  make_float2(h1.z, h1.w)};
+#pragma unroll
+            for (int ii = 0; ii < 8; ii++) {
+                const float2 xx = make_float2(x[ii], x[ii]);
+#pragma unroll
+                for (int jp = 0; jp < 4; jp++) acc[ii][jp] = __ffma2_rn(xx, hp[jp], acc[ii][jp]);
+            }
+        }
+        __syncthreads();
+        if (tid == 0 && c + STAGES < nch) issue(c + STAGES);
+    }
+
+    // ---- write the accumulators that lie on stored diagonals inside the matrix ----
+    float* out = P.nsplit == 1 ? P.G : P.partial + (size_t)z * P.nd * P.S;
+#pragma unroll
+    for (int ii = 0; ii < 8; ii++) {
+        const int i = i0 + 4 * R + (ii & 3) + (ii >> 2) * 64;
+        if (i >= P.h) continue;
+#pragma unroll
+        for (int jj = 0; jj < 8; jj++) {
+            const int j = j0 + 4 * cg + (jj & 3) + (jj >> 2) * 64;
+            const int k = j - i - P.lo;
+            if ((unsigned)k >= (unsigned)P.nd || (unsigned)j >= (unsigned)P.w) continue;
+            const float v = (jj & 1) ? acc[ii][jj >> 1].y : acc[ii][jj >> 1].x;
+            float* cell = out + (size_t)k * P.S + i;
+            if (P.nsplit == 1) {
+                float sv = v;
+                if (P.fa != 1.f) sv = __fmul_rn(P.fa, sv);
+                *cell = (P.fc != 0.f) ? __fadd_rn(__fmul_rn(P.fc, *cell), sv) : sv;
+            } else {
+                *cell = v;
+            }
+        }
+    }
+}
+
+static inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+bool dd2dia_band_applicable(const cuvdia_plan* p, const float* A, int lda, const float* B, int ldb, int ncols) {
+    return p->is_band && p->rf == 1 && al16(A) && al16(B) && lda % 4 == 0 && ldb % 4 == 0 && ncols >= 1 &&
+           p->nd >= 16;
+}
+
+int launch_dd2dia_band(cuvdia_plan* p, float* Cv, const float* A, int lda, const float* B, int ldb, int ncols,
+                       float fa, float fc, cudaStream_t st) {
+    using namespace db;
+    CUtensorMap mapA, mapB;
+    int rc = make_map_2d(&mapA, A, p->h, ncols, lda, TI, KB);
+    if (rc) return rc;
+    rc = make_map_2d(&mapB, B, p->w, ncols, ldb, TJ, KB);
+    if (rc) return rc;
+    DdBandParams P;
+    P.h = p->h; P.w = p->w; P.nd = p->nd; P.lo = p->band_lo; P.S = p->stride; P.ncols = ncols;
+    P.rem = ((p->band_lo % 4) + 4) % 4;
+    P.fa = fa; P.fc = fc; P.G = Cv; P.status = p->d_status;
+    const int gx = (p->h + TI - 1) / TI;
+    const int gy = (p->nd + TI - 1 + P.rem + TJ - 1) / TJ;       // column tiles that cover the band of one row block
+    // split the batch when the tiles alone leave SMs idle or quantise badly into waves
+    const int slots = 2 * sm_count();
+    const int nch_all = (ncols + KB - 1) / KB;
+    int nsplit = 1;
+    double best = 0.0;
+    for (int s = 1; s <= 8 && s <= std::max(1, nch_all / 4); s++) {
+        const long long ctas = (long long)gx * gy * s;
+        const long long waves = (ctas + slots - 1) / slots;
+        const double eff = (double)ctas / (double)(waves * slots);
+        if (eff > best + 0.05) { best = eff; nsplit = s; }
+    }
+    P.nsplit = nsplit;
+    P.partial = nullptr;
+    if (nsplit > 1) {
+        rc = ensure_plan_scratch(p, (size_t)nsplit * p->nd * p->stride, st);
+        if (rc) return rc;
+        P.partial = p->scratch;
+    }
+    static bool attr_done = false;
+    if (!attr_done) {
+        CUVDIA_CUDA(cudaFuncSetAttribute(dd2dia_band_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
+        attr_done = true;
+    }
+    if (gy > 65535 || nsplit > 65535) { set_last_error("band too wide for densedense_to_dia"); return CUVDIA_ERR_UNSUPPORTED; }
+    dd2dia_band_kernel<<<dim3(gx, gy, nsplit), THREADS, SMEM, st>>>(mapA, mapB, P);
+    count_launch();
+    rc = check_launch("dd2dia_band_kernel");
+    if (rc) return rc;
+    if (nsplit > 1) {
+        dim3 g2((p->h + 255) / 256, std::min(p->nd, 65535));
+        dd2dia_combine_kernel<<<g2, 256, 0, st>>>(Cv, p->d_offsets, p->nd, p->h, p->w, p->stride, p->rf, fa, fc,
+                                                  nsplit, P.partial);
+        count_launch();
+        rc = check_launch("dd2dia_combine_kernel");
+    }
+    return rc;
+}
+
+}  // namespace cuvdia

@@ -5,22 +5,27 @@
 
 namespace cuvdia {
 
-template <bool FUSED>
+// VARIANT 0: mul + add, 1: fused multiply-add, 2: packed-pair multiply (f32x2) + two scalar adds,
+// 3: fused multiply-add on packed pairs
+template <int VARIANT>
 __global__ void __launch_bounds__(256)
 fp32_peak_kernel(float* out, int iters, float a, float b) {
-    float x[16];
+    float2 x[8];
 #pragma unroll
-    for (int i = 0; i < 16; i++) x[i] = (float)(threadIdx.x + i);
+    for (int i = 0; i < 8; i++) x[i] = make_float2((float)(threadIdx.x + i), (float)(threadIdx.x - i));
+    const float2 a2 = make_float2(a, a), b2 = make_float2(b, b);
     for (int it = 0; it < iters; it++) {
 #pragma unroll
-        for (int i = 0; i < 16; i++) {
-            if (FUSED) x[i] = fmaf(x[i], a, b);
-            else x[i] = __fadd_rn(__fmul_rn(x[i], a), b);
+        for (int i = 0; i < 8; i++) {
+            if (VARIANT == 0) { x[i].x = __fadd_rn(__fmul_rn(x[i].x, a), b); x[i].y = __fadd_rn(__fmul_rn(x[i].y, a), b); }
+            else if (VARIANT == 1) { x[i].x = fmaf(x[i].x, a, b); x[i].y = fmaf(x[i].y, a, b); }
+            else if (VARIANT == 2) { const float2 p = __fmul2_rn(x[i], a2); x[i].x = __fadd_rn(p.x, b); x[i].y = __fadd_rn(p.y, b); }
+            else x[i] = __ffma2_rn(x[i], a2, b2);
         }
     }
     float s = 0.f;
 #pragma unroll
-    for (int i = 0; i < 16; i++) s += x[i];
+    for (int i = 0; i < 8; i++) s += x[i].x + x[i].y;
     if (s == 12345.678f) out[0] = s;     // never true in practice; keeps the loop alive
 }
 
@@ -39,8 +44,12 @@ extern "C" int cuvdia_fp32_peak_tflops(int fused, float* tflops) {
     float best = 0.f;
     for (int rep = 0; rep < 4; rep++) {
         cudaEventRecord(e0);
-        if (fused) fp32_peak_kernel<true><<<blocks, 256>>>(d, iters, 0.999f, 0.001f);
-        else fp32_peak_kernel<false><<<blocks, 256>>>(d, iters, 0.999f, 0.001f);
+        switch (fused) {
+            case 0: fp32_peak_kernel<0><<<blocks, 256>>>(d, iters, 0.999f, 0.001f); break;
+            case 1: fp32_peak_kernel<1><<<blocks, 256>>>(d, iters, 0.999f, 0.001f); break;
+            case 2: fp32_peak_kernel<2><<<blocks, 256>>>(d, iters, 0.999f, 0.001f); break;
+            default: fp32_peak_kernel<3><<<blocks, 256>>>(d, iters, 0.999f, 0.001f); break;
+        }
         cudaEventRecord(e1);
         count_launch();
         CUVDIA_CUDA(cudaEventSynchronize(e1));

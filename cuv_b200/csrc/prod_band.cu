@@ -41,7 +41,7 @@ __host__ __device__ constexpr size_t align128(size_t x) { return (x + 127) / 128
 template <bool TRANS> __host__ __device__ constexpr size_t raw_bytes() { return align128(sizeof(float) * (TRANS ? RAW_FLOATS_T : RAW_FLOATS_N)); }
 __host__ __device__ constexpr size_t bs_bytes() { return align128(sizeof(float) * BS_FLOATS); }
 template <bool TRANS> __host__ __device__ constexpr size_t smem_bytes() {
-    return 2 * raw_bytes<TRANS>() + 2 * bs_bytes() + sizeof(float) * AS_FLOATS + 64 /*barriers*/ + 128 /*alignment slack*/;
+    return 2 * raw_bytes<TRANS>() + 2 * bs_bytes() + sizeof(float) * AS_FLOATS + 64 /*barriers*/;
 }
 constexpr unsigned SPIN_LIMIT = 1u << 26;   // bounded wait on a TMA completion barrier
 }  // namespace pb
@@ -74,10 +74,20 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
 
+// Two multiply-adds on a packed pair of floats (the f32x2 instructions of sm_100).  FAST is one
+// packed fused multiply-add.  EXACT must round the product and the sum separately: a packed
+// multiply followed by two scalar adds (a packed multiply feeding a packed add is contracted into
+// a fused multiply-add by the assembler even with explicit rounding modifiers, so that pairing
+// cannot be used).
 template <bool EXACT>
-__device__ __forceinline__ void mac(float& acc, float a, float b) {
-    if (EXACT) acc = __fadd_rn(acc, __fmul_rn(a, b));
-    else acc = fmaf(a, b, acc);
+__device__ __forceinline__ void mac2(float2& acc, float2 a, float2 b) {
+    if (EXACT) {
+        const float2 p = __fmul2_rn(a, b);
+        acc.x = __fadd_rn(acc.x, p.x);
+        acc.y = __fadd_rn(acc.y, p.y);
+    } else {
+        acc = __ffma2_rn(a, b, acc);
+    }
 }
 
 struct BandParams {
@@ -97,12 +107,18 @@ __global__ void __launch_bounds__(pb::THREADS, 1)
 prod_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                  const BandParams P) {
     using namespace pb;
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
-    auto raw = [&](int s) { return reinterpret_cast<float*>(base + s * raw_bytes<TRANS>()); };
-    auto Bs = [&](int s) { return reinterpret_cast<float*>(base + 2 * raw_bytes<TRANS>() + s * bs_bytes()); };
-    float* As = reinterpret_cast<float*>(base + 2 * raw_bytes<TRANS>() + 2 * bs_bytes());
-    unsigned long long* full = reinterpret_cast<unsigned long long*>(As + AS_FLOATS);
+    // Dynamic shared memory is the only shared memory of this kernel, so it starts at the aligned
+    // base of the block's window; all sub-buffers are carved by plain offsets so that the compiler
+    // keeps them in the shared address space (LDS/STS, not generic loads).
+    extern __shared__ __align__(1024) float smem_f[];
+    constexpr int RAWF = (int)(raw_bytes<TRANS>() / sizeof(float));
+    constexpr int BSF = (int)(bs_bytes() / sizeof(float));
+    float* const raw0 = smem_f;
+    float* const Bs0 = smem_f + 2 * RAWF;
+    float* const As = smem_f + 2 * RAWF + 2 * BSF;
+    unsigned long long* const full = reinterpret_cast<unsigned long long*>(As + AS_FLOATS);
+    auto raw = [&](int s) { return raw0 + s * RAWF; };
+    auto Bs = [&](int s) { return Bs0 + s * BSF; };
 
     const int tid = threadIdx.x;
     const int t0 = blockIdx.x * TM;               // first output row of the tile
@@ -140,11 +156,12 @@ prod_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         if (P.nchunks > 1) issue(1, 1);
     }
 
-    float acc[8][8];
+    // acc[jp][c] holds rows (2*jp, 2*jp+1) of column c as a packed pair
+    float2 acc[4][8];
 #pragma unroll
-    for (int j = 0; j < 8; j++)
+    for (int jp = 0; jp < 4; jp++)
 #pragma unroll
-        for (int c = 0; c < 8; c++) acc[j][c] = 0.f;
+        for (int c = 0; c < 8; c++) acc[jp][c] = make_float2(0.f, 0.f);
     if (P.fc != 0.f) {
 #pragma unroll
         for (int c = 0; c < 8; c++) {
@@ -152,7 +169,10 @@ prod_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
 #pragma unroll
             for (int j = 0; j < 8; j++) {
                 const int row = t0 + r0 + j;
-                if (col < P.ncols && row < P.rows_out) acc[j][c] = __fmul_rn(P.C[(size_t)col * P.ldc + row], P.fc);
+                if (col < P.ncols && row < P.rows_out) {
+                    const float v = __fmul_rn(P.C[(size_t)col * P.ldc + row], P.fc);
+                    if (j & 1) acc[j >> 1][c].y = v; else acc[j >> 1][c].x = v;
+                }
             }
         }
     }
@@ -167,28 +187,38 @@ prod_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         {
             const int r = tid & (TM - 1);
             const int j = r & 7;
+            const int qq0 = tid >> 7;                                // 0 or 1; this thread does qq0, qq0+2, ...
             const float* rw = raw(s);
             const int y0 = c * KC - P.rem - 7;
+            const int xb = TRANS ? (t0 - P.lo + P.rem + 8 - (c + 1) * KC) : (t0 + P.lo - P.rem + c * KC);
+            // slice element for (qq, r):  'n': row qq-j+7, column r;   't': row qq+j, column (r-j)+KC-1-qq
+            const float* src = TRANS ? rw + (qq0 + j) * WR + (r - j) + KC - 1 - qq0 : rw + (qq0 - j + 7) * TM + r;
+            constexpr int SSTEP = TRANS ? 2 * (WR - 1) : 2 * TM;
+            float* dst = As + qq0 * TM + r;
+            // block-uniform: every cell this chunk touches lies inside the matrix
+            const bool interior = TRANS ? (y0 >= 0 && y0 + NRAW <= P.nd && xb >= 0 && xb + WR <= P.h)
+                                        : (y0 >= 0 && y0 + NRAW <= P.nd && xb >= 0 && xb + TM + KC <= P.w);
+            if (interior && P.fa == 1.f) {
+#pragma unroll
+                for (int it = 0; it < KC / 2; it++) dst[it * 2 * TM] = src[it * SSTEP];
+            } else {
 #pragma unroll 4
-            for (int qq = tid >> 7; qq < KC; qq += THREADS / TM) {
-                float v;
-                bool ok;
-                if (!TRANS) {
-                    const int rr = qq - j + 7;                      // row of the slice (diagonal k = y0 + rr)
-                    const int k = y0 + rr;
-                    const int jb = t0 + r + P.lo + k;               // matrix column of the cell
-                    ok = k >= 0 && k < P.nd && jb >= 0 && jb < P.w;
-                    v = rw[rr * TM + r];
-                } else {
-                    const int rr = qq + j;
-                    const int k = y0 + rr;
-                    const int wr = (r - j) + KC - 1 - qq;           // window row = matrix row - window start
-                    const int i = t0 - P.lo + P.rem + 8 - (c + 1) * KC + wr;
-                    ok = k >= 0 && k < P.nd && i >= 0 && i < P.h;
-                    v = rw[rr * WR + wr];
+                for (int it = 0; it < KC / 2; it++) {
+                    const int qq = qq0 + 2 * it;
+                    bool ok;
+                    if (!TRANS) {
+                        const int k = y0 + qq - j + 7;
+                        const int jb = t0 + r + P.lo + k;               // matrix column of the cell
+                        ok = (unsigned)k < (unsigned)P.nd && (unsigned)jb < (unsigned)P.w;
+                    } else {
+                        const int k = y0 + qq + j;
+                        const int i = xb + (r - j) + KC - 1 - qq;       // matrix row of the cell
+                        ok = (unsigned)k < (unsigned)P.nd && (unsigned)i < (unsigned)P.h;
+                    }
+                    float v = src[it * SSTEP];
+                    if (P.fa != 1.f) v = __fmul_rn(P.fa, v);
+                    dst[it * 2 * TM] = ok ? v : 0.f;
                 }
-                if (P.fa != 1.f) v = __fmul_rn(P.fa, v);
-                As[qq * TM + r] = ok ? v : 0.f;
             }
         }
         __syncthreads();
@@ -205,14 +235,16 @@ prod_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
             for (int u = 0; u < 4; u++) {
                 const float4 a0 = *reinterpret_cast<const float4*>(asp + (4 * g + u) * TM);
                 const float4 a1 = *reinterpret_cast<const float4*>(asp + (4 * g + u) * TM + 4);
-                const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+                const float2 a[4] = {make_float2(a0.x, a0.y), make_float2(a0.z, a0.w), make_float2(a1.x, a1.y),
+                                     make_float2(a1.z, a1.w)};
 #pragma unroll
                 for (int cc = 0; cc < 8; cc++) {
                     float b;
                     if (!TRANS) b = u == 0 ? bw[cc].x : u == 1 ? bw[cc].y : u == 2 ? bw[cc].z : bw[cc].w;
                     else        b = u == 0 ? bw[cc].w : u == 1 ? bw[cc].z : u == 2 ? bw[cc].y : bw[cc].x;
+                    const float2 bb = make_float2(b, b);
 #pragma unroll
-                    for (int j = 0; j < 8; j++) mac<EXACT>(acc[j][cc], a[j], b);
+                    for (int jp = 0; jp < 4; jp++) mac2<EXACT>(acc[jp][cc], a[jp], bb);
                 }
             }
         }
@@ -227,12 +259,12 @@ prod_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         if (col >= P.ncols) continue;
         float* cp = P.C + (size_t)col * P.ldc + t0 + r0;
         if (P.vec_c && t0 + r0 + 8 <= P.rows_out) {
-            *reinterpret_cast<float4*>(cp) = make_float4(acc[0][cc], acc[1][cc], acc[2][cc], acc[3][cc]);
-            *reinterpret_cast<float4*>(cp + 4) = make_float4(acc[4][cc], acc[5][cc], acc[6][cc], acc[7][cc]);
+            *reinterpret_cast<float4*>(cp) = make_float4(acc[0][cc].x, acc[0][cc].y, acc[1][cc].x, acc[1][cc].y);
+            *reinterpret_cast<float4*>(cp + 4) = make_float4(acc[2][cc].x, acc[2][cc].y, acc[3][cc].x, acc[3][cc].y);
         } else {
 #pragma unroll
             for (int j = 0; j < 8; j++)
-                if (t0 + r0 + j < P.rows_out) cp[j] = acc[j][cc];
+                if (t0 + r0 + j < P.rows_out) cp[j] = (j & 1) ? acc[j >> 1][cc].y : acc[j >> 1][cc].x;
         }
     }
 }

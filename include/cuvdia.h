@@ -163,9 +163,11 @@ CUVDIA_API int cuvdia_axpby_f32(float* dst, const float* x, const float* y, floa
                      void* stream);
 
 /* Benchmark aid, no counterpart in CUV: measures the device's FP32 ceiling with a register-resident
- * loop and returns it in TFLOP/s counting a multiply-add as 2 flops.  fused != 0: one fused
- * multiply-add per step (the FAST arithmetic); fused == 0: a separate multiply and add per step
- * (the EXACT arithmetic, half the rate).  Blocking; allocates and frees 4 bytes. */
+ * loop and returns it in TFLOP/s counting a multiply-add as 2 flops.  fused: 0 = a separate multiply
+ * and add per step (the EXACT arithmetic), 1 = one fused multiply-add per step (the FAST arithmetic),
+ * 2 = a packed-pair multiply (f32x2 instruction of sm_100) and two scalar adds (unfused), 3 = a packed
+ * fused multiply-add.  Blocking;
+ * allocates and frees 4 bytes. */
 CUVDIA_API int cuvdia_fp32_peak_tflops(int fused, float* tflops);
 
 #ifdef __cplusplus
