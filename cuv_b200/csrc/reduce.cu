@@ -274,6 +274,120 @@ static int launch_reduce_t(float* dst, const float* src, long long n_contig, lon
     return rc;
 }
 
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant (cuvdia_reduce_noalloc_f32).
+//
+// The split reductions above need a scratch buffer for the per-block partial results and get it
+// from the per-stream workspace, which is created with cudaMalloc on first use.  Some callers must
+// not allocate: code running inside a fixed device-memory budget handed out by a host application,
+// real-time or long-running services that forbid allocator calls after start-up (an allocation can
+// synchronise the whole device), and code that has no way to free what a library allocated behind
+// its back.  For them the partial results live in the array below, which is part of the library
+// image: every device that loads the library holds these bytes until the process exits.
+//
+// In host code `g_noalloc_scratch` only names the symbol; it is NOT a device address, and a kernel
+// handed that host-side name would fault or silently use the wrong memory.  The device address is
+// looked up once per device with cudaGetSymbolAddress while that device is current, and that
+// pointer is what the kernels receive.
+// ------------------------------------------------------------------------------------------------
+constexpr size_t NOALLOC_SCRATCH_BYTES = (size_t)4 << 20;      // 4 MiB per device
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+
+// Device address of the static scratch on the current device (looked up on the first call per device).
+static int noalloc_scratch_ptr(void** out) {
+    static void* cached[64] = {nullptr};
+    int dev = 0;
+    CUVDIA_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) { set_last_error("device index %d out of range", dev); return CUVDIA_ERR_UNSUPPORTED; }
+    if (!cached[dev]) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_noalloc_scratch)");
+        cached[dev] = p;
+    }
+    *out = cached[dev];
+    return CUVDIA_OK;
+}
+
+template <int RF>
+static int launch_reduce_noalloc_t(float* dst, const float* src, long long n_contig, long long n_strided,
+                                   bool over_strided, float fnew, float fold, cudaStream_t st) {
+    const int sms = sm_count();
+    const bool vec = (n_contig % 4 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
+    const long long n_out = over_strided ? n_contig : n_strided;
+    const long long n_red = over_strided ? n_strided : n_contig;
+    // same split heuristics as the allocating entry point
+    int nsplit = 1;
+    long long gx = 0;
+    if (over_strided) {
+        const long long per_block = (long long)RA_THREADS * (vec ? 4 : 1);
+        gx = (n_contig + per_block - 1) / per_block;
+        if (gx < 4LL * sms) nsplit = (int)std::min<long long>((4LL * sms + gx - 1) / gx, std::max<long long>(1, n_strided / 16));
+        nsplit = std::max(1, std::min(nsplit, 1024));
+    } else {
+        if (n_contig <= 4096 && n_strided >= 2LL * sms) {       // a warp per line: no scratch at all
+            const unsigned g = (unsigned)((n_strided + 7) / 8);
+            if (vec) reduce_along_warp_kernel<RF, 4><<<g, 256, 0, st>>>(dst, src, n_contig, (int)n_strided, fnew, fold);
+            else     reduce_along_warp_kernel<RF, 1><<<g, 256, 0, st>>>(dst, src, n_contig, (int)n_strided, fnew, fold);
+            count_launch();
+            return check_launch("reduce_along_warp_kernel");
+        }
+        if (n_strided > 65535) { set_last_error("reduce along lines: more than 65535 long lines"); return CUVDIA_ERR_UNSUPPORTED; }
+        if (n_strided < 4LL * sms) nsplit = (int)std::min<long long>((4LL * sms + n_strided - 1) / n_strided, std::max<long long>(1, n_contig / 4096));
+        nsplit = std::max(1, std::min(nsplit, 4096));
+    }
+    float* pval = nullptr; int* pidx = nullptr;
+    if (nsplit > 1) {
+        const size_t need = (size_t)nsplit * (size_t)n_out * 8;
+        if (need > NOALLOC_SCRATCH_BYTES) {
+            set_last_error("cuvdia_reduce_noalloc_f32: this shape needs %zu bytes of scratch (%d partial results for each "
+                           "of %lld outputs) but the static scratch holds %zu bytes; use cuvdia_reduce_f32",
+                           need, nsplit, n_out, NOALLOC_SCRATCH_BYTES);
+            return CUVDIA_ERR_UNSUPPORTED;
+        }
+        void* ws = nullptr;
+        int rc = noalloc_scratch_ptr(&ws);
+        if (rc) return rc;
+        // every partial slot that the second stage reads is written by the first stage of the same
+        // call, so nothing has to be cleared even though the array keeps the previous call's contents
+        pval = (float*)ws; pidx = (int*)(pval + (size_t)nsplit * n_out);
+    }
+    int rc;
+    if (over_strided) {
+        dim3 grid((unsigned)gx, nsplit);
+        if (vec) reduce_across_kernel<RF, 4><<<grid, RA_THREADS, 0, st>>>(dst, src, n_contig, (int)n_strided, fnew, fold, nsplit, pval, pidx);
+        else     reduce_across_kernel<RF, 1><<<grid, RA_THREADS, 0, st>>>(dst, src, n_contig, (int)n_strided, fnew, fold, nsplit, pval, pidx);
+        count_launch();
+        rc = check_launch("reduce_across_kernel");
+    } else {
+        dim3 grid(nsplit, (unsigned)n_strided);
+        if (vec) reduce_along_block_kernel<RF, 4><<<grid, 256, 0, st>>>(dst, src, n_contig, (int)n_strided, fnew, fold, nsplit, pval, pidx);
+        else     reduce_along_block_kernel<RF, 1><<<grid, 256, 0, st>>>(dst, src, n_contig, (int)n_strided, fnew, fold, nsplit, pval, pidx);
+        count_launch();
+        rc = check_launch("reduce_along_block_kernel");
+    }
+    if (rc) return rc;
+    if (nsplit > 1) {
+        reduce_combine_kernel<RF><<<(unsigned)((n_out + 255) / 256), 256, 0, st>>>(dst, n_out, fnew, fold, nsplit, pval, pidx, (float)n_red);
+        count_launch();
+        rc = check_launch("reduce_combine_kernel");
+    }
+    return rc;
+}
+
+int launch_reduce_noalloc(float* dst, const float* src, long long n_contig, long long n_strided, bool over_strided,
+                          int functor, float fnew, float fold, cudaStream_t st) {
+#define CASE(RF) case RF: return launch_reduce_noalloc_t<RF>(dst, src, n_contig, n_strided, over_strided, fnew, fold, st)
+    switch (functor) {
+        CASE(CUVDIA_RF_ADD); CASE(CUVDIA_RF_MEAN); CASE(CUVDIA_RF_ADD_SQUARED); CASE(CUVDIA_RF_MAX);
+        CASE(CUVDIA_RF_ARGMAX); CASE(CUVDIA_RF_ARGMIN); CASE(CUVDIA_RF_MIN); CASE(CUVDIA_RF_MULT);
+        CASE(CUVDIA_RF_LOGADDEXP); CASE(CUVDIA_RF_ADDEXP);
+    }
+#undef CASE
+    set_last_error("unknown reduce functor %d", functor);
+    return CUVDIA_ERR_INVALID;
+}
+
 int launch_reduce(float* dst, const float* src, long long n_contig, long long n_strided, bool over_strided,
                   int functor, float fnew, float fold, cudaStream_t st) {
 #define CASE(RF) case RF: return launch_reduce_t<RF>(dst, src, n_contig, n_strided, over_strided, fnew, fold, st)
@@ -288,3 +402,20 @@ int launch_reduce(float* dst, const float* src, long long n_contig, long long n_
 }
 
 }  // namespace cuvdia
+
+// The allocation-free entry point is defined beside its scratch array (see the block comment above
+// g_noalloc_scratch).
+extern "C" int cuvdia_reduce_noalloc_f32(float* dst, const float* src, long long n_contig, long long n_strided,
+                                         int over_strided, int functor, float factNew, float factOld, void* stream) {
+    CUVDIA_REQUIRE(dst != nullptr);
+    CUVDIA_REQUIRE(src != nullptr);
+    CUVDIA_REQUIRE(n_contig > 0 && n_strided > 0);
+    CUVDIA_REQUIRE(n_contig * n_strided <= 2147483647LL);
+    CUVDIA_REQUIRE(functor >= CUVDIA_RF_ADD && functor <= CUVDIA_RF_ADDEXP);
+    if (functor == CUVDIA_RF_MEAN) {
+        CUVDIA_REQUIRE(factNew == 1.f);
+        CUVDIA_REQUIRE(factOld == 0.f);
+    }
+    return cuvdia::launch_reduce_noalloc(dst, src, n_contig, n_strided, over_strided != 0, functor, factNew, factOld,
+                                         (cudaStream_t)stream);
+}

@@ -147,6 +147,29 @@ CUVDIA_API int cuvdia_reduce_f32(float* dst, const float* src, long long n_conti
                       int over_strided, int functor, float factNew, float factOld, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * The same reduction as cuvdia_reduce_f32 for callers that must not allocate device memory.
+ * No counterpart in CUV; it exists because cuvdia_reduce_f32 may call cudaMalloc for its per-stream
+ * workspace, and some callers cannot accept that: code that runs inside a fixed device-memory
+ * budget given out by a host application, services that forbid allocator calls once they are up
+ * (an allocation can stall every stream of the device), and callers with no chance to release what
+ * a library allocated for them.  This entry point never calls cudaMalloc, cudaFree or any other
+ * allocating routine.  The partial results of a split reduction live in a 4 MiB array that is part
+ * of the library image (every device that loads the library holds it until the process exits).
+ *  - Shapes whose split needs more than 4 MiB (8 bytes x partial results x outputs) are refused
+ *    with CUVDIA_ERR_UNSUPPORTED and a message that states the need; use cuvdia_reduce_f32 then.
+ *  - The first call on each device looks up the array's device address; make that first call
+ *    outside any stream capture, with the device current.
+ *  - All calls share the one array, which keeps the previous call's contents (nothing in it needs
+ *    clearing: each call writes every slot it later reads).  Two calls that overlap on the GPU -
+ *    different streams or different host threads - race on it; run them in one stream or
+ *    serialise them.
+ * Arguments, semantics and results are those of cuvdia_reduce_f32.
+ * ------------------------------------------------------------------------------------------- */
+CUVDIA_API int cuvdia_reduce_noalloc_f32(float* dst, const float* src, long long n_contig, long long n_strided,
+                                         int over_strided, int functor, float factNew, float factOld,
+                                         void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Element-wise glue of the RBM step on a column-major [units x ncols] activation matrix:
  *   act <- sigmoid(act + bias[unit])      (bias may be NULL)
  *   sample <- act > u ? 1 : 0             (sample and u may both be NULL)
