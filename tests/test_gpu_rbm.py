@@ -43,6 +43,30 @@ def test_cd1_step_matches_oracle(units, nd, nb):
     np.testing.assert_allclose(st.gb.cpu().numpy(), ref["gb"], rtol=0, atol=tol)
 
 
+def test_fused_arithmetic_is_bit_identical_on_binary_operands():
+    """All three products of the step multiply the weights by 0/1 samples, so every product is exact
+    and the fused (FAST) arithmetic must give the same bits as the EXACT one and as the oracle."""
+    import cuv_b200 as cb
+    units, nd, nb = 2048, 128, 160
+    offs = np.arange(-nd // 2, nd // 2, dtype=np.int32)
+    W, V0, U_h, U_v = rbm_oracle.make_inputs(1005, units, units, offs, nb, w_std=0.05)
+    exact = run_gpu_step(cb, W, V0, U_h, U_v, mode=cb.MODE_EXACT)
+    fast = run_gpu_step(cb, W, V0, U_h, U_v, mode=cb.MODE_FAST)
+    for name in ("H0p", "H0", "V1p", "V1", "H1p"):
+        assert_bits_equal(cb.to_host(getattr(fast, name)), cb.to_host(getattr(exact, name)), name)
+    assert_bits_equal(fast.G.vec.cpu().numpy(), exact.G.vec.cpu().numpy(), "G")
+    # and the raw products equal the oracle's bit for bit in FAST mode
+    Wd = cb.dev_dia_matrix_f(W.h, W.w, W.offsets, W.stride, W.rf).set_vec(W.vals)
+    X = cb.colmajor_empty(units, nb)
+    cb.prod(X, Wd, cb.to_device(V0), "n", "n", 1.0, 0.0, cb.MODE_FAST)
+    want = np.zeros((units, nb), dtype=np.float32, order="F")
+    ho.prod(want, W, V0, "n", nthreads=8)
+    assert_bits_equal(cb.to_host(X), want, "prod 'n' FAST vs oracle on 0/1 input")
+    cb.prod(X, Wd, exact.H0, "t", "n", 1.0, 0.0, cb.MODE_FAST)
+    ho.prod(want, W, cb.to_host(exact.H0), "t", nthreads=8)
+    assert_bits_equal(cb.to_host(X), want, "prod 't' FAST vs oracle on 0/1 input")
+
+
 def test_sharded_partials_sum_to_full_batch():
     """Two column shards computed with the global batch in the factors add up to the unsharded step
     (what the all-reduce does across ranks), here on one GPU."""
