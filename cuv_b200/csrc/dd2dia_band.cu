@@ -70,8 +70,10 @@ dd2dia_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int R = warp * 2 + (lane >> 4);        // row group 0..15: rows 4R..4R+3 and 64+4R..64+4R+3 of the tile
     const int cg = lane & 15;                    // column group: columns 4cg..4cg+3 and 64+4cg..64+4cg+3
-    const int i0 = blockIdx.x * TI;
-    const int j0 = i0 + P.lo - P.rem + (int)blockIdx.y * TJ;
+    // the column tiles of one row block are neighbours in the grid: they share the A tile, and
+    // adjacent row blocks share most B tiles, so both operands come from HBM about once
+    const int i0 = blockIdx.y * TI;
+    const int j0 = i0 + P.lo - P.rem + (int)blockIdx.x * TJ;
     const int z = blockIdx.z;
     const int nch_all = (P.ncols + KB - 1) / KB;
     const int ch0 = (int)((long long)nch_all * z / P.nsplit), ch1 = (int)((long long)nch_all * (z + 1) / P.nsplit);
@@ -203,8 +205,8 @@ int launch_dd2dia_band(cuvdia_plan* p, float* Cv, const float* A, int lda, const
         CUVDIA_CUDA(cudaFuncSetAttribute(dd2dia_band_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
         attr_done = true;
     }
-    if (gy > 65535 || nsplit > 65535) { set_last_error("band too wide for densedense_to_dia"); return CUVDIA_ERR_UNSUPPORTED; }
-    dd2dia_band_kernel<<<dim3(gx, gy, nsplit), THREADS, SMEM, st>>>(mapA, mapB, P);
+    if (gx > 65535 || nsplit > 65535) { set_last_error("matrix too tall for the banded densedense_to_dia"); return CUVDIA_ERR_UNSUPPORTED; }
+    dd2dia_band_kernel<<<dim3(gy, gx, nsplit), THREADS, SMEM, st>>>(mapA, mapB, P);
     count_launch();
     rc = check_launch("dd2dia_band_kernel");
     if (rc) return rc;

@@ -121,8 +121,11 @@ prod_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
     auto Bs = [&](int s) { return Bs0 + s * BSF; };
 
     const int tid = threadIdx.x;
-    const int t0 = blockIdx.x * TM;               // first output row of the tile
-    const int n0 = blockIdx.y * TN;               // first batch column of the tile
+    // Column tiles vary fastest across the grid: blocks that run together share one slice of the band
+    // (read once from HBM) and stream different batch columns; neighbouring row tiles re-use most of
+    // each other's B rows out of L2.
+    const int t0 = blockIdx.y * TM;               // first output row of the tile
+    const int n0 = blockIdx.x * TN;               // first batch column of the tile
     const int lane = tid & 31, warp = tid >> 5;
     const int rg = lane >> 4, cg = lane & 15;
     const int r0 = (warp * 2 + rg) * 8;           // this thread's 8 output rows: t0 + r0 .. t0 + r0 + 7
@@ -337,8 +340,8 @@ static int launch_band_t(const cuvdia_plan* p, const float* A, const float* B, i
         attr_done[TRANS][EXACT] = true;
     }
     const int gx = (P.rows_out + TM - 1) / TM, gy = (ncols + TN - 1) / TN;
-    if (gy > 65535) { set_last_error("too many batch columns for the banded kernel"); return CUVDIA_ERR_UNSUPPORTED; }
-    prod_band_kernel<TRANS, EXACT><<<dim3(gx, gy), THREADS, smem_bytes<TRANS>(), st>>>(mapA, mapB, P);
+    if (gx > 65535) { set_last_error("too many rows for the banded kernel"); return CUVDIA_ERR_UNSUPPORTED; }
+    prod_band_kernel<TRANS, EXACT><<<dim3(gy, gx), THREADS, smem_bytes<TRANS>(), st>>>(mapA, mapB, P);
     count_launch();
     return check_launch("prod_band_kernel");
 }
