@@ -227,4 +227,24 @@ int cuvdia_axpby_f32(float* dst, const float* x, const float* y, float a, float 
     return launch_axpby(dst, x, y, a, b, n, (cudaStream_t)stream);
 }
 
+int cuvdia_binary_f32(float* dst, const float* x, const float* y, int op, float p, float p2, long long n, void* stream) {
+    CUVDIA_REQUIRE(dst != nullptr && x != nullptr && y != nullptr);
+    CUVDIA_REQUIRE(op >= CUVDIA_BF_ADD && op <= CUVDIA_BF_AXPBY);
+    CUVDIA_REQUIRE(n >= 0);
+    if (n == 0) return CUVDIA_OK;
+    return launch_binary(dst, x, y, op, p, p2, n, (cudaStream_t)stream);
+}
+
+int cuvdia_fill_f32(float* dst, float value, long long n, void* stream) {
+    CUVDIA_REQUIRE(dst != nullptr && n >= 0);
+    if (n == 0) return CUVDIA_OK;
+    return launch_fill(dst, value, 0, n, (cudaStream_t)stream);
+}
+
+int cuvdia_sequence_f32(float* dst, long long n, void* stream) {
+    CUVDIA_REQUIRE(dst != nullptr && n >= 0);
+    if (n == 0) return CUVDIA_OK;
+    return launch_fill(dst, 0.f, 1, n, (cudaStream_t)stream);
+}
+
 }  // extern "C"

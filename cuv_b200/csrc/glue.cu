@@ -69,4 +69,43 @@ int launch_axpby(float* dst, const float* x, const float* y, float a, float b, l
     return check_launch("axpby_kernel");
 }
 
+// dst[i] = op(x[i], y[i]) with the parameterised functors of apply_binary_functor
+// (tensor_ops/functors.hpp:377-433): op codes are CUVDIA_BF_*.
+__global__ void __launch_bounds__(256)
+binary_kernel(float* dst, const float* x, const float* y, int op, float p, float p2, long long n) {
+    for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < n; t += (long long)gridDim.x * blockDim.x) {
+        const float a = x[t], b = y[t];
+        float r;
+        switch (op) {
+            case CUVDIA_BF_ADD: r = a + b; break;
+            case CUVDIA_BF_SUBTRACT: r = a - b; break;
+            case CUVDIA_BF_MULT: r = a * b; break;
+            case CUVDIA_BF_AXPY: r = p * a + b; break;
+            case CUVDIA_BF_XPBY: r = a + p * b; break;
+            default: r = p * a + p2 * b; break;     // CUVDIA_BF_AXPBY
+        }
+        dst[t] = r;
+    }
+}
+
+int launch_binary(float* dst, const float* x, const float* y, int op, float p, float p2, long long n, cudaStream_t st) {
+    const int blocks = (int)std::min<long long>((n + 255) / 256, 16LL * sm_count());
+    binary_kernel<<<blocks, 256, 0, st>>>(dst, x, y, op, p, p2, n);
+    count_launch();
+    return check_launch("binary_kernel");
+}
+
+// dst[i] = value (sequence == 0) or dst[i] = i (sequence != 0): fill / sequence of tensor_ops.hpp:108-122
+__global__ void __launch_bounds__(256) fill_kernel(float* dst, float value, int sequence, long long n) {
+    for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < n; t += (long long)gridDim.x * blockDim.x)
+        dst[t] = sequence ? (float)t : value;
+}
+
+int launch_fill(float* dst, float value, int sequence, long long n, cudaStream_t st) {
+    const int blocks = (int)std::min<long long>((n + 255) / 256, 16LL * sm_count());
+    fill_kernel<<<blocks, 256, 0, st>>>(dst, value, sequence, n);
+    count_launch();
+    return check_launch("fill_kernel");
+}
+
 }  // namespace cuvdia

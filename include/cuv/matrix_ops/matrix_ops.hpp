@@ -1,0 +1,121 @@
+// prod / spmv with a DIA operand and reduce_to_col / reduce_to_row of the CUV surface
+// (matrix_ops/matrix_ops.hpp:118-119,185-228,277-278 in CUV).  The dev_memory_space versions
+// forward to the cuvdia C ABI and then synchronise, because every CUV operation is blocking
+// (matrix_ops/spmv.cu:99, matrix_ops_reduce.cu:186,214).  The host_memory_space versions are
+// declared only: CUV's own host code is the parity reference and is not part of this library
+// (the test suite links a restatement of it).
+#pragma once
+#include <type_traits>
+
+#include "cuv/basics/dia_matrix.hpp"
+#include "cuv/basics/tensor.hpp"
+
+namespace cuv {
+
+enum reduce_functor {          // matrix_ops/matrix_ops.hpp:185-196
+    RF_ADD, RF_MEAN, RF_ADD_SQUARED, RF_MAX, RF_ARGMAX, RF_ARGMIN, RF_MIN, RF_MULT, RF_LOGADDEXP, RF_ADDEXP
+};
+
+// Arithmetic of the device prod: CUVDIA_MODE_EXACT (default, bit-identical to the host code) or
+// CUVDIA_MODE_FAST (fused multiply-add).  Process-wide switch; CUV's signature has no room for it.
+inline int& dia_prod_mode() { static int mode = CUVDIA_MODE_EXACT; return mode; }
+
+// ---- prod(C, A_dia, B, transA, transB, factAB, factC) -------------------------------------------------
+template <class V, class M, class L>
+void prod(tensor<V, M, L>& C, const dia_matrix<V, M>& A, const tensor<V, M, L>& B, char transA = 'n', char transB = 'n',
+          const float& factAB = 1.f, const float& factC = 0.f);
+
+template <>
+void prod(tensor<float, host_memory_space, column_major>& C, const dia_matrix<float, host_memory_space>& A,
+          const tensor<float, host_memory_space, column_major>& B, char transA, char transB, const float& factAB,
+          const float& factC);        // defined by the reference host code, not by this library
+
+template <>
+inline void prod(tensor<float, dev_memory_space, column_major>& C, const dia_matrix<float, dev_memory_space>& A,
+                 const tensor<float, dev_memory_space, column_major>& B, char transA, char transB,
+                 const float& factAB, const float& factC) {
+    cuvAssert(C.shape().size() == 2);                    // matrix_ops/spmv.cu:229-232
+    cuvAssert(B.shape().size() == 2);
+    cuvAssert(C.shape()[1] == B.shape()[1]);
+    cuvAssert(A.vec_ptr());
+    if (transA == 't') { cuvAssert(A.w() == C.shape()[0]); cuvAssert(A.h() == B.shape()[0]); }
+    else if (transA == 'n') { cuvAssert(A.h() == C.shape()[0]); cuvAssert(A.w() == B.shape()[0]); }
+    cuvdia_check(cuvdia_prod_f32(A.plan(), A.vec().ptr(), B.ptr(), (int)B.shape()[0], C.ptr(), (int)C.shape()[0],
+                                 (int)C.shape()[1], transA, transB, factAB, factC, dia_prod_mode(), 0));
+    cuvSafeCall(cudaDeviceSynchronize());
+}
+
+// ---- spmv(dst, A, v, transA, factAv, factC): vectors packed column-major in 1-D tensors ------------------
+template <class V, class M>
+void spmv(tensor<V, M>& dst, const dia_matrix<V, M>& A, const tensor<V, M>& v, char transA = 'n',
+          const float& factAv = 1.f, const float& factC = 0.f);
+
+template <>
+void spmv(tensor<float, host_memory_space>& dst, const dia_matrix<float, host_memory_space>& A,
+          const tensor<float, host_memory_space>& v, char transA, const float& factAv, const float& factC);
+
+template <>
+inline void spmv(tensor<float, dev_memory_space>& dst, const dia_matrix<float, dev_memory_space>& A,
+                 const tensor<float, dev_memory_space>& v, char transA, const float& factAv, const float& factC) {
+    const unsigned rows_b = transA == 't' ? A.h() : A.w(), rows_c = transA == 't' ? A.w() : A.h();
+    cuvAssert(v.size() % rows_b == 0);
+    const unsigned n = v.size() / rows_b;
+    cuvAssert(dst.size() == n * rows_c);
+    cuvdia_check(cuvdia_prod_f32(A.plan(), A.vec().ptr(), v.ptr(), (int)rows_b, dst.ptr(), (int)rows_c, (int)n, transA,
+                                 'n', factAv, factC, dia_prod_mode(), 0));
+    cuvSafeCall(cudaDeviceSynchronize());
+}
+
+// ---- reductions ------------------------------------------------------------------------------------------
+namespace detail {
+// src viewed as n_strided lines of n_contig contiguous floats (matrix_ops_reduce.cu:348-379)
+template <class L> inline void reduce_dims(const tensor<float, dev_memory_space, L>& m, long long& n_contig, long long& n_strided) {
+    const bool cm = std::is_same<L, column_major>::value;
+    const long long first = m.shape(0), rest = m.size() / m.shape(0);
+    const long long last = m.shape(m.ndim() - 1), front = m.size() / m.shape(m.ndim() - 1);
+    if (cm) { n_contig = first; n_strided = rest; } else { n_contig = last; n_strided = front; }
+}
+void reduce_host(tensor<float, host_memory_space>& v, const float* m, long long n_contig, long long n_strided,
+                 bool over_strided, reduce_functor rf, float factNew, float factOld);   // reference host code
+}  // namespace detail
+
+// dst[i] = factOld*dst[i] + factNew*rf_j(src(i,j)), dst.size() == src.shape(0)
+template <class L>
+void reduce_to_col(tensor<float, dev_memory_space>& dst, const tensor<float, dev_memory_space, L>& src,
+                   reduce_functor rf = RF_ADD, const float& factNew = 1.f, const float& factOld = 0.f) {
+    cuvAssert(src.ptr() != NULL);
+    long long nc, ns;
+    detail::reduce_dims(src, nc, ns);
+    const bool over_strided = std::is_same<L, column_major>::value;    // outputs = first dimension
+    cuvAssert((long long)dst.size() == (over_strided ? nc : ns));
+    cuvdia_check(cuvdia_reduce_f32(dst.ptr(), src.ptr(), nc, ns, over_strided ? 1 : 0, (int)rf, factNew, factOld, 0));
+    cuvSafeCall(cudaDeviceSynchronize());
+}
+// dst[j] = factOld*dst[j] + factNew*rf_i(src(i,j)), dst.size() == src.shape(last)
+template <class L>
+void reduce_to_row(tensor<float, dev_memory_space>& dst, const tensor<float, dev_memory_space, L>& src,
+                   reduce_functor rf = RF_ADD, const float& factNew = 1.f, const float& factOld = 0.f) {
+    cuvAssert(src.ptr() != NULL);
+    long long nc, ns;
+    detail::reduce_dims(src, nc, ns);
+    const bool over_strided = !std::is_same<L, column_major>::value;   // outputs = last dimension
+    cuvAssert((long long)dst.size() == (over_strided ? nc : ns));
+    cuvdia_check(cuvdia_reduce_f32(dst.ptr(), src.ptr(), nc, ns, over_strided ? 1 : 0, (int)rf, factNew, factOld, 0));
+    cuvSafeCall(cudaDeviceSynchronize());
+}
+template <class L>
+void reduce_to_col(tensor<float, host_memory_space>& dst, const tensor<float, host_memory_space, L>& src,
+                   reduce_functor rf = RF_ADD, const float& factNew = 1.f, const float& factOld = 0.f) {
+    const bool cm = std::is_same<L, column_major>::value;
+    const long long nc = cm ? src.shape(0) : src.shape(src.ndim() - 1), ns = src.size() / nc;
+    detail::reduce_host(dst, src.ptr(), nc, ns, cm, rf, factNew, factOld);
+}
+template <class L>
+void reduce_to_row(tensor<float, host_memory_space>& dst, const tensor<float, host_memory_space, L>& src,
+                   reduce_functor rf = RF_ADD, const float& factNew = 1.f, const float& factOld = 0.f) {
+    const bool cm = std::is_same<L, column_major>::value;
+    const long long nc = cm ? src.shape(0) : src.shape(src.ndim() - 1), ns = src.size() / nc;
+    detail::reduce_host(dst, src.ptr(), nc, ns, !cm, rf, factNew, factOld);
+}
+
+}  // namespace cuv

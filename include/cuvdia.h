@@ -185,6 +185,23 @@ CUVDIA_API int cuvdia_bias_sigmoid_sample_f32(float* act, int ld, const float* b
 CUVDIA_API int cuvdia_axpby_f32(float* dst, const float* x, const float* y, float a, float b, long long n,
                      void* stream);
 
+/* dst = op(x, y) element-wise over n floats for the float functors of apply_binary_functor the DIA
+ * path's callers use (tensor_ops/tensor_ops.hpp:460-492,530-655; functors.hpp:377-433):
+ * ADD x+y, SUBTRACT x-y, MULT x*y, AXPY p*x+y, XPBY x+p*y, AXPBY p*x+p2*y.  dst may alias x or y. */
+#define CUVDIA_BF_ADD      0
+#define CUVDIA_BF_SUBTRACT 1
+#define CUVDIA_BF_MULT     2
+#define CUVDIA_BF_AXPY     3
+#define CUVDIA_BF_XPBY     4
+#define CUVDIA_BF_AXPBY    5
+CUVDIA_API int cuvdia_binary_f32(float* dst, const float* x, const float* y, int op, float p, float p2,
+                                 long long n, void* stream);
+
+/* fill(v, value) and sequence(v) (0, 1, 2, ...) on device tensors (tensor_ops/tensor_ops.hpp:108-122;
+ * sequence is thrust::sequence there, tensor_ops.cuh:251-252). */
+CUVDIA_API int cuvdia_fill_f32(float* dst, float value, long long n, void* stream);
+CUVDIA_API int cuvdia_sequence_f32(float* dst, long long n, void* stream);
+
 /* Benchmark aid, no counterpart in CUV: measures the device's FP32 ceiling with a register-resident
  * loop and returns it in TFLOP/s counting a multiply-add as 2 flops.  fused: 0 = a separate multiply
  * and add per step (the EXACT arithmetic), 1 = one fused multiply-add per step (the FAST arithmetic),

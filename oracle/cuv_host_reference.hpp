@@ -1,0 +1,60 @@
+// TEST INFRASTRUCTURE ONLY.  Supplies the host_memory_space halves of the CUV surface (prod, spmv,
+// densedense_to_dia, reductions) by calling the CPU oracle (cuv_host_oracle.c), so that the C++
+// tests can do what CUV's own tests do: run the same template on a host and a device object and
+// compare.  The library never includes or links this file.
+#pragma once
+#include "cuv.hpp"
+
+extern "C" {
+int oracle_prod_dia(float* C, int ldc, const float* vals, const int* offsets, int nd, int h, int w, int stride, int rf,
+                    const float* B, int ldb, int ncols, char transA, float factAB, float factC, int nthreads);
+int oracle_dd2dia(float* Cvals, const int* offsets, int nd, int h, int w, int stride, int rf, const float* A, int lda,
+                  const float* B, int ldb, int ncols, float factAB, float factC, int literal_host, int nthreads);
+int oracle_reduce(float* dst, const float* src, long n_contig, long n_strided, int over_strided, int rf, float factNew,
+                  float factOld, int nthreads);
+}
+
+namespace cuv {
+
+template <>
+inline void prod(tensor<float, host_memory_space, column_major>& C, const dia_matrix<float, host_memory_space>& A,
+                 const tensor<float, host_memory_space, column_major>& B, char transA, char transB, const float& factAB,
+                 const float& factC) {
+    cuvAssert(C.shape().size() == 2);                    // matrix_ops/spmv.cu:211-214
+    cuvAssert(B.shape().size() == 2);
+    cuvAssert(transB == 'n');
+    cuvAssert(C.shape()[1] == B.shape()[1]);
+    if (transA == 't') { cuvAssert(A.h() == B.shape()[0]); cuvAssert(A.w() == C.shape()[0]); }
+    else { cuvAssert(A.w() == B.shape()[0]); cuvAssert(A.h() == C.shape()[0]); }
+    cuvAssert(oracle_prod_dia(C.ptr(), C.shape()[0], A.vec().ptr(), A.get_offsets().ptr(), A.num_dia(), A.h(), A.w(),
+                              A.stride(), A.row_fact(), B.ptr(), B.shape()[0], C.shape()[1], transA, factAB, factC, 1) == 0);
+}
+
+template <>
+inline void spmv(tensor<float, host_memory_space>& dst, const dia_matrix<float, host_memory_space>& A,
+                 const tensor<float, host_memory_space>& v, char transA, const float& factAv, const float& factC) {
+    const unsigned rows_b = transA == 't' ? A.h() : A.w(), rows_c = transA == 't' ? A.w() : A.h();
+    cuvAssert(oracle_prod_dia(dst.ptr(), rows_c, A.vec().ptr(), A.get_offsets().ptr(), A.num_dia(), A.h(), A.w(),
+                              A.stride(), A.row_fact(), v.ptr(), rows_b, v.size() / rows_b, transA, factAv, factC, 1) == 0);
+}
+
+template <class V, class L, class I>
+void densedense_to_dia(dia_matrix<V, host_memory_space, I>& C, const host_block_descriptor<V, I>&,
+                       const tensor<V, host_memory_space, L>& A, const tensor<V, host_memory_space, L>& B,
+                       const V& factAB, const V& factC) {
+    cuvAssert(C.w() == B.shape()[0]);                    // matrix_ops/densedense_to_sparse.cu:214-216
+    cuvAssert(C.h() == A.shape()[0]);
+    cuvAssert(A.shape()[1] == B.shape()[1]);
+    cuvAssert(oracle_dd2dia(C.vec().ptr(), C.get_offsets().ptr(), C.num_dia(), C.h(), C.w(), C.stride(), C.row_fact(),
+                            A.ptr(), A.shape()[0], B.ptr(), B.shape()[0], A.shape()[1], factAB, factC, 0, 1) == 0);
+}
+
+namespace detail {
+inline void reduce_host(tensor<float, host_memory_space>& v, const float* m, long long n_contig, long long n_strided,
+                        bool over_strided, reduce_functor rf, float factNew, float factOld) {
+    cuvAssert((long long)v.size() == (over_strided ? n_contig : n_strided));
+    cuvAssert(oracle_reduce(v.ptr(), m, n_contig, n_strided, over_strided ? 1 : 0, (int)rf, factNew, factOld, 1) == 0);
+}
+}  // namespace detail
+
+}  // namespace cuv

@@ -1,0 +1,246 @@
+// C++ tests of the CUV surface over libcuvdia.so.  They follow CUV's own tests of this path - same
+// fixtures, same "device object vs host object of the same template" pattern:
+//   src/tests/spmv.cpp:49-143, src/tests/densedense_to_dia.cpp:50-197, src/tests/dia_mat.cpp:48-132,
+//   src/tests/convert.cpp:110-129, src/tests/matrix_op.cpp:80-105,858-924.
+// The host halves come from the CPU oracle (oracle/cuv_host_reference.hpp).  Exit code 0 = all passed.
+#include <cmath>
+#include <cstdio>
+#include <string>
+#include <vector>
+
+#include "cuv.hpp"
+#include "cuv_host_reference.hpp"
+
+using namespace cuv;
+
+static int g_fail = 0, g_checks = 0;
+#define CHECK(cond) do { g_checks++; if (!(cond)) { g_fail++; std::printf("FAILED %s:%d: %s\n", __FILE__, __LINE__, #cond); } } while (0)
+
+// MAT_CMP of tools/cuv_test.hpp:39-57: element-wise closeness in PERCENT
+template <class A, class B> static void mat_cmp(const A& x, const B& y, double percent, const char* what) {
+    int bad = 0;
+    for (unsigned i = 0; i < x.shape()[0]; i++)
+        for (unsigned j = 0; j < x.shape()[1]; j++) {
+            const double a = (float)x(i, j), b = (float)y(i, j);
+            const double tol = percent * 0.01 * std::max(std::fabs(a), std::fabs(b));
+            if (!(std::fabs(a - b) <= tol)) bad++;
+        }
+    g_checks++;
+    if (bad) { g_fail++; std::printf("FAILED %s: %d elements differ by more than %g%%\n", what, bad, percent); }
+}
+template <class A, class B> static void mat_eq(const A& x, const B& y, const char* what) { mat_cmp(x, y, 0.0, what); }
+
+// ---- spmv.cpp -----------------------------------------------------------------------------------------------
+static void test_spmv() {
+    const int n = 32, m = 16, k = 6, rf = 1;
+    dia_matrix<float, host_memory_space> A(n, m, 7, std::max(n, m), rf);
+    tensor<float, host_memory_space, column_major> B(m, k), C(n, k);
+    std::vector<int> off;
+    for (int i = -A.num_dia() / 2; i <= A.num_dia() / 2; i++) off.push_back(i);
+    A.set_offsets(off);
+    sequence(A.vec()); sequence(C); sequence(B);
+    dia_matrix<float, dev_memory_space> A2(n, m, A.num_dia(), A.stride(), rf);
+    convert(A2, A);
+    {   // spmv_dev_correctness_trans (:103-115)
+        tensor<float, dev_memory_space, column_major> C2(C.shape()), B2(B.shape());
+        convert(C2, C); convert(B2, B);
+        prod(B, A, C, 't', 'n');
+        prod(B2, A2, C2, 't', 'n');
+        mat_eq(B, B2, "spmv_dev_correctness_trans");       // exact arithmetic: identical, not just within 0.1 %
+    }
+    {   // spmv_dev_correctness (:116-129)
+        sequence(B); sequence(C);
+        tensor<float, dev_memory_space, column_major> C2(C.shape()), B2(B.shape());
+        convert(C2, C); convert(B2, B);
+        prod(C, A, B, 'n', 'n', 2.f, 1.3f);
+        prod(C2, A2, B2, 'n', 'n', 2.f, 1.3f);
+        mat_eq(C, C2, "spmv_dev_correctness");
+    }
+    {   // host DIA vs dense (:130-143): C = 1.3*C + 2*A_dense*B computed densely in double
+        sequence(B); sequence(C);
+        tensor<float, host_memory_space, column_major> A_(n, m), Cd(n, k);
+        convert(A_, A);
+        for (int i = 0; i < n; i++)
+            for (int c = 0; c < k; c++) {
+                double s = 0;
+                for (int j = 0; j < m; j++) s += (double)(float)A_(i, j) * (double)(float)B(j, c);
+                Cd(i, c) = (float)(1.3f * (double)(float)C(i, c) + 2.0 * s);
+            }
+        tensor<float, dev_memory_space, column_major> C2(C.shape()), B2(B.shape());
+        convert(C2, C); convert(B2, B);
+        prod(C2, A2, B2, 'n', 'n', 2.f, 1.3f);
+        mat_cmp(C2, Cd, 0.1, "spmv dev DIA vs dense");
+    }
+    {   // spmv on packed vectors
+        tensor<float, host_memory_space> v(m * 2), d(n * 2);
+        sequence(v); fill(d, 0);
+        tensor<float, dev_memory_space> v2(m * 2), d2(n * 2);
+        v2 = v; d2 = d;
+        spmv(d, A, v, 'n', 1.f, 0.f);
+        spmv(d2, A2, v2, 'n', 1.f, 0.f);
+        int bad = 0;
+        for (int i = 0; i < n * 2; i++) bad += (float)d[i] != (float)d2[i];
+        CHECK(bad == 0);
+    }
+    {   // preconditions throw, as cuvAssert does
+        tensor<float, dev_memory_space, column_major> C2(C.shape()), B2(B.shape());
+        bool threw = false;
+        try { prod(C2, A2, B2, 'n', 't'); } catch (const std::runtime_error&) { threw = true; }
+        CHECK(threw);
+        threw = false;
+        try { prod(B2, A2, C2, 'n', 'n'); } catch (const std::runtime_error&) { threw = true; }
+        CHECK(threw);
+    }
+}
+
+// ---- densedense_to_dia.cpp -----------------------------------------------------------------------------
+static void test_dd2dia() {
+    const int n = 36, m = 19, k = 16, rf = 4;
+    dia_matrix<float, dev_memory_space> C(n, m, 7, std::max(n, m), rf);
+    tensor<float, dev_memory_space, column_major> A(n, k), B(m, k);
+    std::vector<int> off;
+    for (int i = -C.num_dia() / 2; i <= C.num_dia() / 2; i++) off.push_back(i);
+    C.set_offsets(off);
+    fill(C.vec(), 0); sequence(A); sequence(B);
+    dia_matrix<float, host_memory_space> C2(n, m, C.num_dia(), C.stride(), rf);
+    tensor<float, host_memory_space, column_major> A2(A.shape()), B2(B.shape());
+    convert(C2, C); convert(A2, A); convert(B2, B);
+    dev_block_descriptor<float> bd(C);
+    host_block_descriptor<float> bdh(C2);
+    densedense_to_dia(C, bd, A, B);
+    densedense_to_dia(C2, bdh, A2, B2);
+    {   // dd2s_cmp_dev_host (:166-197)
+        int bad = 0;
+        for (int i = 0; i < n; i++)
+            for (int j = 0; j < m; j++) bad += (float)C(i, j) != (float)C2(i, j);
+        CHECK(bad == 0);
+    }
+    {   // dd2s_correctness_dev (:109-137): stored cells equal the dense A*B^T
+        int bad = 0, stored = 0;
+        for (int i = 0; i < n; i++)
+            for (int j = 0; j < m; j++) {
+                if (!C.has(i, j)) { bad += C(i, j) != 0.f; continue; }
+                double s = 0;
+                for (int b = 0; b < k; b++) s += (double)(float)A2(i, b) * (double)(float)B2(j, b);
+                stored++;
+                bad += std::fabs((float)C(i, j) - s) > 1e-4 * std::fabs(s);
+            }
+        CHECK(bad == 0);
+        CHECK(stored > 100);
+    }
+    {   // non-default factors: C = 0.5*C + 0.25*A*B^T, device vs host
+        densedense_to_dia(C, bd, A, B, 0.25f, 0.5f);
+        densedense_to_dia(C2, bdh, A2, B2, 0.25f, 0.5f);
+        int bad = 0;
+        for (int i = 0; i < n; i++)
+            for (int j = 0; j < m; j++) {
+                const float a = C(i, j), b = C2(i, j);
+                bad += std::fabs(a - b) > 1e-5f * std::fabs(b);
+            }
+        CHECK(bad == 0);
+    }
+}
+
+// ---- dia_mat.cpp / convert.cpp ----------------------------------------------------------------------------
+static void test_dia_mat() {
+    const int n = 32, m = 16;
+    dia_matrix<float, host_memory_space> w(n, m, 3, n);
+    std::vector<int> off = {0, 1, -1};
+    w.set_offsets(off);
+    sequence(w.vec());
+    {   // spmv_uninit (:103-108): converting into an empty device matrix allocates it
+        dia_matrix<float, dev_memory_space> w2;
+        convert(w2, w);
+        CHECK(w2.vec_ptr() != nullptr && w2.h() == (unsigned)n && w2.w() == (unsigned)m && w2.num_dia() == 3);
+    }
+    {   // dia2dense (:111-119)
+        tensor<float, host_memory_space, column_major> w2(n, m);
+        convert(w2, w);
+        int bad = 0;
+        for (int i = 0; i < n; i++) for (int j = 0; j < m; j++) bad += (float)w2(i, j) != (float)w(i, j);
+        CHECK(bad == 0);
+    }
+    {   // host2dev and back (:121-132, convert.cpp:110-129)
+        dia_matrix<float, dev_memory_space> w2(n, m, w.num_dia(), w.stride());
+        convert(w2, w);
+        dia_matrix<float, host_memory_space> w3(n, m, w.num_dia(), w.stride());
+        convert(w3, w2);
+        int bad = 0;
+        for (int i = 0; i < n; i++) for (int j = 0; j < m; j++) bad += (float)w(i, j) != (float)w3(i, j) || (float)w(i, j) != (float)w2(i, j);
+        CHECK(bad == 0);
+        for (int s = 0; s < 3; s++) CHECK(w3.get_offset(s) == off[s] && w2.get_offset(s) == off[s]);
+    }
+}
+
+// ---- matrix_op.cpp reductions -----------------------------------------------------------------------------
+template <class L> static void reduce_sweep(const char* layout) {
+    const int n = 270;
+    tensor<float, host_memory_space, L> h(n, n);
+    unsigned s = 12345;
+    for (int i = 0; i < n * n; i++) { s = s * 1664525u + 1013904223u; h[i] = (float)((s >> 8) & 0xffff) / 65536.f + 0.5f; }
+    tensor<float, dev_memory_space, L> d(n, n);
+    convert(d, h);
+    const reduce_functor rfs[] = {RF_ADD, RF_MEAN, RF_ADD_SQUARED, RF_MAX, RF_ARGMAX, RF_ARGMIN, RF_MIN, RF_MULT, RF_LOGADDEXP, RF_ADDEXP};
+    for (reduce_functor rf : rfs)
+        for (int to_col = 0; to_col < 2; to_col++) {
+            tensor<float, host_memory_space> vh(n);
+            tensor<float, dev_memory_space> vd(n);
+            fill(vh, 0); fill(vd, 0);
+            if (to_col) { reduce_to_col(vh, h, rf); reduce_to_col(vd, d, rf); }
+            else { reduce_to_row(vh, h, rf); reduce_to_row(vd, d, rf); }
+            int bad = 0;
+            for (int i = 0; i < n; i++) {
+                const float a = vh[i], b = vd[i];
+                const bool exact = rf == RF_MAX || rf == RF_MIN || rf == RF_ARGMAX || rf == RF_ARGMIN;
+                bad += exact ? (a != b) : !(std::fabs(a - b) <= 1e-3f * std::fabs(a));      // CUV: 0.1 %
+            }
+            if (bad) std::printf("reduce %s rf=%d to_col=%d: %d mismatches\n", layout, (int)rf, to_col, bad);
+            CHECK(bad == 0);
+        }
+    {   // factors (matrix_op.cpp:721-737 pattern): v = 0.5*v + 1.0*sum
+        tensor<float, host_memory_space> vh(n);
+        tensor<float, dev_memory_space> vd(n);
+        sequence(vh); sequence(vd);
+        reduce_to_col(vh, h, RF_ADD, 1.f, 0.5f);
+        reduce_to_col(vd, d, RF_ADD, 1.f, 0.5f);
+        int bad = 0;
+        for (int i = 0; i < n; i++) bad += !(std::fabs((float)vh[i] - (float)vd[i]) <= 1e-4f * std::fabs((float)vh[i]));
+        CHECK(bad == 0);
+    }
+}
+
+static void test_tensor_ops() {
+    tensor<float, host_memory_space> a(100), b(100);
+    sequence(a); fill(b, 2.f);
+    tensor<float, dev_memory_space> a2(100), b2(100);
+    a2 = a; b2 = b;
+    apply_binary_functor(a, b, BF_AXPBY, 0.9f, -0.01f);
+    apply_binary_functor(a2, b2, BF_AXPBY, 0.9f, -0.01f);
+    int bad = 0;
+    for (int i = 0; i < 100; i++) bad += (float)a[i] != (float)a2[i];
+    CHECK(bad == 0);
+    apply_binary_functor(a, b, BF_MULT); apply_binary_functor(a2, b2, BF_MULT);
+    apply_binary_functor(a, a, b, BF_SUBTRACT); apply_binary_functor(a2, a2, b2, BF_SUBTRACT);
+    for (int i = 0; i < 100; i++) bad += (float)a[i] != (float)a2[i];
+    CHECK(bad == 0);
+    tensor<float, dev_memory_space> alias = a2;          // same-type assignment aliases the storage
+    CHECK(alias.ptr() == a2.ptr());
+}
+
+int main() {
+    try {
+        initCUDA(0);
+        test_spmv();
+        test_dd2dia();
+        test_dia_mat();
+        reduce_sweep<column_major>("column_major");
+        reduce_sweep<row_major>("row_major");
+        test_tensor_ops();
+        exitCUDA();
+    } catch (const std::exception& e) {
+        std::printf("EXCEPTION: %s\n", e.what());
+        return 2;
+    }
+    std::printf("%d checks, %d failed, %llu kernels launched through libcuvdia\n", g_checks, g_fail, cuvdia_launch_count());
+    return g_fail ? 1 : 0;
+}
