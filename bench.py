@@ -251,28 +251,31 @@ def run_ours(args, cfg):
         hG = torch.empty(step.G.vec.numel(), dtype=torch.float32, pin_memory=True) if rank == 0 else None
         hb = torch.empty(step.bias_grad.numel(), dtype=torch.float32, pin_memory=True) if rank == 0 else None
 
-        def e2e_step():
-            V0.t().copy_(hV0, non_blocking=True)
-            U_h.t().copy_(hUh, non_blocking=True)
-            U_v.t().copy_(hUv, non_blocking=True)
-            one_step()
-            if rank == 0:
-                hG.copy_(step.G.vec, non_blocking=True)
-                hb.copy_(step.bias_grad, non_blocking=True)
+        fed = rbm.HostFedRBM(step, allreduce=world > 1)
 
-        e2e_step()
+        def e2e_steps(k):
+            # copies of step i+1 overlap the compute of step i; every step's inputs cross PCIe inside the region
+            fed.submit(hV0, hUh, hUv)
+            for i in range(k):
+                if i + 1 < k:
+                    fed.submit(hV0, hUh, hUv)
+                fed.run(hG, hb) if rank == 0 else fed.run()
+            fed.wait()
+
+        e2e_steps(2)
         barrier()
         a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a0.record()
-        for _ in range(args.steps):
-            e2e_step()
+        e2e_steps(args.steps)
         a1.record()
         barrier()
         e2e_ms = max_over_ranks(a0.elapsed_time(a1)) / args.steps
         e2e = {"value": world * work["bytes"] / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
                "h2d_bytes_per_step": int(world * 3 * units * nb * 4),
                "d2h_bytes_per_step": int((step.G.vec.numel() + step.bias_grad.numel()) * 4),
-               "ms_per_step": e2e_ms}
+               "ms_per_step": e2e_ms,
+               "how": "pinned host inputs (V0, U_h, U_v) copied to the device every step on a copy stream, overlapped "
+                      "with the previous step's compute; gradients read back to pinned host memory every step"}
 
     # the products once more in the other arithmetic, for the record (outside every timed region)
     other = cb.MODE_EXACT if mode == cb.MODE_FAST else cb.MODE_FAST

@@ -58,7 +58,12 @@ class SparseRBMStep:
     def step(self, V0, U_h, U_v):
         """One CD-1 gradient evaluation on this rank's batch columns; results in G.vec, gc, gb
         (partial sums when batch_global > batch_local)."""
-        W, inv = self.W, 1.0 / self.B
+        self.forward(V0, U_h, U_v)
+        self.gradients(V0)
+
+    def forward(self, V0, U_h, U_v):
+        """The three products with their bias/logistic/sampling passes."""
+        W = self.W
         t = self._timed
         t("prod_n", lambda: cb.prod(self.H0p, W, V0, "n", "n", 1.0, 0.0, self.mode))
         t("glue", lambda: cb.bias_sigmoid_sample(self.H0p, self.c_hid, U_h, self.H0))
@@ -66,6 +71,11 @@ class SparseRBMStep:
         t("glue", lambda: cb.bias_sigmoid_sample(self.V1p, self.b_vis, U_v, self.V1))
         t("prod_n", lambda: cb.prod(self.H1p, W, self.V1, "n", "n", 1.0, 0.0, self.mode))
         t("glue", lambda: cb.bias_sigmoid_sample(self.H1p, self.c_hid))
+
+    def gradients(self, V0):
+        """Weight-gradient diagonals and bias gradients from the activations of forward()."""
+        inv = 1.0 / self.B
+        t = self._timed
         t("dd2dia", lambda: cb.densedense_to_dia(self.G, self.Gbd, self.H0p, V0, inv, 0.0))
         t("dd2dia", lambda: cb.densedense_to_dia(self.G, self.Gbd, self.H1p, self.V1, -inv, 1.0))
         t("reduce", lambda: cb.reduce_to_col(self.gc, self.H0p, cb.RF_ADD, inv, 0.0))
@@ -77,6 +87,70 @@ class SparseRBMStep:
         """Sum the partial gradients over the ranks (NCCL over NVLink): the diagonals of G and the
         two bias gradients."""
         allreduce_gradients(self.G.vec, self.bias_grad, group)
+
+
+class HostFedRBM:
+    """Runs SparseRBMStep on inputs that live in pinned host memory and returns the gradients to
+    pinned host memory, with the transfers overlapped with compute: the host-to-device copies of step
+    i+1 run on a copy stream while step i computes (two device input sets), and the device-to-host
+    read of step i's gradients runs on a third stream while step i+1's products compute."""
+
+    def __init__(self, step, allreduce=False):
+        import torch
+        self.step, self.allreduce = step, allreduce
+        dev = step.dev
+        E = cb.colmajor_empty
+        self.inputs = [(E(step.vis, step.nb, dev), E(step.hid, step.nb, dev), E(step.vis, step.nb, dev))
+                       for _ in range(2)]
+        self.h2d, self.d2h = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        self.ready = [torch.cuda.Event() for _ in range(2)]
+        self.consumed = [torch.cuda.Event() for _ in range(2)]
+        self.grads_done, self.fetched = torch.cuda.Event(), torch.cuda.Event()
+        self.n_sub = self.n_run = 0
+        self._fetch_pending = False
+
+    def submit(self, hV0, hU_h, hU_v):
+        """Queue the copy of one step's inputs (pinned host tensors holding the column-major matrices,
+        i.e. shape (batch, units) contiguous)."""
+        import torch
+        slot = self.n_sub % 2
+        if self.n_sub >= 2:
+            self.h2d.wait_event(self.consumed[slot])
+        with torch.cuda.stream(self.h2d):
+            for dst, src in zip(self.inputs[slot], (hV0, hU_h, hU_v)):
+                dst.t().copy_(src, non_blocking=True)
+            self.ready[slot].record(self.h2d)
+        self.n_sub += 1
+
+    def run(self, hG=None, hbias=None):
+        """Compute the oldest submitted step; if host buffers are given, queue the read-back of its
+        gradients into them."""
+        import torch
+        cur = torch.cuda.current_stream()
+        slot = self.n_run % 2
+        cur.wait_event(self.ready[slot])
+        V0, U_h, U_v = self.inputs[slot]
+        self.step.forward(V0, U_h, U_v)
+        if self._fetch_pending:
+            cur.wait_event(self.fetched)          # the previous gradients must have left before they are overwritten
+        self.step.gradients(V0)
+        if self.allreduce:
+            self.step.allreduce()
+        self.consumed[slot].record(cur)
+        self.n_run += 1
+        if hG is not None:
+            self.grads_done.record(cur)
+            self.d2h.wait_event(self.grads_done)
+            with torch.cuda.stream(self.d2h):
+                hG.copy_(self.step.G.vec, non_blocking=True)
+                hbias.copy_(self.step.bias_grad, non_blocking=True)
+                self.fetched.record(self.d2h)
+            self._fetch_pending = True
+
+    def wait(self):
+        import torch
+        torch.cuda.current_stream().wait_stream(self.d2h)
+        torch.cuda.current_stream().wait_stream(self.h2d)
 
 
 def shard_columns(batch_global, world, rank):

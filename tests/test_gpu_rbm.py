@@ -86,3 +86,36 @@ def test_sharded_partials_sum_to_full_batch():
     np.testing.assert_allclose(G.cpu().numpy(), full.G.vec.cpu().numpy(), rtol=0, atol=2e-6)
     np.testing.assert_allclose(bias.cpu().numpy(), full.bias_grad.cpu().numpy(), rtol=0, atol=2e-6)
     assert_bits_equal(cb.to_host(parts[1].H0p), np.asfortranarray(cb.to_host(full.H0p)[:, 64:]))
+
+
+def test_host_fed_pipeline_matches_direct_step():
+    """HostFedRBM (pinned host inputs, overlapped copies, gradients read back) gives the bits of the
+    direct device-resident step, for consecutive steps on different inputs."""
+    import torch
+    import cuv_b200 as cb
+    from cuv_b200 import rbm
+    units, nd, nb = 1024, 64, 96
+    offs = np.arange(-nd // 2, nd // 2, dtype=np.int32)
+    sets = [rbm_oracle.make_inputs(2000 + i, units, units, offs, nb, w_std=0.05) for i in range(3)]
+    W = sets[0][0]
+    Wd = cb.dev_dia_matrix_f(W.h, W.w, W.offsets, W.stride, W.rf).set_vec(W.vals)
+    direct = rbm.SparseRBMStep(Wd, nb)
+    want = []
+    for _, V0, U_h, U_v in sets:
+        direct.step(cb.to_device(V0), cb.to_device(U_h), cb.to_device(U_v))
+        want.append((direct.G.vec.cpu().numpy().copy(), direct.bias_grad.cpu().numpy().copy()))
+    st = rbm.SparseRBMStep(Wd, nb)
+    fed = rbm.HostFedRBM(st)
+    pin = lambda a: torch.from_numpy(np.ascontiguousarray(a.T)).pin_memory()
+    hosts = [tuple(pin(a) for a in s[1:]) for s in sets]
+    outs = [(torch.empty(st.G.vec.numel()).pin_memory(), torch.empty(st.bias_grad.numel()).pin_memory()) for _ in sets]
+    fed.submit(*hosts[0])
+    for i in range(3):
+        if i + 1 < 3:
+            fed.submit(*hosts[i + 1])
+        fed.run(*outs[i])
+    fed.wait()
+    torch.cuda.synchronize()
+    for i in range(3):
+        assert_bits_equal(outs[i][0].numpy(), want[i][0], "G of step %d" % i)
+        assert_bits_equal(outs[i][1].numpy(), want[i][1], "bias gradients of step %d" % i)
