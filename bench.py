@@ -44,57 +44,90 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clock, power and throttle reasons of one GPU through NVML on a thread while the timed
+    region runs (every ~10 ms); falls back to one nvidia-smi query if NVML is not importable."""
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown"}
 
     def __init__(self, index):
-        self.index, self.proc, self.path = index, None, "/tmp/cuvdia_clocks_%d_%d.csv" % (os.getpid(), index)
+        self.index, self.samples, self.thread, self.stop_flag = index, [], None, False
+        self.handle = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index(index))
+        except Exception:
+            self.nv = None
+
+    @staticmethod
+    def _physical_index(index):
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [v for v in vis.split(",") if v.strip() != ""]
+            if index < len(ids) and ids[index].strip().isdigit():
+                return int(ids[index])
+        return index
+
+    def _sample(self):
+        nv, h = self.nv, self.handle
+        sm = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+        try:
+            mask = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+        except Exception:
+            mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+        try:
+            power = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
+        except Exception:
+            power = 0.0
+        self.samples.append((sm, mask, power))
+
+    def _loop(self):
+        while not self.stop_flag:
+            try:
+                self._sample()
+            except Exception:
+                break
+            time.sleep(0.01)
 
     def start(self):
-        try:
-            self.out = open(self.path, "w")
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
-                                         stdout=self.out, stderr=subprocess.DEVNULL)
-        except Exception:
-            self.proc = None
+        if self.handle is None:
+            return
+        import threading
+        self.stop_flag = False
+        self.thread = threading.Thread(target=self._loop, daemon=True)
+        self.thread.start()
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
-        self.out.close()
-        sm, smax, power, reasons = [], [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in open(self.path):
-            p = [x.strip() for x in line.split(",")]
-            if len(p) < 8:
-                continue
+        if self.handle is None:
+            return self._smi_once()
+        self.stop_flag = True
+        self.thread.join(timeout=2)
+        if not self.samples:
             try:
-                sm.append(float(p[0])); smax.append(float(p[1])); power.append(float(p[2]))
-            except ValueError:
-                continue
-            for name, val in zip(names, p[4:8]):
-                if val.lower().startswith("active"):
+                self._sample()
+            except Exception:
+                return self._smi_once()
+        smax = self.nv.nvmlDeviceGetMaxClockInfo(self.handle, self.nv.NVML_CLOCK_SM)
+        reasons = set()
+        for _, mask, _ in self.samples:
+            for bit, name in self.REASONS.items():
+                if mask & bit:
                     reasons.add(name)
+        powers = [p for _, _, p in self.samples]
+        cut = statistics.median(powers)
+        loaded = [s for s, _, p in self.samples if p >= cut] or [s for s, _, _ in self.samples]
+        return {"sm_mhz": statistics.median(loaded), "sm_max_mhz": smax, "reasons": sorted(reasons),
+                "samples": len(self.samples), "power_w_max": max(powers)}
+
+    def _smi_once(self):
         try:
-            os.remove(self.path)
-        except OSError:
-            pass
-        if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        # samples under load: the upper half by power draw
-        cut = statistics.median(power)
-        loaded = [s for s, w in zip(sm, power) if w >= cut] or sm
-        return {"sm_mhz": statistics.median(loaded), "sm_max_mhz": max(smax), "reasons": sorted(reasons),
-                "samples": len(sm), "power_w_max": max(power)}
+            out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=clocks.sm,clocks.max.sm",
+                                  "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=10).stdout
+            a, b = [float(x) for x in out.strip().split(",")[:2]]
+            return {"sm_mhz": a, "sm_max_mhz": b, "reasons": ["sampled once after the run (NVML unavailable)"]}
+        except Exception:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["clock sampling unavailable"]}
 
 
 def band_offsets(nd):
@@ -182,6 +215,11 @@ def run_ours(args, cfg):
                          "(use --impl reference for the CPU oracle)")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    # Libraries (NCCL prints its version banner) write to file descriptor 1; point it at stderr for the
+    # run and keep the real stdout for the one JSON line.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     units, nd, batch = cfg["units"], cfg["num_dia"], cfg["batch"]
@@ -348,7 +386,8 @@ def run_ours(args, cfg):
             "value": work["bytes"] / t_full / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
             "sample": "CD-1 step of the CPU oracle on the first %d of %d batch columns, %d threads, %.1f s; "
                       "time scaled linearly to the full batch" % (sample, batch, threads, t)}
-    print(json.dumps(line), flush=True)
+    sys.stdout.flush()
+    os.write(real_stdout, (json.dumps(line) + "\n").encode())
     if world > 1:
         dist.destroy_process_group()
 

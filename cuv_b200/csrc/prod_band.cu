@@ -32,7 +32,9 @@ constexpr int TN = 128;          // batch columns per block
 constexpr int KC = 32;           // steps per chunk
 constexpr int NRAW = KC + 7;     // diagonals a chunk touches
 constexpr int WR = 156;          // rows of the B window (>= KC + 120, = 4 * odd: conflict-free 128-bit loads)
-constexpr int THREADS = 256;
+constexpr int NCONS_WARPS = 8;      // consumer warps: the 128 x 128 tile
+constexpr int NPROD_WARPS = 2;      // producer warps: TMA issue + skew pass
+constexpr int THREADS = 32 * (NCONS_WARPS + NPROD_WARPS);
 constexpr int RAW_FLOATS_N = TM * NRAW;     // 'n': band slice is TM rows wide
 constexpr int RAW_FLOATS_T = WR * NRAW;     // 't': band slice is as wide as the B window
 constexpr int BS_FLOATS = WR * TN;
@@ -41,8 +43,12 @@ __host__ __device__ constexpr size_t align128(size_t x) { return (x + 127) / 128
 template <bool TRANS> __host__ __device__ constexpr size_t raw_bytes() { return align128(sizeof(float) * (TRANS ? RAW_FLOATS_T : RAW_FLOATS_N)); }
 __host__ __device__ constexpr size_t bs_bytes() { return align128(sizeof(float) * BS_FLOATS); }
 template <bool TRANS> __host__ __device__ constexpr size_t smem_bytes() {
-    return 2 * raw_bytes<TRANS>() + 2 * bs_bytes() + sizeof(float) * AS_FLOATS + 64 /*barriers*/;
+    return raw_bytes<TRANS>() + 2 * bs_bytes() + 2 * sizeof(float) * AS_FLOATS + 128 /*barriers*/;
 }
+#ifndef PB_UNROLL
+#define PB_UNROLL 4
+#endif
+constexpr int G_UNROLL = PB_UNROLL;         // unroll factor of the 4-step groups in the main loop
 constexpr unsigned SPIN_LIMIT = 1u << 26;   // bounded wait on a TMA completion barrier
 }  // namespace pb
 
@@ -102,6 +108,21 @@ struct BandParams {
     int* status;              // set to 1 if a TMA wait gave up
 };
 
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Warp-uniform bounded wait: either every lane sees the phase complete or the whole warp gives up.
+__device__ __forceinline__ bool warp_wait(unsigned long long* bar, unsigned parity) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity) ? 1 : 0) != 0;
+}
+
+// Roles: warps 0..7 are consumers (the 128 x 128 tile, 8 x 8 outputs per thread); warps 8 and 9 are
+// producers.  The producers issue the TMA loads and re-lay ("skew") each band slice into the
+// coefficient buffer As while the consumers are still computing the previous chunk, so the consumers
+// never meet a block-wide barrier: every hand-over is an mbarrier with a bounded wait.
+//   raw        one buffer: band slice of chunk c as TMA delivers it          (raw_full / raw_free)
+//   As[2]      skewed, masked, factAB-scaled coefficients of chunks c, c+1   (as_full / as_empty)
+//   Bs[2]      B windows of chunks c, c+1                                    (bs_full / bs_empty)
 template <bool TRANS, bool EXACT>
 __global__ void __launch_bounds__(pb::THREADS, 1)
 prod_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
@@ -113,12 +134,16 @@ prod_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
     extern __shared__ __align__(1024) float smem_f[];
     constexpr int RAWF = (int)(raw_bytes<TRANS>() / sizeof(float));
     constexpr int BSF = (int)(bs_bytes() / sizeof(float));
-    float* const raw0 = smem_f;
-    float* const Bs0 = smem_f + 2 * RAWF;
-    float* const As = smem_f + 2 * RAWF + 2 * BSF;
-    unsigned long long* const full = reinterpret_cast<unsigned long long*>(As + AS_FLOATS);
-    auto raw = [&](int s) { return raw0 + s * RAWF; };
-    auto Bs = [&](int s) { return Bs0 + s * BSF; };
+    float* const raw = smem_f;
+    float* const Bs0 = smem_f + RAWF;
+    float* const As0 = smem_f + RAWF + 2 * BSF;
+    unsigned long long* const bars = reinterpret_cast<unsigned long long*>(As0 + 2 * AS_FLOATS);
+    unsigned long long* const raw_full = bars + 0;
+    unsigned long long* const raw_free = bars + 1;
+    unsigned long long* const as_full = bars + 2;     // [2]
+    unsigned long long* const as_empty = bars + 4;    // [2]
+    unsigned long long* const bs_full = bars + 6;     // [2]
+    unsigned long long* const bs_empty = bars + 8;    // [2]
 
     const int tid = threadIdx.x;
     // Column tiles vary fastest across the grid: blocks that run together share one slice of the band
@@ -127,11 +152,7 @@ prod_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
     const int t0 = blockIdx.y * TM;               // first output row of the tile
     const int n0 = blockIdx.x * TN;               // first batch column of the tile
     const int lane = tid & 31, warp = tid >> 5;
-    const int rg = lane >> 4, cg = lane & 15;
-    const int r0 = (warp * 2 + rg) * 8;           // this thread's 8 output rows: t0 + r0 .. t0 + r0 + 7
-    // this thread's 8 columns: n0 + cg + 16*c
-
-    constexpr unsigned TX_BYTES = sizeof(float) * ((TRANS ? RAW_FLOATS_T : RAW_FLOATS_N) + BS_FLOATS);
+    const int nch = P.nchunks;
 
     // Chunk c covers steps q in [c*KC, (c+1)*KC).
     //  'n': q = j + k + rem           (j = row within the thread's 8, k = diagonal index)
@@ -140,24 +161,106 @@ prod_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
     //  't': q = k - j + 7 + rem
     //       band slice rows k from c*KC - rem - 7, matrix rows = the B window's rows;
     //       B window starts at matrix row t0 - lo + rem + 8 - (c+1)*KC; a thread reads window row r0 + KC-1 - qq.
-    auto issue = [&](int c, int s) {
-        const int y0 = c * KC - P.rem - 7;
-        const int xb = TRANS ? (t0 - P.lo + P.rem + 8 - (c + 1) * KC) : (t0 + P.lo - P.rem + c * KC);
-        mbar_expect_tx(&full[s], TX_BYTES);
-        tma_load_2d(raw(s), &mapA, TRANS ? xb : t0, y0, &full[s]);
-        tma_load_2d(Bs(s), &mapB, xb, n0, &full[s]);
-    };
+    auto win_row0 = [&](int c) { return TRANS ? (t0 - P.lo + P.rem + 8 - (c + 1) * KC) : (t0 + P.lo - P.rem + c * KC); };
 
     if (tid == 0) {
-        mbar_init(&full[0], 1);
-        mbar_init(&full[1], 1);
+        mbar_init(raw_full, 1);
+        mbar_init(raw_free, NPROD_WARPS);
+#pragma unroll
+        for (int s = 0; s < 2; s++) {
+            mbar_init(&as_full[s], NPROD_WARPS);
+            mbar_init(&as_empty[s], NCONS_WARPS);
+            mbar_init(&bs_full[s], 1);
+            mbar_init(&bs_empty[s], NCONS_WARPS);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    if (tid == 0) {
-        issue(0, 0);
-        if (P.nchunks > 1) issue(1, 1);
+
+    if (warp >= NCONS_WARPS) {
+        // =========================== producers ===========================
+        const int pw = warp - NCONS_WARPS;                     // 0 or 1: handles the steps qq = pw, pw+2, ...
+        const bool issuer = pw == 0 && lane == 0;
+        constexpr unsigned RAW_TX = sizeof(float) * (TRANS ? RAW_FLOATS_T : RAW_FLOATS_N);
+        constexpr unsigned BS_TX = sizeof(float) * BS_FLOATS;
+        auto issue_raw = [&](int c) {
+            mbar_expect_tx(raw_full, RAW_TX);
+            tma_load_2d(raw, &mapA, TRANS ? win_row0(c) : t0, c * KC - P.rem - 7, raw_full);
+        };
+        auto issue_b = [&](int c) {
+            mbar_expect_tx(&bs_full[c & 1], BS_TX);
+            tma_load_2d(Bs0 + (c & 1) * BSF, &mapB, win_row0(c), n0, &bs_full[c & 1]);
+        };
+        if (issuer) {
+            issue_raw(0);
+            issue_b(0);
+            if (nch > 1) issue_b(1);
+        }
+        for (int c = 0; c < nch; c++) {
+            bool ok = warp_wait(raw_full, c & 1);
+            if (ok && c >= 2) ok = warp_wait(&as_empty[c & 1], ((c >> 1) + 1) & 1);
+            if (!ok) { if (lane == 0 && P.status) *P.status = 1; return; }
+            // ---- skew: As[qq][r] = factAB * A[k][matrix row], zero where the cell is outside the matrix ----
+            float* as = As0 + (c & 1) * AS_FLOATS;
+            const int y0 = c * KC - P.rem - 7;
+            const int xb = win_row0(c);
+            const int j = lane & 7;
+            // block-uniform: every cell this chunk touches lies inside the matrix
+            const bool interior = TRANS ? (y0 >= 0 && y0 + NRAW <= P.nd && xb >= 0 && xb + WR <= P.h)
+                                        : (y0 >= 0 && y0 + NRAW <= P.nd && xb >= 0 && xb + TM + KC <= P.w);
+            constexpr int SSTEP = TRANS ? 2 * (WR - 1) : 2 * TM;
+#pragma unroll
+            for (int m = 0; m < TM / 32; m++) {
+                const int r = lane + 32 * m;
+                // slice element for (qq, r):  'n': row qq-j+7, column r;   't': row qq+j, column (r-j)+KC-1-qq
+                const float* src = TRANS ? raw + (pw + j) * WR + (r - j) + KC - 1 - pw : raw + (pw - j + 7) * TM + r;
+                float* dst = as + pw * TM + r;
+                if (interior && P.fa == 1.f) {
+#pragma unroll
+                    for (int it = 0; it < KC / 2; it++) dst[it * 2 * TM] = src[it * SSTEP];
+                } else {
+#pragma unroll 4
+                    for (int it = 0; it < KC / 2; it++) {
+                        const int qq = pw + 2 * it;
+                        bool in;
+                        if (!TRANS) {
+                            const int k = y0 + qq - j + 7;
+                            const int jb = t0 + r + P.lo + k;               // matrix column of the cell
+                            in = (unsigned)k < (unsigned)P.nd && (unsigned)jb < (unsigned)P.w;
+                        } else {
+                            const int k = y0 + qq + j;
+                            const int i = xb + (r - j) + KC - 1 - qq;       // matrix row of the cell
+                            in = (unsigned)k < (unsigned)P.nd && (unsigned)i < (unsigned)P.h;
+                        }
+                        float v = src[it * SSTEP];
+                        if (P.fa != 1.f) v = __fmul_rn(P.fa, v);
+                        dst[it * 2 * TM] = in ? v : 0.f;
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(&as_full[c & 1]); mbar_arrive(raw_free); }
+            if (issuer) {
+                // the slice buffer is free once both producer warps are done with it
+                if (c + 1 < nch) {
+                    if (!mbar_wait(raw_free, c & 1)) { if (P.status) *P.status = 1; }
+                    else issue_raw(c + 1);
+                }
+                // the B stage of chunk c-1 is free once the consumers are done with that chunk
+                if (c >= 1 && c + 1 < nch) {
+                    if (!mbar_wait(&bs_empty[(c - 1) & 1], ((c - 1) >> 1) & 1)) { if (P.status) *P.status = 1; }
+                    else issue_b(c + 1);
+                }
+            }
+            __syncwarp();
+        }
+        return;
     }
+
+    // =========================== consumers ===========================
+    const int rg = lane >> 4, cg = lane & 15;
+    const int r0 = (warp * 2 + rg) * 8;           // this thread's 8 output rows: t0 + r0 .. t0 + r0 + 7
+    // this thread's 8 columns: n0 + cg + 16*c
 
     // acc[jp][c] holds rows (2*jp, 2*jp+1) of column c as a packed pair
     float2 acc[4][8];
@@ -180,60 +283,19 @@ prod_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         }
     }
 
-    for (int c = 0; c < P.nchunks; c++) {
+    for (int c = 0; c < nch; c++) {
         const int s = c & 1;
-        if (!mbar_wait(&full[s], (c >> 1) & 1)) {
-            if (P.status) *P.status = 1;
-            return;
-        }
-        // ---- skew pass: As[qq][r] = factAB * A[k][matrix row], zero where the cell is outside the matrix ----
-        {
-            const int r = tid & (TM - 1);
-            const int j = r & 7;
-            const int qq0 = tid >> 7;                                // 0 or 1; this thread does qq0, qq0+2, ...
-            const float* rw = raw(s);
-            const int y0 = c * KC - P.rem - 7;
-            const int xb = TRANS ? (t0 - P.lo + P.rem + 8 - (c + 1) * KC) : (t0 + P.lo - P.rem + c * KC);
-            // slice element for (qq, r):  'n': row qq-j+7, column r;   't': row qq+j, column (r-j)+KC-1-qq
-            const float* src = TRANS ? rw + (qq0 + j) * WR + (r - j) + KC - 1 - qq0 : rw + (qq0 - j + 7) * TM + r;
-            constexpr int SSTEP = TRANS ? 2 * (WR - 1) : 2 * TM;
-            float* dst = As + qq0 * TM + r;
-            // block-uniform: every cell this chunk touches lies inside the matrix
-            const bool interior = TRANS ? (y0 >= 0 && y0 + NRAW <= P.nd && xb >= 0 && xb + WR <= P.h)
-                                        : (y0 >= 0 && y0 + NRAW <= P.nd && xb >= 0 && xb + TM + KC <= P.w);
-            if (interior && P.fa == 1.f) {
-#pragma unroll
-                for (int it = 0; it < KC / 2; it++) dst[it * 2 * TM] = src[it * SSTEP];
-            } else {
-#pragma unroll 4
-                for (int it = 0; it < KC / 2; it++) {
-                    const int qq = qq0 + 2 * it;
-                    bool ok;
-                    if (!TRANS) {
-                        const int k = y0 + qq - j + 7;
-                        const int jb = t0 + r + P.lo + k;               // matrix column of the cell
-                        ok = (unsigned)k < (unsigned)P.nd && (unsigned)jb < (unsigned)P.w;
-                    } else {
-                        const int k = y0 + qq + j;
-                        const int i = xb + (r - j) + KC - 1 - qq;       // matrix row of the cell
-                        ok = (unsigned)k < (unsigned)P.nd && (unsigned)i < (unsigned)P.h;
-                    }
-                    float v = src[it * SSTEP];
-                    if (P.fa != 1.f) v = __fmul_rn(P.fa, v);
-                    dst[it * 2 * TM] = ok ? v : 0.f;
-                }
-            }
-        }
-        __syncthreads();
-        // ---- main loop ----
-        const float* bsp = Bs(s) + (size_t)cg * WR + (TRANS ? (r0 + KC - 4) : r0);
-        const float* asp = As + r0;
-#pragma unroll 2
+        bool ok = warp_wait(&as_full[s], (c >> 1) & 1);
+        if (ok) ok = warp_wait(&bs_full[s], (c >> 1) & 1);
+        if (!ok) { if (lane == 0 && P.status) *P.status = 1; return; }
+        const float* bsp = Bs0 + s * BSF + cg * WR + (TRANS ? (r0 + KC - 4) : r0);
+        const float* asp = As0 + s * AS_FLOATS + r0;
+#pragma unroll G_UNROLL
         for (int g = 0; g < KC / 4; g++) {
             float4 bw[8];
 #pragma unroll
             for (int cc = 0; cc < 8; cc++)
-                bw[cc] = *reinterpret_cast<const float4*>(bsp + (size_t)cc * 16 * WR + (TRANS ? -4 * g : 4 * g));
+                bw[cc] = *reinterpret_cast<const float4*>(bsp + cc * 16 * WR + (TRANS ? -4 * g : 4 * g));
 #pragma unroll
             for (int u = 0; u < 4; u++) {
                 const float4 a0 = *reinterpret_cast<const float4*>(asp + (4 * g + u) * TM);
@@ -251,8 +313,8 @@ prod_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
                 }
             }
         }
-        __syncthreads();                 // everyone is done with stage s and with As
-        if (tid == 0 && c + 2 < P.nchunks) issue(c + 2, s);
+        __syncwarp();
+        if (lane == 0) { mbar_arrive(&as_empty[s]); mbar_arrive(&bs_empty[s]); }
     }
 
     // ---- store ----
