@@ -8,6 +8,8 @@ int launch_prod(const cuvdia_plan* p, const float* A, const float* B, int ldb, f
                 bool trans, float factAB, float factC, int mode, cudaStream_t st) {
     if (prod_band_applicable(p, A, B, ldb, ncols))
         return launch_prod_band(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);
+    if (prod_window_applicable(p, trans, ncols))
+        return launch_prod_window(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);
     return launch_prod_generic(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);
 }
 

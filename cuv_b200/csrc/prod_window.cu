@@ -1,0 +1,251 @@
+// prod with a DIA operand for any diagonal pattern and row factor, with the dense operand staged in
+// shared memory.
+//
+// A block owns T consecutive output rows and CB batch columns.  Every B row those outputs can touch
+// - from the smallest to the largest stored offset - is copied once into shared memory (coalesced
+// along the rows of each column), laid out [column][row] so that consecutive threads read
+// consecutive words (no bank conflicts); for the transposed product with a row factor the rows are
+// de-interleaved by their position inside a group of row_fact rows, which keeps that property.
+// Each thread then walks the diagonals in storage order for its one output row: one coefficient
+// (read from global memory, coalesced along the diagonal) and CB shared-memory words per term.  A B
+// value is fetched from L2 once per block instead of once per diagonal that uses it, which is what
+// bounds the plain generic kernel on scattered patterns.  Per term the kernel does one shared load
+// per multiply-add, so its ceiling is the shared-memory bandwidth (a quarter of the FP32 rate);
+// banded row_fact-1 patterns use the register-tiled kernel in prod_band.cu instead.
+// EXACT accumulates (factAB*d)*x with a separate multiply and add in storage order, bit-identical
+// to CUV's host loop (matrix_ops/spmv.cu:161-198).
+#include "cuvdia_internal.cuh"
+
+namespace cuvdia {
+
+namespace pw {
+constexpr int OFFS = 256;            // offsets staged per pass
+constexpr size_t SMEM_LIMIT = 200 * 1024;
+}
+
+struct WindowParams {
+    int h, w, nd, S, rf;
+    int ldb, ldc, ncols;
+    int off_min, off_max;
+    int wq;                 // positions per de-interleaved plane ('t'): window rows / rf; 'n': window rows
+    int pitch;              // words per column in shared memory
+    float fa, fc;
+    const float* A; const int* offs; const float* B; float* C;
+};
+
+template <bool TRANS, bool EXACT, int T, int CB>
+__global__ void __launch_bounds__(T)
+prod_window_kernel(const WindowParams P) {
+    extern __shared__ __align__(16) float win[];        // [CB][pitch]
+    __shared__ int s_off[pw::OFFS];
+    const int tid = threadIdx.x;
+    const int o0 = blockIdx.x * T;                      // first output row of the block
+    const int c0 = blockIdx.y * CB;
+    const int rf = P.rf;
+    // first B row of the window (a multiple of rf for 't', so groups of rf rows stay together)
+    const int lo = TRANS ? max(0, o0 - P.off_max) * rf : max(0, o0 / rf + P.off_min);
+    const int rows_b = TRANS ? P.h : P.w;
+    const int wrows = TRANS ? P.wq * rf : P.wq;
+    // ---- stage the window: element (row lo+rr, column c0+c) -> win[c*pitch + pos(rr)] ----
+    // Asynchronous 4-byte copies (global -> shared without passing through registers): a thread
+    // issues all of its copies back to back and waits once, so the staging is bandwidth- and not
+    // latency-bound.  Rows or columns outside the operand are written as zeros (source size 0).
+    for (int c = 0; c < CB; c++) {
+        const int col = c0 + c;
+        const float* src = P.B + (size_t)min(col, P.ncols - 1) * P.ldb;
+        const unsigned dst0 = (unsigned)__cvta_generic_to_shared(win + c * P.pitch);
+#pragma unroll 4
+        for (int rr = tid; rr < wrows; rr += T) {
+            const int row = lo + rr;
+            const int pos = TRANS ? (rr % rf) * P.wq + rr / rf : rr;
+            const unsigned nbytes = (row < rows_b && col < P.ncols) ? 4u : 0u;
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;"
+                         ::"r"(dst0 + 4u * pos), "l"(src + min(row, rows_b - 1)), "r"(nbytes) : "memory");
+        }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    const int o = o0 + tid;
+    const int rows_out = TRANS ? P.w : P.h;
+    const bool row_ok = o < rows_out;
+    float acc[CB];
+#pragma unroll
+    for (int c = 0; c < CB; c++) {
+        acc[c] = 0.f;
+        if (P.fc != 0.f && row_ok && c0 + c < P.ncols) acc[c] = __fmul_rn(P.C[(size_t)(c0 + c) * P.ldc + o], P.fc);
+    }
+    const int oq = TRANS ? o : (row_ok ? o / rf : 0);
+    for (int kb = 0; kb < P.nd; kb += pw::OFFS) {
+        const int kn = min(pw::OFFS, P.nd - kb);
+        __syncthreads();                               // window staged / previous offsets consumed
+        for (int t = tid; t < kn; t += T) s_off[t] = P.offs[kb + t];
+        __syncthreads();
+        if (!TRANS) {
+            // term of diagonal k: A[k][o] * B[o/rf + off_k].  The coefficients of the next four diagonals are
+            // fetched while the current four are consumed.
+            float a[4], an[4];
+            int pos[4], posn[4];
+            bool ok[4], okn[4];
+            auto fetch = [&](int kk, float (&av)[4], int (&pv)[4], bool (&ov)[4]) {
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int k = kk + u;
+                    const int j = oq + (k < kn ? s_off[k] : 0);
+                    ov[u] = row_ok && k < kn && j >= 0 && j < P.w;          // spmv.cu:185-189
+                    pv[u] = ov[u] ? j - lo : 0;
+                    av[u] = ov[u] ? __ldg(P.A + (size_t)(kb + k) * P.S + o) : 0.f;
+                }
+            };
+            fetch(0, an, posn, okn);
+            for (int kk = 0; kk < kn; kk += 4) {
+#pragma unroll
+                for (int u = 0; u < 4; u++) { a[u] = an[u]; pos[u] = posn[u]; ok[u] = okn[u]; }
+                if (kk + 4 < kn) fetch(kk + 4, an, posn, okn);
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    if (!ok[u]) continue;
+                    const float av = (P.fa != 1.f) ? __fmul_rn(P.fa, a[u]) : a[u];
+#pragma unroll
+                    for (int c = 0; c < CB; c++) {
+                        const float x = win[c * P.pitch + pos[u]];
+                        acc[c] = EXACT ? __fadd_rn(acc[c], __fmul_rn(av, x)) : fmaf(av, x, acc[c]);
+                    }
+                }
+            }
+        } else {
+            // term (k, l): A[k][m*rf + l] * B[m*rf + l] with m = o - off_k                  (spmv.cu:165-177)
+            const int mlo = lo / rf;
+            const bool vec4 = (rf % 4 == 0) && (P.S % 4 == 0) && ((reinterpret_cast<uintptr_t>(P.A) & 15) == 0);
+            if (vec4) {
+                // groups of four rows are fetched with one 128-bit load, one diagonal ahead
+                auto fetch4 = [&](int kk, int l0, bool& valid, int& m) -> float4 {
+                    m = oq - s_off[kk];
+                    valid = row_ok && m >= 0 && (long long)(m + 1) * rf <= P.h;
+                    if (!valid) return make_float4(0.f, 0.f, 0.f, 0.f);
+                    return __ldg(reinterpret_cast<const float4*>(P.A + (size_t)(kb + kk) * P.S + (size_t)m * rf + l0));
+                };
+                const int nl = rf / 4;                       // 128-bit groups per diagonal
+                const int total = kn * nl;
+                bool vn; int mn;
+                float4 an = fetch4(0, 0, vn, mn);
+                for (int t = 0; t < total; t++) {
+                    const int l0 = (t % nl) * 4;
+                    const float4 a4 = an; const bool valid = vn; const int m = mn;
+                    if (t + 1 < total) an = fetch4((t + 1) / nl, ((t + 1) % nl) * 4, vn, mn);
+                    if (!valid) continue;
+                    const float av[4] = {a4.x, a4.y, a4.z, a4.w};
+                    const float* wp = win + (m - mlo) + l0 * P.wq;
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const float au = (P.fa != 1.f) ? __fmul_rn(P.fa, av[u]) : av[u];
+#pragma unroll
+                        for (int c = 0; c < CB; c++) {
+                            const float x = wp[c * P.pitch + u * P.wq];
+                            acc[c] = EXACT ? __fadd_rn(acc[c], __fmul_rn(au, x)) : fmaf(au, x, acc[c]);
+                        }
+                    }
+                }
+            } else {
+                for (int kk = 0; kk < kn; kk++) {
+                    const int m = oq - s_off[kk];
+                    const bool valid = row_ok && m >= 0 && (long long)(m + 1) * rf <= P.h;
+                    if (!valid) continue;
+                    const float* Ak = P.A + (size_t)(kb + kk) * P.S + (size_t)m * rf;
+                    const float* wp = win + (m - mlo);
+                    for (int l = 0; l < rf; l++) {
+                        float au = __ldg(Ak + l);
+                        if (P.fa != 1.f) au = __fmul_rn(P.fa, au);
+#pragma unroll
+                        for (int c = 0; c < CB; c++) {
+                            const float x = wp[c * P.pitch + l * P.wq];
+                            acc[c] = EXACT ? __fadd_rn(acc[c], __fmul_rn(au, x)) : fmaf(au, x, acc[c]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if (row_ok) {
+#pragma unroll
+        for (int c = 0; c < CB; c++)
+            if (c0 + c < P.ncols) P.C[(size_t)(c0 + c) * P.ldc + o] = acc[c];
+    }
+}
+
+// Window rows (per plane for 't') a block of T outputs needs, or -1 if it cannot fit with CB columns.
+static long long window_q(const cuvdia_plan* p, bool trans, int T) {
+    const long long span = (long long)p->off_max - p->off_min;
+    return trans ? (long long)T + span : ((long long)T - 1) / p->rf + 1 + span + 1;
+}
+
+template <bool TRANS, bool EXACT, int T, int CB>
+static int launch_window_t(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
+                           float fa, float fc, cudaStream_t st) {
+    WindowParams P;
+    P.h = p->h; P.w = p->w; P.nd = p->nd; P.S = p->stride; P.rf = p->rf;
+    P.ldb = ldb; P.ldc = ldc; P.ncols = ncols; P.off_min = p->off_min; P.off_max = p->off_max;
+    long long wq = window_q(p, TRANS, T);
+    // never more rows than the operand has (rounded up to whole groups for 't')
+    const long long cap = TRANS ? ((long long)p->h + p->rf - 1) / p->rf : p->w;
+    wq = std::min(wq, cap);
+    P.wq = (int)wq;
+    const long long wrows = TRANS ? wq * p->rf : wq;
+    P.pitch = (int)(wrows | 1);                          // odd pitch: columns start in different banks
+    P.fa = fa; P.fc = fc; P.A = A; P.offs = p->d_offsets; P.B = B; P.C = C;
+    const size_t smem = sizeof(float) * (size_t)P.pitch * CB;
+    static bool attr_done = false;
+    if (!attr_done) {
+        CUVDIA_CUDA(cudaFuncSetAttribute(prod_window_kernel<TRANS, EXACT, T, CB>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pw::SMEM_LIMIT));
+        attr_done = true;
+    }
+    const int rows_out = TRANS ? p->w : p->h;
+    const int gx = (rows_out + T - 1) / T, gy = (ncols + CB - 1) / CB;
+    if (gy > 65535) { set_last_error("too many batch columns"); return CUVDIA_ERR_UNSUPPORTED; }
+    prod_window_kernel<TRANS, EXACT, T, CB><<<dim3(gx, gy), T, smem, st>>>(P);
+    count_launch();
+    return check_launch("prod_window_kernel");
+}
+
+// Picks (T, CB) so that the window fits in shared memory; returns false if nothing fits.
+static bool window_config(const cuvdia_plan* p, bool trans, int ncols, int* T, int* CB) {
+    // first choice: a configuration whose window leaves room for two blocks per SM; else the largest that fits
+    const int cands[4][2] = {{256, 16}, {256, 8}, {128, 8}, {128, 4}};
+    for (int pass = 0; pass < 2; pass++) {
+        // (only for the transposed product: there the coefficient loads are strided and need the extra warps)
+        const size_t limit = (pass == 0 && trans) ? (size_t)100 * 1024 : pw::SMEM_LIMIT;
+        for (auto& c : cands) {
+            if (c[1] > 8 && ncols < 64) continue;
+            long long wq = window_q(p, trans, c[0]);
+            const long long cap = trans ? ((long long)p->h + p->rf - 1) / p->rf : p->w;
+            wq = std::min(wq, cap);
+            const long long wrows = trans ? wq * p->rf : wq;
+            if ((size_t)(wrows | 1) * c[1] * sizeof(float) <= limit) { *T = c[0]; *CB = c[1]; return true; }
+        }
+    }
+    return false;
+}
+
+bool prod_window_applicable(const cuvdia_plan* p, bool trans, int ncols) {
+    int T, CB;
+    return window_config(p, trans, ncols, &T, &CB);
+}
+
+int launch_prod_window(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
+                       bool trans, float fa, float fc, int mode, cudaStream_t st) {
+    int T = 0, CB = 0;
+    if (!window_config(p, trans, ncols, &T, &CB)) { set_last_error("window does not fit"); return CUVDIA_ERR_UNSUPPORTED; }
+    const bool exact = mode == CUVDIA_MODE_EXACT;
+#define GO(TR, EX, TT, CC) return launch_window_t<TR, EX, TT, CC>(p, A, B, ldb, C, ldc, ncols, fa, fc, st)
+#define PICK(TR, EX)                                    \
+    if (T == 256 && CB == 16) GO(TR, EX, 256, 16);      \
+    if (T == 256 && CB == 8) GO(TR, EX, 256, 8);        \
+    if (T == 128 && CB == 8) GO(TR, EX, 128, 8);        \
+    GO(TR, EX, 128, 4)
+    if (trans) { if (exact) { PICK(true, true); } else { PICK(true, false); } }
+    else { if (exact) { PICK(false, true); } else { PICK(false, false); } }
+#undef PICK
+#undef GO
+}
+
+}  // namespace cuvdia
