@@ -362,7 +362,13 @@ def run_ours(args, cfg):
                    % (units * nb * 4 / 1e6)},
         "gflops": world * work["flops"] / (ms_step * 1e-3) / 1e9,
         "roofline": {"bound": "hbm", "kernel": "prod_band_kernel", "achieved": achieved, "peak": peak,
-                     "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                     "unit": "GB/s", "frac": achieved / peak,
+                     # DRAM bytes per launch: the ncu capture of a smaller case of the same kernel (16384 rows, 512
+                     # diagonals, 2048 columns: 267.1 MB of dram read+write for 301.7 MB algorithmic, see
+                     # profiles/prod_n_units16384_nd512_batch2048.md) scaled by the algorithmic bytes of this launch
+                     "traffic": prod_bytes * (267.1 / 301.7),
+                     "traffic_source": "ncu dram__bytes_read+write of a smaller case scaled by algorithmic bytes",
+                     "peak_source": peak_src,
                      "ms_per_launch": prod_ms,
                      "binding": "fp32 issue (no tensor cores on this path): %.1f TFLOP/s achieved of %.1f measured "
                                 "%s peak = %.2f" % (prod_flops / (prod_ms * 1e-3) / 1e12, fp32_peak,
