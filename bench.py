@@ -486,7 +486,27 @@ def run_single(args, cfg):
         ts.append(a.elapsed_time(b) / reps)
     ms = statistics.median(ts)
     peak, peak_src = load_peaks()
-    print(json.dumps({"case": case, "op": op, "h": h, "w": w, "num_dia": int(nd), "row_fact": rf, "batch": nb,
+    cpu = None
+    if args.cpu and op in ("prod_n", "prod_t", "dd2dia", "reduce"):
+        # the CPU oracle on the same shapes (seeded host inputs), one thread and all threads
+        from oracle import host_oracle as ho
+        Ah = ho.DiaHost(h, w, offs, h, rf, rng.uniform(-1, 1, offs.size * h).astype(np.float32))
+        Xh = np.asfortranarray(rng.uniform(-1, 1, (h, nb)).astype(np.float32))
+        Yh = np.asfortranarray(rng.uniform(-1, 1, (w, nb)).astype(np.float32))
+        vh = np.zeros(h, dtype=np.float32)
+        cpu = {}
+        for label, nt in (("1", 1), (str(os.cpu_count()), os.cpu_count())):
+            t0 = time.perf_counter()
+            if op == "prod_n":
+                ho.prod(Xh, Ah, Yh, "n", 1.0, 0.0, nt)
+            elif op == "prod_t":
+                ho.prod(Yh, Ah, Xh, "t", 1.0, 0.5 if case == "cfg1" else 0.0, nt)
+            elif op == "dd2dia":
+                ho.densedense_to_dia(Ah, Xh, Yh, 0.01, 0.9, nthreads=nt)
+            else:
+                ho.reduce_to_col(vh, Xh, ho.RF_ADD, 1.0, 0.0, nt)
+            cpu["ms_%s_threads" % label] = (time.perf_counter() - t0) * 1e3
+    print(json.dumps({"case": case, "op": op, "cpu_oracle": cpu, "h": h, "w": w, "num_dia": int(nd), "row_fact": rf, "batch": nb,
                       "mode": args.mode, "ms": ms, "ms_min": min(ts), "gbs": byts / (ms * 1e-3) / 1e9,
                       "hbm_frac": byts / (ms * 1e-3) / 1e9 / peak, "tflops": flops / (ms * 1e-3) / 1e12,
                       "l2_flushed": bool(args.flush_l2), "launches_per_timing": reps,
@@ -511,6 +531,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--flush-l2", action="store_true")
+    ap.add_argument("--cpu", action="store_true", help="single-routine cases: also time the CPU oracle")
     args = ap.parse_args()
     cfg = dict(CASES.get(args.case, CASES["rbm_cfg3"]))
     for k, v in (("units", args.units), ("num_dia", args.num_dia), ("batch", args.batch)):
