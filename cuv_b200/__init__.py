@@ -17,7 +17,7 @@ from . import _capi
 from ._capi import (CuvDiaError, MODE_EXACT, MODE_FAST, RF_ADD, RF_MEAN, RF_ADD_SQUARED, RF_MAX, RF_ARGMAX,
                     RF_ARGMIN, RF_MIN, RF_MULT, RF_LOGADDEXP, RF_ADDEXP)
 
-__all__ = ["dev_dia_matrix_f", "dev_block_descriptor_f", "prod", "spmv", "densedense_to_dia", "reduce_to_col",
+__all__ = ["dev_dia_matrix_f", "host_dia_matrix_f", "convert", "pull", "dev_block_descriptor_f", "prod", "spmv", "densedense_to_dia", "reduce_to_col",
            "reduce_to_row", "bias_sigmoid_sample", "axpby", "colmajor_empty", "to_device", "to_host",
            "launch_count", "CuvDiaError", "MODE_EXACT", "MODE_FAST"]
 
@@ -146,6 +146,66 @@ class dev_dia_matrix_f:
             raise CuvDiaError(_capi.ERR_INVALID, "vals.size == num_dia*stride")
         self.vec.copy_(_torch().from_numpy(v))
         return self
+
+
+class host_dia_matrix_f:
+    """``dia_matrix<float, host_memory_space>``: the same container with numpy storage.  It only holds
+    data (conversion source/target); there is no host implementation of the products here."""
+
+    def __init__(self, h, w, offsets, stride=None, row_fact=1):
+        self.h, self.w, self.row_fact = int(h), int(w), int(row_fact)
+        self.offsets = np.ascontiguousarray(offsets, dtype=np.int32).reshape(-1)
+        self.num_dia = int(self.offsets.size)
+        self.stride = int(stride) if stride is not None else max(self.h, self.w)
+        self.vec = np.empty(self.num_dia * self.stride, dtype=np.float32)
+
+    @property
+    def shape(self):
+        return (self.h, self.w)
+
+    def _slot(self, i, j):
+        hit = np.nonzero(self.offsets == j - i // self.row_fact)[0]
+        return int(hit[-1]) if hit.size else None
+
+    def has(self, i, j):
+        return self._slot(i, j) is not None
+
+    def __call__(self, i, j):
+        s = self._slot(i, j)
+        return float(self.vec[s * self.stride + i]) if s is not None else 0.0
+
+    def set(self, i, j, val):
+        s = self._slot(i, j)
+        if s is not None:
+            self.vec[s * self.stride + i] = val
+
+
+def convert(dst, src):
+    """``cuv::convert`` for the DIA path (convert/convert.cu:42-112): host DIA <-> device DIA (offsets
+    and values) and host DIA -> dense (returns a Fortran-ordered numpy matrix when ``dst`` is None)."""
+    if isinstance(dst, dev_dia_matrix_f) and isinstance(src, host_dia_matrix_f):
+        if (dst.shape, dst.num_dia, dst.stride, dst.row_fact) != (src.shape, src.num_dia, src.stride, src.row_fact) \
+                or not np.array_equal(dst.offsets, src.offsets):
+            dst.__init__(src.h, src.w, src.offsets, src.stride, src.row_fact, device=dst.vec.device)
+        return dst.set_vec(src.vec)
+    if isinstance(dst, host_dia_matrix_f) and isinstance(src, dev_dia_matrix_f):
+        dst.__init__(src.h, src.w, src.offsets, src.stride, src.row_fact)
+        dst.vec[:] = src.vec.detach().cpu().numpy()
+        return dst
+    if dst is None and isinstance(src, host_dia_matrix_f):
+        dense = np.zeros((src.h, src.w), dtype=np.float32, order="F")
+        rows = np.arange(src.h)
+        for s, o in enumerate(src.offsets.tolist()):
+            cols = rows // src.row_fact + o
+            ok = (cols >= 0) & (cols < src.w)
+            dense[rows[ok], cols[ok]] = src.vec[s * src.stride + rows[ok]]
+        return dense
+    raise CuvDiaError(_capi.ERR_UNSUPPORTED, "convert: unsupported pair of types")
+
+
+def pull(mat):
+    """Device DIA matrix -> dense host matrix (``pull`` of src/cuv_python/export_dia_mat.cpp:158-167)."""
+    return convert(None, convert(host_dia_matrix_f(mat.h, mat.w, mat.offsets, mat.stride, mat.row_fact), mat))
 
 
 class dev_block_descriptor_f:

@@ -73,6 +73,12 @@ int get_workspace(cudaStream_t stream, size_t bytes, void** ptr) {
 
 using namespace cuvdia;
 
+// A plan's device arrays live on the device that was current when it was created.
+static bool plan_on_current_device(const cuvdia_plan* p) {
+    int dev = -1;
+    return cudaGetDevice(&dev) == cudaSuccess && dev == p->device;
+}
+
 extern "C" {
 
 const char* cuvdia_error_string(int code) {
@@ -174,6 +180,7 @@ int cuvdia_prod_f32(const cuvdia_plan* p, const float* A_vals, const float* B, i
     CUVDIA_REQUIRE(B != nullptr);                        // spmv.cu:235
     CUVDIA_REQUIRE(ncols >= 0);
     CUVDIA_REQUIRE(mode == CUVDIA_MODE_EXACT || mode == CUVDIA_MODE_FAST);
+    CUVDIA_REQUIRE(plan_on_current_device(p));
     const bool trans = transA == 't';
     const int rows_b = trans ? p->h : p->w, rows_c = trans ? p->w : p->h;
     CUVDIA_REQUIRE(ldb >= rows_b);                       // spmv.cu:159,180 (operand heights)
@@ -191,6 +198,7 @@ int cuvdia_dd2dia_f32(cuvdia_plan* p, float* C_vals, const float* A, int lda, co
     CUVDIA_REQUIRE(lda >= p->h);                         // densedense_to_sparse.cu:215,277
     CUVDIA_REQUIRE(ldb >= p->w);                         // densedense_to_sparse.cu:214,276
     CUVDIA_REQUIRE(p->h % p->rf == 0);                   // densedense_to_sparse.cu:244-249 overruns otherwise
+    CUVDIA_REQUIRE(plan_on_current_device(p));
     return launch_dd2dia(p, C_vals, A, lda, B, ldb, ncols, factAB, factC, (cudaStream_t)stream);
 }
 

@@ -39,6 +39,20 @@ int get_workspace(cudaStream_t stream, size_t bytes, void** ptr);
 
 int sm_count();
 
+// Raises a kernel's dynamic shared-memory limit once per device (the attribute belongs to the device's
+// context, so a process that uses several GPUs must set it on each).
+template <class K>
+inline int allow_dynamic_smem(K kernel, size_t bytes, bool (&done)[64]) {
+    int dev = 0;
+    CUVDIA_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) { set_last_error("device index %d out of range", dev); return CUVDIA_ERR_UNSUPPORTED; }
+    if (!done[dev]) {
+        CUVDIA_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+        done[dev] = true;
+    }
+    return CUVDIA_OK;
+}
+
 }  // namespace cuvdia
 
 // ---- plan ------------------------------------------------------------------------------------------

@@ -29,7 +29,7 @@ __global__ void dd2dia_combine_kernel(float* __restrict__ Cv, const int* __restr
 namespace db {
 constexpr int TI = 128, TJ = 128, KB = 32, STAGES = 3, THREADS = 256;
 constexpr int TILE_FLOATS = TI * KB;                 // one operand tile of one stage
-constexpr size_t SMEM = sizeof(float) * 2 * TILE_FLOATS * STAGES + 64;
+constexpr size_t SMEM = sizeof(float) * 2 * TILE_FLOATS * STAGES + 128;
 constexpr unsigned SPIN_LIMIT = 1u << 26;
 }  // namespace db
 
@@ -66,6 +66,7 @@ dd2dia_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
     float* const Xs0 = smem_f;                                  // [STAGES][KB][TI]
     float* const Hs0 = smem_f + STAGES * TILE_FLOATS;           // [STAGES][KB][TJ]
     unsigned long long* const full = reinterpret_cast<unsigned long long*>(smem_f + 2 * STAGES * TILE_FLOATS);
+    unsigned long long* const empty = full + STAGES;      // one arrival per warp when it is done with a stage
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int R = warp * 2 + (lane >> 4);        // row group 0..15: rows 4R..4R+3 and 64+4R..64+4R+3 of the tile
@@ -94,8 +95,10 @@ dd2dia_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
 
     if (tid == 0) {
 #pragma unroll
-        for (int s = 0; s < STAGES; s++)
+        for (int s = 0; s < STAGES; s++) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(dsmem_u32(&full[s])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(dsmem_u32(&empty[s])), "r"(THREADS / 32));
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -133,8 +136,15 @@ dd2dia_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
                 for (int jp = 0; jp < 4; jp++) acc[ii][jp] = __ffma2_rn(xx, hp[jp], acc[ii][jp]);
             }
         }
-        __syncthreads();
-        if (tid == 0 && c + STAGES < nch) issue(c + STAGES);
+        // hand the stage back: one arrival per warp; only the issuing thread waits for all of them, so the
+        // other warps run ahead into the stages that are already loaded instead of meeting a block barrier
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(dsmem_u32(&empty[s])) : "memory");
+        if (tid == 0 && c + STAGES < nch) {
+            if (!dmbar_wait(&empty[s], (c / STAGES) & 1)) { if (P.status) *P.status = 2; }
+            else issue(c + STAGES);
+        }
+        __syncwarp();
     }
 
     // ---- write the accumulators that lie on stored diagonals inside the matrix ----
@@ -200,11 +210,9 @@ int launch_dd2dia_band(cuvdia_plan* p, float* Cv, const float* A, int lda, const
         if (rc) return rc;
         P.partial = p->scratch;
     }
-    static bool attr_done = false;
-    if (!attr_done) {
-        CUVDIA_CUDA(cudaFuncSetAttribute(dd2dia_band_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
-        attr_done = true;
-    }
+    static bool attr_done[64] = {false};
+    rc = allow_dynamic_smem(dd2dia_band_kernel, SMEM, attr_done);
+    if (rc) return rc;
     if (gx > 65535 || nsplit > 65535) { set_last_error("matrix too tall for the banded densedense_to_dia"); return CUVDIA_ERR_UNSUPPORTED; }
     dd2dia_band_kernel<<<dim3(gy, gx, nsplit), THREADS, SMEM, st>>>(mapA, mapB, P);
     count_launch();

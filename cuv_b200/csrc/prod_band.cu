@@ -395,12 +395,9 @@ static int launch_band_t(const cuvdia_plan* p, const float* A, const float* B, i
     P.fa = fa; P.fc = fc;
     P.vec_c = (al16(C) && ldc % 4 == 0) ? 1 : 0;
     P.C = C; P.status = p->d_status;
-    static bool attr_done[2][2] = {{false, false}, {false, false}};
-    if (!attr_done[TRANS][EXACT]) {
-        CUVDIA_CUDA(cudaFuncSetAttribute(prod_band_kernel<TRANS, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem_bytes<TRANS>()));
-        attr_done[TRANS][EXACT] = true;
-    }
+    static bool attr_done[64] = {false};          // one flag set per template instantiation
+    rc = allow_dynamic_smem(prod_band_kernel<TRANS, EXACT>, smem_bytes<TRANS>(), attr_done);
+    if (rc) return rc;
     const int gx = (P.rows_out + TM - 1) / TM, gy = (ncols + TN - 1) / TN;
     if (gx > 65535) { set_last_error("too many rows for the banded kernel"); return CUVDIA_ERR_UNSUPPORTED; }
     prod_band_kernel<TRANS, EXACT><<<dim3(gy, gx), THREADS, smem_bytes<TRANS>(), st>>>(mapA, mapB, P);

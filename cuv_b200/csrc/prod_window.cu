@@ -193,12 +193,9 @@ static int launch_window_t(const cuvdia_plan* p, const float* A, const float* B,
     P.pitch = (int)(wrows | 1);                          // odd pitch: columns start in different banks
     P.fa = fa; P.fc = fc; P.A = A; P.offs = p->d_offsets; P.B = B; P.C = C;
     const size_t smem = sizeof(float) * (size_t)P.pitch * CB;
-    static bool attr_done = false;
-    if (!attr_done) {
-        CUVDIA_CUDA(cudaFuncSetAttribute(prod_window_kernel<TRANS, EXACT, T, CB>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pw::SMEM_LIMIT));
-        attr_done = true;
-    }
+    static bool attr_done[64] = {false};
+    const int arc = allow_dynamic_smem(prod_window_kernel<TRANS, EXACT, T, CB>, pw::SMEM_LIMIT, attr_done);
+    if (arc) return arc;
     const int rows_out = TRANS ? p->w : p->h;
     const int gx = (rows_out + T - 1) / T, gy = (ncols + CB - 1) / CB;
     if (gy > 65535) { set_last_error("too many batch columns"); return CUVDIA_ERR_UNSUPPORTED; }

@@ -318,3 +318,19 @@ def test_axpby(cb):
     xd, yd = cb.to_device(x), cb.to_device(y)
     cb.axpby(xd, xd, yd, 0.9, -0.01)
     assert_bits_equal(xd.cpu().numpy(), np.float32(0.9) * x + np.float32(-0.01) * y)
+
+
+def test_convert_and_pull(cb, golden):
+    """dia_mat.cpp:111-132 / convert.cpp:110-129 on the Python mirror: host -> device -> host round trip and
+    dia -> dense equal the reference fixture."""
+    g = golden
+    H = cb.host_dia_matrix_f(int(g["diamat_h"]), int(g["diamat_w"]), g["diamat_offsets"], int(g["diamat_stride"]))
+    H.vec[:] = g["diamat_vals"]
+    D = cb.dev_dia_matrix_f(int(g["diamat_h"]), int(g["diamat_w"]), g["diamat_offsets"], int(g["diamat_stride"]))
+    cb.convert(D, H)
+    H2 = cb.host_dia_matrix_f(1, 1, [0])
+    cb.convert(H2, D)
+    assert np.array_equal(H2.vec, H.vec) and np.array_equal(H2.offsets, H.offsets)
+    assert np.array_equal(cb.convert(None, H), g["diamat_dense"])
+    assert np.array_equal(cb.pull(D), g["diamat_dense"])
+    assert D(3, 4) == H(3, 4) == g["diamat_dense"][3, 4] and not H.has(0, 5)
