@@ -18,7 +18,7 @@ from ._capi import (CuvDiaError, MODE_EXACT, MODE_FAST, RF_ADD, RF_MEAN, RF_ADD_
                     RF_ARGMIN, RF_MIN, RF_MULT, RF_LOGADDEXP, RF_ADDEXP)
 
 __all__ = ["dev_dia_matrix_f", "host_dia_matrix_f", "convert", "pull", "dev_block_descriptor_f", "prod", "spmv", "densedense_to_dia", "reduce_to_col",
-           "reduce_to_row", "bias_sigmoid_sample", "axpby", "colmajor_empty", "to_device", "to_host",
+           "reduce_to_row", "bias_sigmoid_sample", "prod_bias_sigmoid_sample", "axpby", "colmajor_empty", "to_device", "to_host",
            "launch_count", "CuvDiaError", "MODE_EXACT", "MODE_FAST"]
 
 
@@ -234,6 +234,29 @@ def prod(C, A, B, transA="n", transB="n", factAB=1.0, factC=0.0, mode=MODE_EXACT
     _capi.check(_capi.lib().cuvdia_prod_f32(A._plan, _ptr(A.vec), _ptr(B), ldb, _ptr(C), ldc, int(C.shape[1]),
                                             transA.encode(), transB.encode(), factAB, factC, mode, _stream()))
     return C
+
+
+def prod_bias_sigmoid_sample(C, A, B, transA="n", factAB=1.0, factC=0.0, mode=MODE_EXACT, bias=None, u=None,
+                             sample=None):
+    """One call for what an RBM/MLP layer does after the product (examples/rbm/base.py:48-54,93-106):
+    C <- sigmoid(factC*C + factAB*op(A)*B + bias[:, None]); sample <- (C > u) as 0/1 floats if ``u`` is given.
+    Same results as :func:`prod` followed by :func:`bias_sigmoid_sample`."""
+    ldc, ldb = _check_colmajor(C, "C"), _check_colmajor(B, "B")
+    if C.shape[1] != B.shape[1]:
+        raise CuvDiaError(_capi.ERR_INVALID, "dst.shape()[1] == B.shape()[1]")
+    rows_b, rows_c = (A.h, A.w) if transA == "t" else (A.w, A.h)
+    if transA in ("n", "t") and (B.shape[0] != rows_b or C.shape[0] != rows_c):
+        raise CuvDiaError(_capi.ERR_INVALID, "operand heights match the matrix (spmv.cu:159-160,180-181)")
+    ldu = lds = 0
+    if u is not None:
+        ldu = _check_colmajor(u, "u")
+        if sample is None:
+            sample = colmajor_empty(C.shape[0], C.shape[1], C.device)
+        lds = _check_colmajor(sample, "sample")
+    _capi.check(_capi.lib().cuvdia_prod_bias_sigmoid_sample_f32(
+        A._plan, _ptr(A.vec), _ptr(B), ldb, _ptr(C), ldc, int(C.shape[1]), transA.encode(), factAB, factC, mode,
+        _ptr(bias), _ptr(u), ldu, _ptr(sample), lds, _stream()))
+    return sample
 
 
 def spmv(dst, A, v, transA="n", factAv=1.0, factC=0.0, mode=MODE_EXACT):

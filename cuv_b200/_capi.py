@@ -25,6 +25,8 @@ SIGNATURES = {
     "cuvdia_plan_offsets_device": (_vp, [_vp]),
     "cuvdia_plan_status": (_i, [_vp, ctypes.POINTER(_i)]),
     "cuvdia_prod_f32": (_i, [_vp, _vp, _vp, _i, _vp, _i, _i, _c, _c, _f, _f, _i, _vp]),
+    "cuvdia_prod_bias_sigmoid_sample_f32": (_i, [_vp, _vp, _vp, _i, _vp, _i, _i, _c, _f, _f, _i, _vp, _vp, _i, _vp, _i,
+                                                 _vp]),
     "cuvdia_dd2dia_f32": (_i, [_vp, _vp, _vp, _i, _vp, _i, _i, _f, _f, _vp]),
     "cuvdia_reduce_f32": (_i, [_vp, _vp, _ll, _ll, _i, _i, _f, _f, _vp]),
     "cuvdia_reduce_noalloc_f32": (_i, [_vp, _vp, _ll, _ll, _i, _i, _f, _f, _vp]),

@@ -186,7 +186,28 @@ int cuvdia_prod_f32(const cuvdia_plan* p, const float* A_vals, const float* B, i
     CUVDIA_REQUIRE(ldb >= rows_b);                       // spmv.cu:159,180 (operand heights)
     CUVDIA_REQUIRE(ldc >= rows_c);                       // spmv.cu:160,181,236-240
     if (ncols == 0) return CUVDIA_OK;
-    return launch_prod(p, A_vals, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, (cudaStream_t)stream);
+    return launch_prod(p, A_vals, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, nullptr, (cudaStream_t)stream);
+}
+
+int cuvdia_prod_bias_sigmoid_sample_f32(const cuvdia_plan* p, const float* A_vals, const float* B, int ldb, float* C,
+                                        int ldc, int ncols, char transA, float factAB, float factC, int mode,
+                                        const float* bias, const float* u, int ldu, float* sample, int lds,
+                                        void* stream) {
+    CUVDIA_REQUIRE(p != nullptr);
+    CUVDIA_REQUIRE(transA == 'n' || transA == 't');
+    CUVDIA_REQUIRE(C != nullptr && A_vals != nullptr && B != nullptr);
+    CUVDIA_REQUIRE(ncols >= 0);
+    CUVDIA_REQUIRE(mode == CUVDIA_MODE_EXACT || mode == CUVDIA_MODE_FAST);
+    CUVDIA_REQUIRE(plan_on_current_device(p));
+    const bool trans = transA == 't';
+    const int rows_b = trans ? p->h : p->w, rows_c = trans ? p->w : p->h;
+    CUVDIA_REQUIRE(ldb >= rows_b);
+    CUVDIA_REQUIRE(ldc >= rows_c);
+    CUVDIA_REQUIRE((u == nullptr) == (sample == nullptr));
+    if (u) { CUVDIA_REQUIRE(ldu >= rows_c); CUVDIA_REQUIRE(lds >= rows_c); }
+    if (ncols == 0) return CUVDIA_OK;
+    ProdEpilogue ep = {bias, u, ldu, sample, lds};
+    return launch_prod(p, A_vals, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, &ep, (cudaStream_t)stream);
 }
 
 int cuvdia_dd2dia_f32(cuvdia_plan* p, float* C_vals, const float* A, int lda, const float* B, int ldb, int ncols,

@@ -73,9 +73,15 @@ struct cuvdia_plan {
 };
 
 namespace cuvdia {
+// Optional element-wise tail of prod: C <- sigmoid(C + bias[row]); S <- C > U ? 1 : 0.
+struct ProdEpilogue {
+    const float* bias;       // may be null
+    const float* U; int ldu; // null: no sampling
+    float* S; int lds;
+};
 // kernels' host-side launchers (each returns a CUVDIA_* code)
 int launch_prod(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
-                bool trans, float factAB, float factC, int mode, cudaStream_t st);
+                bool trans, float factAB, float factC, int mode, const ProdEpilogue* ep, cudaStream_t st);
 int launch_dd2dia(cuvdia_plan* p, float* Cv, const float* A, int lda, const float* B, int ldb, int ncols,
                   float factAB, float factC, cudaStream_t st);
 int launch_prod_generic(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,

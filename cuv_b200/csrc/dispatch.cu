@@ -5,12 +5,19 @@
 namespace cuvdia {
 
 int launch_prod(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
-                bool trans, float factAB, float factC, int mode, cudaStream_t st) {
+                bool trans, float factAB, float factC, int mode, const ProdEpilogue* ep, cudaStream_t st) {
+    int rc;
     if (prod_band_applicable(p, A, B, ldb, ncols))
-        return launch_prod_band(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);
-    if (prod_window_applicable(p, trans, ncols))
-        return launch_prod_window(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);
-    return launch_prod_generic(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);
+        rc = launch_prod_band(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);
+    else if (prod_window_applicable(p, trans, ncols))
+        rc = launch_prod_window(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);
+    else
+        rc = launch_prod_generic(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);
+    if (rc || !ep) return rc;
+    // The element-wise tail runs as a second, bandwidth-bound pass over C.  Applying it inside the banded
+    // kernel's epilogue was measured slower: with one block per SM the loads of the uniform numbers and
+    // the exponentials at the end of every block are not overlapped with any other block's arithmetic.
+    return launch_bias_sigmoid_sample(C, ldc, ep->bias, ep->U, ep->ldu, ep->S, ep->lds, trans ? p->w : p->h, ncols, st);
 }
 
 int launch_dd2dia(cuvdia_plan* p, float* Cv, const float* A, int lda, const float* B, int ldb, int ncols,

@@ -21,13 +21,14 @@ import cuv_b200 as cb
 
 
 class SparseRBMStep:
-    def __init__(self, W, batch_local, batch_global=None, mode=cb.MODE_EXACT, device="cuda"):
+    def __init__(self, W, batch_local, batch_global=None, mode=cb.MODE_EXACT, device="cuda", fused=False):
         import torch
         self.W = W
         self.hid, self.vis = W.h, W.w
         self.nb = int(batch_local)
         self.B = int(batch_global if batch_global is not None else batch_local)
         self.mode = mode
+        self.fused = fused        # call the combined product + bias/logistic/compare entry point (same bits)
         self.dev = device
         E = cb.colmajor_empty
         self.H0p, self.H0 = E(self.hid, self.nb, device), E(self.hid, self.nb, device)
@@ -65,6 +66,12 @@ class SparseRBMStep:
         """The three products with their bias/logistic/sampling passes."""
         W = self.W
         t = self._timed
+        if self.fused:
+            F = cb.prod_bias_sigmoid_sample
+            t("prod_n", lambda: F(self.H0p, W, V0, "n", 1.0, 0.0, self.mode, self.c_hid, U_h, self.H0))
+            t("prod_t", lambda: F(self.V1p, W, self.H0, "t", 1.0, 0.0, self.mode, self.b_vis, U_v, self.V1))
+            t("prod_n", lambda: F(self.H1p, W, self.V1, "n", 1.0, 0.0, self.mode, self.c_hid))
+            return
         t("prod_n", lambda: cb.prod(self.H0p, W, V0, "n", "n", 1.0, 0.0, self.mode))
         t("glue", lambda: cb.bias_sigmoid_sample(self.H0p, self.c_hid, U_h, self.H0))
         t("prod_t", lambda: cb.prod(self.V1p, W, self.H0, "t", "n", 1.0, 0.0, self.mode))

@@ -180,6 +180,17 @@ CUVDIA_API int cuvdia_reduce_noalloc_f32(float* dst, const float* src, long long
 CUVDIA_API int cuvdia_bias_sigmoid_sample_f32(float* act, int ld, const float* bias, const float* u, int ldu,
                                    float* sample, int lds, int units, int ncols, void* stream);
 
+/* prod followed by the element-wise tail of an RBM/MLP layer in one call:
+ *   C <- sigmoid(factC*C + factAB*op(A)*B + bias[row]);   sample <- C > u ? 1 : 0   (u, sample may be NULL)
+ * i.e. cuvdia_prod_f32 + cuvdia_bias_sigmoid_sample_f32, which is what upPass/downPass of
+ * examples/rbm/base.py:48-54,93-106 issue back to back (prod, matrix_plus_col, SF_SIGM, rnd_binarize).
+ * One entry point, two stream-ordered kernels (the product, then a bandwidth-bound pass over C);
+ * results are identical to the two separate calls. */
+CUVDIA_API int cuvdia_prod_bias_sigmoid_sample_f32(const cuvdia_plan* plan, const float* A_vals, const float* B,
+                                                   int ldb, float* C, int ldc, int ncols, char transA, float factAB,
+                                                   float factC, int mode, const float* bias, const float* u, int ldu,
+                                                   float* sample, int lds, void* stream);
+
 /* dst = a*x + b*y element-wise over n floats (apply_binary_functor BF_AXPBY,
  * tensor_ops/tensor_ops.hpp:530-655, tensor_ops/functors.hpp:412-433); dst may alias x or y. */
 CUVDIA_API int cuvdia_axpby_f32(float* dst, const float* x, const float* y, float a, float b, long long n,

@@ -9,10 +9,10 @@ from tests.helpers import assert_bits_equal
 pytestmark = pytest.mark.gpu
 
 
-def run_gpu_step(cb, W, V0, U_h, U_v, batch_global=None, mode=None):
+def run_gpu_step(cb, W, V0, U_h, U_v, batch_global=None, mode=None, fused=True):
     from cuv_b200 import rbm
     Wd = cb.dev_dia_matrix_f(W.h, W.w, W.offsets, W.stride, W.rf).set_vec(W.vals)
-    st = rbm.SparseRBMStep(Wd, V0.shape[1], batch_global, cb.MODE_EXACT if mode is None else mode)
+    st = rbm.SparseRBMStep(Wd, V0.shape[1], batch_global, cb.MODE_EXACT if mode is None else mode, fused=fused)
     st.step(cb.to_device(V0), cb.to_device(U_h), cb.to_device(U_v))
     return st
 
@@ -119,3 +119,18 @@ def test_host_fed_pipeline_matches_direct_step():
     for i in range(3):
         assert_bits_equal(outs[i][0].numpy(), want[i][0], "G of step %d" % i)
         assert_bits_equal(outs[i][1].numpy(), want[i][1], "bias gradients of step %d" % i)
+
+
+@pytest.mark.parametrize("units,nd,nb", [(1024, 64, 96), (1000, 37, 50), (1001, 37, 50)])
+def test_combined_entry_point_gives_the_bits_of_the_separate_calls(units, nd, nb):
+    """The combined entry point (product + bias/logistic/compare) == prod followed by the element-wise
+    call, bit for bit, on shapes that reach the banded and the windowed kernels."""
+    import cuv_b200 as cb
+    offs = np.arange(-(nd // 2), nd - nd // 2, dtype=np.int32)
+    W, V0, U_h, U_v = rbm_oracle.make_inputs(3000 + nd, units, units, offs, nb, w_std=0.05)
+    a = run_gpu_step(cb, W, V0, U_h, U_v, fused=True)
+    b = run_gpu_step(cb, W, V0, U_h, U_v, fused=False)
+    for name in ("H0p", "H0", "V1p", "V1", "H1p"):
+        assert_bits_equal(cb.to_host(getattr(a, name)), cb.to_host(getattr(b, name)), name)
+    assert_bits_equal(a.G.vec.cpu().numpy(), b.G.vec.cpu().numpy(), "G")
+    assert_bits_equal(a.bias_grad.cpu().numpy(), b.bias_grad.cpu().numpy(), "bias gradients")
