@@ -92,6 +92,9 @@ int ensure_plan_scratch(cuvdia_plan* p, size_t floats, cudaStream_t st);
 bool prod_band_applicable(const cuvdia_plan* p, const float* A, const float* B, int ldb, int ncols);
 int launch_prod_band(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
                      bool trans, float factAB, float factC, int mode, cudaStream_t st);
+bool prod_narrow_applicable(const cuvdia_plan* p, const float* A, const float* B, int ldb, int ncols);
+int launch_prod_narrow(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
+                       bool trans, float factAB, float factC, int mode, cudaStream_t st);
 bool prod_window_applicable(const cuvdia_plan* p, bool trans, int ncols);
 int launch_prod_window(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
                        bool trans, float factAB, float factC, int mode, cudaStream_t st);

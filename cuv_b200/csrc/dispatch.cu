@@ -7,7 +7,9 @@ namespace cuvdia {
 int launch_prod(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
                 bool trans, float factAB, float factC, int mode, const ProdEpilogue* ep, cudaStream_t st) {
     int rc;
-    if (prod_band_applicable(p, A, B, ldb, ncols))
+    if (prod_narrow_applicable(p, A, B, ldb, ncols))
+        rc = launch_prod_narrow(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);
+    else if (prod_band_applicable(p, A, B, ldb, ncols))
         rc = launch_prod_band(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);
     else if (prod_window_applicable(p, trans, ncols))
         rc = launch_prod_window(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);

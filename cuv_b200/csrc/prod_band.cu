@@ -372,7 +372,9 @@ int make_map_2d(CUtensorMap* m, const float* base, long long dim0, long long dim
 static inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 bool prod_band_applicable(const cuvdia_plan* p, const float* A, const float* B, int ldb, int ncols) {
-    (void)ncols;
+    // The 128 x 128 tiles walk the band 32 steps at a time: with few batch columns or a narrow band most of a
+    // tile is padding, and the staged-window kernel (one pass over A, B and C) is the better fit.
+    if (ncols < 64 || p->nd < 24) return false;
     return p->is_band && p->rf == 1 && al16(A) && al16(B) && p->stride % 4 == 0 && ldb % 4 == 0 &&
            get_encode() != nullptr;
 }
