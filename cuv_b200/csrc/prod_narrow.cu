@@ -12,6 +12,8 @@
 // so its slice of A is re-read from L1/L2, not from HBM.  No shared memory, no barriers.
 // Accumulation per output is in diagonal storage order; EXACT uses a separate multiply and add and
 // reproduces CUV's host loop (matrix_ops/spmv.cu:161-198) bit for bit.
+#include <cuda.h>
+
 #include "cuvdia_internal.cuh"
 
 namespace cuvdia {
@@ -158,6 +160,172 @@ prod_narrow_kernel(const NarrowParams P) {
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Streaming variant for bands of at most 16 diagonals: the same arithmetic, but A and B reach the SM
+// through TMA (cp.async.bulk.tensor, no multicast) instead of through per-thread loads.  An SM can
+// keep only so many L1 misses in flight, which caps prod_narrow_kernel at about a third of the HBM
+// bandwidth; the copy engine has no such limit.  A block owns 512 output rows: its slice of the
+// band (16 x 544 floats) and the B window of up to 32 batch columns (544 rows each) are fetched by
+// eight tile loads onto one mbarrier (bounded wait), two blocks share an SM so one computes while
+// the other's loads are in flight.  The coefficients of a thread's 4 rows stay in registers for all
+// column groups.  Tiles are 136 rows tall (4 x 34: TMA boxes are limited to 256 rows); a window row
+// r lives at [r / 136][column][r % 136].
+// ------------------------------------------------------------------------------------------------
+namespace ps {
+constexpr int THREADS = 128;
+constexpr int TR = 4 * THREADS;       // output rows per block
+constexpr int BOXR = 136;             // rows per TMA box
+constexpr int NBOX = 4;               // boxes per window: 544 rows >= 512 + 24 + 3
+constexpr int NC = 32;                // batch columns per round
+constexpr int A_FLOATS = NBOX * pn::KD * BOXR;
+constexpr int B_FLOATS = NBOX * NC * BOXR;
+constexpr size_t SMEM = sizeof(float) * (A_FLOATS + B_FLOATS) + 64;
+constexpr unsigned SPIN_LIMIT = 1u << 26;
+}
+
+struct StreamParams {
+    int h, w, nd, lo, ldc, ncols;
+    float fa, fc;
+    float* C;
+    int* status;
+};
+
+__device__ __forceinline__ unsigned s_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+// element (window row r, plane y) of a buffer made of NBOX boxes of [planes][BOXR]
+__device__ __forceinline__ int box_index(int r, int y, int planes) {
+    const int b = (r >= ps::BOXR) + (r >= 2 * ps::BOXR) + (r >= 3 * ps::BOXR);
+    return (b * planes + y) * ps::BOXR + (r - b * ps::BOXR);
+}
+
+template <bool TRANS, bool EXACT, int L>
+__global__ void __launch_bounds__(ps::THREADS, 2)
+prod_stream_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                   const StreamParams P) {
+    using namespace ps;
+    constexpr int KD = pn::KD, CB = pn::CB, NW = pn::NW;
+    constexpr int RA = (4 - L) % 4;
+    constexpr int RT = (RA + 1) % 4;
+    extern __shared__ __align__(1024) float sm[];
+    float* const As = sm;                       // [NBOX][KD][BOXR]
+    float* const Bs = sm + A_FLOATS;            // [NBOX][NC][BOXR]
+    unsigned long long* const bar = reinterpret_cast<unsigned long long*>(sm + A_FLOATS + B_FLOATS);
+    const int tid = threadIdx.x;
+    const int o0 = blockIdx.x * TR;             // first output row of the block
+    const int rows_out = TRANS ? P.w : P.h;
+    const int rows_b = TRANS ? P.h : P.w;
+    // first matrix row of the B window (multiple of 4) and of the A window
+    const int wsB = TRANS ? (o0 - P.lo - (KD - 1) - RT) : (o0 + P.lo - L);
+    const int wsA = TRANS ? wsB : o0;
+    if (tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s_u32(bar)));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const int i0 = o0 + 4 * tid;                // this thread's 4 output rows
+    // block-uniform: every cell the block touches lies inside the matrix and every output row exists
+    const int cell0 = TRANS ? (o0 - P.lo - (KD - 1)) : (o0 + P.lo);
+    const bool interior = P.nd == KD && o0 + TR <= rows_out && cell0 >= 0 && cell0 + TR - 1 + (KD - 1) < rows_b;
+    float a[KD][4];
+    unsigned phase = 0;
+    for (int cbase = 0; cbase < P.ncols; cbase += NC) {
+        if (tid == 0) {
+            const unsigned nbytes = sizeof(float) * ((cbase == 0 ? A_FLOATS : 0) + B_FLOATS);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s_u32(bar)), "r"(nbytes) : "memory");
+#pragma unroll
+            for (int b = 0; b < NBOX; b++) {
+                if (cbase == 0)
+                    asm volatile(
+                        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                        ::"r"(s_u32(As + b * KD * BOXR)), "l"(&mapA), "r"(wsA + b * BOXR), "r"(0), "r"(s_u32(bar)) : "memory");
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                    ::"r"(s_u32(Bs + b * NC * BOXR)), "l"(&mapB), "r"(wsB + b * BOXR), "r"(cbase), "r"(s_u32(bar)) : "memory");
+            }
+        }
+        bool done = false;
+        for (unsigned it = 0; it < SPIN_LIMIT && !done; it++) {
+            unsigned d;
+            asm volatile(
+                "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                : "=r"(d) : "r"(s_u32(bar)), "r"(phase) : "memory");
+            done = d != 0;
+        }
+        if (!done) { if (P.status) *P.status = 3; return; }
+        phase ^= 1;
+        if (cbase == 0) {
+            // coefficients of this thread's 4 rows, kept in registers for every column group
+#pragma unroll
+            for (int k = 0; k < KD; k++) {
+                if (!TRANS) {
+                    const float4 t = *reinterpret_cast<const float4*>(As + box_index(4 * tid, k, KD));
+                    a[k][0] = t.x; a[k][1] = t.y; a[k][2] = t.z; a[k][3] = t.w;
+                } else {
+                    // cell (j,k) reads matrix row i0 - lo - k + j = wsA + (KD-1) + RT + 4*tid - k + j
+                    const int off = ((RA - k) % 4 + 4) % 4;
+                    const int r = (KD - 1) + RT + 4 * tid - k - off;       // aligned window row
+                    const float4 t0 = *reinterpret_cast<const float4*>(As + box_index(r, k, KD));
+                    const float4 t1 = *reinterpret_cast<const float4*>(As + box_index(r + 4, k, KD));
+                    const float av[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
+#pragma unroll
+                    for (int j = 0; j < 4; j++) a[k][j] = av[off + j];
+                }
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    if (!interior) {
+                        // cells outside the matrix (their storage may hold anything) count as zero
+                        const int x = TRANS ? (i0 + j - P.lo - k) : (i0 + j + P.lo + k);   // matrix row ('t') or column ('n')
+                        const bool ok = k < P.nd && i0 + j < rows_out && x >= 0 && x < rows_b;
+                        if (!ok) a[k][j] = 0.f;
+                    }
+                    if (P.fa != 1.f) a[k][j] = __fmul_rn(P.fa, a[k][j]);
+                }
+            }
+        }
+        const int ncb = min(NC, P.ncols - cbase);
+        for (int c0 = 0; c0 < ncb; c0 += CB) {
+            float acc[CB][4];
+            float wv[CB][4 * NW];
+#pragma unroll
+            for (int c = 0; c < CB; c++) {
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    acc[c][j] = 0.f;
+                    if (P.fc != 0.f && c0 + c < ncb && i0 + j < rows_out)
+                        acc[c][j] = __fmul_rn(P.C[(size_t)(cbase + c0 + c) * P.ldc + i0 + j], P.fc);
+                }
+#pragma unroll
+                for (int v = 0; v < NW; v++) {
+                    const float4 x = *reinterpret_cast<const float4*>(Bs + box_index(4 * tid + 4 * v, min(c0 + c, NC - 1), NC));
+                    wv[c][4 * v] = x.x; wv[c][4 * v + 1] = x.y; wv[c][4 * v + 2] = x.z; wv[c][4 * v + 3] = x.w;
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < KD; k++)
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+#pragma unroll
+                    for (int c = 0; c < CB; c++) {
+                        const float x = TRANS ? wv[c][(KD - 1) + RT + j - k] : wv[c][L + j + k];
+                        acc[c][j] = EXACT ? __fadd_rn(acc[c][j], __fmul_rn(a[k][j], x)) : fmaf(a[k][j], x, acc[c][j]);
+                    }
+            const bool vec_c = (P.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(P.C) & 15) == 0 && i0 + 4 <= rows_out;
+#pragma unroll
+            for (int c = 0; c < CB; c++) {
+                if (c0 + c >= ncb) continue;
+                float* cp = P.C + (size_t)(cbase + c0 + c) * P.ldc + i0;
+                if (vec_c) *reinterpret_cast<float4*>(cp) = make_float4(acc[c][0], acc[c][1], acc[c][2], acc[c][3]);
+                else {
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+                        if (i0 + j < rows_out) cp[j] = acc[c][j];
+                }
+            }
+        }
+        __syncthreads();          // all threads are done with the B window before the next round overwrites it
+    }
+}
+
 static inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 // Banded, row_fact 1, 16-byte aligned operands, and little enough work per output row that HBM
@@ -183,8 +351,50 @@ static int launch_narrow_t(const cuvdia_plan* p, const NarrowParams& P, cudaStre
     return check_launch("prod_narrow_kernel");
 }
 
+int make_map_2d(CUtensorMap* m, const float* base, long long dim0, long long dim1, long long pitch, int box0, int box1);
+
+template <bool TRANS, bool EXACT>
+static int launch_stream_t(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
+                           float fa, float fc, cudaStream_t st) {
+    using namespace ps;
+    CUtensorMap mapA, mapB;
+    int rc = make_map_2d(&mapA, A, p->h, p->nd, p->stride, BOXR, pn::KD);
+    if (rc) return rc;
+    rc = make_map_2d(&mapB, B, TRANS ? p->h : p->w, ncols, ldb, BOXR, NC);
+    if (rc) return rc;
+    StreamParams P;
+    P.h = p->h; P.w = p->w; P.nd = p->nd; P.lo = p->band_lo; P.ldc = ldc; P.ncols = ncols;
+    P.fa = fa; P.fc = fc; P.C = C; P.status = p->d_status;
+    const int rows_out = TRANS ? p->w : p->h;
+    const int blocks = (rows_out + TR - 1) / TR;
+    const int L = ((p->band_lo % 4) + 4) % 4;
+#define GO(LV)                                                                                          \
+    do {                                                                                                \
+        static bool attr[64] = {false};                                                                 \
+        rc = allow_dynamic_smem(prod_stream_kernel<TRANS, EXACT, LV>, SMEM, attr);                      \
+        if (rc) return rc;                                                                              \
+        prod_stream_kernel<TRANS, EXACT, LV><<<blocks, THREADS, SMEM, st>>>(mapA, mapB, P);             \
+    } while (0)
+    switch (L) { case 0: GO(0); break; case 1: GO(1); break; case 2: GO(2); break; default: GO(3); break; }
+#undef GO
+    count_launch();
+    return check_launch("prod_stream_kernel");
+}
+
+// The streaming variant needs the whole band in one pass and enough rows to fill the GPU.
+static bool stream_applicable(const cuvdia_plan* p, bool trans) {
+    return p->nd <= pn::KD && (trans ? p->w : p->h) >= 64 * ps::TR;
+}
+
 int launch_prod_narrow(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
                        bool trans, float fa, float fc, int mode, cudaStream_t st) {
+    if (stream_applicable(p, trans)) {
+        const bool ex = mode == CUVDIA_MODE_EXACT;
+        if (trans) return ex ? launch_stream_t<true, true>(p, A, B, ldb, C, ldc, ncols, fa, fc, st)
+                             : launch_stream_t<true, false>(p, A, B, ldb, C, ldc, ncols, fa, fc, st);
+        return ex ? launch_stream_t<false, true>(p, A, B, ldb, C, ldc, ncols, fa, fc, st)
+                  : launch_stream_t<false, false>(p, A, B, ldb, C, ldc, ncols, fa, fc, st);
+    }
     NarrowParams P;
     P.h = p->h; P.w = p->w; P.nd = p->nd; P.lo = p->band_lo; P.S = p->stride;
     P.ldb = ldb; P.ldc = ldc; P.ncols = ncols; P.fa = fa; P.fc = fc; P.A = A; P.B = B; P.C = C;

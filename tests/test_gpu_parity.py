@@ -334,3 +334,28 @@ def test_convert_and_pull(cb, golden):
     assert np.array_equal(cb.convert(None, H), g["diamat_dense"])
     assert np.array_equal(cb.pull(D), g["diamat_dense"])
     assert D(3, 4) == H(3, 4) == g["diamat_dense"][3, 4] and not H.has(0, 5)
+
+
+@pytest.mark.parametrize("trans", ["n", "t"])
+@pytest.mark.parametrize("lo,nd", [(-8, 16), (-5, 11), (3, 16), (-2, 5), (1, 16)])
+def test_prod_streaming_narrow_band(cb, trans, lo, nd):
+    """Long, narrow bands (the TMA streaming kernel: >= 32768 rows, <= 16 diagonals), all four alignments of the
+    first offset, ragged row counts, more than 32 columns, factC != 0."""
+    rng = np.random.default_rng(900 + nd + 31 * (trans == "t") + lo)
+    offs = np.arange(lo, lo + nd, dtype=np.int32)
+    prod_case(cb, rng, 40004, 36008, offs, 1, 5, trans, 1.0, 0.0)
+    prod_case(cb, rng, 36008, 40004, offs, 1, 40, trans, 0.75, 2.0)
+
+
+def test_spmv_long_tridiagonal(cb):
+    """The classical DIA use: a tridiagonal operator times one vector, through spmv."""
+    rng = np.random.default_rng(17)
+    n = 1 << 17
+    A = make_dia(rng, n, n, np.array([-1, 0, 1], dtype=np.int32))
+    v = rng.uniform(-1, 1, n).astype(np.float32)
+    D = to_dev_dia(A)
+    dst = cb.to_device(np.zeros(n, dtype=np.float32))
+    cb.spmv(dst, D, cb.to_device(v), "n")
+    want = F(np.zeros((n, 1)))
+    ho.prod(want, A, F(v.reshape(n, 1)), "n")
+    assert_bits_equal(cb.to_host(dst), want[:, 0])
