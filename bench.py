@@ -418,6 +418,10 @@ def run_single(args, cfg):
     elif case == "cfg2":
         h = w = 4096; nb = 1024; rf = 1
         offs = np.sort(rng.choice(np.arange(-2047, 2048), 128, replace=False)).astype(np.int32); op = "dd2dia"
+    elif case == "membound_dd":
+        # densedense_to_dia where HBM bounds it: 2^20 rows, 16 diagonals, 32 batch columns
+        h = w = 1 << 20; nb = 32; rf = 1
+        offs = band_offsets(16); op = "dd2dia"
     elif case in ("membound_n", "membound_t"):
         # a shape where HBM, not FP32, bounds prod: 2^20 rows, 16 diagonals, 32 batch columns (3 flop/B)
         h = w = 1 << 20; nb = 32; rf = 1

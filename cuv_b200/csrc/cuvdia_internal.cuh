@@ -98,6 +98,10 @@ int launch_prod_narrow(const cuvdia_plan* p, const float* A, const float* B, int
 bool prod_window_applicable(const cuvdia_plan* p, bool trans, int ncols);
 int launch_prod_window(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
                        bool trans, float factAB, float factC, int mode, cudaStream_t st);
+bool dd2dia_stream_applicable(const cuvdia_plan* p, const float* Cv, const float* A, int lda, const float* B, int ldb,
+                              int ncols);
+int launch_dd2dia_stream(cuvdia_plan* p, float* Cv, const float* A, int lda, const float* B, int ldb, int ncols,
+                         float factAB, float factC, cudaStream_t st);
 bool dd2dia_band_applicable(const cuvdia_plan* p, const float* A, int lda, const float* B, int ldb, int ncols);
 int launch_dd2dia_band(cuvdia_plan* p, float* Cv, const float* A, int lda, const float* B, int ldb, int ncols,
                        float factAB, float factC, cudaStream_t st);

@@ -24,6 +24,8 @@ int launch_prod(const cuvdia_plan* p, const float* A, const float* B, int ldb, f
 
 int launch_dd2dia(cuvdia_plan* p, float* Cv, const float* A, int lda, const float* B, int ldb, int ncols,
                   float factAB, float factC, cudaStream_t st) {
+    if (dd2dia_stream_applicable(p, Cv, A, lda, B, ldb, ncols))
+        return launch_dd2dia_stream(p, Cv, A, lda, B, ldb, ncols, factAB, factC, st);
     if (dd2dia_band_applicable(p, A, lda, B, ldb, ncols))
         return launch_dd2dia_band(p, Cv, A, lda, B, ldb, ncols, factAB, factC, st);
     return launch_dd2dia_generic(p, Cv, A, lda, B, ldb, ncols, factAB, factC, st);

@@ -359,3 +359,13 @@ def test_spmv_long_tridiagonal(cb):
     want = F(np.zeros((n, 1)))
     ho.prod(want, A, F(v.reshape(n, 1)), "n")
     assert_bits_equal(cb.to_host(dst), want[:, 0])
+
+
+@pytest.mark.parametrize("lo,nd", [(-8, 16), (-5, 11), (3, 16), (-2, 5), (1, 16)])
+def test_dd2dia_streaming_narrow_band(cb, lo, nd):
+    """Long, narrow bands (the TMA streaming densedense_to_dia: >= 32768 rows, <= 16 diagonals): all alignments
+    of the first offset, ragged sizes, batch not a multiple of the round, both factor paths."""
+    rng = np.random.default_rng(950 + nd + lo)
+    offs = np.arange(lo, lo + nd, dtype=np.int32)
+    dd_case(cb, rng, 40004, 36008, offs, 1, 40, 1.0, 0.0)
+    dd_case(cb, rng, 36008, 40004, offs, 1, 21, 0.01, 0.9, dist="uniform")
