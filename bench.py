@@ -384,6 +384,20 @@ def run_ours(args, cfg):
     }
     if e2e:
         line["e2e"] = e2e
+    if world == 1 and not args.no_extra:
+        # The step's big kernels are bound by FP32 issue.  Beside them, the same routines on a shape that HBM
+        # bounds (2^20 rows, 16 diagonals, 32 columns; operands larger than L2), as a fraction of the HBM peak.
+        del step, V0, U_h, U_v
+        torch.cuda.empty_cache()
+        shapes = {}
+        for case, key in (("membound_n", "prod"), ("membound_t", "prod_transposed"), ("membound_dd", "densedense_to_dia")):
+            sub = argparse.Namespace(**vars(args))
+            sub.case, sub.steps, sub.warmup, sub.flush_l2, sub.cpu = case, 10, 3, False, False
+            r = measure_single(sub, cfg)
+            shapes[key] = {"GB/s": r["gbs"], "frac_of_hbm_peak": r["hbm_frac"], "us": r["ms"] * 1e3,
+                           "arithmetic": args.mode if key != "densedense_to_dia" else "fused"}
+        line["hbm_bound_shape"] = {"shape": "2^20 x 2^20, 16 diagonals, 32 batch columns (335 MB algorithmic, ~3 flop/B)",
+                                   "peak_GB/s": peak, "routines": shapes}
     if world == 1 and not args.no_cpu:
         sample = min(batch, args.cpu_sample_cols)
         t, threads, _ = cpu_rbm(units, nd, batch, sample, 1, 0)
@@ -400,6 +414,10 @@ def run_ours(args, cfg):
 
 def run_single(args, cfg):
     """One routine on one GPU (profiling and per-configuration figures)."""
+    print(json.dumps(measure_single(args, cfg)), flush=True)
+
+
+def measure_single(args, cfg):
     import numpy as np
     import torch
     import cuv_b200 as cb
@@ -514,12 +532,12 @@ def run_single(args, cfg):
             else:
                 ho.reduce_to_col(vh, Xh, ho.RF_ADD, 1.0, 0.0, nt)
             cpu["ms_%s_threads" % label] = (time.perf_counter() - t0) * 1e3
-    print(json.dumps({"case": case, "op": op, "cpu_oracle": cpu, "h": h, "w": w, "num_dia": int(nd), "row_fact": rf, "batch": nb,
-                      "mode": args.mode, "ms": ms, "ms_min": min(ts), "gbs": byts / (ms * 1e-3) / 1e9,
-                      "hbm_frac": byts / (ms * 1e-3) / 1e9 / peak, "tflops": flops / (ms * 1e-3) / 1e12,
-                      "l2_flushed": bool(args.flush_l2), "launches_per_timing": reps,
-                      "timing": "CUDA graph of %d back-to-back launches" % reps if reps > 1 else "single launch",
-                      "gpu_launches": int(cb.launch_count() - l0) if reps == 1 else reps * args.steps}), flush=True)
+    return {"case": case, "op": op, "cpu_oracle": cpu, "h": h, "w": w, "num_dia": int(nd), "row_fact": rf, "batch": nb,
+            "mode": args.mode, "ms": ms, "ms_min": min(ts), "gbs": byts / (ms * 1e-3) / 1e9,
+            "hbm_frac": byts / (ms * 1e-3) / 1e9 / peak, "tflops": flops / (ms * 1e-3) / 1e12,
+            "l2_flushed": bool(args.flush_l2), "launches_per_timing": reps,
+            "timing": "CUDA graph of %d back-to-back launches" % reps if reps > 1 else "single launch",
+            "gpu_launches": int(cb.launch_count() - l0) if reps == 1 else reps * args.steps}
 
 
 def main():
@@ -538,6 +556,7 @@ def main():
     ap.add_argument("--cpu-sample-cols", type=int, default=64)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the HBM-bound side measurement of the default run")
     ap.add_argument("--flush-l2", action="store_true")
     ap.add_argument("--cpu", action="store_true", help="single-routine cases: also time the CPU oracle")
     args = ap.parse_args()
