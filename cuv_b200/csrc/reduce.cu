@@ -152,6 +152,7 @@ __device__ __forceinline__ void line_scan(const float* __restrict__ line, long l
                                           float& val, int& idx) {
     using F = Fn<RF>;
     if (VEC == 4) {
+#pragma unroll 4
         for (long long j = lo + (long long)tid * 4; j < hi; j += (long long)step * 4) {
             if (j + 4 <= hi) {
                 const float4 x = __ldg(reinterpret_cast<const float4*>(line + j));
@@ -210,12 +211,99 @@ reduce_along_block_kernel(float* __restrict__ dst, const float* __restrict__ src
     }
 }
 
+// ---- short lines ------------------------------------------------------------------------------------
+// along lines shorter than a warp's reach: LPL lanes per line, 32/LPL lines per warp, so a warp
+// still reads one contiguous run of memory with all lanes busy
+template <int RF, int VEC, int LPL>
+__global__ void __launch_bounds__(256)
+reduce_along_subwarp_kernel(float* __restrict__ dst, const float* __restrict__ src, long long n_contig, int n_strided,
+                            float fnew, float fold) {
+    using F = Fn<RF>;
+    const int lane = threadIdx.x & 31, sub = lane % LPL;
+    const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const long long line = warp * (32 / LPL) + lane / LPL;
+    float val = F::init();
+    int idx = 0;
+    if (line < n_strided) line_scan<RF, VEC>(src + line * n_contig, 0, n_contig, sub, LPL, val, idx);
+#pragma unroll
+    for (int d = LPL / 2; d > 0; d >>= 1) {
+        const float v2 = __shfl_down_sync(0xffffffffu, val, d, LPL);
+        const int i2 = __shfl_down_sync(0xffffffffu, idx, d, LPL);
+        F::rr(val, idx, v2, i2);
+    }
+    if (sub == 0 && line < n_strided) F::finish(dst + line, val, idx, fnew, fold, (float)n_contig);
+}
+
+// across lines when a line is at most 256 floats (NV = n_contig/4 vectors, a power of two): thread t
+// owns vector t % NV of the lines t / NV, t / NV + G, ... (G = 256 / NV line groups per block); the G
+// partial vectors of a block are folded in group order through shared memory
+template <int RF>
+__global__ void __launch_bounds__(256)
+reduce_across_small_kernel(float* __restrict__ dst, const float* __restrict__ src, int n_contig, int n_strided,
+                           float fnew, float fold, int nsplit, float* __restrict__ pval, int* __restrict__ pidx) {
+    using F = Fn<RF>;
+    __shared__ float s_val[1024];
+    __shared__ int s_idx[1024];
+    const int nv = n_contig >> 2, groups = 256 / nv;
+    const int q = threadIdx.x % nv, grp = threadIdx.x / nv;
+    const int z = blockIdx.x;
+    const int j0 = (int)((long long)n_strided * z / nsplit), j1 = (int)((long long)n_strided * (z + 1) / nsplit);
+    float val[4];
+    int idx[4];
+#pragma unroll
+    for (int v = 0; v < 4; v++) { val[v] = F::init(); idx[v] = 0; }
+    const float* p = src + 4 * q;
+#pragma unroll 4
+    for (int j = j0 + grp; j < j1; j += groups) {
+        const float4 x = __ldg(reinterpret_cast<const float4*>(p + (size_t)j * n_contig));
+        F::rv(val[0], idx[0], x.x, j); F::rv(val[1], idx[1], x.y, j);
+        F::rv(val[2], idx[2], x.z, j); F::rv(val[3], idx[3], x.w, j);
+    }
+#pragma unroll
+    for (int v = 0; v < 4; v++) { s_val[threadIdx.x * 4 + v] = val[v]; s_idx[threadIdx.x * 4 + v] = idx[v]; }
+    __syncthreads();
+    if (threadIdx.x < n_contig) {
+        const int o = threadIdx.x;
+        // words of output o: group g holds it at ((g*nv + o/4)*4 + o%4) = g*n_contig + o
+        float r = s_val[o];
+        int ri = s_idx[o];
+        for (int g = 1; g < groups; g++) F::rr(r, ri, s_val[g * n_contig + o], s_idx[g * n_contig + o]);
+        if (nsplit == 1) F::finish(dst + o, r, ri, fnew, fold, (float)n_strided);
+        else {
+            pval[(size_t)z * n_contig + o] = r;
+            if (F::is_arg) pidx[(size_t)z * n_contig + o] = ri;
+        }
+    }
+}
+
 template <int RF>
 static int launch_reduce_t(float* dst, const float* src, long long n_contig, long long n_strided, bool over_strided,
                            float fnew, float fold, cudaStream_t st) {
     const int sms = sm_count();
     const bool vec = (n_contig % 4 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
     int rc;
+    if (over_strided && vec && n_contig <= 256 && ((n_contig >> 2) & ((n_contig >> 2) - 1)) == 0 && n_strided >= 4096) {
+        // few outputs, many lines: blocks split the lines, every thread of a block reads
+        int nsplit = (int)std::min<long long>(8LL * sms, n_strided / 1024);
+        nsplit = std::max(1, nsplit);
+        float* pval = nullptr; int* pidx = nullptr;
+        if (nsplit > 1) {
+            void* ws;
+            rc = get_workspace(st, (size_t)nsplit * n_contig * 8, &ws);
+            if (rc) return rc;
+            pval = (float*)ws; pidx = (int*)(pval + (size_t)nsplit * n_contig);
+        }
+        reduce_across_small_kernel<RF><<<nsplit, 256, 0, st>>>(dst, src, (int)n_contig, (int)n_strided, fnew, fold, nsplit, pval, pidx);
+        count_launch();
+        rc = check_launch("reduce_across_small_kernel");
+        if (rc) return rc;
+        if (nsplit > 1) {
+            reduce_combine_kernel<RF><<<(unsigned)((n_contig + 255) / 256), 256, 0, st>>>(dst, n_contig, fnew, fold, nsplit, pval, pidx, (float)n_strided);
+            count_launch();
+            rc = check_launch("reduce_combine_kernel");
+        }
+        return rc;
+    }
     if (over_strided) {
         const long long per_block = (long long)RA_THREADS * (vec ? 4 : 1);
         const long long gx = (n_contig + per_block - 1) / per_block;
@@ -241,6 +329,17 @@ static int launch_reduce_t(float* dst, const float* src, long long n_contig, lon
             rc = check_launch("reduce_combine_kernel");
         }
         return rc;
+    }
+    if (vec && n_contig <= 64 && n_strided >= 2LL * sms) {
+        // lines of at most 16 vectors: 2, 4 or 8 lanes per line
+        const int lpl = n_contig <= 16 ? 2 : n_contig <= 32 ? 4 : 8;
+        const long long lines_per_block = 8LL * (32 / lpl);
+        const unsigned gx = (unsigned)((n_strided + lines_per_block - 1) / lines_per_block);
+        if (lpl == 2) reduce_along_subwarp_kernel<RF, 4, 2><<<gx, 256, 0, st>>>(dst, src, n_contig, (int)n_strided, fnew, fold);
+        else if (lpl == 4) reduce_along_subwarp_kernel<RF, 4, 4><<<gx, 256, 0, st>>>(dst, src, n_contig, (int)n_strided, fnew, fold);
+        else reduce_along_subwarp_kernel<RF, 4, 8><<<gx, 256, 0, st>>>(dst, src, n_contig, (int)n_strided, fnew, fold);
+        count_launch();
+        return check_launch("reduce_along_subwarp_kernel");
     }
     if (n_contig <= 4096 && n_strided >= 2LL * sms) {
         const unsigned gx = (unsigned)((n_strided + 7) / 8);

@@ -261,7 +261,8 @@ def test_reduce_reference_sweep(cb, rf, to_col, row_major):
 @pytest.mark.parametrize("to_col", [True, False])
 def test_reduce_shapes_and_factors(cb, to_col):
     rng = np.random.default_rng(55 + to_col)
-    for rows, cols in [(1, 1), (1, 300), (300, 1), (4096, 96), (96, 4096), (33, 70001), (70001, 33), (2048, 2048)]:
+    for rows, cols in [(1, 1), (1, 300), (300, 1), (4096, 96), (96, 4096), (33, 70001), (70001, 33), (2048, 2048),
+                       (32, 65536), (65536, 32), (8, 100000), (100000, 8), (256, 5000), (64, 8192), (16, 4100)]:
         reduce_case(cb, rng, rows, cols, to_col, ho.RF_ADD, 0.25, 0.5)
         reduce_case(cb, rng, rows, cols, to_col, ho.RF_ARGMAX)
     reduce_case(cb, rng, 16384, 256, to_col, ho.RF_ADD, 1.0 / 256, 1.0)
