@@ -17,7 +17,7 @@ from . import _capi
 from ._capi import (CuvDiaError, MODE_EXACT, MODE_FAST, RF_ADD, RF_MEAN, RF_ADD_SQUARED, RF_MAX, RF_ARGMAX,
                     RF_ARGMIN, RF_MIN, RF_MULT, RF_LOGADDEXP, RF_ADDEXP)
 
-__all__ = ["dev_dia_matrix_f", "host_dia_matrix_f", "convert", "pull", "dev_block_descriptor_f", "prod", "spmv", "densedense_to_dia", "reduce_to_col",
+__all__ = ["dev_dia_matrix_f", "host_dia_matrix_f", "convert", "pull", "save_dia_mat", "load_dia_mat", "dev_block_descriptor_f", "prod", "spmv", "densedense_to_dia", "reduce_to_col",
            "reduce_to_row", "bias_sigmoid_sample", "prod_bias_sigmoid_sample", "axpby", "colmajor_empty", "to_device", "to_host",
            "launch_count", "CuvDiaError", "MODE_EXACT", "MODE_FAST"]
 
@@ -178,6 +178,39 @@ class host_dia_matrix_f:
         s = self._slot(i, j)
         if s is not None:
             self.vec[s * self.stride + i] = val
+
+
+_DIA_MAGIC = b"CUVDIA1\0"
+
+
+def save_dia_mat(mat, filename):
+    """Write a DIA matrix (host or device) to a file: the seven fields CUV serialises - width, height,
+    num_dia, stride, row_fact, offsets, values (basics/sparse_matrix_io.hpp:59-72), in that order - as a
+    little-endian record (8-byte tag, five int32, int32 offsets, float32 values) instead of a Boost archive."""
+    vals = mat.vec.detach().cpu().numpy() if isinstance(mat, dev_dia_matrix_f) else mat.vec
+    with open(filename, "wb") as f:
+        f.write(_DIA_MAGIC)
+        np.array([mat.w, mat.h, mat.num_dia, mat.stride, mat.row_fact], dtype="<i4").tofile(f)
+        mat.offsets.astype("<i4").tofile(f)
+        np.ascontiguousarray(vals, dtype="<f4").tofile(f)
+
+
+def load_dia_mat(filename, device=None):
+    """Read a record written by :func:`save_dia_mat`; returns a host matrix, or a device matrix if
+    ``device`` is given (``load`` of src/cuv_python/export_dia_mat.cpp:96-110)."""
+    with open(filename, "rb") as f:
+        if f.read(8) != _DIA_MAGIC:
+            raise CuvDiaError(_capi.ERR_INVALID, "not a DIA matrix record")
+        w, h, nd, stride, rf = np.fromfile(f, dtype="<i4", count=5).tolist()
+        offsets = np.fromfile(f, dtype="<i4", count=nd)
+        vals = np.fromfile(f, dtype="<f4", count=nd * stride)
+    if offsets.size != nd or vals.size != nd * stride:
+        raise CuvDiaError(_capi.ERR_INVALID, "truncated DIA matrix record")
+    host = host_dia_matrix_f(h, w, offsets, stride, rf)
+    host.vec[:] = vals
+    if device is None:
+        return host
+    return convert(dev_dia_matrix_f(h, w, offsets, stride, rf, device=device), host)
 
 
 def convert(dst, src):

@@ -5,6 +5,7 @@
 // The host halves come from the CPU oracle (oracle/cuv_host_reference.hpp).  Exit code 0 = all passed.
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <string>
 #include <vector>
 
@@ -152,6 +153,19 @@ static void test_dia_mat() {
         dia_matrix<float, dev_memory_space> w2;
         convert(w2, w);
         CHECK(w2.vec_ptr() != nullptr && w2.h() == (unsigned)n && w2.w() == (unsigned)m && w2.num_dia() == 3);
+    }
+    {   // save / load (:84-101): the seven serialised fields survive a round trip, as does the device copy
+        const std::string fn = "/tmp/cuvdia_test_matrix.bin";
+        save_dia_matrix(w, fn);
+        dia_matrix<float, host_memory_space> w2;
+        load_dia_matrix(w2, fn);
+        std::remove(fn.c_str());
+        CHECK(w2.h() == w.h() && w2.w() == w.w() && w2.num_dia() == w.num_dia() && w2.stride() == w.stride() &&
+              w2.row_fact() == w.row_fact());
+        int bad = 0;
+        for (int i = 0; i < n; i++) for (int j = 0; j < m; j++) bad += (float)w(i, j) != (float)w2(i, j);
+        for (int s = 0; s < 3; s++) bad += w2.get_offset(s) != off[s];
+        CHECK(bad == 0);
     }
     {   // dia2dense (:111-119)
         tensor<float, host_memory_space, column_major> w2(n, m);
