@@ -13,7 +13,7 @@ and bias gradients.  Inputs are synthetic with the configuration's shapes and di
 CUV's host code) on all host cores on a bounded batch slice of the same workload.
 
 Other cases (single routines, used for profiling and for the per-configuration table):
-``--case prod_n|prod_t|dd2dia|reduce|glue`` on the band shape given by --units/--num-dia/--batch, and
+``--case prod_n|prod_t|dd2dia|reduce|glue|update`` on the band shape given by --units/--num-dia/--batch, and
 ``--case cfg0|cfg1|cfg2|rbm_cfg3`` for the other BASELINE configurations.
 """
 import argparse
@@ -472,6 +472,11 @@ def measure_single(args, cfg):
         S = cb.colmajor_empty(h, nb)
         fn = lambda: cb.bias_sigmoid_sample(X, vec, Y[:h] if w >= h else X, S)
         byts, flops = 16 * h * nb, 4.0 * h * nb
+    elif op == "update":
+        # the weight update of the step over the diagonals' whole value array (12 bytes per value)
+        Gd = torch.empty_like(A.vec).uniform_(-1, 1)
+        fn = lambda: cb.learn_step_weight_decay(A, Gd, 0.01, 0.05)
+        byts, flops = 12 * A.vec.numel(), 3.0 * A.vec.numel()
     else:
         raise SystemExit("unknown case " + case)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if args.flush_l2 else None

@@ -18,7 +18,8 @@ from ._capi import (CuvDiaError, MODE_EXACT, MODE_FAST, RF_ADD, RF_MEAN, RF_ADD_
                     RF_ARGMIN, RF_MIN, RF_MULT, RF_LOGADDEXP, RF_ADDEXP)
 
 __all__ = ["dev_dia_matrix_f", "host_dia_matrix_f", "convert", "pull", "save_dia_mat", "load_dia_mat", "dev_block_descriptor_f", "prod", "spmv", "densedense_to_dia", "reduce_to_col",
-           "reduce_to_row", "bias_sigmoid_sample", "prod_bias_sigmoid_sample", "axpby", "colmajor_empty", "to_device", "to_host",
+           "reduce_to_row", "bias_sigmoid_sample", "prod_bias_sigmoid_sample", "axpby", "learn_step_weight_decay",
+           "learn_step_weight_decay_momentum", "colmajor_empty", "to_device", "to_host",
            "launch_count", "CuvDiaError", "MODE_EXACT", "MODE_FAST"]
 
 
@@ -366,3 +367,32 @@ def axpby(dst, x, y, a, b):
         raise CuvDiaError(_capi.ERR_INVALID, "sizes match")
     _capi.check(_capi.lib().cuvdia_axpby_f32(_ptr(dst), _ptr(x), _ptr(y), a, b, dst.numel(), _stream()))
     return dst
+
+
+def _flat_values(x):
+    """The flat float storage of a DIA matrix (its whole value array) or of a tensor."""
+    return x.vec if isinstance(x, dev_dia_matrix_f) else x
+
+
+def learn_step_weight_decay(W, dW, learnrate, decay=0.0, sparsedecay=0.0):
+    """W = -learnrate*dW + (1 - learnrate*decay)*W in place (tensor_ops/rprop.hpp:117-128).
+
+    ``W`` and ``dW`` are device tensors or DIA matrices of equal storage size; the update of the sparse
+    RBM passes the weight matrix and its gradient (examples/rbm/base.py:72-75).  ``sparsedecay`` is
+    accepted and ignored, as in the reference (its L1 term is commented out)."""
+    w, g = _flat_values(W), _flat_values(dW)
+    if w.numel() != g.numel():
+        raise CuvDiaError(_capi.ERR_INVALID, "W.size() == dW.size()")
+    _capi.check(_capi.lib().cuvdia_learn_step_weight_decay_f32(_ptr(w), _ptr(g), w.numel(), float(learnrate),
+                                                               float(decay), _stream()))
+    return W
+
+
+def learn_step_weight_decay_momentum(W, momentum, dW, learnrate, momentum_weight=0.9, decay=0.0, sparsedecay=0.0):
+    """m = momentum_weight*m - learnrate*(dW + decay*W); W += m (tensor_ops/rprop.hpp:130-143, rprop.cu:158-170)."""
+    w, m, g = _flat_values(W), _flat_values(momentum), _flat_values(dW)
+    if not (w.numel() == g.numel() == m.numel()):
+        raise CuvDiaError(_capi.ERR_INVALID, "W.size() == dW.size() == momentum.size()")
+    _capi.check(_capi.lib().cuvdia_learn_step_weight_decay_momentum_f32(
+        _ptr(w), _ptr(m), _ptr(g), w.numel(), float(learnrate), float(momentum_weight), float(decay), _stream()))
+    return W

@@ -32,6 +32,8 @@ SIGNATURES = {
     "cuvdia_reduce_noalloc_f32": (_i, [_vp, _vp, _ll, _ll, _i, _i, _f, _f, _vp]),
     "cuvdia_bias_sigmoid_sample_f32": (_i, [_vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _vp]),
     "cuvdia_axpby_f32": (_i, [_vp, _vp, _vp, _f, _f, _ll, _vp]),
+    "cuvdia_learn_step_weight_decay_f32": (_i, [_vp, _vp, _ll, _f, _f, _vp]),
+    "cuvdia_learn_step_weight_decay_momentum_f32": (_i, [_vp, _vp, _vp, _ll, _f, _f, _f, _vp]),
     "cuvdia_binary_f32": (_i, [_vp, _vp, _vp, _i, _f, _f, _ll, _vp]),
     "cuvdia_fill_f32": (_i, [_vp, _f, _ll, _vp]),
     "cuvdia_sequence_f32": (_i, [_vp, _ll, _vp]),

@@ -256,6 +256,25 @@ int cuvdia_axpby_f32(float* dst, const float* x, const float* y, float a, float 
     return launch_axpby(dst, x, y, a, b, n, (cudaStream_t)stream);
 }
 
+int cuvdia_learn_step_weight_decay_f32(float* W, const float* dW, long long n, float learnrate, float decay,
+                                       void* stream) {
+    CUVDIA_REQUIRE(W != nullptr && dW != nullptr);
+    CUVDIA_REQUIRE(n >= 0);
+    if (n == 0) return CUVDIA_OK;
+    // the factors are formed in float exactly as the reference forms them (tensor_ops/rprop.cu:345)
+    const float alpha = -learnrate;
+    const float beta = 1.f - learnrate * decay;
+    return launch_learn_step(W, nullptr, dW, alpha, beta, 0.f, n, (cudaStream_t)stream);
+}
+
+int cuvdia_learn_step_weight_decay_momentum_f32(float* W, float* momentum, const float* dW, long long n,
+                                                float learnrate, float momentum_weight, float decay, void* stream) {
+    CUVDIA_REQUIRE(W != nullptr && dW != nullptr && momentum != nullptr);
+    CUVDIA_REQUIRE(n >= 0);
+    if (n == 0) return CUVDIA_OK;
+    return launch_learn_step(W, momentum, dW, learnrate, momentum_weight, decay, n, (cudaStream_t)stream);
+}
+
 int cuvdia_binary_f32(float* dst, const float* x, const float* y, int op, float p, float p2, long long n, void* stream) {
     CUVDIA_REQUIRE(dst != nullptr && x != nullptr && y != nullptr);
     CUVDIA_REQUIRE(op >= CUVDIA_BF_ADD && op <= CUVDIA_BF_AXPBY);

@@ -110,6 +110,8 @@ int launch_reduce(float* dst, const float* src, long long n_contig, long long n_
 int launch_bias_sigmoid_sample(float* act, int ld, const float* bias, const float* u, int ldu, float* sample,
                                int lds, int units, int ncols, cudaStream_t st);
 int launch_axpby(float* dst, const float* x, const float* y, float a, float b, long long n, cudaStream_t st);
+// momentum-free when M is null: (a, b) = (alpha, beta); with momentum (a, b, c) = (lr, momentum weight, l2 decay)
+int launch_learn_step(float* W, float* M, const float* dW, float a, float b, float c, long long n, cudaStream_t st);
 int launch_binary(float* dst, const float* x, const float* y, int op, float p, float p2, long long n, cudaStream_t st);
 int launch_fill(float* dst, float value, int sequence, long long n, cudaStream_t st);
 }  // namespace cuvdia

@@ -69,6 +69,77 @@ int launch_axpby(float* dst, const float* x, const float* y, float a, float b, l
     return check_launch("axpby_kernel");
 }
 
+// Gradient step with L2 weight decay, W = alpha*dW + beta*W with alpha = -learnrate and
+// beta = 1 - learnrate*decay (tensor_ops/rprop.cu:147-156,341-346): two multiplies and an add, unfused,
+// like the host loop (rprop.cu:331-339).  Four values per thread when the pointers allow.
+template <bool VEC>
+__global__ void __launch_bounds__(256)
+learn_step_kernel(float* __restrict__ W, const float* __restrict__ dW, float alpha, float beta, long long n) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    if (VEC) {
+        const long long n4 = n / 4;
+        for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < n4; t += stride) {
+            const float4 g = __ldg(reinterpret_cast<const float4*>(dW) + t);
+            float4 w = reinterpret_cast<float4*>(W)[t];
+            w.x = __fadd_rn(__fmul_rn(alpha, g.x), __fmul_rn(beta, w.x));
+            w.y = __fadd_rn(__fmul_rn(alpha, g.y), __fmul_rn(beta, w.y));
+            w.z = __fadd_rn(__fmul_rn(alpha, g.z), __fmul_rn(beta, w.z));
+            w.w = __fadd_rn(__fmul_rn(alpha, g.w), __fmul_rn(beta, w.w));
+            reinterpret_cast<float4*>(W)[t] = w;
+        }
+        for (long long t = 4 * n4 + (long long)blockIdx.x * blockDim.x + threadIdx.x; t < n; t += stride)
+            W[t] = __fadd_rn(__fmul_rn(alpha, dW[t]), __fmul_rn(beta, W[t]));
+    } else {
+        for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < n; t += stride)
+            W[t] = __fadd_rn(__fmul_rn(alpha, dW[t]), __fmul_rn(beta, W[t]));
+    }
+}
+
+// The same step with momentum (tensor_ops/rprop.cu:158-170, the device kernel's formula):
+//   m = momentum_weight*m - lr*(dW + l2decay*W);  W += m;  M = m
+template <bool VEC>
+__global__ void __launch_bounds__(256)
+learn_step_momentum_kernel(float* __restrict__ W, float* __restrict__ M, const float* __restrict__ dW, float lr,
+                           float mw, float l2, long long n) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    auto one = [&](float w, float m, float g, float& w_out, float& m_out) {
+        m_out = __fsub_rn(__fmul_rn(mw, m), __fmul_rn(lr, __fadd_rn(g, __fmul_rn(l2, w))));
+        w_out = __fadd_rn(w, m_out);
+    };
+    if (VEC) {
+        const long long n4 = n / 4;
+        for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < n4; t += stride) {
+            const float4 g = __ldg(reinterpret_cast<const float4*>(dW) + t);
+            float4 w = reinterpret_cast<float4*>(W)[t];
+            float4 m = reinterpret_cast<float4*>(M)[t];
+            one(w.x, m.x, g.x, w.x, m.x); one(w.y, m.y, g.y, w.y, m.y);
+            one(w.z, m.z, g.z, w.z, m.z); one(w.w, m.w, g.w, w.w, m.w);
+            reinterpret_cast<float4*>(W)[t] = w;
+            reinterpret_cast<float4*>(M)[t] = m;
+        }
+        for (long long t = 4 * n4 + (long long)blockIdx.x * blockDim.x + threadIdx.x; t < n; t += stride)
+            one(W[t], M[t], dW[t], W[t], M[t]);
+    } else {
+        for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < n; t += stride)
+            one(W[t], M[t], dW[t], W[t], M[t]);
+    }
+}
+
+int launch_learn_step(float* W, float* M, const float* dW, float a, float b, float c, long long n, cudaStream_t st) {
+    const bool vec = aligned16(W) && aligned16(dW) && (!M || aligned16(M));
+    const long long work = vec ? (n + 3) / 4 : n;
+    const int blocks = (int)std::max<long long>(1, std::min<long long>((work + 255) / 256, 16LL * sm_count()));
+    if (M) {
+        if (vec) learn_step_momentum_kernel<true><<<blocks, 256, 0, st>>>(W, M, dW, a, b, c, n);
+        else     learn_step_momentum_kernel<false><<<blocks, 256, 0, st>>>(W, M, dW, a, b, c, n);
+    } else {
+        if (vec) learn_step_kernel<true><<<blocks, 256, 0, st>>>(W, dW, a, b, n);
+        else     learn_step_kernel<false><<<blocks, 256, 0, st>>>(W, dW, a, b, n);
+    }
+    count_launch();
+    return check_launch(M ? "learn_step_momentum_kernel" : "learn_step_kernel");
+}
+
 // dst[i] = op(x[i], y[i]) with the parameterised functors of apply_binary_functor
 // (tensor_ops/functors.hpp:377-433): op codes are CUVDIA_BF_*.
 __global__ void __launch_bounds__(256)

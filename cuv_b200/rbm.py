@@ -95,6 +95,15 @@ class SparseRBMStep:
         two bias gradients."""
         allreduce_gradients(self.G.vec, self.bias_grad, group)
 
+    def update(self, learnrate, decay=0.0):
+        """The trainer's update step (examples/rbm/base.py:72-75): learn_step_weight_decay on the weight
+        diagonals and on both bias vectors with the gradients of the last step (after allreduce() when
+        there are several ranks, so that every rank applies the same full-batch gradient)."""
+        t = self._timed
+        t("update", lambda: cb.learn_step_weight_decay(self.W, self.G, learnrate, decay))
+        t("update", lambda: cb.learn_step_weight_decay(self.c_hid, self.gc, learnrate, decay))
+        t("update", lambda: cb.learn_step_weight_decay(self.b_vis, self.gb, learnrate, decay))
+
 
 class HostFedRBM:
     """Runs SparseRBMStep on inputs that live in pinned host memory and returns the gradients to

@@ -7,5 +7,6 @@
 #include "cuv/convert/convert.hpp"
 #include "cuv/matrix_ops/densedense_to_sparse.hpp"
 #include "cuv/matrix_ops/matrix_ops.hpp"
+#include "cuv/tensor_ops/rprop.hpp"
 #include "cuv/tensor_ops/tensor_ops.hpp"
 #include "cuv/tools/cuv_general.hpp"

@@ -196,6 +196,24 @@ CUVDIA_API int cuvdia_prod_bias_sigmoid_sample_f32(const cuvdia_plan* plan, cons
 CUVDIA_API int cuvdia_axpby_f32(float* dst, const float* x, const float* y, float a, float b, long long n,
                      void* stream);
 
+/* Gradient step with L2 weight decay over n floats, in place:
+ *   W = (-learnrate)*dW + (1 - learnrate*decay)*W
+ * (learn_step_weight_decay, tensor_ops/rprop.hpp:117-128, rprop.cu:147-156,331-346; the L1 term
+ * `sparsedecay` is commented out in both of the reference's implementations and has no effect there).
+ * For a DIA matrix pass its value array and num_dia*stride, as examples/rbm/base.py:72-75 does with
+ * the weight matrix and the two bias vectors.  Bit-identical to the host loop. */
+CUVDIA_API int cuvdia_learn_step_weight_decay_f32(float* W, const float* dW, long long n, float learnrate,
+                                                  float decay, void* stream);
+
+/* The same step with momentum (learn_step_weight_decay_momentum, tensor_ops/rprop.hpp:130-143), with
+ * the formula of the reference's device kernel (rprop.cu:158-170):
+ *   m = momentum_weight*m - learnrate*(dW + decay*W);   W += m;   momentum = m
+ * (the reference's host loop, rprop.cu:356-367, has `dW - decay*W` instead; with decay == 0, the only
+ * value its tests use, the two agree). */
+CUVDIA_API int cuvdia_learn_step_weight_decay_momentum_f32(float* W, float* momentum, const float* dW, long long n,
+                                                           float learnrate, float momentum_weight, float decay,
+                                                           void* stream);
+
 /* dst = op(x, y) element-wise over n floats for the float functors of apply_binary_functor the DIA
  * path's callers use (tensor_ops/tensor_ops.hpp:460-492,530-655; functors.hpp:377-433):
  * ADD x+y, SUBTRACT x-y, MULT x*y, AXPY p*x+y, XPBY x+p*y, AXPBY p*x+p2*y.  dst may alias x or y. */

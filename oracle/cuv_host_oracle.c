@@ -381,3 +381,31 @@ ORACLE_API void oracle_bias_sigmoid_sample(float *act, const float *bias, const 
     act_ctx c = { act, bias, u, sample, units, ncols };
     parallel_ranges(act_range, &c, ncols, nthreads);
 }
+
+/* ---- gradient step with weight decay -------------------------------------------------------------
+ * learn_step_weight_decay (tensor_ops/rprop.cu:331-346): alpha = -learnrate, beta = 1 - learnrate*decay,
+ * both formed in float, then W[i] = alpha*dW[i] + beta*W[i]. */
+ORACLE_API void oracle_learn_step_weight_decay(float *W, const float *dW, long n, float learnrate, float decay)
+{
+    const float alpha = -learnrate;
+    const float beta = 1.f - learnrate * decay;
+    for (long i = 0; i < n; i++)
+        W[i] = alpha * dW[i] + beta * W[i];
+}
+
+/* learn_step_weight_decay_momentum.  device_formula != 0: the kernel's update (rprop.cu:158-170),
+ * m = mw*m - lr*(dW + l2*W); otherwise the host loop as written (rprop.cu:356-367), which has
+ * dW - l2*W.  Then W += m and M = m. */
+ORACLE_API void oracle_learn_step_weight_decay_momentum(float *W, float *M, const float *dW, long n, float lr,
+                                                        float mw, float l2, int device_formula)
+{
+    for (long i = 0; i < n; i++) {
+        float m = M[i];
+        if (device_formula)
+            m = mw * m - lr * (dW[i] + l2 * W[i]);
+        else
+            m = mw * m - lr * (dW[i] - l2 * W[i]);
+        W[i] += m;
+        M[i] = m;
+    }
+}

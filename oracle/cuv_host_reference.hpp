@@ -12,6 +12,9 @@ int oracle_dd2dia(float* Cvals, const int* offsets, int nd, int h, int w, int st
                   const float* B, int ldb, int ncols, float factAB, float factC, int literal_host, int nthreads);
 int oracle_reduce(float* dst, const float* src, long n_contig, long n_strided, int over_strided, int rf, float factNew,
                   float factOld, int nthreads);
+void oracle_learn_step_weight_decay(float* W, const float* dW, long n, float learnrate, float decay);
+void oracle_learn_step_weight_decay_momentum(float* W, float* M, const float* dW, long n, float lr, float mw, float l2,
+                                             int device_formula);
 }
 
 namespace cuv {
@@ -54,6 +57,13 @@ inline void reduce_host(tensor<float, host_memory_space>& v, const float* m, lon
                         bool over_strided, reduce_functor rf, float factNew, float factOld) {
     cuvAssert((long long)v.size() == (over_strided ? n_contig : n_strided));
     cuvAssert(oracle_reduce(v.ptr(), m, n_contig, n_strided, over_strided ? 1 : 0, (int)rf, factNew, factOld, 1) == 0);
+}
+inline void learn_step_host(float* W, const float* dW, unsigned long long n, float learnrate, float decay) {
+    oracle_learn_step_weight_decay(W, dW, (long)n, learnrate, decay);
+}
+inline void learn_step_momentum_host(float* W, float* momentum, const float* dW, unsigned long long n, float learnrate,
+                                     float momentum_weight, float decay) {
+    oracle_learn_step_weight_decay_momentum(W, momentum, dW, (long)n, learnrate, momentum_weight, decay, 1);
 }
 }  // namespace detail
 

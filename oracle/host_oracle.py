@@ -53,6 +53,11 @@ def lib():
         L.oracle_bias_sigmoid_sample.restype = None
         L.oracle_bias_sigmoid_sample.argtypes = [_f32p, _f32p, _f32p, _f32p, ctypes.c_long, ctypes.c_long,
                                                  ctypes.c_int]
+        L.oracle_learn_step_weight_decay.restype = None
+        L.oracle_learn_step_weight_decay.argtypes = [_f32p, _f32p, ctypes.c_long, ctypes.c_float, ctypes.c_float]
+        L.oracle_learn_step_weight_decay_momentum.restype = None
+        L.oracle_learn_step_weight_decay_momentum.argtypes = [_f32p, _f32p, _f32p, ctypes.c_long, ctypes.c_float,
+                                                              ctypes.c_float, ctypes.c_float, ctypes.c_int]
         _lib = L
     return _lib
 
@@ -168,3 +173,19 @@ def bias_sigmoid_sample(act, bias=None, u=None, nthreads=1):
         sample = np.empty_like(act, order="F")
     lib().oracle_bias_sigmoid_sample(_fp(act), _fp(bias), _fp(u), _fp(sample), act.shape[0], act.shape[1], nthreads)
     return sample
+
+
+def learn_step_weight_decay(W, dW, learnrate, decay=0.0):
+    """W = -learnrate*dW + (1 - learnrate*decay)*W in place on flat float32 arrays (tensor_ops/rprop.cu:331-346)."""
+    assert W.dtype == np.float32 and dW.dtype == np.float32 and W.size == dW.size
+    assert W.flags.c_contiguous or W.flags.f_contiguous
+    lib().oracle_learn_step_weight_decay(_fp(W), _fp(dW), W.size, learnrate, decay)
+    return W
+
+
+def learn_step_weight_decay_momentum(W, M, dW, learnrate, momentum_weight=0.9, decay=0.0, device_formula=True):
+    """Momentum step in place (tensor_ops/rprop.cu:158-170 device formula, :356-367 host loop)."""
+    assert W.dtype == M.dtype == dW.dtype == np.float32 and W.size == dW.size == M.size
+    lib().oracle_learn_step_weight_decay_momentum(_fp(W), _fp(M), _fp(dW), W.size, learnrate, momentum_weight, decay,
+                                                  1 if device_formula else 0)
+    return W

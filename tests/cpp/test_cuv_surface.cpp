@@ -1,7 +1,7 @@
 // C++ tests of the CUV surface over libcuvdia.so.  They follow CUV's own tests of this path - same
 // fixtures, same "device object vs host object of the same template" pattern:
 //   src/tests/spmv.cpp:49-143, src/tests/densedense_to_dia.cpp:50-197, src/tests/dia_mat.cpp:48-132,
-//   src/tests/convert.cpp:110-129, src/tests/matrix_op.cpp:80-105,858-924.
+//   src/tests/convert.cpp:110-129, src/tests/matrix_op.cpp:80-105,858-924, src/tests/optimize.cpp:59-121.
 // The host halves come from the CPU oracle (oracle/cuv_host_reference.hpp).  Exit code 0 = all passed.
 #include <cmath>
 #include <cstdio>
@@ -241,6 +241,57 @@ static void test_tensor_ops() {
     CHECK(alias.ptr() == a2.ptr());
 }
 
+// ---- optimize.cpp: the gradient step minimises f(W) = 2 (W - optimum)^2 -------------------------------------
+template <class M> static void lswd_optimization(int N, bool momentum, const char* what) {
+    tensor<float, host_memory_space> h_opt(N), h_w(N);
+    unsigned s = 12345u;
+    for (int i = 0; i < N; i++) { s = s * 1664525u + 1013904223u; h_opt[i] = (s >> 8) * (1.f / 16777216.f); }
+    for (int i = 0; i < N; i++) { s = s * 1664525u + 1013904223u; h_w[i] = (s >> 8) * (1.f / 16777216.f); }
+    tensor<float, M> W(N), dW(N), mom(N), optimum(N);
+    W = h_w; optimum = h_opt;
+    fill(mom, 0.f);
+    const int max_iter = 1000;
+    for (int iter = 0; iter < max_iter; ++iter) {
+        apply_binary_functor(dW, W, optimum, BF_SUBTRACT);
+        if (momentum) learn_step_weight_decay_momentum(W, mom, dW, 0.01f, 1.f - iter / (float)max_iter, 0.0f);
+        else learn_step_weight_decay(W, dW, 0.01f, 0.0f);
+    }
+    tensor<float, host_memory_space> res(N);
+    res = W;
+    int bad = 0;
+    double err = 0;
+    for (int i = 0; i < N; i++) {
+        const float a = (float)res[i] + 1.f, b = (float)h_opt[i] + 1.f;
+        bad += !(std::fabs(a - b) <= 1e-4f * std::max(std::fabs(a), std::fabs(b)));     // BOOST_CHECK_CLOSE 0.01 %
+        err += 2.0 * ((float)res[i] - (float)h_opt[i]) * ((float)res[i] - (float)h_opt[i]);
+    }
+    g_checks++;
+    if (bad || !(err / N <= 1e-4)) { g_fail++; std::printf("FAILED %s: %d weights off the optimum, mean error %g\n", what, bad, err / N); }
+}
+
+static void test_learn_step() {
+    lswd_optimization<host_memory_space>(8092, false, "lswd host");
+    lswd_optimization<dev_memory_space>(8092, false, "lswd dev");
+    lswd_optimization<host_memory_space>(8092, true, "lswd momentum host");
+    lswd_optimization<dev_memory_space>(8092, true, "lswd momentum dev");
+    // host and device objects of the same template agree bit for bit, decay included, on a DIA matrix's values
+    const int n = 96, nd = 5;
+    dia_matrix<float, host_memory_space> Wh(n, n, nd, n), Gh(n, n, nd, n);
+    std::vector<int> off = {-2, -1, 0, 1, 2};
+    Wh.set_offsets(off); Gh.set_offsets(off);
+    sequence(Wh.vec()); sequence(Gh.vec());
+    apply_binary_functor(Gh.vec(), Wh.vec(), BF_AXPBY, 0.37f, -0.001f);
+    dia_matrix<float, dev_memory_space> Wd(n, n, nd, n), Gd(n, n, nd, n);
+    convert(Wd, Wh); convert(Gd, Gh);
+    learn_step_weight_decay(Wh, Gh, 0.03f, 0.2f);
+    learn_step_weight_decay(Wd, Gd, 0.03f, 0.2f);
+    dia_matrix<float, host_memory_space> back(n, n, nd, n);
+    convert(back, Wd);
+    int bad = 0;
+    for (unsigned i = 0; i < Wh.vec().size(); i++) bad += (float)Wh.vec()[i] != (float)back.vec()[i];
+    CHECK(bad == 0);
+}
+
 int main() {
     try {
         initCUDA(0);
@@ -250,6 +301,7 @@ int main() {
         reduce_sweep<column_major>("column_major");
         reduce_sweep<row_major>("row_major");
         test_tensor_ops();
+        test_learn_step();
         exitCUDA();
     } catch (const std::exception& e) {
         std::printf("EXCEPTION: %s\n", e.what());

@@ -321,6 +321,54 @@ def test_axpby(cb):
     assert_bits_equal(xd.cpu().numpy(), np.float32(0.9) * x + np.float32(-0.01) * y)
 
 
+@pytest.mark.parametrize("n,skip", [(1, 0), (1001, 0), (4096, 0), (70001, 1), (1 << 20, 3)])
+@pytest.mark.parametrize("lr,decay", [(0.01, 0.0), (0.1, 0.05), (1.0, 0.05)])
+def test_learn_step_weight_decay(cb, n, skip, lr, decay):
+    """W = -lr*dW + (1 - lr*decay)*W, bit for bit with the host loop (tensor_ops/rprop.cu:331-346), at sizes that are
+    not a multiple of four and from pointers that are not 16-byte aligned; 1.f/0.05f is tensor_op_speed.cpp:177."""
+    import torch
+    rng = np.random.default_rng(n + skip)
+    w, g = rng.standard_normal(n + skip).astype(np.float32), rng.standard_normal(n + skip).astype(np.float32)
+    wd, gd = cb.to_device(w), cb.to_device(g)
+    cb.learn_step_weight_decay(wd[skip:], gd[skip:], lr, decay)
+    torch.cuda.synchronize()
+    ref = w.copy()
+    ho.learn_step_weight_decay(ref[skip:], g[skip:], lr, decay)
+    assert_bits_equal(wd.cpu().numpy(), ref)
+
+
+@pytest.mark.parametrize("n,skip", [(1001, 0), (70001, 1), (1 << 18, 0)])
+def test_learn_step_weight_decay_momentum(cb, n, skip):
+    """The momentum step with the device kernel's formula (tensor_ops/rprop.cu:158-170), three steps in a row."""
+    import torch
+    rng = np.random.default_rng(n)
+    w, g, m = (rng.standard_normal(n + skip).astype(np.float32) for _ in range(3))
+    wd, gd, md = cb.to_device(w), cb.to_device(g), cb.to_device(m)
+    wr, mr = w.copy(), m.copy()
+    for it in range(3):
+        cb.learn_step_weight_decay_momentum(wd[skip:], md[skip:], gd[skip:], 0.01, 0.9 - 0.1 * it, 0.002)
+        ho.learn_step_weight_decay_momentum(wr[skip:], mr[skip:], g[skip:], 0.01, 0.9 - 0.1 * it, 0.002)
+    torch.cuda.synchronize()
+    assert_bits_equal(wd.cpu().numpy(), wr)
+    assert_bits_equal(md.cpu().numpy(), mr)
+
+
+def test_learn_step_on_dia_matrix(cb):
+    """The sparse RBM's update (examples/rbm/base.py:72-73): the step over a DIA matrix's whole value array."""
+    offs = np.arange(-3, 4, dtype=np.int32)
+    W = cb.dev_dia_matrix_f(200, 200, offs)
+    G = cb.dev_dia_matrix_f(200, 200, offs)
+    rng = np.random.default_rng(5)
+    w, g = rng.standard_normal(W.vec.numel()).astype(np.float32), rng.standard_normal(W.vec.numel()).astype(np.float32)
+    W.set_vec(w); G.set_vec(g)
+    cb.learn_step_weight_decay(W, G, 0.05, 0.01)
+    ref = w.copy()
+    ho.learn_step_weight_decay(ref, g, 0.05, 0.01)
+    assert_bits_equal(W.vec.cpu().numpy(), ref)
+    with pytest.raises(cb.CuvDiaError):
+        cb.learn_step_weight_decay(W, G.vec[:-1], 0.05)
+
+
 def test_convert_and_pull(cb, golden):
     """dia_mat.cpp:111-132 / convert.cpp:110-129 on the Python mirror: host -> device -> host round trip and
     dia -> dense equal the reference fixture."""

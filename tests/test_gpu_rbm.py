@@ -134,3 +134,27 @@ def test_combined_entry_point_gives_the_bits_of_the_separate_calls(units, nd, nb
         assert_bits_equal(cb.to_host(getattr(a, name)), cb.to_host(getattr(b, name)), name)
     assert_bits_equal(a.G.vec.cpu().numpy(), b.G.vec.cpu().numpy(), "G")
     assert_bits_equal(a.bias_grad.cpu().numpy(), b.bias_grad.cpu().numpy(), "bias gradients")
+
+
+def test_update_step_applies_the_gradients():
+    """updateStep of the trainer (examples/rbm/base.py:72-75): after a step, learn_step_weight_decay on the weight
+    diagonals and both biases equals the host loop applied to the GPU's own gradients, bit for bit, and the next
+    step runs on the updated weights."""
+    import cuv_b200 as cb
+    units, nd, nb = 1024, 32, 96
+    offs = np.arange(-nd // 2, nd // 2, dtype=np.int32)
+    W, V0, U_h, U_v = rbm_oracle.make_inputs(1006, units, units, offs, nb, w_std=0.05)
+    st = run_gpu_step(cb, W, V0, U_h, U_v)
+    w0, g = st.W.vec.cpu().numpy().copy(), st.G.vec.cpu().numpy().copy()
+    c0, b0 = st.c_hid.cpu().numpy().copy(), st.b_vis.cpu().numpy().copy()
+    gc, gb = st.gc.cpu().numpy().copy(), st.gb.cpu().numpy().copy()
+    st.update(0.1, 0.002)
+    assert_bits_equal(st.W.vec.cpu().numpy(), ho.learn_step_weight_decay(w0, g, 0.1, 0.002), "W")
+    assert_bits_equal(st.c_hid.cpu().numpy(), ho.learn_step_weight_decay(c0, gc, 0.1, 0.002), "bias_hi")
+    assert_bits_equal(st.b_vis.cpu().numpy(), ho.learn_step_weight_decay(b0, gb, 0.1, 0.002), "bias_lo")
+    # second step on the updated model against the oracle's step on the same updated model (the hidden
+    # probabilities do not depend on samples, so no tie between a probability and a uniform can matter)
+    W2 = ho.DiaHost(W.h, W.w, W.offsets, W.stride, 1, st.W.vec.cpu().numpy())
+    ref = rbm_oracle.cd1_step(W2, V0, U_h, U_v, b=st.b_vis.cpu().numpy(), c=st.c_hid.cpu().numpy(), nthreads=8)
+    st.step(cb.to_device(V0), cb.to_device(U_h), cb.to_device(U_v))
+    np.testing.assert_allclose(cb.to_host(st.H0p), ref["H0p"], rtol=1e-5)

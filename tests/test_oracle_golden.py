@@ -160,3 +160,30 @@ def test_bias_sigmoid_sample():
     s = ho.bias_sigmoid_sample(a, b, u)
     np.testing.assert_allclose(a, p, rtol=1e-6)
     assert np.array_equal(s, (a > u).astype(np.float32))
+
+
+def test_learn_step_weight_decay_oracle():
+    """The update step's restatement against the formula spelled out in numpy float32, and the reference's own
+    test of it (src/tests/optimize.cpp:59-87,89-121): 1000 steps on f(W) = 2 (W - optimum)^2 reach the optimum."""
+    rng = np.random.default_rng(7)
+    w, g = rng.standard_normal(1001).astype(np.float32), rng.standard_normal(1001).astype(np.float32)
+    lr, decay = np.float32(0.1), np.float32(0.05)
+    want = (-lr) * g + (np.float32(1) - lr * decay) * w
+    got = ho.learn_step_weight_decay(w.copy(), g, 0.1, 0.05)
+    assert np.array_equal(got.view(np.uint32), want.astype(np.float32).view(np.uint32))
+    for momentum in (False, True):
+        N = 8092
+        opt, W = rng.random(N, dtype=np.float32), rng.random(N, dtype=np.float32)
+        M = np.zeros(N, dtype=np.float32)
+        for it in range(1000):
+            dW = W - opt
+            if momentum:
+                ho.learn_step_weight_decay_momentum(W, M, dW, 0.01, 1.0 - it / 1000.0, 0.0)
+            else:
+                ho.learn_step_weight_decay(W, dW, 0.01, 0.0)
+        np.testing.assert_allclose(W + 1, opt + 1, rtol=1e-4)
+    # with a decay the reference's host loop and device kernel differ in one sign; both are restated
+    w1, w2, m1, m2 = w.copy(), w.copy(), np.zeros_like(w), np.zeros_like(w)
+    ho.learn_step_weight_decay_momentum(w1, m1, g, 0.1, 0.9, 0.05, device_formula=True)
+    ho.learn_step_weight_decay_momentum(w2, m2, g, 0.1, 0.9, 0.05, device_formula=False)
+    assert np.array_equal(m1, -lr * (g + decay * w)) and np.array_equal(m2, -lr * (g - decay * w))
