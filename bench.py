@@ -14,7 +14,8 @@ CUV's host code) on all host cores on a bounded batch slice of the same workload
 
 Other cases (single routines, used for profiling and for the per-configuration table):
 ``--case prod_n|prod_t|dd2dia|reduce|glue|update`` on the band shape given by --units/--num-dia/--batch, and
-``--case cfg0|cfg1|cfg2|rbm_cfg3`` for the other BASELINE configurations.
+``--case cfg0|cfg1|cfg2|rbm_cfg3`` for the other BASELINE configurations, ``--case spmv_speed_n|spmv_speed_t`` for
+the reference's own speed fixture (a convolution-pattern matrix).
 """
 import argparse
 import json
@@ -444,6 +445,13 @@ def measure_single(args, cfg):
         # a shape where HBM, not FP32, bounds prod: 2^20 rows, 16 diagonals, 32 batch columns (3 flop/B)
         h = w = 1 << 20; nb = 32; rf = 1
         offs = band_offsets(16); op = "prod_n" if case == "membound_n" else "prod_t"
+    elif case in ("spmv_speed_n", "spmv_speed_t"):
+        # the reference's own speed fixture (src/tests/spmv_speed.cpp:50-104,155-176): a 256x256 image, 16 output
+        # maps, 8x8 filters stored as offsets i*px + j once per map, 14 images, factAv 2, factC 1.3
+        px, fs, nm = 256, 8, 16
+        h, w, nb, rf = px * px, 16 * px * px, 14, 1
+        offs = np.array([i * px + j for _ in range(nm) for i in range(fs) for j in range(fs)], dtype=np.int32)
+        op = "prod_n" if case == "spmv_speed_n" else "prod_t"
     else:
         h = w = cfg["units"]; nb = cfg["batch"]; rf = 1
         offs = band_offsets(cfg["num_dia"]); op = case
@@ -454,12 +462,14 @@ def measure_single(args, cfg):
     vec = torch.empty(h, device="cuda")
     nnz, nd = A.nnz, offs.size
     if op == "prod_n":
-        fc = 0.0
-        fn = lambda: cb.prod(X, A, Y, "n", "n", 1.0, fc, mode)
-        byts, flops = 4 * (nnz + nd + w * nb + h * nb), 2.0 * nnz * nb
+        fa, fc = (2.0, 1.3) if case.startswith("spmv_speed") else (1.0, 0.0)
+        fn = lambda: cb.prod(X, A, Y, "n", "n", fa, fc, mode)
+        # B rows the stored cells can address (all of them unless the matrix is much wider than tall)
+        b_rows = min(w, h // rf + int(offs.max()) + 1) - max(0, int(offs.min()))
+        byts, flops = 4 * (nnz + nd + b_rows * nb + h * nb * (2 if fc else 1)), 2.0 * nnz * nb
     elif op == "prod_t":
-        fc = 0.5 if case == "cfg1" else 0.0
-        fn = lambda: cb.prod(Y, A, X, "t", "n", 1.0, fc, mode)
+        fa, fc = (2.0, 1.3) if case.startswith("spmv_speed") else (1.0, 0.5 if case == "cfg1" else 0.0)
+        fn = lambda: cb.prod(Y, A, X, "t", "n", fa, fc, mode)
         byts, flops = 4 * (nnz + nd + h * nb + w * nb * (2 if fc else 1)), 2.0 * nnz * nb
     elif op == "dd2dia":
         fa, fc = (0.01, 0.9) if case == "cfg2" else (1.0 / nb, 0.0)
@@ -529,9 +539,9 @@ def measure_single(args, cfg):
         for label, nt in (("1", 1), (str(os.cpu_count()), os.cpu_count())):
             t0 = time.perf_counter()
             if op == "prod_n":
-                ho.prod(Xh, Ah, Yh, "n", 1.0, 0.0, nt)
+                ho.prod(Xh, Ah, Yh, "n", fa, fc, nt)
             elif op == "prod_t":
-                ho.prod(Yh, Ah, Xh, "t", 1.0, 0.5 if case == "cfg1" else 0.0, nt)
+                ho.prod(Yh, Ah, Xh, "t", fa, fc, nt)
             elif op == "dd2dia":
                 ho.densedense_to_dia(Ah, Xh, Yh, 0.01, 0.9, nthreads=nt)
             else:

@@ -106,18 +106,11 @@ int cuvdia_plan_create(cuvdia_plan** out, int h, int w, int num_dia, int stride,
     CUVDIA_REQUIRE(stride >= h);                        // cells are indexed by row (dia_matrix.hpp:234,242)
     CUVDIA_REQUIRE(offsets_host != nullptr);
     CUVDIA_REQUIRE((long long)num_dia * (long long)stride <= 2147483647LL);   // basics/tensor.hpp:209-213
-    std::set<int> seen;
-    for (int k = 0; k < num_dia; k++) {
-        if (!seen.insert(offsets_host[k]).second) {
-            set_last_error("offsets must be distinct (offset %d appears twice)", offsets_host[k]);
-            return CUVDIA_ERR_INVALID;
-        }
-    }
     cuvdia_plan* p = new (std::nothrow) cuvdia_plan();
     if (!p) { set_last_error("host allocation failed"); return CUVDIA_ERR_NOMEM; }
     p->h = h; p->w = w; p->nd = num_dia; p->stride = stride; p->rf = row_fact;
     p->offsets.assign(offsets_host, offsets_host + num_dia);
-    p->d_offsets = nullptr; p->scratch = nullptr; p->scratch_floats = 0; p->d_status = nullptr;
+    p->d_offsets = nullptr; p->scratch = nullptr; p->scratch_floats = 0; p->d_status = nullptr; p->d_passes = nullptr;
     p->is_band = true;
     for (int k = 1; k < num_dia; k++) if (p->offsets[k] != p->offsets[0] + k) { p->is_band = false; break; }
     p->band_lo = p->offsets[0];
@@ -130,8 +123,27 @@ int cuvdia_plan_create(cuvdia_plan** out, int h, int w, int num_dia, int stride,
         long long n = std::min((long long)h - rs, (long long)row_fact * ((long long)w - js));
         if (n > 0) p->nnz += n;
     }
+    // runs of consecutive diagonal numbers, cut into passes of at most 8
+    std::vector<int> passes;
+    for (int k = 0; k < num_dia;) {
+        int len = 1;
+        while (k + len < num_dia && p->offsets[k + len] == p->offsets[k + len - 1] + 1) len++;
+        for (int s = 0; s < len; s += 8) {
+            passes.push_back(k + s); passes.push_back(p->offsets[k] + s); passes.push_back(std::min(8, len - s));
+            passes.push_back(0);
+        }
+        k += len;
+    }
+    p->npass = (int)(passes.size() / 4);
+    p->is_runs = row_fact == 1 && num_dia >= 8 && (long long)p->npass * 4 <= num_dia;
+    p->d_passes = nullptr;
     cudaError_t e = cudaGetDevice(&p->device);
     if (e == cudaSuccess) e = cudaMalloc(&p->d_offsets, sizeof(int) * (size_t)num_dia);
+    if (e == cudaSuccess && p->is_runs) {
+        e = cudaMalloc(&p->d_passes, sizeof(int) * passes.size());
+        if (e == cudaSuccess)
+            e = cudaMemcpy(p->d_passes, passes.data(), sizeof(int) * passes.size(), cudaMemcpyHostToDevice);
+    }
     if (e == cudaSuccess)
         e = cudaMemcpy(p->d_offsets, p->offsets.data(), sizeof(int) * (size_t)num_dia, cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMalloc(&p->d_status, sizeof(int));
@@ -139,6 +151,7 @@ int cuvdia_plan_create(cuvdia_plan** out, int h, int w, int num_dia, int stride,
     if (e != cudaSuccess) {
         if (p->d_offsets) cudaFree(p->d_offsets);
         if (p->d_status) cudaFree(p->d_status);
+        if (p->d_passes) cudaFree(p->d_passes);
         delete p;
         return cuda_fail(e, "cuvdia_plan_create");
     }
@@ -151,6 +164,7 @@ int cuvdia_plan_destroy(cuvdia_plan* p) {
     if (p->d_offsets) cudaFree(p->d_offsets);
     if (p->scratch) cudaFree(p->scratch);
     if (p->d_status) cudaFree(p->d_status);
+    if (p->d_passes) cudaFree(p->d_passes);
     delete p;
     return CUVDIA_OK;
 }

@@ -70,6 +70,11 @@ struct cuvdia_plan {
     size_t scratch_floats;
     // device word set non-zero by a kernel whose bounded wait on a TMA barrier gave up
     int* d_status;
+    // the offset list cut, in storage order, into passes of up to 8 consecutive diagonal numbers:
+    // (first slot, first offset, count, 0) per pass; on the device only when the pattern is made of runs
+    bool is_runs;
+    int npass;
+    int* d_passes;
 };
 
 namespace cuvdia {
@@ -95,6 +100,9 @@ int launch_prod_band(const cuvdia_plan* p, const float* A, const float* B, int l
 bool prod_narrow_applicable(const cuvdia_plan* p, const float* A, const float* B, int ldb, int ncols);
 int launch_prod_narrow(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
                        bool trans, float factAB, float factC, int mode, cudaStream_t st);
+bool prod_runs_applicable(const cuvdia_plan* p, const float* A, const float* B, int ldb);
+int launch_prod_runs(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
+                     bool trans, float factAB, float factC, int mode, cudaStream_t st);
 bool prod_window_applicable(const cuvdia_plan* p, bool trans, int ncols);
 int launch_prod_window(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
                        bool trans, float factAB, float factC, int mode, cudaStream_t st);

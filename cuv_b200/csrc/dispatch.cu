@@ -11,6 +11,8 @@ int launch_prod(const cuvdia_plan* p, const float* A, const float* B, int ldb, f
         rc = launch_prod_narrow(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);
     else if (prod_band_applicable(p, A, B, ldb, ncols))
         rc = launch_prod_band(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);
+    else if (prod_runs_applicable(p, A, B, ldb))
+        rc = launch_prod_runs(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);
     else if (prod_window_applicable(p, trans, ncols))
         rc = launch_prod_window(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);
     else

@@ -75,7 +75,10 @@ CUVDIA_API unsigned long long cuvdia_launch_count(void);
  *             indexed by the ROW of the matrix: value(i,j) = vals[slot*stride + i], :228-243)
  * row_fact    "steepness": diagonal k holds the cells (i, i/row_fact + k)   (:81,230)
  * offsets_host  num_dia diagonal numbers in the caller's order; the order is the storage order
- *             and is never changed (basics/dia_matrix.hpp:156-185).  Must be distinct.
+ *             and is never changed (basics/dia_matrix.hpp:156-185).  A diagonal number may occur more
+ *             than once, as in CUV (its speed fixture does that, src/tests/spmv_speed.cpp:96-104): prod
+ *             sums every stored diagonal, densedense_to_dia fills every one of them, and element access
+ *             (dia_matrix.hpp:181-185,236-243) sees the last.
  * The plan is bound to the CUDA device that is current when it is created.
  * ------------------------------------------------------------------------------------------- */
 typedef struct cuvdia_plan cuvdia_plan;

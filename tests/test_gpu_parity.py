@@ -139,10 +139,115 @@ def test_prod_preconditions(cb):
         cb.prod(C, D, cb.colmajor_empty(16, 5))
     with pytest.raises(cb.CuvDiaError):
         cb.prod(B, D, C, "n")                         # heights swapped
-    with pytest.raises(cb.CuvDiaError, match="distinct"):
-        cb.dev_dia_matrix_f(8, 8, [0, 1, 1])
     with pytest.raises(cb.CuvDiaError, match="row_fact > 0"):
         cb.dev_dia_matrix_f(8, 8, [0], row_fact=0)
+
+
+@pytest.mark.parametrize("trans", ["n", "t"])
+def test_prod_with_repeated_offsets(cb, trans):
+    """A diagonal number may occur in several slots (the reference's speed fixture stores each of its fs*fs
+    offsets once per map, src/tests/spmv_speed.cpp:96-104): prod sums every stored diagonal."""
+    rng = np.random.default_rng(21)
+    px, fs, nm = 16, 3, 4
+    h, w = px * px, 2 * px * px
+    offs = np.array([i * px + j for _ in range(nm) for i in range(fs) for j in range(fs)], dtype=np.int32)
+    A = make_dia(rng, h, w, offs, 1)
+    rows_b, rows_c = (h, w) if trans == "t" else (w, h)
+    B = np.asfortranarray(rng.standard_normal((rows_b, 14)).astype(np.float32))
+    C0 = np.asfortranarray(rng.standard_normal((rows_c, 14)).astype(np.float32))
+    want = C0.copy(order="F")
+    ho.prod(want, A, B, trans, 2.0, 1.3)
+    Cd = cb.to_device(C0)
+    cb.prod(Cd, to_dev_dia(A), cb.to_device(B), trans, "n", 2.0, 1.3, cb.MODE_EXACT)
+    assert_bits_equal(cb.to_host(Cd), want, "prod %s with repeated offsets" % trans)
+
+
+def test_dd2dia_with_repeated_offsets(cb):
+    """densedense_to_dia fills every slot, repeated diagonal numbers included; element access sees the last."""
+    rng = np.random.default_rng(22)
+    offs = np.array([0, 3, 0, -2, 3], dtype=np.int32)
+    h = w = 96
+    X = np.asfortranarray(rng.standard_normal((h, 40)).astype(np.float32))
+    Y = np.asfortranarray(rng.standard_normal((w, 40)).astype(np.float32))
+    ref = ho.DiaHost(h, w, offs, h, 1)
+    ho.densedense_to_dia(ref, X, Y, 1.0, 0.0)
+    D = cb.dev_dia_matrix_f(h, w, offs)
+    D.vec.zero_()
+    cb.densedense_to_dia(D, None, cb.to_device(X), cb.to_device(Y), 1.0, 0.0)
+    got = D.vec.cpu().numpy()
+    m = ref.valid_mask().reshape(-1)
+    np.testing.assert_allclose(got[m], ref.vals[m], rtol=1e-4, atol=1e-5)
+    assert np.array_equal(got[:h], got[2 * h:3 * h]) and D(5, 5) == got[2 * h + 5]
+
+
+def dev_padded(cb, M):
+    """Device copy of a column-major host matrix whose leading dimension is rounded up to a multiple of four (the
+    padding rows hold NaN), as a view of its real rows: the 16-byte column alignment the vector kernels want."""
+    rows, cols = M.shape
+    buf = cb.colmajor_empty(rows + (4 - rows % 4) % 4, cols)
+    buf.fill_(float("nan"))
+    buf[:rows].copy_(cb.to_device(M))
+    return buf[:rows]
+
+
+def conv_offsets(px, py, fs, maps_in, maps_out):
+    """Diagonal numbers of a convolution matrix as basics/filter_factory.hpp:58-76 builds them: per map block a run
+    of fs diagonals per filter row, the next filter row one image line further, centred on the filter's middle."""
+    offs = [i * px + j + m * px * py for m in range(maps_out + maps_in - 1) for i in range(fs) for j in range(fs)]
+    return np.array(offs, dtype=np.int32) - (px + 1) * (fs // 2) - (maps_in - 1) * px * py
+
+
+@pytest.mark.parametrize("trans", ["n", "t"])
+@pytest.mark.parametrize("px,fs,mi,mo,ncols,fab,fc", [
+    (16, 8, 1, 1, 14, 2.0, 1.3),        # one map, full passes of 8
+    (16, 8, 1, 3, 14, 1.0, 0.0),        # three output maps: the matrix is three images wide
+    (17, 5, 1, 2, 16, 0.5, 0.0),        # odd line length: every run has another alignment; runs shorter than a pass
+    (12, 11, 2, 2, 33, 1.0, -1.0),      # runs of 11 = 8 + 3, two input maps (negative offsets), three column groups
+    (20, 4, 1, 1, 1, 1.0, 0.0),         # spmv
+])
+def test_prod_convolution_pattern(cb, trans, px, fs, mi, mo, ncols, fab, fc):
+    """Diagonals in runs (a convolution written as a DIA matrix) take the run-walking kernel; bit-exact against the
+    host loop in EXACT mode, and within rounding of it in FAST mode."""
+    rng = np.random.default_rng(px * 100 + fs)
+    h, w = px * px * mi, px * px * mo
+    offs = conv_offsets(px, px, fs, mi, mo)
+    A = make_dia(rng, h, w, offs, 1)
+    assert to_dev_dia(A).nnz > 0
+    rows_b, rows_c = (h, w) if trans == "t" else (w, h)
+    B = np.asfortranarray(rng.standard_normal((rows_b, ncols)).astype(np.float32))
+    C0 = np.asfortranarray(rng.standard_normal((rows_c, ncols)).astype(np.float32))
+    if fc == 0.0:
+        C0[:] = np.nan                                 # factC == 0 must not read C
+    want = C0.copy(order="F")
+    ho.prod(want, A, B, trans, fab, fc)
+    D = to_dev_dia(A)
+    Cd = cb.to_device(C0)
+    cb.prod(Cd, D, dev_padded(cb, B), trans, "n", fab, fc, cb.MODE_EXACT)
+    assert_bits_equal(cb.to_host(Cd), want, "conv-pattern prod %s" % trans)
+    Cd = cb.to_device(C0)
+    cb.prod(Cd, D, dev_padded(cb, B), trans, "n", fab, fc, cb.MODE_FAST)
+    scale = np.zeros_like(want)
+    ho.prod(scale, ho.DiaHost(A.h, A.w, A.offsets, A.stride, 1, np.abs(np.nan_to_num(A.vals))), np.abs(B), trans, abs(fab), 0.0)
+    assert np.all(np.abs(cb.to_host(Cd) - want) <= 1e-5 * (scale + np.abs(np.nan_to_num(C0) * fc)) + 1e-30)
+
+
+@pytest.mark.parametrize("trans", ["n", "t"])
+def test_prod_runs_ragged_and_repeated(cb, trans):
+    """Runs on a matrix whose sizes are not multiples of four, wider than tall, with one run stored twice and a
+    single stray diagonal between runs."""
+    rng = np.random.default_rng(77)
+    h, w = 203, 517
+    offs = np.concatenate([np.arange(-9, -1), np.arange(40, 52), [300], np.arange(40, 48), np.arange(100, 109),
+                           np.arange(-203, -195), np.arange(509, 517)]).astype(np.int32)
+    A = make_dia(rng, h, w, offs, 1, stride=208)
+    rows_b, rows_c = (h, w) if trans == "t" else (w, h)
+    B = np.asfortranarray(rng.standard_normal((rows_b, 19)).astype(np.float32))
+    C0 = np.asfortranarray(rng.standard_normal((rows_c, 19)).astype(np.float32))
+    want = C0.copy(order="F")
+    ho.prod(want, A, B, trans, 1.5, 0.25)
+    Cd = cb.to_device(C0)
+    cb.prod(Cd, to_dev_dia(A), dev_padded(cb, B), trans, "n", 1.5, 0.25, cb.MODE_EXACT)
+    assert_bits_equal(cb.to_host(Cd), want, "runs, ragged %s" % trans)
 
 
 # ---- densedense_to_dia -------------------------------------------------------------------------------
