@@ -98,6 +98,8 @@ bool prod_band_applicable(const cuvdia_plan* p, const float* A, const float* B, 
 int launch_prod_band(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
                      bool trans, float factAB, float factC, int mode, cudaStream_t st);
 bool prod_narrow_applicable(const cuvdia_plan* p, const float* A, const float* B, int ldb, int ncols);
+// true if launch_prod_narrow would take its TMA streaming variant (at most 16 diagonals, many rows)
+bool prod_narrow_streams(const cuvdia_plan* p, bool trans);
 int launch_prod_narrow(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
                        bool trans, float factAB, float factC, int mode, cudaStream_t st);
 bool prod_runs_applicable(const cuvdia_plan* p, const float* A, const float* B, int ldb);

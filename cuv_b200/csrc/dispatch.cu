@@ -7,11 +7,14 @@ namespace cuvdia {
 int launch_prod(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
                 bool trans, float factAB, float factC, int mode, const ProdEpilogue* ep, cudaStream_t st) {
     int rc;
-    if (prod_narrow_applicable(p, A, B, ldb, ncols))
+    // few diagonals or few columns: the streaming kernel if the band has at most 16 diagonals; wider bands are
+    // better served by the run-walking kernel (TMA ring) than by the per-thread loads of the narrow kernel
+    const bool runs = prod_runs_applicable(p, A, B, ldb);
+    if (prod_narrow_applicable(p, A, B, ldb, ncols) && (prod_narrow_streams(p, trans) || !runs))
         rc = launch_prod_narrow(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);
     else if (prod_band_applicable(p, A, B, ldb, ncols))
         rc = launch_prod_band(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);
-    else if (prod_runs_applicable(p, A, B, ldb))
+    else if (runs)
         rc = launch_prod_runs(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);
     else if (prod_window_applicable(p, trans, ncols))
         rc = launch_prod_window(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);

@@ -382,13 +382,13 @@ static int launch_stream_t(const cuvdia_plan* p, const float* A, const float* B,
 }
 
 // The streaming variant needs the whole band in one pass and enough rows to fill the GPU.
-static bool stream_applicable(const cuvdia_plan* p, bool trans) {
+bool prod_narrow_streams(const cuvdia_plan* p, bool trans) {
     return p->nd <= pn::KD && (trans ? p->w : p->h) >= 64 * ps::TR;
 }
 
 int launch_prod_narrow(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
                        bool trans, float fa, float fc, int mode, cudaStream_t st) {
-    if (stream_applicable(p, trans)) {
+    if (prod_narrow_streams(p, trans)) {
         const bool ex = mode == CUVDIA_MODE_EXACT;
         if (trans) return ex ? launch_stream_t<true, true>(p, A, B, ldb, C, ldc, ncols, fa, fc, st)
                              : launch_stream_t<true, false>(p, A, B, ldb, C, ldc, ncols, fa, fc, st);

@@ -11,9 +11,10 @@
 // (used once, from HBM) and another window of the dense operand (from L2): per-thread loads cannot
 // keep enough of them in flight.  So one producer thread streams both through a four-stage ring in
 // shared memory with TMA tile loads (cp.async.bulk.tensor, no multicast; rows or diagonals outside
-// the operands arrive as zeros) and full/empty mbarriers with bounded waits, two blocks per SM, while
-// 64 consumer threads compute: a thread owns 4 rows, reads the 8 x 4 coefficients of the pass and,
-// per column, the 11 dense rows its 4 x 8 cells touch as four aligned 128-bit shared loads into a
+// the operands arrive as zeros) and full/empty mbarriers with bounded waits, two blocks per SM, and
+// asks for the coefficient tiles a dozen passes ahead to be brought into L2 (tensor prefetch), while
+// 128 consumer threads compute: a thread owns 4 rows and 8 of the columns, reads the 8 x 4 coefficients
+// of the pass and, per column, the 11 dense rows its 4 x 8 cells touch as four aligned 128-bit shared loads into a
 // register window (cell (row j, diagonal k) reads entry L + j + k, L = alignment of the run's first
 // offset, a template parameter so that the index is a compile-time constant), then issues 32
 // multiply-adds.  Passes that touch the border of the matrix, or are shorter than 8, zero the
@@ -30,11 +31,13 @@ namespace cuvdia {
 int make_map_2d(CUtensorMap* m, const float* base, long long dim0, long long dim1, long long pitch, int box0, int box1);
 
 namespace pr {
-constexpr int CONSUMERS = 64;
-constexpr int THREADS = CONSUMERS + 32;     // two consumer warps and the producer's warp
-constexpr int TR = 4 * CONSUMERS;           // output rows per block
+constexpr int ROWTHREADS = 64;              // threads along the rows; each owns 4 consecutive rows
+constexpr int CONSUMERS = 2 * ROWTHREADS;   // two halves of the block's columns
+constexpr int THREADS = CONSUMERS + 32;     // four consumer warps and the producer's warp
+constexpr int TR = 4 * ROWTHREADS;          // output rows per block
 constexpr int KD = 8;                       // diagonals per pass
 constexpr int CG = 16;                      // batch columns per block
+constexpr int CT = CG / 2;                  // batch columns per thread
 constexpr int NW = 4;                       // 128-bit loads per column: 16 window entries >= 3 + 4 + 7
 constexpr int BOXR = 136;                   // rows per TMA box of a window of TR + 16 rows (two boxes)
 constexpr int NS = 4;                       // ring stages
@@ -42,6 +45,7 @@ constexpr int A_FLOATS = 2 * KD * BOXR;
 constexpr int B_FLOATS = 2 * CG * BOXR;
 constexpr int STAGE_FLOATS = A_FLOATS + B_FLOATS;
 constexpr size_t SMEM = sizeof(float) * NS * STAGE_FLOATS + 2 * NS * sizeof(unsigned long long);
+constexpr int AHEAD = 12;                   // passes between the L2 prefetch of a coefficient tile and its load
 constexpr unsigned SPIN_LIMIT = 1u << 26;
 template <bool TRANS> __host__ __device__ constexpr int abox() { return TRANS ? BOXR : TR / 2; }
 template <bool TRANS> __host__ __device__ constexpr unsigned stage_bytes() {
@@ -59,6 +63,14 @@ struct RunsParams {
 };
 
 __device__ __forceinline__ unsigned r_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+// A pass descriptor, read-only path.  Volatile so that the load stays where it is written - at the top of an
+// iteration, a whole pass before its value is needed - instead of sinking to its first use.
+__device__ __forceinline__ int4 ld_desc(const int4* p) {
+    int4 v;
+    asm volatile("ld.global.nc.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
 
 // bounded wait on an mbarrier phase; false if it gave up
 __device__ __forceinline__ bool r_wait(unsigned long long* bar, unsigned parity) {
@@ -80,7 +92,7 @@ __device__ __forceinline__ bool r_wait(unsigned long long* bar, unsigned parity)
 //      start at offset (RA - k) mod 4 of an aligned 8-vector, RA = (-lo) mod 4.
 template <bool TRANS, bool EXACT, int L, bool INTERIOR>
 __device__ __forceinline__ void runs_pass(const float* __restrict__ As, const float* __restrict__ Bs,
-                                          float (&acc)[pr::CG][4], const int (&hoff)[pr::NW], int tid, int nc,
+                                          float (&acc)[pr::CT][4], const int (&hoff)[pr::NW], int tid, int nc,
                                           const RunsParams& P, int i0, int lo, int cnt) {
     using namespace pr;
     constexpr int RA = (4 - L) % 4;
@@ -114,22 +126,32 @@ __device__ __forceinline__ void runs_pass(const float* __restrict__ As, const fl
             if (P.fa != 1.f) a[k][j] = __fmul_rn(P.fa, a[k][j]);
         }
     }
+    // entries the cells use: 'n' L .. L+10, 't' RT .. RT+10; the last 128-bit load is needed only beyond 12
+    constexpr int NWL = ((TRANS ? RT : L) + 11 + 3) / 4;
+    // Two columns at a time: eight independent accumulation chains.  A pair is computed if its first column
+    // exists; a second column past the batch reads the zeros TMA wrote there and its sums are never stored.
 #pragma unroll
-    for (int c = 0; c < CG; c++) {
+    for (int c = 0; c < CT; c += 2) {
         if (c < nc) {
-            float wv[4 * NW];
+            float wv[2][4 * NW];
 #pragma unroll
-            for (int v = 0; v < NW; v++) {
-                const float4 x = *reinterpret_cast<const float4*>(Bs + hoff[v] + c * BOXR);
-                wv[4 * v] = x.x; wv[4 * v + 1] = x.y; wv[4 * v + 2] = x.z; wv[4 * v + 3] = x.w;
-            }
+            for (int cc = 0; cc < 2; cc++)
+#pragma unroll
+                for (int v = 0; v < NWL; v++) {
+                    const float4 x = *reinterpret_cast<const float4*>(Bs + hoff[v] + (c + cc) * BOXR);
+                    wv[cc][4 * v] = x.x; wv[cc][4 * v + 1] = x.y; wv[cc][4 * v + 2] = x.z; wv[cc][4 * v + 3] = x.w;
+                }
 #pragma unroll
             for (int k = 0; k < KD; k++) {
                 if (INTERIOR || k < cnt) {
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
-                        const float x = TRANS ? wv[(KD - 1) + RT + j - k] : wv[L + j + k];
-                        acc[c][j] = EXACT ? __fadd_rn(acc[c][j], __fmul_rn(a[k][j], x)) : fmaf(a[k][j], x, acc[c][j]);
+#pragma unroll
+                        for (int cc = 0; cc < 2; cc++) {
+                            const float x = wv[cc][TRANS ? (KD - 1) + RT + j - k : L + j + k];
+                            acc[c + cc][j] = EXACT ? __fadd_rn(acc[c + cc][j], __fmul_rn(a[k][j], x))
+                                                   : fmaf(a[k][j], x, acc[c + cc][j]);
+                        }
                     }
                 }
             }
@@ -151,12 +173,11 @@ prod_runs_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
     const int cgi = blockIdx.x % ngroups;                 // column groups of one row block are neighbours in launch
     const int rb = blockIdx.x / ngroups;                  // order, so they find its coefficients in L2
     const int c0 = cgi * CG;
-    const int nc = min(CG, P.ncols - c0);
     const int o0 = rb * TR;
     if (tid == 0) {
         for (int s = 0; s < NS; s++) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(r_u32(full + s)));
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 2;" ::"r"(r_u32(empty + s)));     // one arrival per consumer warp
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;" ::"r"(r_u32(empty + s)));     // one arrival per consumer warp
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -173,10 +194,25 @@ prod_runs_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
     if (tid >= CONSUMERS) {
         // ---- producer: one thread feeds the ring ----
         if (tid != CONSUMERS || !reachable) return;
+        // The coefficients come from HBM, and four stages do not cover that latency: ask for the tiles of a
+        // later pass to be brought into L2 now, so that the ring's loads find them there.
+        auto prefetch_A = [&](int p) {
+            const int4 e = __ldg(P.passes + p);
+            if (!touches(e.y, e.z)) return;
+            const int Lp = ((e.y % 4) + 4) % 4;
+            const int RTp = (((4 - Lp) % 4) + 1) % 4;
+            const int x0 = TRANS ? (o0 - e.y - (KD - 1) - RTp) : o0;
+#pragma unroll
+            for (int b = 0; b < 2; b++)
+                asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+                             ::"l"(&mapA), "r"(x0 + b * abox<TRANS>()), "r"(e.x) : "memory");
+        };
+        for (int p = NS; p < min(AHEAD, P.npass); p++) prefetch_A(p);
         int n = 0;
         for (int p = 0; p < P.npass; p++) {
             const int4 d = __ldg(P.passes + p);
             const int slot0 = d.x, lo = d.y, cnt = d.z;
+            if (p + AHEAD < P.npass) prefetch_A(p + AHEAD);
             if (!touches(lo, cnt)) continue;
             const int s = n % NS;
             if (n >= NS && !r_wait(empty + s, ((n / NS) - 1) & 1)) { if (P.status) *P.status = 5; break; }
@@ -205,28 +241,32 @@ prod_runs_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         return;
     }
 
-    // ---- consumers ----
-    const int i0 = o0 + 4 * tid;
-    float acc[CG][4];
+    // ---- consumers: row thread rt owns rows 4*rt.., column half ch the columns 8*ch.. of the block's 16 ----
+    const int rt = tid % ROWTHREADS, ch = tid / ROWTHREADS;
+    const int i0 = o0 + 4 * rt;
+    const int cb = c0 + ch * CT;                           // first column of this thread
+    const int ncl = max(0, min(CT, P.ncols - cb));         // columns of this thread that exist
+    float acc[CT][4];
 #pragma unroll
-    for (int c = 0; c < CG; c++)
+    for (int c = 0; c < CT; c++)
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             acc[c][j] = 0.f;
-            if (P.fc != 0.f && c < nc && i0 + j < rows_out)
-                acc[c][j] = __fmul_rn(P.C[(size_t)(c0 + c) * P.ldc + i0 + j], P.fc);
+            if (P.fc != 0.f && c < ncl && i0 + j < rows_out)
+                acc[c][j] = __fmul_rn(P.C[(size_t)(cb + c) * P.ldc + i0 + j], P.fc);
         }
     int hoff[NW];
 #pragma unroll
     for (int v = 0; v < NW; v++) {
-        const int r = 4 * tid + 4 * v, b = r >= BOXR ? 1 : 0;
-        hoff[v] = b * CG * BOXR + (r - b * BOXR);
+        const int r = 4 * rt + 4 * v, b = r >= BOXR ? 1 : 0;
+        hoff[v] = (b * CG + ch * CT) * BOXR + (r - b * BOXR);
     }
     if (reachable) {
         int n = 0;
+        int4 d = ld_desc(P.passes);
         for (int p = 0; p < P.npass; p++) {
-            const int4 d = __ldg(P.passes + p);
             const int lo = d.y, cnt = d.z;
+            if (p + 1 < P.npass) d = ld_desc(P.passes + p + 1);        // the next descriptor is in flight during this pass
             if (!touches(lo, cnt)) continue;
             const int s = n % NS;
             if (!r_wait(full + s, (n / NS) & 1)) { if (P.status) *P.status = 6; return; }
@@ -239,8 +279,8 @@ prod_runs_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
                                          : (o0 + lo >= 0 && o0 + TR - 1 + lo + (KD - 1) < P.w));
 #define RUNS_GO(LV)                                                                                        \
             do {                                                                                           \
-                if (interior) runs_pass<TRANS, EXACT, LV, true>(As, Bs, acc, hoff, tid, nc, P, i0, lo, cnt);    \
-                else runs_pass<TRANS, EXACT, LV, false>(As, Bs, acc, hoff, tid, nc, P, i0, lo, cnt);           \
+                if (interior) runs_pass<TRANS, EXACT, LV, true>(As, Bs, acc, hoff, rt, ncl, P, i0, lo, cnt);    \
+                else runs_pass<TRANS, EXACT, LV, false>(As, Bs, acc, hoff, rt, ncl, P, i0, lo, cnt);           \
             } while (0)
             switch (L) { case 0: RUNS_GO(0); break; case 1: RUNS_GO(1); break; case 2: RUNS_GO(2); break; default: RUNS_GO(3); break; }
 #undef RUNS_GO
@@ -253,9 +293,9 @@ prod_runs_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
     if (i0 >= rows_out) return;
     const bool vec_c = i0 + 4 <= rows_out && (P.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(P.C) & 15) == 0;
 #pragma unroll
-    for (int c = 0; c < CG; c++) {
-        if (c >= nc) continue;
-        float* cp = P.C + (size_t)(c0 + c) * P.ldc + i0;
+    for (int c = 0; c < CT; c++) {
+        if (c >= ncl) continue;
+        float* cp = P.C + (size_t)(cb + c) * P.ldc + i0;
         if (vec_c) {
             *reinterpret_cast<float4*>(cp) = make_float4(acc[c][0], acc[c][1], acc[c][2], acc[c][3]);
         } else {
