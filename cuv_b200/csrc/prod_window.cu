@@ -29,6 +29,7 @@ struct WindowParams {
     int off_min, off_max;
     int wq;                 // positions per de-interleaved plane ('t'): window rows / rf; 'n': window rows
     int pitch;              // words per column in shared memory
+    int tiles;              // row tiles of T outputs a block works through with one staged window
     float fa, fc;
     const float* A; const int* offs; const float* B; float* C;
 };
@@ -39,7 +40,7 @@ prod_window_kernel(const WindowParams P) {
     extern __shared__ __align__(16) float win[];        // [CB][pitch]
     __shared__ int s_off[pw::OFFS];
     const int tid = threadIdx.x;
-    const int o0 = blockIdx.x * T;                      // first output row of the block
+    const int o0 = blockIdx.x * T * P.tiles;            // first output row of the block
     const int c0 = blockIdx.y * CB;
     const int rf = P.rf;
     // first B row of the window (a multiple of rf for 't', so groups of rf rows stay together)
@@ -65,8 +66,11 @@ prod_window_kernel(const WindowParams P) {
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group 0;" ::: "memory");
-    const int o = o0 + tid;
     const int rows_out = TRANS ? P.w : P.h;
+    // When the offsets span far more rows than a tile has, the window is nearly the same for neighbouring
+    // tiles: the block stages it once and works through several tiles.
+    for (int rt = 0; rt < P.tiles; rt++) {
+    const int o = o0 + rt * T + tid;
     const bool row_ok = o < rows_out;
     float acc[CB];
 #pragma unroll
@@ -81,14 +85,15 @@ prod_window_kernel(const WindowParams P) {
         for (int t = tid; t < kn; t += T) s_off[t] = P.offs[kb + t];
         __syncthreads();
         if (!TRANS) {
-            // term of diagonal k: A[k][o] * B[o/rf + off_k].  The coefficients of the next four diagonals are
-            // fetched while the current four are consumed.
-            float a[4], an[4];
-            int pos[4], posn[4];
-            bool ok[4], okn[4];
-            auto fetch = [&](int kk, float (&av)[4], int (&pv)[4], bool (&ov)[4]) {
+            // term of diagonal k: A[k][o] * B[o/rf + off_k].  The coefficients of the next eight diagonals are
+            // fetched while the current eight are consumed.
+            constexpr int U = 8;
+            float a[U], an[U];
+            int pos[U], posn[U];
+            bool ok[U], okn[U];
+            auto fetch = [&](int kk, float (&av)[U], int (&pv)[U], bool (&ov)[U]) {
 #pragma unroll
-                for (int u = 0; u < 4; u++) {
+                for (int u = 0; u < U; u++) {
                     const int k = kk + u;
                     const int j = oq + (k < kn ? s_off[k] : 0);
                     ov[u] = row_ok && k < kn && j >= 0 && j < P.w;          // spmv.cu:185-189
@@ -97,12 +102,12 @@ prod_window_kernel(const WindowParams P) {
                 }
             };
             fetch(0, an, posn, okn);
-            for (int kk = 0; kk < kn; kk += 4) {
+            for (int kk = 0; kk < kn; kk += U) {
 #pragma unroll
-                for (int u = 0; u < 4; u++) { a[u] = an[u]; pos[u] = posn[u]; ok[u] = okn[u]; }
-                if (kk + 4 < kn) fetch(kk + 4, an, posn, okn);
+                for (int u = 0; u < U; u++) { a[u] = an[u]; pos[u] = posn[u]; ok[u] = okn[u]; }
+                if (kk + U < kn) fetch(kk + U, an, posn, okn);
 #pragma unroll
-                for (int u = 0; u < 4; u++) {
+                for (int u = 0; u < U; u++) {
                     if (!ok[u]) continue;
                     const float av = (P.fa != 1.f) ? __fmul_rn(P.fa, a[u]) : a[u];
 #pragma unroll
@@ -170,26 +175,34 @@ prod_window_kernel(const WindowParams P) {
         for (int c = 0; c < CB; c++)
             if (c0 + c < P.ncols) P.C[(size_t)(c0 + c) * P.ldc + o] = acc[c];
     }
+    }   // row tiles
 }
 
-// Window rows (per plane for 't') a block of T outputs needs, or -1 if it cannot fit with CB columns.
-static long long window_q(const cuvdia_plan* p, bool trans, int T) {
+// Window rows (per plane for 't') a block of R outputs needs.
+static long long window_q(const cuvdia_plan* p, bool trans, int R) {
     const long long span = (long long)p->off_max - p->off_min;
-    return trans ? (long long)T + span : ((long long)T - 1) / p->rf + 1 + span + 1;
+    return trans ? (long long)R + span : ((long long)R - 1) / p->rf + 1 + span + 1;
+}
+
+// rows of the staged window for a block of R outputs: never more than the operand has (whole groups for 't')
+static long long window_rows(const cuvdia_plan* p, bool trans, int R, long long* wq_out) {
+    long long wq = window_q(p, trans, R);
+    const long long cap = trans ? ((long long)p->h + p->rf - 1) / p->rf : p->w;
+    wq = std::min(wq, cap);
+    if (wq_out) *wq_out = wq;
+    return trans ? wq * p->rf : wq;
 }
 
 template <bool TRANS, bool EXACT, int T, int CB>
 static int launch_window_t(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
-                           float fa, float fc, cudaStream_t st) {
+                           float fa, float fc, int tiles, cudaStream_t st) {
     WindowParams P;
     P.h = p->h; P.w = p->w; P.nd = p->nd; P.S = p->stride; P.rf = p->rf;
     P.ldb = ldb; P.ldc = ldc; P.ncols = ncols; P.off_min = p->off_min; P.off_max = p->off_max;
-    long long wq = window_q(p, TRANS, T);
-    // never more rows than the operand has (rounded up to whole groups for 't')
-    const long long cap = TRANS ? ((long long)p->h + p->rf - 1) / p->rf : p->w;
-    wq = std::min(wq, cap);
+    long long wq = 0;
+    const long long wrows = window_rows(p, TRANS, T * tiles, &wq);
     P.wq = (int)wq;
-    const long long wrows = TRANS ? wq * p->rf : wq;
+    P.tiles = tiles;
     P.pitch = (int)(wrows | 1);                          // odd pitch: columns start in different banks
     P.fa = fa; P.fc = fc; P.A = A; P.offs = p->d_offsets; P.B = B; P.C = C;
     const size_t smem = sizeof(float) * (size_t)P.pitch * CB;
@@ -197,43 +210,64 @@ static int launch_window_t(const cuvdia_plan* p, const float* A, const float* B,
     const int arc = allow_dynamic_smem(prod_window_kernel<TRANS, EXACT, T, CB>, pw::SMEM_LIMIT, attr_done);
     if (arc) return arc;
     const int rows_out = TRANS ? p->w : p->h;
-    const int gx = (rows_out + T - 1) / T, gy = (ncols + CB - 1) / CB;
+    const int gx = (rows_out + T * tiles - 1) / (T * tiles), gy = (ncols + CB - 1) / CB;
     if (gy > 65535) { set_last_error("too many batch columns"); return CUVDIA_ERR_UNSUPPORTED; }
     prod_window_kernel<TRANS, EXACT, T, CB><<<dim3(gx, gy), T, smem, st>>>(P);
     count_launch();
     return check_launch("prod_window_kernel");
 }
 
-// Picks (T, CB) so that the window fits in shared memory; returns false if nothing fits.
-static bool window_config(const cuvdia_plan* p, bool trans, int ncols, int* T, int* CB) {
-    // first choice: a configuration whose window leaves room for two blocks per SM; else the largest that fits
+// Picks (T, CB, row tiles per block) by a small cost model in shared-memory wavefronts: a block pays for staging
+// its window (twice the copy's wavefronts, for the latency of the fetch) and one wavefront per term, column and
+// warp; the blocks of the grid are spread over the SMs.  Returns false if no window fits.
+static bool window_config(const cuvdia_plan* p, bool trans, int ncols, int* T, int* CB, int* tiles) {
     const int cands[4][2] = {{256, 16}, {256, 8}, {128, 8}, {128, 4}};
-    for (int pass = 0; pass < 2; pass++) {
-        // (only for the transposed product: there the coefficient loads are strided and need the extra warps)
+    const long long rows_out = trans ? p->w : p->h;
+    const long long terms = (long long)p->nd * (trans ? p->rf : 1);        // terms per output row
+    const int sms = std::max(1, sm_count());
+    double best = -1.0;
+    // the transposed product reads its coefficients with a stride and wants two blocks per SM to hide that: first
+    // look among the windows that leave room for two, then among all that fit
+    for (int pass = 0; pass < 2 && best < 0; pass++) {
         const size_t limit = (pass == 0 && trans) ? (size_t)100 * 1024 : pw::SMEM_LIMIT;
         for (auto& c : cands) {
             if (c[1] > 8 && ncols < 64) continue;
-            long long wq = window_q(p, trans, c[0]);
-            const long long cap = trans ? ((long long)p->h + p->rf - 1) / p->rf : p->w;
-            wq = std::min(wq, cap);
-            const long long wrows = trans ? wq * p->rf : wq;
-            if ((size_t)(wrows | 1) * c[1] * sizeof(float) <= limit) { *T = c[0]; *CB = c[1]; return true; }
+            for (int nt = 1; nt <= 8; nt *= 2) {
+                if (nt > 1 && (long long)c[0] * nt > rows_out) break;
+                const long long wrows = window_rows(p, trans, c[0] * nt, nullptr);
+                if ((size_t)(wrows | 1) * c[1] * sizeof(float) > limit) continue;
+                const size_t smem = (size_t)(wrows | 1) * c[1] * sizeof(float);
+                const long long blocks = ((rows_out + (long long)c[0] * nt - 1) / ((long long)c[0] * nt)) *
+                                         ((ncols + c[1] - 1) / c[1]);
+                // blocks that share an SM (shared memory, 2048 threads), and the rounds the grid needs on them
+                const long long bps = std::max<long long>(1, std::min<long long>((size_t)227 * 1024 / (smem + 1024), 2048 / c[0]));
+                const long long rounds = (blocks + (long long)sms * bps - 1) / ((long long)sms * bps);
+                // throughput: staging (twice the copy's wavefronts), one shared-memory wavefront per term, column and
+                // warp, two for the coefficient load of every term and warp
+                const double per_block = (double)wrows * c[1] / 16.0 + (double)nt * terms * (c[1] + 2) * (c[0] / 32);
+                const double throughput = (double)((blocks + sms - 1) / sms) * per_block;
+                // latency: a thread walks its terms four at a time, each group waits for its coefficients (~400 cycles; groups of eight for 'n'),
+                // and a round starts with the fetch of its window (~2000 cycles)
+                const double latency = (double)rounds * (2000.0 + (double)nt * (double)terms / (trans ? 4.0 : 8.0) * 400.0);
+                const double cost = std::max(throughput, latency);
+                if (best < 0 || cost < best * 0.999) { best = cost; *T = c[0]; *CB = c[1]; *tiles = nt; }
+            }
         }
     }
-    return false;
+    return best >= 0;
 }
 
 bool prod_window_applicable(const cuvdia_plan* p, bool trans, int ncols) {
-    int T, CB;
-    return window_config(p, trans, ncols, &T, &CB);
+    int T, CB, tiles;
+    return window_config(p, trans, ncols, &T, &CB, &tiles);
 }
 
 int launch_prod_window(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
                        bool trans, float fa, float fc, int mode, cudaStream_t st) {
-    int T = 0, CB = 0;
-    if (!window_config(p, trans, ncols, &T, &CB)) { set_last_error("window does not fit"); return CUVDIA_ERR_UNSUPPORTED; }
+    int T = 0, CB = 0, tiles = 1;
+    if (!window_config(p, trans, ncols, &T, &CB, &tiles)) { set_last_error("window does not fit"); return CUVDIA_ERR_UNSUPPORTED; }
     const bool exact = mode == CUVDIA_MODE_EXACT;
-#define GO(TR, EX, TT, CC) return launch_window_t<TR, EX, TT, CC>(p, A, B, ldb, C, ldc, ncols, fa, fc, st)
+#define GO(TR, EX, TT, CC) return launch_window_t<TR, EX, TT, CC>(p, A, B, ldb, C, ldc, ncols, fa, fc, tiles, st)
 #define PICK(TR, EX)                                    \
     if (T == 256 && CB == 16) GO(TR, EX, 256, 16);      \
     if (T == 256 && CB == 8) GO(TR, EX, 256, 8);        \
