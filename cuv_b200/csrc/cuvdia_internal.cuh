@@ -75,6 +75,10 @@ struct cuvdia_plan {
     bool is_runs;
     int npass;
     int* d_passes;
+    // the diagonals in ascending order of their offsets: nd storage slots followed by nd offsets (device), and the
+    // largest number of dense rows that 16 ([0]) and 32 ([1]) neighbours in that order span
+    int* d_sorted;
+    int group_window_max[2];
 };
 
 namespace cuvdia {
@@ -111,6 +115,9 @@ int launch_prod_window(const cuvdia_plan* p, const float* A, const float* B, int
 bool dd2dia_stream_applicable(const cuvdia_plan* p, const float* Cv, const float* A, int lda, const float* B, int ldb,
                               int ncols);
 int launch_dd2dia_stream(cuvdia_plan* p, float* Cv, const float* A, int lda, const float* B, int ldb, int ncols,
+                         float factAB, float factC, cudaStream_t st);
+bool dd2dia_window_applicable(const cuvdia_plan* p, const float* A, int lda, const float* B, int ldb, int ncols);
+int launch_dd2dia_window(cuvdia_plan* p, float* Cv, const float* A, int lda, const float* B, int ldb, int ncols,
                          float factAB, float factC, cudaStream_t st);
 bool dd2dia_band_applicable(const cuvdia_plan* p, const float* A, int lda, const float* B, int ldb, int ncols);
 int launch_dd2dia_band(cuvdia_plan* p, float* Cv, const float* A, int lda, const float* B, int ldb, int ncols,

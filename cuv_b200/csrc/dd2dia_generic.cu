@@ -105,6 +105,15 @@ int ensure_plan_scratch(cuvdia_plan* p, size_t floats, cudaStream_t st) {
     return CUVDIA_OK;
 }
 
+int launch_dd2dia_combine(const cuvdia_plan* p, float* Cv, float fa, float fc, int nsplit, const float* partial,
+                          cudaStream_t st) {
+    dim3 g2((p->h + 255) / 256, std::min(p->nd, 65535));
+    dd2dia_combine_kernel<<<g2, 256, 0, st>>>(Cv, p->d_offsets, p->nd, p->h, p->w, p->stride, p->rf, fa, fc, nsplit,
+                                              partial);
+    count_launch();
+    return check_launch("dd2dia_combine_kernel");
+}
+
 int launch_dd2dia_generic(cuvdia_plan* p, float* Cv, const float* A, int lda, const float* B, int ldb, int ncols,
                           float fa, float fc, cudaStream_t st) {
     constexpr int KD = 8;
@@ -127,13 +136,7 @@ int launch_dd2dia_generic(cuvdia_plan* p, float* Cv, const float* A, int lda, co
     count_launch();
     int rc = check_launch("dd2dia_generic_kernel");
     if (rc) return rc;
-    if (nsplit > 1) {
-        dim3 g2((p->h + 255) / 256, std::min(p->nd, 65535));
-        dd2dia_combine_kernel<<<g2, 256, 0, st>>>(Cv, p->d_offsets, p->nd, p->h, p->w, p->stride, p->rf, fa, fc,
-                                                  nsplit, partial);
-        count_launch();
-        rc = check_launch("dd2dia_combine_kernel");
-    }
+    if (nsplit > 1) rc = launch_dd2dia_combine(p, Cv, fa, fc, nsplit, partial, st);
     return rc;
 }
 

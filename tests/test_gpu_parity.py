@@ -277,6 +277,20 @@ def dd_case(cb, rng, h, w, offsets, rf, ncols, fab, fc, stride=None, dist="rbm")
     assert_bits_equal(D2.vec.cpu().numpy()[m], got[m], "run-to-run reproducibility")
 
 
+@pytest.mark.parametrize("rf,h,w,nd,ncols,fab,fc", [
+    (1, 1000, 1000, 70, 96, 1.0, 0.0),        # three groups of neighbours, the last one partial; ragged rows
+    (1, 517, 900, 33, 100, 0.01, 0.9),        # wider than tall, batch not a multiple of the staged chunk
+    (2, 1024, 700, 40, 64, -0.5, 1.0),        # row factor 2: two rows share a row of the second operand
+    (4, 2048, 600, 64, 256, 1.0, 0.0),
+])
+def test_dd2dia_scattered_windowed(cb, rf, h, w, nd, ncols, fab, fc):
+    """Scattered offsets whose neighbours (in offset order) lie close enough for the staged-window kernel: unsorted
+    storage order, offsets reaching outside the matrix on both sides, every row factor."""
+    rng = np.random.default_rng(300 + rf + nd)
+    offs = scattered_offsets(rng, nd, -(h // rf) + 1, w - 1, sort=False)
+    dd_case(cb, rng, h, w, offs, rf, ncols, fab, fc)
+
+
 def test_reference_fixture_dd2dia(cb, golden):
     g = golden                                           # src/tests/densedense_to_dia.cpp:109-137,166-197
     h, w, rf, S = int(g["dd2dia_h"]), int(g["dd2dia_w"]), int(g["dd2dia_rf"]), int(g["dd2dia_stride"])
