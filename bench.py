@@ -165,8 +165,14 @@ def run_reference(args, cfg):
     if rank != 0:
         return
     units, nd, batch = cfg["units"], cfg["num_dia"], cfg["batch"]
-    sample = min(batch, args.cpu_sample_cols)
-    t, threads, nnz = cpu_rbm(units, nd, batch, sample, max(1, args.steps), max(0, min(args.warmup, 1)))
+    # a first, small slice tells how long a column takes; the timed slice is then sized so that all steps together
+    # stay near two minutes of host time (at most --cpu-sample-cols columns)
+    probe = min(batch, 64)
+    t_probe, _, _ = cpu_rbm(units, nd, batch, probe, 1, 0)
+    steps, warm = max(1, args.steps), max(0, min(args.warmup, 1))
+    budget_cols = int(120.0 / max(t_probe / probe, 1e-9) / (steps + warm))
+    sample = max(probe, min(batch, args.cpu_sample_cols, budget_cols // 64 * 64))
+    t, threads, nnz = cpu_rbm(units, nd, batch, sample, steps, warm)
     work = rbm.algorithmic_work(units, units, nd, nnz, batch)
     t_full = t * (batch / float(sample))
     value = work["bytes"] / t_full / 1e9
@@ -568,7 +574,8 @@ def main():
     ap.add_argument("--units", type=int)
     ap.add_argument("--num-dia", type=int)
     ap.add_argument("--batch", type=int)
-    ap.add_argument("--cpu-sample-cols", type=int, default=64)
+    ap.add_argument("--cpu-sample-cols", type=int, default=512,
+                    help="batch columns of the workload the CPU oracle is timed on (its time is scaled to the full batch)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the HBM-bound side measurement of the default run")
