@@ -69,26 +69,36 @@ dd2dia_window_kernel(const DdWindowParams P) {
     for (int kk = 0; kk < KG; kk++) acc[kk] = 0.f;
 
     const unsigned sm_u = (unsigned)__cvta_generic_to_shared(smem);
-    // 16-byte asynchronous copies; bytes past the end of an operand (or of this split's columns) arrive as zeros
+    // 16-byte asynchronous copies; bytes past the end of an operand (or of this split's columns) arrive as zeros.
+    // What does not depend on the chunk is worked out once: this thread's piece of the A tile (two columns per
+    // chunk half) and its pieces of a B column.
+    const int qa = tid & (THREADS / 4 - 1), ca = tid / (THREADS / 4);      // A: piece qa of columns ca, ca+4
+    const int rowa = i0 + 4 * qa;
+    const unsigned bytes_a = 4u * (unsigned)max(0, min(4, P.h - rowa));
+    const float* const srca = P.A + min(rowa, (P.h - 1) & ~3);
+    const unsigned dsta = 4u * (unsigned)(ca * THREADS + 4 * qa);
     auto stage = [&](int buf, int cb) {
         const unsigned base = sm_u + 4u * (unsigned)(buf * STAGE);
-        for (int t = tid; t < BC * (THREADS / 4); t += THREADS) {          // A tile
-            const int c = t / (THREADS / 4), q = t - c * (THREADS / 4);
-            const int row = i0 + 4 * q;
+#pragma unroll
+        for (int u = 0; u < BC / 4; u++) {                                  // A tile
+            const int c = ca + 4 * u;
             const bool col_ok = cb + c < b1;
-            const int nrows = col_ok ? max(0, min(4, P.h - row)) : 0;
-            const float* src = P.A + (size_t)(col_ok ? cb + c : b0) * P.lda + min(row, (P.h - 1) & ~3);
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
-                         ::"r"(base + 4u * (unsigned)(c * THREADS + 4 * q)), "l"(src), "r"(4 * nrows) : "memory");
+                         ::"r"(base + dsta + 4u * (unsigned)(4 * u * THREADS)),
+                           "l"(srca + (size_t)(col_ok ? cb + c : b0) * P.lda), "r"(col_ok ? bytes_a : 0u) : "memory");
         }
-        for (int t = tid; t < BC * wchunks; t += THREADS) {                 // B window
-            const int c = t / wchunks, q = t - c * wchunks;
+        for (int q = tid; q < wchunks; q += THREADS) {                      // B window: piece q of every column
             const int row = wbase + 4 * q;
-            const bool col_ok = cb + c < b1;
-            const int nrows = (col_ok && row >= 0) ? max(0, min(4, P.w - row)) : 0;
-            const float* src = P.B + (size_t)(col_ok ? cb + c : b0) * P.ldb + min(max(row, 0), (P.w - 1) & ~3);
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
-                         ::"r"(base + 4u * (unsigned)(BC * THREADS + c * PITCH + 4 * q)), "l"(src), "r"(4 * nrows) : "memory");
+            const unsigned bytes_b = row >= 0 ? 4u * (unsigned)max(0, min(4, P.w - row)) : 0u;
+            const float* const srcb = P.B + min(max(row, 0), (P.w - 1) & ~3);
+            const unsigned dstb = base + 4u * (unsigned)(BC * THREADS + 4 * q);
+#pragma unroll
+            for (int c = 0; c < BC; c++) {
+                const bool col_ok = cb + c < b1;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                             ::"r"(dstb + 4u * (unsigned)(c * PITCH)), "l"(srcb + (size_t)(col_ok ? cb + c : b0) * P.ldb),
+                               "r"(col_ok ? bytes_b : 0u) : "memory");
+            }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
