@@ -33,7 +33,10 @@ constexpr int KC = 32;           // steps per chunk
 constexpr int NRAW = KC + 7;     // diagonals a chunk touches
 constexpr int WR = 156;          // rows of the B window (>= KC + 120, = 4 * odd: conflict-free 128-bit loads)
 constexpr int NCONS_WARPS = 8;      // consumer warps: the 128 x 128 tile
-constexpr int NPROD_WARPS = 2;      // producer warps: TMA issue + skew pass
+#ifndef PB_NPROD
+#define PB_NPROD 4
+#endif
+constexpr int NPROD_WARPS = PB_NPROD; // producer warps: TMA issue + skew pass
 constexpr int THREADS = 32 * (NCONS_WARPS + NPROD_WARPS);
 constexpr int RAW_FLOATS_N = TM * NRAW;     // 'n': band slice is TM rows wide
 constexpr int RAW_FLOATS_T = WR * NRAW;     // 't': band slice is as wide as the B window
@@ -116,8 +119,9 @@ __device__ __forceinline__ bool warp_wait(unsigned long long* bar, unsigned pari
     return __all_sync(0xffffffffu, mbar_wait(bar, parity) ? 1 : 0) != 0;
 }
 
-// Roles: warps 0..7 are consumers (the 128 x 128 tile, 8 x 8 outputs per thread); warps 8 and 9 are
-// producers.  The producers issue the TMA loads and re-lay ("skew") each band slice into the
+// Roles: warps 0..7 are consumers (the 128 x 128 tile, 8 x 8 outputs per thread); warps 8..11 are
+// producers (four of them: one per scheduler, so that a chunk's coefficients are ready well before the
+// consumers ask for them; two were measured 4 % slower).  The producers issue the TMA loads and re-lay ("skew") each band slice into the
 // coefficient buffer As while the consumers are still computing the previous chunk, so the consumers
 // never meet a block-wide barrier: every hand-over is an mbarrier with a bounded wait.
 //   raw        one buffer: band slice of chunk c as TMA delivers it          (raw_full / raw_free)
@@ -179,7 +183,7 @@ prod_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
 
     if (warp >= NCONS_WARPS) {
         // =========================== producers ===========================
-        const int pw = warp - NCONS_WARPS;                     // 0 or 1: handles the steps qq = pw, pw+2, ...
+        const int pw = warp - NCONS_WARPS;                     // handles the steps qq = pw, pw + NPROD_WARPS, ...
         const bool issuer = pw == 0 && lane == 0;
         constexpr unsigned RAW_TX = sizeof(float) * (TRANS ? RAW_FLOATS_T : RAW_FLOATS_N);
         constexpr unsigned BS_TX = sizeof(float) * BS_FLOATS;
@@ -208,7 +212,7 @@ prod_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
             // block-uniform: every cell this chunk touches lies inside the matrix
             const bool interior = TRANS ? (y0 >= 0 && y0 + NRAW <= P.nd && xb >= 0 && xb + WR <= P.h)
                                         : (y0 >= 0 && y0 + NRAW <= P.nd && xb >= 0 && xb + TM + KC <= P.w);
-            constexpr int SSTEP = TRANS ? 2 * (WR - 1) : 2 * TM;
+            constexpr int SSTEP = TRANS ? NPROD_WARPS * (WR - 1) : NPROD_WARPS * TM;
 #pragma unroll
             for (int m = 0; m < TM / 32; m++) {
                 const int r = lane + 32 * m;
@@ -217,11 +221,11 @@ prod_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
                 float* dst = as + pw * TM + r;
                 if (interior && P.fa == 1.f) {
 #pragma unroll
-                    for (int it = 0; it < KC / 2; it++) dst[it * 2 * TM] = src[it * SSTEP];
+                    for (int it = 0; it < KC / NPROD_WARPS; it++) dst[it * NPROD_WARPS * TM] = src[it * SSTEP];
                 } else {
 #pragma unroll 4
-                    for (int it = 0; it < KC / 2; it++) {
-                        const int qq = pw + 2 * it;
+                    for (int it = 0; it < KC / NPROD_WARPS; it++) {
+                        const int qq = pw + NPROD_WARPS * it;
                         bool in;
                         if (!TRANS) {
                             const int k = y0 + qq - j + 7;
@@ -234,14 +238,14 @@ prod_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
                         }
                         float v = src[it * SSTEP];
                         if (P.fa != 1.f) v = __fmul_rn(P.fa, v);
-                        dst[it * 2 * TM] = in ? v : 0.f;
+                        dst[it * NPROD_WARPS * TM] = in ? v : 0.f;
                     }
                 }
             }
             __syncwarp();
             if (lane == 0) { mbar_arrive(&as_full[c & 1]); mbar_arrive(raw_free); }
             if (issuer) {
-                // the slice buffer is free once both producer warps are done with it
+                // the slice buffer is free once every producer warp is done with it
                 if (c + 1 < nch) {
                     if (!mbar_wait(raw_free, c & 1)) { if (P.status) *P.status = 1; }
                     else issue_raw(c + 1);
