@@ -30,6 +30,7 @@ struct WindowParams {
     int wq;                 // positions per de-interleaved plane ('t'): window rows / rf; 'n': window rows
     int pitch;              // words per column in shared memory
     int tiles;              // row tiles of T outputs a block works through with one staged window
+    int natural;            // 't' with a row factor that is a multiple of 4: rows stay in memory order (see kernel)
     float fa, fc;
     const float* A; const int* offs; const float* B; float* C;
 };
@@ -51,6 +52,23 @@ prod_window_kernel(const WindowParams P) {
     // Asynchronous 4-byte copies (global -> shared without passing through registers): a thread
     // issues all of its copies back to back and waits once, so the staging is bandwidth- and not
     // latency-bound.  Rows or columns outside the operand are written as zeros (source size 0).
+    // With a row factor that is a multiple of 4 the transposed product needs no de-interleaving: the rf rows of
+    // a group are contiguous and 16-byte aligned, so the window keeps memory order, is staged with 16-byte copies
+    // and read with 128-bit loads (consecutive threads read consecutive groups: no bank conflicts).
+    const bool natural = TRANS && P.natural;
+    if (natural) {
+        for (int c = 0; c < CB; c++) {
+            const int col = c0 + c;
+            const float* src = P.B + (size_t)min(col, P.ncols - 1) * P.ldb;
+            const unsigned dst0 = (unsigned)__cvta_generic_to_shared(win + c * P.pitch);
+            for (int q = tid; 4 * q < wrows; q += T) {
+                const int row = lo + 4 * q;
+                const unsigned nbytes = col < P.ncols ? 4u * (unsigned)max(0, min(4, rows_b - row)) : 0u;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                             ::"r"(dst0 + 16u * q), "l"(src + min(row, (rows_b - 1) & ~3)), "r"(nbytes) : "memory");
+            }
+        }
+    } else
     for (int c = 0; c < CB; c++) {
         const int col = c0 + c;
         const float* src = P.B + (size_t)min(col, P.ncols - 1) * P.ldb;
@@ -139,6 +157,20 @@ prod_window_kernel(const WindowParams P) {
                     if (t + 1 < total) an = fetch4((t + 1) / nl, ((t + 1) % nl) * 4, vn, mn);
                     if (!valid) continue;
                     const float av[4] = {a4.x, a4.y, a4.z, a4.w};
+                    if (natural) {
+                        const float* wn = win + (size_t)(m - mlo) * rf + l0;
+#pragma unroll
+                        for (int c = 0; c < CB; c++) {
+                            const float4 x4 = *reinterpret_cast<const float4*>(wn + c * P.pitch);
+                            const float xv[4] = {x4.x, x4.y, x4.z, x4.w};
+#pragma unroll
+                            for (int u = 0; u < 4; u++) {
+                                const float au = (P.fa != 1.f) ? __fmul_rn(P.fa, av[u]) : av[u];
+                                acc[c] = EXACT ? __fadd_rn(acc[c], __fmul_rn(au, xv[u])) : fmaf(au, xv[u], acc[c]);
+                            }
+                        }
+                        continue;
+                    }
                     const float* wp = win + (m - mlo) + l0 * P.wq;
 #pragma unroll
                     for (int u = 0; u < 4; u++) {
@@ -203,7 +235,10 @@ static int launch_window_t(const cuvdia_plan* p, const float* A, const float* B,
     const long long wrows = window_rows(p, TRANS, T * tiles, &wq);
     P.wq = (int)wq;
     P.tiles = tiles;
-    P.pitch = (int)(wrows | 1);                          // odd pitch: columns start in different banks
+    P.natural = (TRANS && p->rf % 4 == 0 && p->stride % 4 == 0 && ldb % 4 == 0 &&
+                 (reinterpret_cast<uintptr_t>(A) & 15) == 0 && (reinterpret_cast<uintptr_t>(B) & 15) == 0) ? 1 : 0;
+    // odd pitch: columns start in different banks; the memory-order window needs 16-byte aligned columns instead
+    P.pitch = P.natural ? (int)((wrows + 3) / 4 * 4) : (int)(wrows | 1);
     P.fa = fa; P.fc = fc; P.A = A; P.offs = p->d_offsets; P.B = B; P.C = C;
     const size_t smem = sizeof(float) * (size_t)P.pitch * CB;
     static bool attr_done[64] = {false};
@@ -235,8 +270,8 @@ static bool window_config(const cuvdia_plan* p, bool trans, int ncols, int* T, i
             for (int nt = 1; nt <= 8; nt *= 2) {
                 if (nt > 1 && (long long)c[0] * nt > rows_out) break;
                 const long long wrows = window_rows(p, trans, c[0] * nt, nullptr);
-                if ((size_t)(wrows | 1) * c[1] * sizeof(float) > limit) continue;
-                const size_t smem = (size_t)(wrows | 1) * c[1] * sizeof(float);
+                const size_t smem = (size_t)(wrows + 4) * c[1] * sizeof(float);      // covers either pitch
+                if (smem > limit) continue;
                 const long long blocks = ((rows_out + (long long)c[0] * nt - 1) / ((long long)c[0] * nt)) *
                                          ((ncols + c[1] - 1) / c[1]);
                 // blocks that share an SM (shared memory, 2048 threads), and the rounds the grid needs on them
