@@ -24,6 +24,8 @@ SIGNATURES = {
     "cuvdia_plan_info": (_i, [_vp, ctypes.POINTER(_i), ctypes.POINTER(_ll)]),
     "cuvdia_plan_offsets_device": (_vp, [_vp]),
     "cuvdia_plan_status": (_i, [_vp, ctypes.POINTER(_i)]),
+    "cuvdia_plan_status_clear": (_i, [_vp, _vp]),
+    "cuvdia_selftest_bounded_wait": (_i, [_vp, ctypes.c_uint, _vp]),
     "cuvdia_prod_f32": (_i, [_vp, _vp, _vp, _i, _vp, _i, _i, _c, _c, _f, _f, _i, _vp]),
     "cuvdia_prod_bias_sigmoid_sample_f32": (_i, [_vp, _vp, _vp, _i, _vp, _i, _i, _c, _f, _f, _i, _vp, _vp, _i, _vp, _i,
                                                  _vp]),

@@ -204,6 +204,20 @@ int cuvdia_plan_status(const cuvdia_plan* p, int* status) {
 
 const int* cuvdia_plan_offsets_device(const cuvdia_plan* p) { return p ? p->d_offsets : nullptr; }
 
+int cuvdia_plan_status_clear(cuvdia_plan* p, void* stream) {
+    CUVDIA_REQUIRE(p != nullptr);
+    CUVDIA_REQUIRE(plan_on_current_device(p));
+    CUVDIA_CUDA(cudaMemsetAsync(p->d_status, 0, sizeof(int), (cudaStream_t)stream));
+    return CUVDIA_OK;
+}
+
+int cuvdia_selftest_bounded_wait(cuvdia_plan* p, unsigned max_polls, void* stream) {
+    CUVDIA_REQUIRE(p != nullptr);
+    CUVDIA_REQUIRE(max_polls >= 1 && max_polls <= (1u << 20));       // a self-test, not a stress test
+    CUVDIA_REQUIRE(plan_on_current_device(p));
+    return launch_selftest_wait(p->d_status, max_polls, (cudaStream_t)stream);
+}
+
 int cuvdia_prod_f32(const cuvdia_plan* p, const float* A_vals, const float* B, int ldb, float* C, int ldc,
                     int ncols, char transA, char transB, float factAB, float factC, int mode, void* stream) {
     CUVDIA_REQUIRE(p != nullptr);

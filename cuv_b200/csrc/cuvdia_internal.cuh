@@ -131,4 +131,5 @@ int launch_axpby(float* dst, const float* x, const float* y, float a, float b, l
 int launch_learn_step(float* W, float* M, const float* dW, float a, float b, float c, long long n, cudaStream_t st);
 int launch_binary(float* dst, const float* x, const float* y, int op, float p, float p2, long long n, cudaStream_t st);
 int launch_fill(float* dst, float value, int sequence, long long n, cudaStream_t st);
+int launch_selftest_wait(int* status, unsigned max_polls, cudaStream_t st);
 }  // namespace cuvdia

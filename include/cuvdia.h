@@ -98,6 +98,15 @@ CUVDIA_API int cuvdia_plan_info(const cuvdia_plan* plan, int* is_band, long long
  * engine cannot hang the GPU. */
 CUVDIA_API int cuvdia_plan_status(const cuvdia_plan* plan, int* status);
 
+/* Sets the plan's health word back to 0 (stream-ordered).  No counterpart in CUV. */
+CUVDIA_API int cuvdia_plan_status_clear(cuvdia_plan* plan, void* stream);
+
+/* Self-test of the bounded waits, no counterpart in CUV: launches one warp that waits, like the kernels of
+ * this library do, for a copy-completion barrier - one that nothing will ever complete - gives up after
+ * max_polls polls, writes the code 9 into the plan's health word and returns.  Nothing hangs and nothing
+ * faults; afterwards cuvdia_plan_status reports 9 and the device is as usable as before. */
+CUVDIA_API int cuvdia_selftest_bounded_wait(cuvdia_plan* plan, unsigned max_polls, void* stream);
+
 /* Device pointer to the plan's copy of the offsets (int32, storage order), e.g. to initialise a
  * dia_matrix<float,dev_memory_space>::get_offsets() tensor. */
 CUVDIA_API const int* cuvdia_plan_offsets_device(const cuvdia_plan* plan);

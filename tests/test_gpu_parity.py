@@ -291,6 +291,17 @@ def test_dd2dia_scattered_windowed(cb, rf, h, w, nd, ncols, fab, fc):
     dd_case(cb, rng, h, w, offs, rf, ncols, fab, fc)
 
 
+def test_dd2dia_convolution_pattern(cb):
+    """The weight gradient of a convolution-pattern matrix (runs of consecutive diagonals one image line apart,
+    two input and two output maps): neighbouring runs share the staged window."""
+    rng = np.random.default_rng(41)
+    px, fs = 16, 5
+    h, w = px * px * 2, px * px * 2
+    offs = conv_offsets(px, px, fs, 2, 2)
+    dd_case(cb, rng, h, w, offs, 1, 72, 1.0 / 72, 0.0)
+    dd_case(cb, rng, h, w, offs, 1, 72, -1.0 / 72, 1.0, dist="uniform")
+
+
 def test_reference_fixture_dd2dia(cb, golden):
     g = golden                                           # src/tests/densedense_to_dia.cpp:109-137,166-197
     h, w, rf, S = int(g["dd2dia_h"]), int(g["dd2dia_w"]), int(g["dd2dia_rf"]), int(g["dd2dia_stride"])
@@ -537,3 +548,32 @@ def test_dd2dia_streaming_narrow_band(cb, lo, nd):
     offs = np.arange(lo, lo + nd, dtype=np.int32)
     dd_case(cb, rng, 40004, 36008, offs, 1, 40, 1.0, 0.0)
     dd_case(cb, rng, 36008, 40004, offs, 1, 21, 0.01, 0.9, dist="uniform")
+
+
+def test_bounded_wait_gives_up_with_a_status(cb):
+    """A wait that nothing will ever satisfy runs out after its poll limit, leaves a code in the plan's health word
+    and returns; the device stays usable (the next product is bit-exact) and the word can be cleared."""
+    import ctypes
+    import torch
+    from cuv_b200 import _capi
+    L = _capi.lib()
+    rng = np.random.default_rng(5)
+    A = make_dia(rng, 300, 300, np.arange(-20, 20, dtype=np.int32), 1, stride=304)
+    D = to_dev_dia(A)
+    st = ctypes.c_int(-1)
+    _capi.check(L.cuvdia_plan_status(D._plan, ctypes.byref(st)))
+    assert st.value == 0
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    _capi.check(L.cuvdia_selftest_bounded_wait(D._plan, 2000, stream))
+    _capi.check(L.cuvdia_plan_status(D._plan, ctypes.byref(st)))
+    assert st.value == 9
+    assert L.cuvdia_selftest_bounded_wait(D._plan, 0, stream) == _capi.ERR_INVALID
+    _capi.check(L.cuvdia_plan_status_clear(D._plan, stream))
+    B = np.asfortranarray(rng.standard_normal((300, 70)).astype(np.float32))
+    want = np.zeros((300, 70), dtype=np.float32, order="F")
+    ho.prod(want, A, B, "n")
+    C = cb.colmajor_empty(300, 70)
+    cb.prod(C, D, dev_padded(cb, B), "n", "n", 1.0, 0.0, cb.MODE_EXACT)
+    assert_bits_equal(cb.to_host(C), want, "prod after the self-test")
+    _capi.check(L.cuvdia_plan_status(D._plan, ctypes.byref(st)))
+    assert st.value == 0
