@@ -52,7 +52,8 @@ def build(force=False, verbose=False):
         failed = failed or pr.returncode != 0
     if failed:
         raise RuntimeError("nvcc failed")
-    subprocess.check_call([_nvcc(), "-shared", "-o", LIB] + objs + ["-Xcompiler", "-fPIC"])
+    subprocess.check_call([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", LIB] + objs +
+                          ["-Xcompiler", "-fPIC"])
     return LIB
 
 
