@@ -22,9 +22,10 @@
 namespace cuvdia {
 
 namespace dw {
-constexpr int THREADS = 256;         // rows per block
+constexpr int THREADS = 256;
 constexpr int BC = 8;                // batch columns per staged chunk
-constexpr int PITCH = 1032;          // words per staged B column: two 41 KB stages, two blocks per SM
+// words per staged B column for one and two rows per thread: two stages of 41 / 53.5 KB, two blocks per SM
+template <int RPT> __host__ __device__ constexpr int pitch() { return RPT == 1 ? 1032 : 1160; }
 }
 
 struct DdWindowParams {
@@ -36,62 +37,70 @@ struct DdWindowParams {
     const int* sorted_off;           // the k-th smallest offset
 };
 
-// KG: diagonals per group (32, or 16 where 32 neighbours span too many rows for the window).  The pitch of a staged
-// column is a compile-time constant, so that a cell's shared-memory address is a register plus an immediate.
-template <int KG>
+// KG: diagonals per group (32, or 16 where 32 neighbours span too many rows for the window).  RPT: rows per thread
+// (2 where the row factor divides 256, so that the second row's cells sit a constant distance from the first's).
+// The pitch of a staged column is a compile-time constant, so that a cell's shared-memory address is a register
+// plus an immediate.
+template <int KG, int RPT>
 __global__ void __launch_bounds__(dw::THREADS, 2)
 dd2dia_window_kernel(const DdWindowParams P) {
     using namespace dw;
-    constexpr int STAGE = BC * (THREADS + PITCH);    // words per stage: A tile [BC][THREADS], B window [BC][PITCH]
+    constexpr int TR = RPT * THREADS;                // rows per block
+    constexpr int PITCH = pitch<RPT>();
+    constexpr int STAGE = BC * (TR + PITCH);         // words per stage: A tile [BC][TR], B window [BC][PITCH]
     extern __shared__ __align__(16) float smem[];    // two stages
     const int tid = threadIdx.x;
-    const int i0 = blockIdx.x * THREADS;
+    const int i0 = blockIdx.x * TR;
     const int g0 = blockIdx.y * KG;                  // first diagonal (in offset order) of the group
     const int gn = min(KG, P.nd - g0);
     const int z = blockIdx.z;
     const int b0 = (int)((long long)P.ncols * z / P.nsplit), b1 = (int)((long long)P.ncols * (z + 1) / P.nsplit);
     const int gmin = P.sorted_off[g0], gmax = P.sorted_off[g0 + gn - 1];
-    const int i = i0 + tid;
-    const int last = min(i0 + THREADS, P.h) - 1;     // last row of the block
     const int wbase = (i0 / P.rf + gmin) & ~3;       // first staged B row: the window's first row rounded down to 4
-    const int wchunks = (last / P.rf + gmax - wbase + 4) / 4;      // 16-byte pieces per staged column
+    // 16-byte pieces per staged column: the rows a full tile can touch (rows outside B arrive as zeros)
+    const int wchunks = ((i0 + TR - 1) / P.rf + gmax - wbase + 4) / 4;
+    const int roff = THREADS / P.rf;                 // distance between the cells of a thread's two rows (RPT == 2)
 
-    // word index of this thread's 32 cells inside stage 0 (indices into the shared array itself, so that the
-    // loads below stay in the shared address space)
+    // word index of the cells of this thread's first row inside stage 0 (indices into the shared array itself, so
+    // that the loads below stay in the shared address space)
     int cell[KG];
 #pragma unroll
     for (int kk = 0; kk < KG; kk++) {
         const int off = kk < gn ? P.sorted_off[g0 + kk] : gmin;
-        cell[kk] = BC * THREADS + (min(i, last) / P.rf + off - wbase);
+        cell[kk] = BC * TR + ((i0 + tid) / P.rf + off - wbase);
     }
-    float acc[KG];
+    float acc[RPT][KG];
 #pragma unroll
-    for (int kk = 0; kk < KG; kk++) acc[kk] = 0.f;
+    for (int r = 0; r < RPT; r++)
+#pragma unroll
+        for (int kk = 0; kk < KG; kk++) acc[r][kk] = 0.f;
 
     const unsigned sm_u = (unsigned)__cvta_generic_to_shared(smem);
     // 16-byte asynchronous copies; bytes past the end of an operand (or of this split's columns) arrive as zeros.
-    // What does not depend on the chunk is worked out once: this thread's piece of the A tile (two columns per
-    // chunk half) and its pieces of a B column.
-    const int qa = tid & (THREADS / 4 - 1), ca = tid / (THREADS / 4);      // A: piece qa of columns ca, ca+4
+    // What does not depend on the chunk is worked out once: this thread's piece of the A tile (in every CPASS-th
+    // column) and its pieces of a B column.
+    constexpr int PPC = TR / 4;                      // 16-byte pieces per A column
+    constexpr int CPASS = THREADS / PPC;             // A columns covered by one pass of the block
+    const int qa = tid % PPC, ca = tid / PPC;
     const int rowa = i0 + 4 * qa;
     const unsigned bytes_a = 4u * (unsigned)max(0, min(4, P.h - rowa));
     const float* const srca = P.A + min(rowa, (P.h - 1) & ~3);
-    const unsigned dsta = 4u * (unsigned)(ca * THREADS + 4 * qa);
+    const unsigned dsta = 4u * (unsigned)(ca * TR + 4 * qa);
     auto stage = [&](int buf, int cb) {
         const unsigned base = sm_u + 4u * (unsigned)(buf * STAGE);
 #pragma unroll
-        for (int u = 0; u < BC / 4; u++) {                                  // A tile
-            const int c = ca + 4 * u;
+        for (int u = 0; u < BC / CPASS; u++) {                              // A tile
+            const int c = ca + CPASS * u;
             const bool col_ok = cb + c < b1;
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
-                         ::"r"(base + dsta + 4u * (unsigned)(4 * u * THREADS)),
+                         ::"r"(base + dsta + 4u * (unsigned)(CPASS * u * TR)),
                            "l"(srca + (size_t)(col_ok ? cb + c : b0) * P.lda), "r"(col_ok ? bytes_a : 0u) : "memory");
         }
         for (int q = tid; q < wchunks; q += THREADS) {                      // B window: piece q of every column
             const int row = wbase + 4 * q;
             const unsigned bytes_b = row >= 0 ? 4u * (unsigned)max(0, min(4, P.w - row)) : 0u;
             const float* const srcb = P.B + min(max(row, 0), (P.w - 1) & ~3);
-            const unsigned dstb = base + 4u * (unsigned)(BC * THREADS + 4 * q);
+            const unsigned dstb = base + 4u * (unsigned)(BC * TR + 4 * q);
 #pragma unroll
             for (int c = 0; c < BC; c++) {
                 const bool col_ok = cb + c < b1;
@@ -111,29 +120,38 @@ dd2dia_window_kernel(const DdWindowParams P) {
         else asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
         const float* st = smem + buf * STAGE;
-        // ---- 8 columns x 32 cells per thread ----
+        const float* st2 = st + roff;                // the second row's cells
+        // ---- 8 columns x KG cells x RPT rows per thread ----
 #pragma unroll
         for (int c = 0; c < BC; c++) {
-            const float a = st[c * THREADS + tid];
+            const float a0 = st[c * TR + tid];
+            const float a1 = RPT == 2 ? st[c * TR + THREADS + tid] : 0.f;
 #pragma unroll
-            for (int kk = 0; kk < KG; kk++) acc[kk] = fmaf(a, st[cell[kk] + c * PITCH], acc[kk]);
+            for (int kk = 0; kk < KG; kk++) {
+                acc[0][kk] = fmaf(a0, st[cell[kk] + c * PITCH], acc[0][kk]);
+                if (RPT == 2) acc[RPT - 1][kk] = fmaf(a1, st2[cell[kk] + c * PITCH], acc[RPT - 1][kk]);
+            }
         }
         __syncthreads();                             // everyone is done with this stage before it is refilled
     }
 
-    if (i >= P.h) return;
 #pragma unroll
-    for (int kk = 0; kk < KG; kk++) {
-        if (kk >= gn) break;
-        const int jj = i / P.rf + P.sorted_off[g0 + kk];
-        if (jj < 0 || jj >= P.w) continue;
-        const size_t cellidx = (size_t)P.sorted_slot[g0 + kk] * P.S + i;
-        if (P.nsplit == 1) {
-            float s = acc[kk];
-            if (P.fa != 1.f) s = __fmul_rn(P.fa, s);
-            P.C[cellidx] = (P.fc != 0.f) ? __fadd_rn(__fmul_rn(P.fc, P.C[cellidx]), s) : s;
-        } else {
-            P.partial[(size_t)z * P.nd * P.S + cellidx] = acc[kk];
+    for (int r = 0; r < RPT; r++) {
+        const int i = i0 + r * THREADS + tid;
+        if (i >= P.h) continue;
+#pragma unroll
+        for (int kk = 0; kk < KG; kk++) {
+            if (kk >= gn) break;
+            const int jj = i / P.rf + P.sorted_off[g0 + kk];
+            if (jj < 0 || jj >= P.w) continue;
+            const size_t cellidx = (size_t)P.sorted_slot[g0 + kk] * P.S + i;
+            if (P.nsplit == 1) {
+                float s = acc[r][kk];
+                if (P.fa != 1.f) s = __fmul_rn(P.fa, s);
+                P.C[cellidx] = (P.fc != 0.f) ? __fadd_rn(__fmul_rn(P.fc, P.C[cellidx]), s) : s;
+            } else {
+                P.partial[(size_t)z * P.nd * P.S + cellidx] = acc[r][kk];
+            }
         }
     }
 }
@@ -141,12 +159,21 @@ dd2dia_window_kernel(const DdWindowParams P) {
 int launch_dd2dia_combine(const cuvdia_plan* p, float* Cv, float fa, float fc, int nsplit, const float* partial,
                           cudaStream_t st);
 
-// Diagonals per group for this plan: 32 if the rows such a group can touch fit the staged window, else 16, else 0.
-static int window_group(const cuvdia_plan* p) {
-    const int tile = (dw::THREADS - 1) / p->rf + 1;
-    if (p->group_window_max[1] > 0 && tile + p->group_window_max[1] + 7 <= dw::PITCH) return 32;
-    if (p->group_window_max[0] > 0 && tile + p->group_window_max[0] + 7 <= dw::PITCH) return 16;
-    return 0;
+// Rows per thread and diagonals per group for this plan: two rows where the row factor divides 256 and the matrix
+// has rows to fill the GPU with such tiles, 32 diagonals if the rows a group can touch fit the staged window, else
+// 16; false if nothing fits.
+static bool window_shape(const cuvdia_plan* p, int* rpt, int* kg) {
+    for (int r = 2; r >= 1; r--) {
+        if (r == 2 && (dw::THREADS % p->rf != 0 || p->h < 4 * 2 * dw::THREADS)) continue;
+        const int tile = (r * dw::THREADS - 1) / p->rf + 1;
+        const int pitch = r == 2 ? dw::pitch<2>() : dw::pitch<1>();
+        for (int v = (r == 2 ? 0 : 1); v >= 0; v--)           // two rows x 32 diagonals would not fit the registers
+            if (p->group_window_max[v] > 0 && tile + p->group_window_max[v] + 7 <= pitch) {
+                *rpt = r; *kg = v == 1 ? 32 : 16;
+                return true;
+            }
+    }
+    return false;
 }
 
 // Neighbouring diagonals (in offset order) close enough for the window, 16-byte aligned operands, and enough work
@@ -154,7 +181,8 @@ static int window_group(const cuvdia_plan* p) {
 bool dd2dia_window_applicable(const cuvdia_plan* p, const float* A, int lda, const float* B, int ldb, int ncols) {
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
     if (!(al16(A) && al16(B) && lda % 4 == 0 && ldb % 4 == 0)) return false;
-    return p->d_sorted != nullptr && window_group(p) != 0 && p->nd >= 16 && ncols >= 32;
+    int rpt, kg;
+    return p->d_sorted != nullptr && window_shape(p, &rpt, &kg) && p->nd >= 16 && ncols >= 32;
 }
 
 int launch_dd2dia_window(cuvdia_plan* p, float* Cv, const float* A, int lda, const float* B, int ldb, int ncols,
@@ -163,11 +191,12 @@ int launch_dd2dia_window(cuvdia_plan* p, float* Cv, const float* A, int lda, con
     DdWindowParams P;
     P.h = p->h; P.w = p->w; P.nd = p->nd; P.S = p->stride; P.rf = p->rf;
     P.lda = lda; P.ldb = ldb; P.ncols = ncols;
-    const int KG = window_group(p);
-    if (KG == 0) { set_last_error("window does not fit"); return CUVDIA_ERR_UNSUPPORTED; }
+    int RPT = 1, KG = 16;
+    if (!window_shape(p, &RPT, &KG)) { set_last_error("window does not fit"); return CUVDIA_ERR_UNSUPPORTED; }
     P.fa = fa; P.fc = fc; P.A = A; P.B = B; P.C = Cv;
     P.sorted_slot = p->d_sorted; P.sorted_off = p->d_sorted + p->nd;
-    const int gx = (p->h + THREADS - 1) / THREADS, gy = (p->nd + KG - 1) / KG;
+    const int TR = RPT * THREADS;
+    const int gx = (p->h + TR - 1) / TR, gy = (p->nd + KG - 1) / KG;
     if (gy > 65535) { set_last_error("num_dia too large for densedense_to_dia"); return CUVDIA_ERR_UNSUPPORTED; }
     int nsplit = 1;
     const long long ctas = (long long)gx * gy, want = 4LL * sm_count();
@@ -181,15 +210,16 @@ int launch_dd2dia_window(cuvdia_plan* p, float* Cv, const float* A, int lda, con
         P.partial = p->scratch;
     }
     int rc = CUVDIA_OK;
-#define DW_GO(KGV)                                                                                \
+#define DW_GO(KGV, RV)                                                                            \
     do {                                                                                          \
-        const size_t smem = sizeof(float) * 2 * (size_t)BC * (THREADS + PITCH);                   \
+        const size_t smem = sizeof(float) * 2 * (size_t)BC * (RV * THREADS + pitch<RV>());        \
         static bool attr[64] = {false};                                                           \
-        rc = allow_dynamic_smem(dd2dia_window_kernel<KGV>, smem, attr);                           \
+        rc = allow_dynamic_smem(dd2dia_window_kernel<KGV, RV>, smem, attr);                       \
         if (rc) return rc;                                                                        \
-        dd2dia_window_kernel<KGV><<<dim3(gx, gy, nsplit), THREADS, smem, st>>>(P);                \
+        dd2dia_window_kernel<KGV, RV><<<dim3(gx, gy, nsplit), THREADS, smem, st>>>(P);            \
     } while (0)
-    if (KG == 32) DW_GO(32); else DW_GO(16);
+    if (RPT == 2) DW_GO(16, 2);
+    else          { if (KG == 32) DW_GO(32, 1); else DW_GO(16, 1); }
 #undef DW_GO
     count_launch();
     rc = check_launch("dd2dia_window_kernel");
