@@ -8,7 +8,8 @@
 // registers and the ceiling is one shared-memory word per multiply-add (a quarter of the FP32
 // rate).  What can be saved is the traffic behind it: the plain kernel fetches every B value from
 // L2 once per cell.  Here the diagonals are taken in ascending order of their offsets, 32 (or 16) at a
-// time; a block owns 256 rows and one such group, and stages, per 8 batch columns, its 256 x 8
+// time; a block owns 256 rows (512, two per thread, where the row factor divides 256) and one such
+// group, and stages, per 8 batch columns, its
 // tile of A and the window of B rows the group can touch (rows i/rf + off_min .. off_max of the
 // group; rows outside B arrive as zeros) with 16-byte asynchronous copies, one chunk ahead of the
 // arithmetic (two stages).  A staged B value then serves
