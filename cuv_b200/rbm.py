@@ -95,6 +95,24 @@ class SparseRBMStep:
         two bias gradients."""
         allreduce_gradients(self.G.vec, self.bias_grad, group)
 
+    def capture(self, V0, U_h, U_v):
+        """Records one step on the given (static) input tensors into a CUDA graph and returns it; ``graph.replay()``
+        then runs the 16 kernels of a step with a single launch.  The library allocates its scratch buffers on first
+        use, so one ordinary step is run first; nothing is allocated while recording."""
+        import torch
+        timers, self.timers = self.timers, None          # events cannot be recorded into the graph this way
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            self.step(V0, U_h, U_v)                      # on the recording stream: the reductions' workspace is per stream
+            side.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                self.step(V0, U_h, U_v)
+        torch.cuda.current_stream().wait_stream(side)
+        self.timers = timers
+        return graph
+
     def update(self, learnrate, decay=0.0):
         """The trainer's update step (examples/rbm/base.py:72-75): learn_step_weight_decay on the weight
         diagonals and on both bias vectors with the gradients of the last step (after allreduce() when

@@ -158,3 +158,35 @@ def test_update_step_applies_the_gradients():
     ref = rbm_oracle.cd1_step(W2, V0, U_h, U_v, b=st.b_vis.cpu().numpy(), c=st.c_hid.cpu().numpy(), nthreads=8)
     st.step(cb.to_device(V0), cb.to_device(U_h), cb.to_device(U_v))
     np.testing.assert_allclose(cb.to_host(st.H0p), ref["H0p"], rtol=1e-5)
+
+
+def test_step_replayed_from_a_cuda_graph():
+    """A step recorded into a CUDA graph (after one ordinary step has made the library allocate its scratch) replays
+    with the same bits, also on new contents of the same input tensors."""
+    import torch
+    import cuv_b200 as cb
+    from cuv_b200 import rbm
+    units, nd, nb = 1024, 64, 128
+    offs = np.arange(-nd // 2, nd // 2, dtype=np.int32)
+    W, V0, U_h, U_v = rbm_oracle.make_inputs(1007, units, units, offs, nb, w_std=0.05)
+    Wd = cb.dev_dia_matrix_f(W.h, W.w, W.offsets, W.stride, W.rf).set_vec(W.vals)
+    st = rbm.SparseRBMStep(Wd, nb)
+    dV0, dUh, dUv = cb.to_device(V0), cb.to_device(U_h), cb.to_device(U_v)
+    graph = st.capture(dV0, dUh, dUv)
+    eager = {k: getattr(st, k).clone() for k in ("H0p", "H0", "V1p", "V1", "H1p")}
+    g_eager, b_eager = st.G.vec.clone(), st.bias_grad.clone()
+    st.G.vec.zero_(); st.bias_grad.zero_(); st.H1p.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    for k, v in eager.items():
+        assert torch.equal(getattr(st, k), v), k
+    assert torch.equal(st.G.vec, g_eager) and torch.equal(st.bias_grad, b_eager)
+    # new data in the same tensors: the replay follows it
+    _, V0b, U_hb, U_vb = rbm_oracle.make_inputs(1008, units, units, offs, nb, w_std=0.05)
+    dV0.copy_(cb.to_device(V0b)); dUh.copy_(cb.to_device(U_hb)); dUv.copy_(cb.to_device(U_vb))
+    graph.replay()
+    torch.cuda.synchronize()
+    replayed = st.G.vec.clone()
+    st.step(dV0, dUh, dUv)
+    torch.cuda.synchronize()
+    assert torch.equal(st.G.vec, replayed)
