@@ -62,19 +62,32 @@ class SparseRBMStep:
         self.forward(V0, U_h, U_v)
         self.gradients(V0)
 
-    def forward(self, V0, U_h, U_v):
-        """The three products with their bias/logistic/sampling passes."""
+    def forward(self, V0, U_h, U_v, arrived=None):
+        """The three products with their bias/logistic/sampling passes.  ``arrived``: optional events
+        (V0, U_h, U_v) that the current stream waits for just before the first use of each input, so that a
+        step can start on V0 while the uniform numbers are still on their way."""
         W = self.W
         t = self._timed
+
+        def need(k):
+            if arrived is not None:
+                import torch
+                torch.cuda.current_stream().wait_event(arrived[k])
+
         if self.fused:
             F = cb.prod_bias_sigmoid_sample
+            need(0); need(1)
             t("prod_n", lambda: F(self.H0p, W, V0, "n", 1.0, 0.0, self.mode, self.c_hid, U_h, self.H0))
+            need(2)
             t("prod_t", lambda: F(self.V1p, W, self.H0, "t", 1.0, 0.0, self.mode, self.b_vis, U_v, self.V1))
             t("prod_n", lambda: F(self.H1p, W, self.V1, "n", 1.0, 0.0, self.mode, self.c_hid))
             return
+        need(0)
         t("prod_n", lambda: cb.prod(self.H0p, W, V0, "n", "n", 1.0, 0.0, self.mode))
+        need(1)
         t("glue", lambda: cb.bias_sigmoid_sample(self.H0p, self.c_hid, U_h, self.H0))
         t("prod_t", lambda: cb.prod(self.V1p, W, self.H0, "t", "n", 1.0, 0.0, self.mode))
+        need(2)
         t("glue", lambda: cb.bias_sigmoid_sample(self.V1p, self.b_vis, U_v, self.V1))
         t("prod_n", lambda: cb.prod(self.H1p, W, self.V1, "n", "n", 1.0, 0.0, self.mode))
         t("glue", lambda: cb.bias_sigmoid_sample(self.H1p, self.c_hid))
@@ -126,8 +139,10 @@ class SparseRBMStep:
 class HostFedRBM:
     """Runs SparseRBMStep on inputs that live in pinned host memory and returns the gradients to
     pinned host memory, with the transfers overlapped with compute: the host-to-device copies of step
-    i+1 run on a copy stream while step i computes (two device input sets), and the device-to-host
-    read of step i's gradients runs on a third stream while step i+1's products compute."""
+    i+1 run on a copy stream while step i computes (two device input sets), a step starts as soon as
+    its first input has arrived (the uniform numbers are awaited where they are first used), and the
+    device-to-host read of step i's gradients runs on a third stream while step i+1's products
+    compute."""
 
     def __init__(self, step, allreduce=False):
         import torch
@@ -137,7 +152,7 @@ class HostFedRBM:
         self.inputs = [(E(step.vis, step.nb, dev), E(step.hid, step.nb, dev), E(step.vis, step.nb, dev))
                        for _ in range(2)]
         self.h2d, self.d2h = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
-        self.ready = [torch.cuda.Event() for _ in range(2)]
+        self.ready = [[torch.cuda.Event() for _ in range(3)] for _ in range(2)]     # per slot: V0, U_h, U_v arrived
         self.consumed = [torch.cuda.Event() for _ in range(2)]
         self.grads_done, self.fetched = torch.cuda.Event(), torch.cuda.Event()
         self.n_sub = self.n_run = 0
@@ -151,9 +166,9 @@ class HostFedRBM:
         if self.n_sub >= 2:
             self.h2d.wait_event(self.consumed[slot])
         with torch.cuda.stream(self.h2d):
-            for dst, src in zip(self.inputs[slot], (hV0, hU_h, hU_v)):
+            for k, (dst, src) in enumerate(zip(self.inputs[slot], (hV0, hU_h, hU_v))):
                 dst.t().copy_(src, non_blocking=True)
-            self.ready[slot].record(self.h2d)
+                self.ready[slot][k].record(self.h2d)
         self.n_sub += 1
 
     def run(self, hG=None, hbias=None):
@@ -162,9 +177,8 @@ class HostFedRBM:
         import torch
         cur = torch.cuda.current_stream()
         slot = self.n_run % 2
-        cur.wait_event(self.ready[slot])
         V0, U_h, U_v = self.inputs[slot]
-        self.step.forward(V0, U_h, U_v)
+        self.step.forward(V0, U_h, U_v, arrived=self.ready[slot])       # each input is awaited where it is first used
         if self._fetch_pending:
             cur.wait_event(self.fetched)          # the previous gradients must have left before they are overwritten
         self.step.gradients(V0)
