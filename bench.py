@@ -192,6 +192,29 @@ def run_reference(args, cfg):
     print(json.dumps(line), flush=True)
 
 
+def pin_to_gpu_numa_node(torch, local):
+    """Restricts this process to the CPUs next to its GPU (the PCI device's local_cpulist in sysfs), so that the
+    pinned host buffers it allocates and fills afterwards land in that NUMA node's memory: with several ranks on
+    one host, input copies that cross the socket interconnect share its bandwidth.  Returns the CPU list used, or
+    None if the topology cannot be read (then nothing is changed)."""
+    try:
+        prop = torch.cuda.get_device_properties(local)
+        bdf = "%04x:%02x:%02x.0" % (prop.pci_domain_id, prop.pci_bus_id, prop.pci_device_id)
+        with open("/sys/bus/pci/devices/%s/local_cpulist" % bdf) as f:
+            text = f.read().strip()
+        cpus = set()
+        for part in text.split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return text
+    except Exception:
+        pass
+    return None
+
+
 def workload_name(case, cfg):
     if case == "rbm_cfg4":
         return ("BASELINE config 4: sparse RBM CD-1 step, visible=hidden=%d, DIA weights num_dia=%d row_fact=1 "
@@ -222,6 +245,7 @@ def run_ours(args, cfg):
                          "(use --impl reference for the CPU oracle)")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    numa = pin_to_gpu_numa_node(torch, local) if world > 1 else None
     # Libraries (NCCL prints its version banner) write to file descriptor 1; point it at stderr for the
     # run and keep the real stdout for the one JSON line.
     sys.stdout.flush()
@@ -387,7 +411,7 @@ def run_ours(args, cfg):
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload_name(args.case, cfg), "units": units, "num_dia": nd, "row_fact": 1,
-                   "global_batch": batch, "batch_per_gpu": nb, "parallelism": "batch columns x%d" % world,
+                   "global_batch": batch, "batch_per_gpu": nb, "parallelism": "batch columns x%d" % world, "host_cpus": numa,
                    "prod_arithmetic": args.mode + (" (fused multiply-add; bit-identical to the reference on this workload: "
                                                      "the dense operand of every product is 0/1)" if args.mode == "fast" else
                                                      " (separate multiply and add, reference order)"), "l2": "inputs larger than L2 (each activation matrix %.0f MB)"
