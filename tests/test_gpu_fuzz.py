@@ -1,0 +1,108 @@
+"""Seeded random sweep over shapes, diagonal patterns, row factors, batch sizes, factors and operand
+alignments: whatever kernel the dispatcher picks, prod must reproduce the host loop bit for bit in the EXACT
+arithmetic and densedense_to_dia must stay within the gradient tolerance and leave padding cells untouched."""
+import numpy as np
+import pytest
+
+from oracle import host_oracle as ho
+from tests.helpers import F, assert_bits_equal, make_dia, to_dev_dia
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def cb():
+    import cuv_b200
+    return cuv_b200
+
+
+def random_offsets(rng, h, w, rf):
+    """One of the pattern classes the plan distinguishes: a band, runs of consecutive diagonals (a convolution
+    pattern), scattered offsets, scattered offsets with repeats; in storage order that is sorted or shuffled."""
+    lo_min, hi_max = -(h // rf) + 1, w - 1
+    span = hi_max - lo_min + 1
+    kind = rng.integers(0, 4)
+    if kind == 0:                                             # band
+        nd = int(rng.integers(1, min(80, span) + 1))
+        lo = int(rng.integers(lo_min, hi_max - nd + 2))
+        offs = np.arange(lo, lo + nd)
+    elif kind == 1:                                           # runs
+        runs, fs, step = int(rng.integers(2, 7)), int(rng.integers(3, 13)), int(rng.integers(13, 60))
+        lo = int(rng.integers(lo_min, max(lo_min + 1, hi_max - runs * step - fs)))
+        offs = np.concatenate([lo + r * step + np.arange(fs) for r in range(runs)])
+        offs = offs[(offs >= lo_min) & (offs <= hi_max)]
+        if offs.size == 0:
+            offs = np.array([0])
+        if rng.integers(0, 3) == 0:                           # the same runs stored twice, as the speed fixture does
+            offs = np.concatenate([offs, offs])
+    else:                                                     # scattered
+        nd = int(rng.integers(1, min(70, span) + 1))
+        offs = rng.choice(np.arange(lo_min, hi_max + 1), nd, replace=False)
+        offs = np.sort(offs) if rng.integers(0, 2) else offs
+        if kind == 3 and nd > 2:
+            offs[int(rng.integers(0, nd))] = offs[int(rng.integers(0, nd))]
+    return offs.astype(np.int32)
+
+
+def device_matrix(cb, rng, M, pad):
+    """Device copy of a column-major host matrix; with ``pad`` the leading dimension is rounded up to a multiple of
+    four (NaN in the padding rows) so that the vector kernels qualify, without it they do not when rows % 4 != 0."""
+    if not pad:
+        return cb.to_device(M)
+    rows, cols = M.shape
+    buf = cb.colmajor_empty(rows + (4 - rows % 4) % 4, cols)
+    buf.fill_(float("nan"))
+    buf[:rows].copy_(cb.to_device(M))
+    return buf[:rows]
+
+
+@pytest.mark.parametrize("seed", range(60))
+def test_prod_random_case(cb, seed):
+    rng = np.random.default_rng(9000 + seed)
+    rf = int(rng.choice([1, 1, 1, 2, 3, 4, 8]))
+    h = int(rng.integers(1, 160)) * rf if rf > 1 else int(rng.integers(1, 1400))
+    w = int(rng.integers(1, 1400))
+    offs = random_offsets(rng, h, w, rf)
+    stride = h + int(rng.choice([0, 0, 3, 4]))
+    stride += (4 - stride % 4) % 4 if rng.integers(0, 2) else 0
+    A = make_dia(rng, h, w, offs, rf, stride=max(stride, h))
+    trans = "t" if rng.integers(0, 2) else "n"
+    ncols = int(rng.choice([1, 3, 14, 16, 17, 40, 64, 70]))
+    fab = float(rng.choice([1.0, 2.0, -0.5]))
+    fc = float(rng.choice([0.0, 0.0, 1.0, 1.3]))
+    rows_b, rows_c = (h, w) if trans == "t" else (w, h)
+    B = F(rng.standard_normal((rows_b, ncols)))
+    C0 = F(rng.standard_normal((rows_c, ncols)))
+    if fc == 0.0:
+        C0[:] = np.nan
+    want = C0.copy(order="F")
+    ho.prod(want, A, B, trans, fab, fc)
+    Cd = device_matrix(cb, rng, C0, bool(rng.integers(0, 2)))
+    cb.prod(Cd, to_dev_dia(A), device_matrix(cb, rng, B, bool(rng.integers(0, 2))), trans, "n", fab, fc, cb.MODE_EXACT)
+    assert_bits_equal(cb.to_host(Cd), want, "seed %d: prod %s h=%d w=%d rf=%d nd=%d ncols=%d" %
+                      (seed, trans, h, w, rf, offs.size, ncols))
+
+
+@pytest.mark.parametrize("seed", range(30))
+def test_dd2dia_random_case(cb, seed):
+    rng = np.random.default_rng(9500 + seed)
+    rf = int(rng.choice([1, 1, 2, 4]))
+    h = int(rng.integers(1, 200)) * rf if rf > 1 else int(rng.integers(1, 1200))
+    w = int(rng.integers(1, 1200))
+    offs = random_offsets(rng, h, w, rf)
+    ncols = int(rng.choice([1, 8, 31, 32, 33, 72, 130]))
+    fab, fc = float(rng.choice([1.0, 0.01, -1.0 / 64])), float(rng.choice([0.0, 0.9, 1.0]))
+    C = make_dia(rng, h, w, offs, rf, stride=h + (4 - h % 4) % 4)
+    X, Y = F(rng.uniform(0, 1, (h, ncols))), F(rng.uniform(0, 1, (w, ncols)))
+    want = ho.DiaHost(h, w, C.offsets, C.stride, rf, C.vals.copy())
+    m = C.valid_mask().reshape(-1)
+    if fc == 0:
+        C.vals[m] = np.nan
+    ho.densedense_to_dia(want, X, Y, fab, fc, nthreads=4)
+    D = to_dev_dia(C)
+    pad = bool(rng.integers(0, 2))
+    cb.densedense_to_dia(D, None, device_matrix(cb, rng, X, pad), device_matrix(cb, rng, Y, pad), fab, fc)
+    got = D.vec.cpu().numpy()
+    assert_bits_equal(got[~m], C.vals[~m], "seed %d: cells outside the diagonals' ranges must be untouched" % seed)
+    tol = 1e-4 * np.sqrt(max(ncols, 128) / 128.0)
+    np.testing.assert_allclose(got[m], want.vals[m], rtol=tol, atol=tol * 1e-3 * max(1.0, abs(fab) * ncols))
