@@ -1,6 +1,8 @@
 """Seeded random sweep over shapes, diagonal patterns, row factors, batch sizes, factors and operand
 alignments: whatever kernel the dispatcher picks, prod must reproduce the host loop bit for bit in the EXACT
 arithmetic and densedense_to_dia must stay within the gradient tolerance and leave padding cells untouched."""
+import os
+
 import numpy as np
 import pytest
 
@@ -8,6 +10,9 @@ from oracle import host_oracle as ho
 from tests.helpers import F, assert_bits_equal, make_dia, to_dev_dia
 
 pytestmark = pytest.mark.gpu
+
+# more seeds for an occasional longer hunt: CUVDIA_FUZZ_SCALE=10 runs ten times as many cases
+SCALE = int(os.environ.get("CUVDIA_FUZZ_SCALE", "1"))
 
 
 @pytest.fixture(scope="module")
@@ -56,7 +61,7 @@ def device_matrix(cb, rng, M, pad):
     return buf[:rows]
 
 
-@pytest.mark.parametrize("seed", range(60))
+@pytest.mark.parametrize("seed", range(60 * SCALE))
 def test_prod_random_case(cb, seed):
     rng = np.random.default_rng(9000 + seed)
     rf = int(rng.choice([1, 1, 1, 2, 3, 4, 8]))
@@ -83,7 +88,7 @@ def test_prod_random_case(cb, seed):
                       (seed, trans, h, w, rf, offs.size, ncols))
 
 
-@pytest.mark.parametrize("seed", range(30))
+@pytest.mark.parametrize("seed", range(30 * SCALE))
 def test_dd2dia_random_case(cb, seed):
     rng = np.random.default_rng(9500 + seed)
     rf = int(rng.choice([1, 1, 2, 4]))
@@ -106,3 +111,36 @@ def test_dd2dia_random_case(cb, seed):
     assert_bits_equal(got[~m], C.vals[~m], "seed %d: cells outside the diagonals' ranges must be untouched" % seed)
     tol = 1e-4 * np.sqrt(max(ncols, 128) / 128.0)
     np.testing.assert_allclose(got[m], want.vals[m], rtol=tol, atol=tol * 1e-3 * max(1.0, abs(fab) * ncols))
+
+
+@pytest.mark.parametrize("seed", range(6 * SCALE))
+def test_prod_random_large_case(cb, seed):
+    """Tall matrices with aligned operands: the streaming kernels (at most 16 diagonals on tens of thousands of
+    rows), the tiled kernel over many row tiles and the run-walking kernel over many blocks."""
+    rng = np.random.default_rng(9800 + seed)
+    h = int(rng.integers(8200, 17000)) * 4
+    w = h + 4 * int(rng.integers(-500, 500))
+    kind = int(rng.integers(0, 3))
+    if kind == 0:                                             # narrow band
+        nd = int(rng.integers(1, 17)); lo = int(rng.integers(-40, 40)); offs = np.arange(lo, lo + nd)
+        ncols = int(rng.choice([1, 5, 32, 40]))
+    elif kind == 1:                                           # wide band, many columns
+        nd = int(rng.integers(24, 150)); lo = int(rng.integers(-100, 20)); offs = np.arange(lo, lo + nd)
+        ncols = int(rng.choice([64, 100, 130]))
+    else:                                                     # convolution pattern
+        px, fs = int(rng.choice([64, 100, 128])), int(rng.choice([5, 8, 11]))
+        offs = np.array([i * px + j for i in range(fs) for j in range(fs)]) - (px + 1) * (fs // 2)
+        ncols = int(rng.choice([3, 14, 20]))
+    offs = offs.astype(np.int32)
+    A = make_dia(rng, h, w, offs, 1, stride=h)
+    trans = "t" if rng.integers(0, 2) else "n"
+    fab, fc = float(rng.choice([1.0, 2.0])), float(rng.choice([0.0, 1.3]))
+    rows_b, rows_c = (h, w) if trans == "t" else (w, h)
+    B = F(rng.standard_normal((rows_b, ncols)))
+    C0 = F(rng.standard_normal((rows_c, ncols)))
+    want = C0.copy(order="F")
+    ho.prod(want, A, B, trans, fab, fc, 8)
+    Cd = cb.to_device(C0)
+    cb.prod(Cd, to_dev_dia(A), cb.to_device(B), trans, "n", fab, fc, cb.MODE_EXACT)
+    assert_bits_equal(cb.to_host(Cd), want, "seed %d: prod %s h=%d w=%d nd=%d ncols=%d" %
+                      (seed, trans, h, w, offs.size, ncols))
