@@ -140,8 +140,17 @@ class tensor {
     const reference_type operator()(index_type i) const { return reference_type(m_ptr + i); }
     reference_type operator()(index_type i, index_type j) { return reference_type(m_ptr + offset2(i, j)); }
     const reference_type operator()(index_type i, index_type j) const { return reference_type(m_ptr + offset2(i, j)); }
+    reference_type operator()(index_type i, index_type j, index_type k) { return reference_type(m_ptr + offset3(i, j, k)); }
+    const reference_type operator()(index_type i, index_type j, index_type k) const {
+        return reference_type(m_ptr + offset3(i, j, k));
+    }
 
   private:
+    // element (i, j, k) of a 3-D tensor: the last index runs fastest in row-major storage, the first in column-major
+    size_t offset3(index_type i, index_type j, index_type k) const {
+        return std::is_same<L, column_major>::value ? ((size_t)k * m_shape[1] + j) * m_shape[0] + i
+                                                    : ((size_t)i * m_shape[1] + j) * m_shape[2] + k;
+    }
     size_t offset2(index_type i, index_type j) const {
         return std::is_same<L, column_major>::value ? (size_t)j * m_shape[0] + i : (size_t)i * m_shape[1] + j;
     }

@@ -1,7 +1,7 @@
 // C++ tests of the CUV surface over libcuvdia.so.  They follow CUV's own tests of this path - same
 // fixtures, same "device object vs host object of the same template" pattern:
 //   src/tests/spmv.cpp:49-143, src/tests/densedense_to_dia.cpp:50-197, src/tests/dia_mat.cpp:48-132,
-//   src/tests/convert.cpp:110-129, src/tests/matrix_op.cpp:80-105,858-924, src/tests/optimize.cpp:59-121.
+//   src/tests/convert.cpp:110-129, src/tests/matrix_op.cpp:80-105,574-628,858-924, src/tests/optimize.cpp:59-121.
 // The host halves come from the CPU oracle (oracle/cuv_host_reference.hpp).  Exit code 0 = all passed.
 #include <cmath>
 #include <cstdio>
@@ -292,6 +292,41 @@ static void test_learn_step() {
     CHECK(bad == 0);
 }
 
+// ---- matrix_op.cpp:574-628: reductions of a 3-D tensor (the leading or the trailing dimension survives) --------
+static void test_reduce_3d() {
+    tensor<float, dev_memory_space> Md(extents[5][4][3]);
+    tensor<float, host_memory_space> Mh(extents[5][4][3]);
+    sequence(Md); sequence(Mh);
+    {
+        tensor<float, dev_memory_space> vd(extents[3]);
+        tensor<float, host_memory_space> vh(extents[3]);
+        sequence(vd); sequence(vh);
+        reduce_to_row(vd, Md);
+        reduce_to_row(vh, Mh);
+        for (int k = 0; k < 3; k++) {
+            float sum = 0.f;
+            for (int i = 0; i < 5; i++)
+                for (int j = 0; j < 4; j++) sum += (float)Mh(i, j, k);
+            CHECK(std::fabs((float)vd[k] - (float)vh[k]) <= 1e-4f * std::fabs((float)vh[k]));
+            CHECK(std::fabs((float)vh[k] - sum) <= 1e-4f * std::fabs(sum));
+        }
+    }
+    {
+        tensor<float, dev_memory_space> vd(extents[5]);
+        tensor<float, host_memory_space> vh(extents[5]);
+        sequence(vd); sequence(vh);
+        reduce_to_col(vd, Md);
+        reduce_to_col(vh, Mh);
+        for (int i = 0; i < 5; i++) {
+            float sum = 0.f;
+            for (int j = 0; j < 4; j++)
+                for (int k = 0; k < 3; k++) sum += (float)Mh(i, j, k);
+            CHECK(std::fabs((float)vd[i] - (float)vh[i]) <= 1e-4f * std::fabs((float)vh[i]));
+            CHECK(std::fabs((float)vh[i] - sum) <= 1e-4f * std::fabs(sum));
+        }
+    }
+}
+
 int main() {
     try {
         initCUDA(0);
@@ -301,6 +336,7 @@ int main() {
         reduce_sweep<column_major>("column_major");
         reduce_sweep<row_major>("row_major");
         test_tensor_ops();
+        test_reduce_3d();
         test_learn_step();
         exitCUDA();
     } catch (const std::exception& e) {
