@@ -14,8 +14,8 @@ CUV's host code) on all host cores on a bounded batch slice of the same workload
 
 Other cases (single routines, used for profiling and for the per-configuration table):
 ``--case prod_n|prod_t|dd2dia|reduce|glue|update`` on the band shape given by --units/--num-dia/--batch, and
-``--case cfg0|cfg1|cfg2|rbm_cfg3`` for the other BASELINE configurations, ``--case spmv_speed_n|spmv_speed_t`` for
-the reference's own speed fixture (a convolution-pattern matrix).
+``--case cfg0|cfg1|cfg2|rbm_cfg3`` for the other BASELINE configurations, ``--case spmv_speed_n|spmv_speed_t|dd2dia_speed``
+for the reference's own speed fixtures (convolution-pattern matrices).
 """
 import argparse
 import json
@@ -507,6 +507,12 @@ def measure_single(args, cfg):
         h, w, nb, rf = px * px, 16 * px * px, 14, 1
         offs = np.array([i * px + j for _ in range(nm) for i in range(fs) for j in range(fs)], dtype=np.int32)
         op = "prod_n" if case == "spmv_speed_n" else "prod_t"
+    elif case == "dd2dia_speed":
+        # the reference's densedense_to_dia speed fixture (src/tests/densedense_to_dia_speed.cpp:65-106): a 28x28
+        # image, two output maps, 8x8 filters stored as offsets i*28 + j once per map, 96 images
+        h, w, nb, rf = 784, 2 * 784, 96, 1
+        offs = np.array([i * 28 + j for _ in range(2) for i in range(8) for j in range(8)], dtype=np.int32)
+        op = "dd2dia"
     else:
         h = w = cfg["units"]; nb = cfg["batch"]; rf = 1
         offs = band_offsets(cfg["num_dia"]); op = case
@@ -527,7 +533,7 @@ def measure_single(args, cfg):
         fn = lambda: cb.prod(Y, A, X, "t", "n", fa, fc, mode)
         byts, flops = 4 * (nnz + nd + h * nb + w * nb * (2 if fc else 1)), 2.0 * nnz * nb
     elif op == "dd2dia":
-        fa, fc = (0.01, 0.9) if case == "cfg2" else (1.0 / nb, 0.0)
+        fa, fc = (0.01, 0.9) if case == "cfg2" else (1.0, 0.0) if case == "dd2dia_speed" else (1.0 / nb, 0.0)
         fn = lambda: cb.densedense_to_dia(A, None, X, Y, fa, fc)
         byts, flops = 4 * (h * nb + w * nb + nd + nnz * (2 if fc else 1)), 2.0 * nnz * nb
     elif op == "reduce":
@@ -598,7 +604,7 @@ def measure_single(args, cfg):
             elif op == "prod_t":
                 ho.prod(Yh, Ah, Xh, "t", fa, fc, nt)
             elif op == "dd2dia":
-                ho.densedense_to_dia(Ah, Xh, Yh, 0.01, 0.9, nthreads=nt)
+                ho.densedense_to_dia(Ah, Xh, Yh, fa, fc, nthreads=nt)
             else:
                 ho.reduce_to_col(vh, Xh, ho.RF_ADD, 1.0, 0.0, nt)
             cpu["ms_%s_threads" % label] = (time.perf_counter() - t0) * 1e3

@@ -68,12 +68,18 @@ inline void spmv(tensor<float, dev_memory_space>& dst, const dia_matrix<float, d
 
 // ---- reductions ------------------------------------------------------------------------------------------
 namespace detail {
-// src viewed as n_strided lines of n_contig contiguous floats (matrix_ops_reduce.cu:348-379)
-template <class L> inline void reduce_dims(const tensor<float, dev_memory_space, L>& m, long long& n_contig, long long& n_strided) {
+// src viewed as n_strided lines of n_contig contiguous floats.  A tensor of more than two dimensions is reduced
+// like the matrix that keeps the surviving dimension and flattens the others (matrix_ops_reduce.cu:228-231,348-379):
+// reduce_to_col keeps the first dimension, reduce_to_row the last.  Returns whether the reduction runs over the
+// strided direction (the outputs are then the contiguous one).
+template <class M, class L>
+inline bool reduce_dims(const tensor<float, M, L>& m, bool keep_first, long long& n_contig, long long& n_strided) {
     const bool cm = std::is_same<L, column_major>::value;
-    const long long first = m.shape(0), rest = m.size() / m.shape(0);
-    const long long last = m.shape(m.ndim() - 1), front = m.size() / m.shape(m.ndim() - 1);
-    if (cm) { n_contig = first; n_strided = rest; } else { n_contig = last; n_strided = front; }
+    const long long kept = keep_first ? m.shape(0) : m.shape(m.ndim() - 1), others = m.size() / kept;
+    const bool kept_is_contiguous = keep_first ? cm : !cm;
+    if (kept_is_contiguous) { n_contig = kept; n_strided = others; return true; }
+    n_contig = others; n_strided = kept;
+    return false;
 }
 void reduce_host(tensor<float, host_memory_space>& v, const float* m, long long n_contig, long long n_strided,
                  bool over_strided, reduce_functor rf, float factNew, float factOld);   // reference host code
@@ -85,8 +91,7 @@ void reduce_to_col(tensor<float, dev_memory_space>& dst, const tensor<float, dev
                    reduce_functor rf = RF_ADD, const float& factNew = 1.f, const float& factOld = 0.f) {
     cuvAssert(src.ptr() != NULL);
     long long nc, ns;
-    detail::reduce_dims(src, nc, ns);
-    const bool over_strided = std::is_same<L, column_major>::value;    // outputs = first dimension
+    const bool over_strided = detail::reduce_dims(src, true, nc, ns);
     cuvAssert((long long)dst.size() == (over_strided ? nc : ns));
     cuvdia_check(cuvdia_reduce_f32(dst.ptr(), src.ptr(), nc, ns, over_strided ? 1 : 0, (int)rf, factNew, factOld, 0));
     cuvSafeCall(cudaDeviceSynchronize());
@@ -97,8 +102,7 @@ void reduce_to_row(tensor<float, dev_memory_space>& dst, const tensor<float, dev
                    reduce_functor rf = RF_ADD, const float& factNew = 1.f, const float& factOld = 0.f) {
     cuvAssert(src.ptr() != NULL);
     long long nc, ns;
-    detail::reduce_dims(src, nc, ns);
-    const bool over_strided = !std::is_same<L, column_major>::value;   // outputs = last dimension
+    const bool over_strided = detail::reduce_dims(src, false, nc, ns);
     cuvAssert((long long)dst.size() == (over_strided ? nc : ns));
     cuvdia_check(cuvdia_reduce_f32(dst.ptr(), src.ptr(), nc, ns, over_strided ? 1 : 0, (int)rf, factNew, factOld, 0));
     cuvSafeCall(cudaDeviceSynchronize());
@@ -106,16 +110,16 @@ void reduce_to_row(tensor<float, dev_memory_space>& dst, const tensor<float, dev
 template <class L>
 void reduce_to_col(tensor<float, host_memory_space>& dst, const tensor<float, host_memory_space, L>& src,
                    reduce_functor rf = RF_ADD, const float& factNew = 1.f, const float& factOld = 0.f) {
-    const bool cm = std::is_same<L, column_major>::value;
-    const long long nc = cm ? src.shape(0) : src.shape(src.ndim() - 1), ns = src.size() / nc;
-    detail::reduce_host(dst, src.ptr(), nc, ns, cm, rf, factNew, factOld);
+    long long nc, ns;
+    const bool over_strided = detail::reduce_dims(src, true, nc, ns);
+    detail::reduce_host(dst, src.ptr(), nc, ns, over_strided, rf, factNew, factOld);
 }
 template <class L>
 void reduce_to_row(tensor<float, host_memory_space>& dst, const tensor<float, host_memory_space, L>& src,
                    reduce_functor rf = RF_ADD, const float& factNew = 1.f, const float& factOld = 0.f) {
-    const bool cm = std::is_same<L, column_major>::value;
-    const long long nc = cm ? src.shape(0) : src.shape(src.ndim() - 1), ns = src.size() / nc;
-    detail::reduce_host(dst, src.ptr(), nc, ns, !cm, rf, factNew, factOld);
+    long long nc, ns;
+    const bool over_strided = detail::reduce_dims(src, false, nc, ns);
+    detail::reduce_host(dst, src.ptr(), nc, ns, over_strided, rf, factNew, factOld);
 }
 
 }  // namespace cuv
