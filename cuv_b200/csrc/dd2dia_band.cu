@@ -13,8 +13,9 @@
 // that lies on a stored diagonal inside the matrix is written to its DIA cell (cells outside the
 // diagonals' ranges are never touched, matrix_ops/densedense_to_sparse.cu:104-119); with a batch
 // split the partial tiles go to plan-owned scratch and dd2dia_combine_kernel adds them in split
-// order.  The two triangular end tiles of each row block compute products the band does not need;
-// that is the price of the dense formulation (128/nd of the work).
+// order.  The two triangular end tiles of each row block compute products the band does not need -
+// the price of the dense formulation (128/nd of the work); the quadrant of an end tile that lies
+// entirely outside the band is left out, which takes a quarter off that price.
 #include <cuda.h>
 
 #include "cuvdia_internal.cuh"
@@ -58,6 +59,34 @@ struct DdBandParams {
     int* status;
 };
 
+// One stage: 32 batch columns of the 8 x 8 outer product of a thread.  SKIP names a quadrant of the tile that lies
+// entirely outside the band and is left out (block-uniform): 1 = rows 64.. x columns ..63 (the first tile of a
+// row block, below the first diagonal), 2 = rows ..63 x columns 64.. (the last tile, above the last diagonal).
+template <int SKIP>
+__device__ __forceinline__ void dd_band_stage(const float* xs, const float* hs, float2 (&acc)[8][4]) {
+    using namespace db;
+#pragma unroll 8
+    for (int b = 0; b < KB; b++) {
+        const float4 x0 = *reinterpret_cast<const float4*>(xs + b * TI);
+        const float4 x1 = *reinterpret_cast<const float4*>(xs + b * TI + 64);
+        const float4 h0 = *reinterpret_cast<const float4*>(hs + b * TJ);
+        const float4 h1 = *reinterpret_cast<const float4*>(hs + b * TJ + 64);
+        const float x[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+        const float2 hp[4] = {make_float2(h0.x, h0.y), make_float2(h0.z, h0.w), make_float2(h1.x, h1.y),
+                              make_float2(h1.z, h1.w)};
+#pragma unroll
+        for (int ii = 0; ii < 8; ii++) {
+            const float2 xx = make_float2(x[ii], x[ii]);
+#pragma unroll
+            for (int jp = 0; jp < 4; jp++) {
+                if (SKIP == 1 && ii >= 4 && jp < 2) continue;
+                if (SKIP == 2 && ii < 4 && jp >= 2) continue;
+                acc[ii][jp] = __ffma2_rn(xx, hp[jp], acc[ii][jp]);
+            }
+        }
+    }
+}
+
 __global__ void __launch_bounds__(db::THREADS, 2)
 dd2dia_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                    const DdBandParams P) {
@@ -79,6 +108,12 @@ dd2dia_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
     const int nch_all = (P.ncols + KB - 1) / KB;
     const int ch0 = (int)((long long)nch_all * z / P.nsplit), ch1 = (int)((long long)nch_all * (z + 1) / P.nsplit);
     const int nch = ch1 - ch0;
+
+    // A cell (row ir, column jc of the tile) is on a stored diagonal iff 0 <= jc - ir - rem + 128*t < nd.  In the
+    // first tile of a row block the quadrant rows 64.. x columns ..63 never is; in the last one the quadrant
+    // rows ..63 x columns 64.. is not either when the band ends at or before the tile's main diagonal.
+    const int dlast = P.nd + P.rem - TJ * (int)blockIdx.x;        // cells of this tile need jc - ir < dlast
+    const int skip = blockIdx.x == 0 ? 1 : (blockIdx.x == gridDim.x - 1 && dlast <= 1) ? 2 : 0;
 
     constexpr unsigned TX_BYTES = sizeof(float) * 2 * TILE_FLOATS;
     auto issue = [&](int c) {
@@ -120,22 +155,9 @@ dd2dia_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
         }
         const float* xs = Xs0 + s * TILE_FLOATS + 4 * R;
         const float* hs = Hs0 + s * TILE_FLOATS + 4 * cg;
-#pragma unroll 8
-        for (int b = 0; b < KB; b++) {
-            const float4 x0 = *reinterpret_cast<const float4*>(xs + b * TI);
-            const float4 x1 = *reinterpret_cast<const float4*>(xs + b * TI + 64);
-            const float4 h0 = *reinterpret_cast<const float4*>(hs + b * TJ);
-            const float4 h1 = *reinterpret_cast<const float4*>(hs + b * TJ + 64);
-            const float x[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-            const float2 hp[4] = {make_float2(h0.x, h0.y), make_float2(h0.z, h0.w), make_float2(h1.x, h1.y),
-                                  make_float2(h1.z, h1.w)};
-#pragma unroll
-            for (int ii = 0; ii < 8; ii++) {
-                const float2 xx = make_float2(x[ii], x[ii]);
-#pragma unroll
-                for (int jp = 0; jp < 4; jp++) acc[ii][jp] = __ffma2_rn(xx, hp[jp], acc[ii][jp]);
-            }
-        }
+        if (skip == 0) dd_band_stage<0>(xs, hs, acc);
+        else if (skip == 1) dd_band_stage<1>(xs, hs, acc);
+        else dd_band_stage<2>(xs, hs, acc);
         // hand the stage back: one arrival per warp; only the issuing thread waits for all of them, so the
         // other warps run ahead into the stages that are already loaded instead of meeting a block barrier
         __syncwarp();
