@@ -61,7 +61,8 @@ struct DdBandParams {
 
 // One stage: 32 batch columns of the 8 x 8 outer product of a thread.  SKIP names a quadrant of the tile that lies
 // entirely outside the band and is left out (block-uniform): 1 = rows 64.. x columns ..63 (the first tile of a
-// row block, below the first diagonal), 2 = rows ..63 x columns 64.. (the last tile, above the last diagonal).
+// row block, below the first diagonal), 2 = rows ..63 x columns 64.. (the last tile, above the last diagonal),
+// 3 = everything but rows 64.. x columns ..63 (a last tile that the band only touches in that corner).
 template <int SKIP>
 __device__ __forceinline__ void dd_band_stage(const float* xs, const float* hs, float2 (&acc)[8][4]) {
     using namespace db;
@@ -81,6 +82,7 @@ __device__ __forceinline__ void dd_band_stage(const float* xs, const float* hs, 
             for (int jp = 0; jp < 4; jp++) {
                 if (SKIP == 1 && ii >= 4 && jp < 2) continue;
                 if (SKIP == 2 && ii < 4 && jp >= 2) continue;
+                if (SKIP == 3 && !(ii >= 4 && jp < 2)) continue;
                 acc[ii][jp] = __ffma2_rn(xx, hp[jp], acc[ii][jp]);
             }
         }
@@ -111,9 +113,10 @@ dd2dia_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
 
     // A cell (row ir, column jc of the tile) is on a stored diagonal iff 0 <= jc - ir - rem + 128*t < nd.  In the
     // first tile of a row block the quadrant rows 64.. x columns ..63 never is; in the last one the quadrant
-    // rows ..63 x columns 64.. is not either when the band ends at or before the tile's main diagonal.
+    // rows ..63 x columns 64.. is not either when the band ends at or before the tile's main diagonal, and when it
+    // ends 63 or more diagonals before it only the quadrant rows 64.. x columns ..63 is left.
     const int dlast = P.nd + P.rem - TJ * (int)blockIdx.x;        // cells of this tile need jc - ir < dlast
-    const int skip = blockIdx.x == 0 ? 1 : (blockIdx.x == gridDim.x - 1 && dlast <= 1) ? 2 : 0;
+    const int skip = blockIdx.x == 0 ? 1 : (blockIdx.x == gridDim.x - 1 && dlast <= 1) ? (dlast <= -63 ? 3 : 2) : 0;
 
     constexpr unsigned TX_BYTES = sizeof(float) * 2 * TILE_FLOATS;
     auto issue = [&](int c) {
@@ -157,7 +160,8 @@ dd2dia_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
         const float* hs = Hs0 + s * TILE_FLOATS + 4 * cg;
         if (skip == 0) dd_band_stage<0>(xs, hs, acc);
         else if (skip == 1) dd_band_stage<1>(xs, hs, acc);
-        else dd_band_stage<2>(xs, hs, acc);
+        else if (skip == 2) dd_band_stage<2>(xs, hs, acc);
+        else dd_band_stage<3>(xs, hs, acc);
         // hand the stage back: one arrival per warp; only the issuing thread waits for all of them, so the
         // other warps run ahead into the stages that are already loaded instead of meeting a block barrier
         __syncwarp();
