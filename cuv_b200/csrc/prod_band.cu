@@ -105,6 +105,7 @@ struct BandParams {
     int ncols, ldc;
     int rem;                  // lo mod 4 (non-negative): shift that keeps TMA x coordinates 16-byte aligned
     int nchunks;
+    int last_groups;          // 4-step groups of the last chunk that contain steps of the band (1..KC/4)
     float fa, fc;
     int vec_c;                // C allows 128-bit accesses
     float* C;
@@ -294,8 +295,10 @@ prod_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         if (!ok) { if (lane == 0 && P.status) *P.status = 1; return; }
         const float* bsp = Bs0 + s * BSF + cg * WR + (TRANS ? (r0 + KC - 4) : r0);
         const float* asp = As0 + s * AS_FLOATS + r0;
+        // the steps past the band's last one (the tail of the last chunk) have zero coefficients: leave them out
+        const int ng = c == nch - 1 ? P.last_groups : KC / 4;
 #pragma unroll G_UNROLL
-        for (int g = 0; g < KC / 4; g++) {
+        for (int g = 0; g < ng; g++) {
             float4 bw[8];
 #pragma unroll
             for (int cc = 0; cc < 8; cc++)
@@ -398,6 +401,7 @@ static int launch_band_t(const cuvdia_plan* p, const float* A, const float* B, i
     P.ncols = ncols; P.ldc = ldc;
     P.rem = ((p->band_lo % 4) + 4) % 4;
     P.nchunks = (p->nd + P.rem + 7 + KC - 1) / KC;
+    P.last_groups = ((p->nd + P.rem + 7) - (P.nchunks - 1) * KC + 3) / 4;
     P.fa = fa; P.fc = fc;
     P.vec_c = (al16(C) && ldc % 4 == 0) ? 1 : 0;
     P.C = C; P.status = p->d_status;
