@@ -7,14 +7,13 @@
 // scattered offsets no two cells of a thread share a B row, so B values cannot be reused from
 // registers and the ceiling is one shared-memory word per multiply-add (a quarter of the FP32
 // rate).  What can be saved is the traffic behind it: the plain kernel fetches every B value from
-// L2 once per cell.  Here the diagonals are taken in ascending order of their offsets, 32 (or 16) at a
-// time; a block owns 256 rows (512, two per thread, where the row factor divides 256) and one such
-// group, and stages, per 8 batch columns, its
-// tile of A and the window of B rows the group can touch (rows i/rf + off_min .. off_max of the
-// group; rows outside B arrive as zeros) with 16-byte asynchronous copies, one chunk ahead of the
-// arithmetic (two stages).  A staged B value then serves
-// every cell of the block on its row - about 256*32/window times - and each thread keeps 32
-// running sums.  Several blocks share an SM, so one block's copies overlap another's arithmetic.
+// L2 once per cell.  Here the diagonals are taken in ascending order of their offsets, 32 (or 16)
+// at a time; a block owns 256 rows (512, two per thread, where the row factor divides 256) and one
+// such group, and stages, per 8 batch columns, its tile of A and the window of B rows the group can
+// touch (rows i/rf + off_min .. off_max of the group; rows outside B arrive as zeros) with 16-byte
+// asynchronous copies, one chunk ahead of the arithmetic (two stages).  A staged B value then serves
+// every cell of the block on its row - about rows*32/window times - and each thread keeps 32 running
+// sums.  Two blocks share an SM, so one block's copies overlap the other's arithmetic.
 // The batch is summed in column order within a split and the splits in order by a second kernel,
 // so the result does not depend on scheduling.  Only cells inside a diagonal's valid range are
 // written (matrix_ops/densedense_to_sparse.cu:104-119).

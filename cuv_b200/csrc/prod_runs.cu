@@ -13,9 +13,9 @@
 // shared memory with TMA tile loads (cp.async.bulk.tensor, no multicast; rows or diagonals outside
 // the operands arrive as zeros) and full/empty mbarriers with bounded waits, two blocks per SM, and
 // asks for the coefficient tiles a dozen passes ahead to be brought into L2 (tensor prefetch), while
-// 128 consumer threads compute: a thread owns 4 rows and 8 of the columns, reads the 8 x 4 coefficients
-// of the pass and, per column, the 11 dense rows its 4 x 8 cells touch as four aligned 128-bit shared loads into a
-// register window (cell (row j, diagonal k) reads entry L + j + k, L = alignment of the run's first
+// 128 consumer threads compute: a thread owns 4 rows and 8 of the columns, reads the 8 x 4
+// coefficients of the pass and, per column, the 11 dense rows its 4 x 8 cells touch as three or four
+// aligned 128-bit shared loads into a register window (cell (row j, diagonal k) reads entry L + j + k, L = alignment of the run's first
 // offset, a template parameter so that the index is a compile-time constant), then issues 32
 // multiply-adds.  Passes that touch the border of the matrix, or are shorter than 8, zero the
 // coefficients of cells outside the matrix (the dense rows they would read are outside too and
