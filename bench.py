@@ -131,6 +131,23 @@ class ClockSampler:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["clock sampling unavailable"]}
 
 
+def fp32_peak_tflops(fused=True):
+    """FP32 issue ceiling of the current device in TFLOP/s (a multiply-add = 2 flops), measured by the bench-side
+    library ``libbench_fp32_peak.so`` (bench_fp32_peak.cu; not part of the product library): a register-resident
+    loop of fused multiply-adds, or of separate multiplies and adds (the EXACT arithmetic of prod)."""
+    import ctypes
+    lib = os.path.join(ROOT, "libbench_fp32_peak.so")
+    if not os.path.exists(lib):
+        subprocess.check_call(["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "--fmad=false", "-shared",
+                               "-Xcompiler", "-fPIC", os.path.join(ROOT, "bench_fp32_peak.cu"), "-o", lib])
+    L = ctypes.CDLL(lib)
+    out = ctypes.c_float()
+    rc = L.bench_fp32_peak_tflops(1 if fused else 0, ctypes.byref(out))
+    if rc != 0:
+        raise RuntimeError("bench_fp32_peak_tflops failed with CUDA error %d" % rc)
+    return float(out.value)
+
+
 def band_offsets(nd):
     import numpy as np
     return np.arange(-(nd // 2), nd - nd // 2, dtype=np.int32)
@@ -230,6 +247,66 @@ def workload_name(case, cfg):
 # GPU arm
 # ---------------------------------------------------------------------------------------------------
 
+def binding_bound(byts, flops, ms, hbm_peak, fp32_peak):
+    """SURVEY-style roofline position of one routine: t_min = max(bytes / HBM peak, flops / FP32 peak); the larger
+    term names the bound and frac = t_min / t_measured."""
+    t_mem, t_fp = byts / (hbm_peak * 1e9), flops / (fp32_peak * 1e12)
+    t = ms * 1e-3
+    return {"bound": "fp32" if t_fp > t_mem else "hbm", "frac": max(t_mem, t_fp) / t,
+            "t_min_us": max(t_mem, t_fp) * 1e6, "t_mem_us": t_mem * 1e6, "t_fp32_us": t_fp * 1e6,
+            "hbm_frac": t_mem / t, "fp32_frac": t_fp / t}
+
+
+def shard_inputs(cb, torch, units, nb, dev, shard):
+    """The batch columns of shard ``shard`` of the global batch: V0 ~ Bernoulli(0.3), U_h, U_v ~ U[0,1).  Every
+    shard has its own seed, so any rank can rebuild any other rank's columns (the unsharded check does)."""
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(2000 + shard)
+    V0 = cb.colmajor_empty(units, nb, dev)
+    tmp = torch.rand((nb, units), device=dev, generator=gen)
+    V0.t().copy_((tmp < 0.3).float())
+    U_h, U_v = cb.colmajor_empty(units, nb, dev), cb.colmajor_empty(units, nb, dev)
+    U_h.t().copy_(torch.rand((nb, units), device=dev, generator=gen))
+    U_v.t().copy_(torch.rand((nb, units), device=dev, generator=gen))
+    return V0, U_h, U_v
+
+
+def check_allreduce(cb, rbm, torch, dist, step, V0, U_h, U_v, W, units, nd, batch, world, rank, dev, mode):
+    """Outside every timed region: (1) three diagonals (first, middle, last) of the all-reduced gradient against the
+    rank-order sum of the per-rank partial values gathered to rank 0; (2) on rank 0, the whole all-reduced gradient and
+    the bias gradients against the unsharded step on the full batch (all shards rebuilt from their seeds)."""
+    stride = W.stride
+    some = [0, nd // 2, nd - 1]
+    step.step(V0, U_h, U_v)
+    part = torch.cat([step.G.vec[k * stride:(k + 1) * stride] for k in some]).clone()
+    parts = [torch.empty_like(part) for _ in range(world)] if rank == 0 else None
+    dist.gather(part, parts, dst=0)
+    step.allreduce()
+    torch.cuda.synchronize()
+    if rank != 0:
+        return None
+    got = torch.cat([step.G.vec[k * stride:(k + 1) * stride] for k in some])
+    want = parts[0].clone()
+    for q in parts[1:]:
+        want += q
+    d1 = float((got - want).abs().max().item())
+    full_in = [shard_inputs(cb, torch, units, batch // world, dev, s) for s in range(world)]
+    cat = lambda k: torch.cat([f[k].t() for f in full_in], dim=0).t()        # column blocks side by side
+    FV0, FUh, FUv = cat(0), cat(1), cat(2)
+    del full_in
+    full = rbm.SparseRBMStep(W, batch, batch, mode, dev)
+    full.step(FV0, FUh, FUv)
+    torch.cuda.synchronize()
+    d2 = float((step.G.vec - full.G.vec).abs().max().item())
+    d3 = float((step.bias_grad - full.bias_grad).abs().max().item())
+    ok = d1 <= 2e-6 and d2 <= 2e-6 and d3 <= 2e-6
+    del full, FV0, FUh, FUv
+    torch.cuda.empty_cache()
+    return {"result": "ok" if ok else "MISMATCH", "tolerance_abs": 2e-6,
+            "max_abs_diff_vs_sum_of_gathered_partials_3_diagonals": d1,
+            "max_abs_diff_G_vs_unsharded_step_on_rank0": d2, "max_abs_diff_bias_grad_vs_unsharded_step_on_rank0": d3}
+
+
 def run_ours(args, cfg):
     import numpy as np
     import torch
@@ -261,21 +338,17 @@ def run_ours(args, cfg):
     gen.manual_seed(1004)                      # identical weights on every rank
     W = cb.dev_dia_matrix_f(units, units, band_offsets(nd), units, 1, device=dev)
     W.vec.normal_(0.0, 0.01, generator=gen)
-    gen.manual_seed(2000 + rank)               # rank-specific batch columns
-    V0 = cb.colmajor_empty(units, nb, dev)
-    tmp = torch.rand((nb, units), device=dev, generator=gen)
-    V0.t().copy_((tmp < 0.3).float())
-    U_h, U_v = cb.colmajor_empty(units, nb, dev), cb.colmajor_empty(units, nb, dev)
-    U_h.t().copy_(torch.rand((nb, units), device=dev, generator=gen))
-    U_v.t().copy_(torch.rand((nb, units), device=dev, generator=gen))
-    del tmp
-    step = rbm.SparseRBMStep(W, nb, batch, mode, dev)
-    work = rbm.algorithmic_work(units, units, nd, W.nnz, nb)
+    V0, U_h, U_v = shard_inputs(cb, torch, units, nb, dev, rank)        # this rank's batch columns
+    step = rbm.SparseRBMStep(W, nb, batch, mode, dev, keep_v1p=False)
+    # The metric counts the GLOBAL problem's algorithmic bytes at every N (strong scaling: value_N / value_1 is the
+    # ratio of the step times); `local` is this rank's share, used for the per-kernel figures.
+    work = rbm.algorithmic_work(units, units, nd, W.nnz, batch)
+    local_work = rbm.algorithmic_work(units, units, nd, W.nnz, nb)
 
     def one_step():
-        step.step(V0, U_h, U_v)
+        step.step(V0, U_h, U_v)                # one call of the C ABI: cuvdia_rbm_cd1_step_f32
         if world > 1:
-            step.allreduce()
+            step.allreduce()                   # cuvdia_allreduce_grad
 
     def barrier():
         torch.cuda.synchronize()
@@ -296,7 +369,6 @@ def run_ours(args, cfg):
     barrier()
     sampler = ClockSampler(local)
     sampler.start()
-    step.timers = {}
     launches0 = cb.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -308,8 +380,21 @@ def run_ours(args, cfg):
     clocks = sampler.stop()
     ms_total = max_over_ranks(e0.elapsed_time(e1))
     ms_step = ms_total / args.steps
+
+    # ---- the same kernels call by call with an event pair around each (outside the timed region) ----
+    step.timers = {}
+    for _ in range(3):
+        step.step(V0, U_h, U_v)
+    torch.cuda.synchronize()
     op_ms = {k: statistics.mean(event_ms(v)) for k, v in step.timers.items()}
     step.timers = None
+    ar_ms = None
+    if world > 1:
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        a0.record(); step.allreduce(); a1.record()
+        torch.cuda.synchronize()
+        ar_ms = max_over_ranks(a0.elapsed_time(a1))
 
     # ---- end to end: host buffers in, results out, every step ----
     e2e = None
@@ -355,19 +440,30 @@ def run_ours(args, cfg):
         steady_ms = max_over_ranks(s0.elapsed_time(s1)) / args.steps
         fed.run()                                        # consume the copy that is still queued
         torch.cuda.synchronize()
-        # the host link alone: one input matrix copied with nothing else running
-        l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        l0.record()
-        fed.inputs[0][0].t().copy_(hV0, non_blocking=True)
-        l1.record()
-        torch.cuda.synchronize()
-        link_gbs = units * nb * 4 / (l0.elapsed_time(l1) * 1e-3) / 1e9
-        e2e = {"value": world * work["bytes"] / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
-               "h2d_bytes_per_step": int(world * 3 * units * nb * 4),
+        # the host link alone: one step's three input matrices copied with no kernel running - first on this rank
+        # alone (rank 0), then on all ranks at once (what a step's input copies share when several GPUs hang off
+        # one host)
+        def copy_inputs_ms():
+            l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            l0.record()
+            for dst, src in zip(fed.inputs[0], (hV0, hUh, hUv)):
+                dst.t().copy_(src, non_blocking=True)
+            l1.record()
+            torch.cuda.synchronize()
+            return l0.elapsed_time(l1)
+        in_bytes = 3 * units * nb * 4
+        alone_ms = copy_inputs_ms() if rank == 0 else 0.0
+        barrier()
+        all_ms = max_over_ranks(copy_inputs_ms())
+        barrier()
+        e2e = {"value": work["bytes"] / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+               "h2d_bytes_per_step": int(world * in_bytes),
                "d2h_bytes_per_step": int((step.G.vec.numel() + step.bias_grad.numel()) * 4),
                "ms_per_step": e2e_ms,
                "ms_per_step_pipeline_primed": steady_ms,
-               "host_link_GB/s_one_copy_alone": link_gbs,
+               "host_link_GB/s_one_rank_alone": max_over_ranks(in_bytes / (alone_ms * 1e-3) / 1e9 if rank == 0 else 0.0),
+               "host_link_GB/s_all_ranks_at_once": world * in_bytes / (all_ms * 1e-3) / 1e9,
+               "ms_input_copies_all_ranks_at_once": all_ms,
                "how": "pinned host inputs (V0, U_h, U_v) copied to the device every step on a copy stream, overlapped "
                       "with the previous step's compute; gradients read back to pinned host memory every step"}
 
@@ -380,34 +476,67 @@ def run_ours(args, cfg):
     other_ms = {k: min(event_ms(v)) for k, v in step.timers.items() if k.startswith("prod")}
     step.mode, step.timers = mode, None
 
-    status = 0
-    if rank == 0:
-        import ctypes
-        st = ctypes.c_int()
-        cb._capi.check(cb._capi.lib().cuvdia_plan_status(W._plan, ctypes.byref(st)))
-        status = st.value
+    ar_check = None
+    if world > 1:
+        ar_check = check_allreduce(cb, rbm, torch, dist, step, V0, U_h, U_v, W, units, nd, batch, world, rank, dev, mode)
+
+    status = cb.plan_status(W) if rank == 0 else 0
 
     if rank != 0:
         if world > 1:
+            step._reducer.close()
             dist.destroy_process_group()
         return
 
     peak, peak_src = load_peaks()
-    fp32_fused = cb.fp32_peak_tflops(True)
-    fp32_split = cb.fp32_peak_tflops(False)
+    fp32_fused = fp32_peak_tflops(True)
+    fp32_split = fp32_peak_tflops(False)
     # dominant kernel: the banded prod (3 of the 5 large launches per step)
     prod_ms = (2 * op_ms["prod_n"] + op_ms["prod_t"]) / 3.0
-    prod_bytes = (2 * work["per_call_bytes"]["prod_n"] + work["per_call_bytes"]["prod_t"]) / 3.0
-    prod_flops = work["per_call_flops"]["prod_n"]
-    achieved = prod_bytes / (prod_ms * 1e-3) / 1e9
+    prod_bytes = (2 * local_work["per_call_bytes"]["prod_n"] + local_work["per_call_bytes"]["prod_t"]) / 3.0
+    prod_flops = local_work["per_call_flops"]["prod_n"]
     fp32_peak = fp32_fused if args.mode == "fast" else fp32_split
+    pos = binding_bound(prod_bytes, prod_flops, prod_ms, peak, fp32_peak)
     per_op = {}
     for k, ms in op_ms.items():
-        per_op[k] = {"ms": ms, "gbs": work["per_call_bytes"][k] / (ms * 1e-3) / 1e9}
-        if k in work["per_call_flops"]:
-            per_op[k]["tflops"] = work["per_call_flops"][k] / (ms * 1e-3) / 1e12
+        per_op[k] = {"ms": ms, "calls_per_step": {"prod_n": 2, "prod_t": 1, "dd2dia": 2, "glue": 3, "reduce": 1}.get(k),
+                     "gbs": local_work["per_call_bytes"]["reduce_v0" if k == "reduce" else k] / (ms * 1e-3) / 1e9}
+        if k in local_work["per_call_flops"]:
+            per_op[k]["tflops"] = local_work["per_call_flops"][k] / (ms * 1e-3) / 1e12
+            per_op[k]["roofline"] = binding_bound(local_work["per_call_bytes"][k], local_work["per_call_flops"][k], ms, peak,
+                                                  fp32_fused if (k == "dd2dia" or args.mode == "fast") else fp32_split)
+        else:
+            per_op[k]["hbm_frac"] = per_op[k]["gbs"] / peak
+    if ar_ms is not None:
+        n_ar = step.G.vec.numel() + step.bias_grad.numel()
+        per_op["allreduce"] = {"ms": ar_ms, "bytes": 4 * n_ar,
+                               "bus_GB/s": 4 * n_ar * 2.0 * (world - 1) / world / (ar_ms * 1e-3) / 1e9,
+                               "how": "one ncclAllReduce over the diagonals' values and both bias gradients (one buffer), "
+                                      "issued through cuvdia_allreduce_grad after the step; not overlapped: the last "
+                                      "densedense_to_dia finishes whole rows of all diagonals, not diagonal slabs"}
+    tflops = prod_flops / (prod_ms * 1e-3) / 1e12
+    if pos["bound"] == "fp32":
+        roof = {"bound": "fp32", "achieved": tflops, "peak": fp32_peak, "unit": "TFLOP/s", "frac": tflops / fp32_peak,
+                "peak_source": "measured on this device by bench_fp32_peak.cu (register-resident %s loop); "
+                               "MEASURED_PEAKS.json has no FP32 CUDA-core entry"
+                               % ("fused multiply-add" if args.mode == "fast" else "multiply + add")}
+    else:
+        roof = {"bound": "hbm", "achieved": prod_bytes / (prod_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                "frac": prod_bytes / (prod_ms * 1e-3) / 1e9 / peak, "peak_source": peak_src}
+    roof.update({
+        "kernel": "prod_band_kernel", "ms_per_launch": prod_ms,
+        "why_this_bound": "t_min = max(bytes / HBM peak, flops / FP32 peak) = max(%.0f, %.0f) us: no tensor cores on "
+                          "this path, so FP32 issue binds" % (pos["t_mem_us"], pos["t_fp32_us"]),
+        "hbm_achieved": prod_bytes / (prod_ms * 1e-3) / 1e9, "hbm_peak": peak, "hbm_unit": "GB/s",
+        "hbm_frac": prod_bytes / (prod_ms * 1e-3) / 1e9 / peak, "hbm_peak_source": peak_src,
+        # DRAM bytes per launch: the ncu capture of a smaller case of the same kernel (16384 rows, 512
+        # diagonals, 2048 columns: 267.1 MB of dram read+write for 301.7 MB algorithmic, see
+        # profiles/prod_n_units16384_nd512_batch2048.md) scaled by the algorithmic bytes of this launch
+        "traffic": prod_bytes * (267.1 / 301.7),
+        "traffic_source": "ncu dram__bytes_read+write of a smaller case (16384 rows, 512 diagonals, 2048 columns) "
+                          "scaled by the algorithmic bytes of this launch"})
     line = {
-        "metric": METRIC, "value": world * work["bytes"] / (ms_step * 1e-3) / 1e9, "unit": "GB/s",
+        "metric": METRIC, "value": work["bytes"] / (ms_step * 1e-3) / 1e9, "unit": "GB/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload_name(args.case, cfg), "units": units, "num_dia": nd, "row_fact": 1,
@@ -415,29 +544,23 @@ def run_ours(args, cfg):
                    "prod_arithmetic": args.mode + (" (fused multiply-add; bit-identical to the reference on this workload: "
                                                      "the dense operand of every product is 0/1)" if args.mode == "fast" else
                                                      " (separate multiply and add, reference order)"), "l2": "inputs larger than L2 (each activation matrix %.0f MB)"
-                   % (units * nb * 4 / 1e6)},
-        "gflops": world * work["flops"] / (ms_step * 1e-3) / 1e9,
-        "roofline": {"bound": "hbm", "kernel": "prod_band_kernel", "achieved": achieved, "peak": peak,
-                     "unit": "GB/s", "frac": achieved / peak,
-                     # DRAM bytes per launch: the ncu capture of a smaller case of the same kernel (16384 rows, 512
-                     # diagonals, 2048 columns: 267.1 MB of dram read+write for 301.7 MB algorithmic, see
-                     # profiles/prod_n_units16384_nd512_batch2048.md) scaled by the algorithmic bytes of this launch
-                     "traffic": prod_bytes * (267.1 / 301.7),
-                     "traffic_source": "ncu dram__bytes_read+write of a smaller case scaled by algorithmic bytes",
-                     "peak_source": peak_src,
-                     "ms_per_launch": prod_ms,
-                     "binding": "fp32 issue (no tensor cores on this path): %.1f TFLOP/s achieved of %.1f measured "
-                                "%s peak = %.2f" % (prod_flops / (prod_ms * 1e-3) / 1e12, fp32_peak,
-                                                    "fused" if args.mode == "fast" else "mul+add",
-                                                    prod_flops / (prod_ms * 1e-3) / 1e12 / fp32_peak)},
-        "fp32": {"achieved_tflops": prod_flops / (prod_ms * 1e-3) / 1e12, "peak_fused_tflops": fp32_fused,
-                 "peak_mul_add_tflops": fp32_split, "frac": prod_flops / (prod_ms * 1e-3) / 1e12 / fp32_peak},
+                   % (units * nb * 4 / 1e6),
+                   "algorithmic_bytes_per_step": work["bytes"],
+                   "bytes_counted": "the global problem's routines as the reference issues them (3 prod, 2 "
+                                    "densedense_to_dia, 4 reduce_to_col), the same number at every N"},
+        "gflops": work["flops"] / (ms_step * 1e-3) / 1e9,
+        "roofline": roof,
+        "fp32": {"achieved_tflops": tflops, "peak_fused_tflops": fp32_fused,
+                 "peak_mul_add_tflops": fp32_split, "frac": tflops / fp32_peak},
         "per_op": per_op,
         "prod_other_arithmetic": {"mode": "exact" if args.mode == "fast" else "fast",
                                   "ms": other_ms,
-                                  "tflops": {k: work["per_call_flops"][k] / (v * 1e-3) / 1e12 for k, v in other_ms.items()}},
+                                  "tflops": {k: local_work["per_call_flops"][k] / (v * 1e-3) / 1e12 for k, v in other_ms.items()}},
         "clocks": clocks, "gpu_launches": int(launches), "plan_status": status,
     }
+    if ar_check is not None:
+        line["allreduce_check"] = ar_check["result"]
+        line["allreduce_check_detail"] = ar_check
     if e2e:
         line["e2e"] = e2e
     if world == 1 and not args.no_extra:
@@ -454,6 +577,9 @@ def run_ours(args, cfg):
                            "arithmetic": args.mode if key != "densedense_to_dia" else "fused"}
         line["hbm_bound_shape"] = {"shape": "2^20 x 2^20, 16 diagonals, 32 batch columns (335 MB algorithmic, ~3 flop/B)",
                                    "peak_GB/s": peak, "routines": shapes}
+        # The other BASELINE configurations (single routines and the config-3 step), each against the roofline that
+        # binds it; parity for them is in the tests, these are their speeds in the same driver-run record.
+        line["configs"] = other_configs(args, cfg, peak, fp32_fused, fp32_split)
     if world == 1 and not args.no_cpu:
         sample = min(batch, args.cpu_sample_cols)
         t, threads, _ = cpu_rbm(units, nd, batch, sample, 1, 0)
@@ -465,7 +591,52 @@ def run_ours(args, cfg):
     sys.stdout.flush()
     os.write(real_stdout, (json.dumps(line) + "\n").encode())
     if world > 1:
+        step._reducer.close()
         dist.destroy_process_group()
+
+
+def other_configs(args, cfg, peak, fp32_fused, fp32_split):
+    """BASELINE configs 0-2 (single routines, timed as CUDA graphs of back-to-back launches, exact arithmetic) and
+    the config-3 RBM step, each with its binding roofline."""
+    import torch
+    import cuv_b200 as cb
+    from cuv_b200 import rbm
+    out = {}
+    for case in ("cfg0", "cfg1", "cfg2"):
+        sub = argparse.Namespace(**vars(args))
+        sub.case, sub.steps, sub.warmup, sub.flush_l2, sub.cpu, sub.mode = case, 10, 3, False, False, "exact"
+        r = measure_single(sub, cfg)
+        pk = fp32_fused if r["op"] == "dd2dia" else fp32_split
+        out[case] = {"routine": r["op"], "shape": "%dx%d, %d diagonals, row_fact %d, batch %d" % (
+                         r["h"], r["w"], r["num_dia"], r["row_fact"], r["batch"]),
+                     "us": r["ms"] * 1e3, "GB/s": r["gbs"], "TFLOP/s": r["tflops"], "timing": r["timing"],
+                     "arithmetic": "fused" if r["op"] == "dd2dia" else "exact",
+                     "roofline": binding_bound(r["bytes"], r["flops"], r["ms"], peak, pk)}
+        torch.cuda.empty_cache()
+    c3 = CASES["rbm_cfg3"]
+    units, nd, nb = c3["units"], c3["num_dia"], c3["batch"]
+    dev = torch.device("cuda", torch.cuda.current_device())
+    gen = torch.Generator(device=dev); gen.manual_seed(1003)
+    W = cb.dev_dia_matrix_f(units, units, band_offsets(nd), units, 1, device=dev)
+    W.vec.normal_(0.0, 0.01, generator=gen)
+    V0, U_h, U_v = shard_inputs(cb, torch, units, nb, dev, 0)
+    step = rbm.SparseRBMStep(W, nb, nb, cb.MODE_FAST, dev, keep_v1p=False)
+    for _ in range(3):
+        step.step(V0, U_h, U_v)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(20):
+        step.step(V0, U_h, U_v)
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / 20
+    work = rbm.algorithmic_work(units, units, nd, W.nnz, nb)
+    out["rbm_cfg3"] = {"routine": "CD-1 step", "shape": "%d units, %d diagonals, batch %d" % (units, nd, nb),
+                       "us": ms * 1e3, "GB/s": work["bytes"] / (ms * 1e-3) / 1e9, "TFLOP/s": work["flops"] / (ms * 1e-3) / 1e12,
+                       "arithmetic": "fast (0/1 operands: bit-identical to exact)", "timing": "20 steps back to back",
+                       "roofline": binding_bound(work["bytes"], work["flops"], ms, peak, fp32_fused)}
+    return out
 
 
 def run_single(args, cfg):
@@ -609,7 +780,8 @@ def measure_single(args, cfg):
                 ho.reduce_to_col(vh, Xh, ho.RF_ADD, 1.0, 0.0, nt)
             cpu["ms_%s_threads" % label] = (time.perf_counter() - t0) * 1e3
     return {"case": case, "op": op, "cpu_oracle": cpu, "h": h, "w": w, "num_dia": int(nd), "row_fact": rf, "batch": nb,
-            "mode": args.mode, "ms": ms, "ms_min": min(ts), "gbs": byts / (ms * 1e-3) / 1e9,
+            "mode": args.mode, "ms": ms, "ms_min": min(ts), "bytes": float(byts), "flops": float(flops),
+            "gbs": byts / (ms * 1e-3) / 1e9,
             "hbm_frac": byts / (ms * 1e-3) / 1e9 / peak, "tflops": flops / (ms * 1e-3) / 1e12,
             "l2_flushed": bool(args.flush_l2), "launches_per_timing": reps,
             "timing": "CUDA graph of %d back-to-back launches" % reps if reps > 1 else "single launch",

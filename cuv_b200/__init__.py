@@ -18,9 +18,9 @@ from ._capi import (CuvDiaError, MODE_EXACT, MODE_FAST, RF_ADD, RF_MEAN, RF_ADD_
                     RF_ARGMIN, RF_MIN, RF_MULT, RF_LOGADDEXP, RF_ADDEXP)
 
 __all__ = ["dev_dia_matrix_f", "host_dia_matrix_f", "convert", "pull", "save_dia_mat", "load_dia_mat", "dev_block_descriptor_f", "prod", "spmv", "densedense_to_dia", "reduce_to_col",
-           "reduce_to_row", "bias_sigmoid_sample", "prod_bias_sigmoid_sample", "axpby", "learn_step_weight_decay",
+           "reduce_to_row", "bias_sigmoid_sample", "bias_sigmoid_sample_sum", "prod_bias_sigmoid_sample", "axpby", "learn_step_weight_decay",
            "learn_step_weight_decay_momentum", "colmajor_empty", "to_device", "to_host",
-           "launch_count", "CuvDiaError", "MODE_EXACT", "MODE_FAST"]
+           "launch_count", "plan_status", "raise_if_gave_up", "CuvDiaError", "MODE_EXACT", "MODE_FAST"]
 
 
 def _torch():
@@ -34,14 +34,6 @@ def _stream():
 
 def _ptr(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else None
-
-
-def fp32_peak_tflops(fused=True, packed=False):
-    """Measured FP32 ceiling of the current device in TFLOP/s (multiply-add = 2 flops), with scalar or
-    packed-pair (f32x2) instructions."""
-    out = ctypes.c_float()
-    _capi.check(_capi.lib().cuvdia_fp32_peak_tflops((1 if fused else 0) + (2 if packed else 0), ctypes.byref(out)))
-    return float(out.value)
 
 
 def launch_count():
@@ -257,8 +249,30 @@ class dev_block_descriptor_f:
 
 # ---- operations --------------------------------------------------------------------------------------
 
-def prod(C, A, B, transA="n", transB="n", factAB=1.0, factC=0.0, mode=MODE_EXACT):
-    """C = factC*C + factAB*op(A)*B (matrix_ops/matrix_ops.hpp:118-119, matrix_ops/spmv.cu:221-247)."""
+def plan_status(A):
+    """The health word of the matrix's plan (blocking): 0, or the code left by a kernel that gave up a bounded
+    wait on an asynchronous copy and returned with its output incomplete."""
+    st = ctypes.c_int()
+    _capi.check(_capi.lib().cuvdia_plan_status(A._plan, ctypes.byref(st)))
+    return int(st.value)
+
+
+def raise_if_gave_up(A):
+    """Blocking check after operations on ``A``: waits for the device, and if a kernel of the plan gave up a bounded
+    wait, clears the word and raises, as CUV throws from a failed blocking operation (tools/cuv_general.cu:51-61).
+    The calls of this module are stream-ordered and do not look at the word themselves unless asked to
+    (``check_status=True``), because looking means waiting for the device."""
+    _torch().cuda.synchronize()
+    st = plan_status(A)
+    if st:
+        _capi.check(_capi.lib().cuvdia_plan_status_clear(A._plan, _stream()))
+        raise CuvDiaError(_capi.ERR_CUDA, "a kernel gave up a bounded wait on an asynchronous copy (status %d): "
+                                          "the output is incomplete" % st)
+
+
+def prod(C, A, B, transA="n", transB="n", factAB=1.0, factC=0.0, mode=MODE_EXACT, check_status=False):
+    """C = factC*C + factAB*op(A)*B (matrix_ops/matrix_ops.hpp:118-119, matrix_ops/spmv.cu:221-247).
+    ``check_status=True`` makes the call blocking, like CUV's, and raises if a kernel gave up a bounded wait."""
     ldc, ldb = _check_colmajor(C, "C"), _check_colmajor(B, "B")
     if C.shape[1] != B.shape[1]:
         raise CuvDiaError(_capi.ERR_INVALID, "dst.shape()[1] == B.shape()[1]")
@@ -267,6 +281,8 @@ def prod(C, A, B, transA="n", transB="n", factAB=1.0, factC=0.0, mode=MODE_EXACT
         raise CuvDiaError(_capi.ERR_INVALID, "operand heights match the matrix (spmv.cu:159-160,180-181)")
     _capi.check(_capi.lib().cuvdia_prod_f32(A._plan, _ptr(A.vec), _ptr(B), ldb, _ptr(C), ldc, int(C.shape[1]),
                                             transA.encode(), transB.encode(), factAB, factC, mode, _stream()))
+    if check_status:
+        raise_if_gave_up(A)
     return C
 
 
@@ -293,7 +309,7 @@ def prod_bias_sigmoid_sample(C, A, B, transA="n", factAB=1.0, factC=0.0, mode=MO
     return sample
 
 
-def spmv(dst, A, v, transA="n", factAv=1.0, factC=0.0, mode=MODE_EXACT):
+def spmv(dst, A, v, transA="n", factAv=1.0, factC=0.0, mode=MODE_EXACT, check_status=False):
     """dst = factC*dst + factAv*op(A)*v for one or several vectors packed column-major in 1-D tensors
     (matrix_ops/matrix_ops.hpp:277-278, spmv.cu:248-253)."""
     rows_b, rows_c = (A.h, A.w) if transA == "t" else (A.w, A.h)
@@ -302,10 +318,12 @@ def spmv(dst, A, v, transA="n", factAv=1.0, factC=0.0, mode=MODE_EXACT):
     n = v.numel() // rows_b
     _capi.check(_capi.lib().cuvdia_prod_f32(A._plan, _ptr(A.vec), _ptr(v), rows_b, _ptr(dst), rows_c, n,
                                             transA.encode(), b"n", factAv, factC, mode, _stream()))
+    if check_status:
+        raise_if_gave_up(A)
     return dst
 
 
-def densedense_to_dia(C, Cbd, A, B, factAB=1.0, factC=0.0):
+def densedense_to_dia(C, Cbd, A, B, factAB=1.0, factC=0.0, check_status=False):
     """C_dia = factC*C_dia + factAB*(A*B^T on the stored diagonals)
     (matrix_ops/densedense_to_sparse.hpp:123-130)."""
     lda, ldb = _check_colmajor(A, "A"), _check_colmajor(B, "B")
@@ -314,6 +332,8 @@ def densedense_to_dia(C, Cbd, A, B, factAB=1.0, factC=0.0):
                                              "A.shape()[1]==B.shape()[1]")
     _capi.check(_capi.lib().cuvdia_dd2dia_f32(C._plan, _ptr(C.vec), _ptr(A), lda, _ptr(B), ldb, int(A.shape[1]),
                                               factAB, factC, _stream()))
+    if check_status:
+        raise_if_gave_up(C)
     return C
 
 
@@ -358,6 +378,25 @@ def bias_sigmoid_sample(act, bias=None, u=None, sample=None):
         lds = _check_colmajor(sample, "sample")
     _capi.check(_capi.lib().cuvdia_bias_sigmoid_sample_f32(_ptr(act), ld, _ptr(bias), _ptr(u), ldu, _ptr(sample),
                                                            lds, int(act.shape[0]), int(act.shape[1]), _stream()))
+    return sample
+
+
+def bias_sigmoid_sample_sum(act, bias, u, sample, sum_dst, sum_of_sample=False, factNew=1.0, factOld=0.0,
+                            store_act=True):
+    """:func:`bias_sigmoid_sample` that also accumulates ``sum_dst[i] = factOld*sum_dst[i] + factNew*sum_j x[i, j]``
+    in the same pass, x being the activation after the logistic or (``sum_of_sample``) the 0/1 sample: the
+    ``reduce_to_col`` of the trainer's bias gradients (examples/rbm/base.py:76-83) without a second read of the
+    matrix.  ``store_act=False`` leaves ``act`` unwritten."""
+    ld = _check_colmajor(act, "act")
+    ldu = lds = 0
+    if u is not None:
+        ldu = _check_colmajor(u, "u")
+        lds = _check_colmajor(sample, "sample")
+    if sum_dst.numel() != act.shape[0] or not sum_dst.is_contiguous():
+        raise CuvDiaError(_capi.ERR_INVALID, "main_dim == v.size()")
+    _capi.check(_capi.lib().cuvdia_bias_sigmoid_sample_sum_f32(
+        _ptr(act), ld, _ptr(bias), _ptr(u), ldu, _ptr(sample), lds, int(act.shape[0]), int(act.shape[1]),
+        _ptr(sum_dst), 1 if sum_of_sample else 0, factNew, factOld, 1 if store_act else 0, _stream()))
     return sample
 
 

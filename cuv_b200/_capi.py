@@ -19,6 +19,7 @@ SIGNATURES = {
     "cuvdia_error_string": (ctypes.c_char_p, [_i]),
     "cuvdia_last_error_message": (ctypes.c_char_p, []),
     "cuvdia_launch_count": (ctypes.c_ulonglong, []),
+    "cuvdia_release_workspaces": (_i, []),
     "cuvdia_plan_create": (_i, [ctypes.POINTER(_vp), _i, _i, _i, _i, _i, ctypes.POINTER(_i)]),
     "cuvdia_plan_destroy": (_i, [_vp]),
     "cuvdia_plan_info": (_i, [_vp, ctypes.POINTER(_i), ctypes.POINTER(_ll)]),
@@ -33,14 +34,25 @@ SIGNATURES = {
     "cuvdia_reduce_f32": (_i, [_vp, _vp, _ll, _ll, _i, _i, _f, _f, _vp]),
     "cuvdia_reduce_noalloc_f32": (_i, [_vp, _vp, _ll, _ll, _i, _i, _f, _f, _vp]),
     "cuvdia_bias_sigmoid_sample_f32": (_i, [_vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _vp]),
+    "cuvdia_bias_sigmoid_sample_sum_f32": (_i, [_vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _vp, _i, _f, _f, _i, _vp]),
+    "cuvdia_rbm_cd1_step_f32": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "cuvdia_allreduce_grad": (_i, [_vp, _vp, _ll, _vp, _ll, _vp]),
+    "cuvdia_nccl_unique_id": (_i, [ctypes.c_char_p]),
+    "cuvdia_nccl_comm_create": (_i, [ctypes.POINTER(_vp), _i, _i, ctypes.c_char_p]),
+    "cuvdia_nccl_comm_destroy": (_i, [_vp]),
     "cuvdia_axpby_f32": (_i, [_vp, _vp, _vp, _f, _f, _ll, _vp]),
     "cuvdia_learn_step_weight_decay_f32": (_i, [_vp, _vp, _ll, _f, _f, _vp]),
     "cuvdia_learn_step_weight_decay_momentum_f32": (_i, [_vp, _vp, _vp, _ll, _f, _f, _f, _vp]),
     "cuvdia_binary_f32": (_i, [_vp, _vp, _vp, _i, _f, _f, _ll, _vp]),
     "cuvdia_fill_f32": (_i, [_vp, _f, _ll, _vp]),
     "cuvdia_sequence_f32": (_i, [_vp, _ll, _vp]),
-    "cuvdia_fp32_peak_tflops": (_i, [_i, ctypes.POINTER(_f)]),
 }
+
+
+class RbmCd1Buffers(ctypes.Structure):
+    """``cuvdia_rbm_cd1_buffers`` of include/cuvdia.h."""
+    _fields_ = [(n, _vp) for n in ("V0", "U_h", "U_v", "b_vis", "c_hid", "H0p", "H0", "V1p", "V1", "H1p", "G_vals",
+                                   "gc", "gb")]
 
 
 class CuvDiaError(RuntimeError):

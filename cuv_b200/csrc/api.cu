@@ -69,6 +69,20 @@ int get_workspace(cudaStream_t stream, size_t bytes, void** ptr) {
     return CUVDIA_OK;
 }
 
+int release_workspaces() {
+    CUVDIA_CUDA(cudaDeviceSynchronize());
+    int dev = 0;
+    CUVDIA_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(g_ws_mutex);
+    for (auto it = g_ws.begin(); it != g_ws.end();) {
+        if (it->first.first == dev) {
+            if (it->second.ptr) cudaFree(it->second.ptr);
+            it = g_ws.erase(it);
+        } else ++it;
+    }
+    return CUVDIA_OK;
+}
+
 }  // namespace cuvdia
 
 using namespace cuvdia;
@@ -93,6 +107,8 @@ const char* cuvdia_error_string(int code) {
 }
 
 const char* cuvdia_last_error_message(void) { return t_last_error.c_str(); }
+
+int cuvdia_release_workspaces(void) { return release_workspaces(); }
 
 unsigned long long cuvdia_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
@@ -295,6 +311,21 @@ int cuvdia_bias_sigmoid_sample_f32(float* act, int ld, const float* bias, const 
     if (u) { CUVDIA_REQUIRE(ldu >= units); CUVDIA_REQUIRE(lds >= units); }
     if (ncols == 0) return CUVDIA_OK;
     return launch_bias_sigmoid_sample(act, ld, bias, u, ldu, sample, lds, units, ncols, (cudaStream_t)stream);
+}
+
+int cuvdia_bias_sigmoid_sample_sum_f32(float* act, int ld, const float* bias, const float* u, int ldu, float* sample,
+                                       int lds, int units, int ncols, float* sum_dst, int sum_of_sample, float factNew,
+                                       float factOld, int store_act, void* stream) {
+    CUVDIA_REQUIRE(act != nullptr);
+    CUVDIA_REQUIRE(sum_dst != nullptr);
+    CUVDIA_REQUIRE(units > 0 && ncols > 0);
+    CUVDIA_REQUIRE(ld >= units);
+    CUVDIA_REQUIRE((u == nullptr) == (sample == nullptr));
+    if (u) { CUVDIA_REQUIRE(ldu >= units); CUVDIA_REQUIRE(lds >= units); }
+    CUVDIA_REQUIRE(!sum_of_sample || sample != nullptr);
+    CUVDIA_REQUIRE(store_act || sample != nullptr);      // something must be produced besides the sum
+    return launch_bias_sigmoid_sample_sum(act, ld, bias, u, ldu, sample, lds, units, ncols, sum_dst, sum_of_sample ? 1 : 0,
+                                          factNew, factOld, store_act ? 1 : 0, (cudaStream_t)stream);
 }
 
 int cuvdia_axpby_f32(float* dst, const float* x, const float* y, float a, float b, long long n, void* stream) {

@@ -39,6 +39,10 @@ int get_workspace(cudaStream_t stream, size_t bytes, void** ptr);
 
 int sm_count();
 
+// The TMA kernels need cuTensorMapEncodeTiled from the driver; false if it cannot be resolved (they are then not
+// chosen and the kernels with plain loads run).
+bool tma_available();
+
 // Raises a kernel's dynamic shared-memory limit once per device (the attribute belongs to the device's
 // context, so a process that uses several GPUs must set it on each).
 template <class K>
@@ -126,6 +130,13 @@ int launch_reduce(float* dst, const float* src, long long n_contig, long long n_
                   int functor, float factNew, float factOld, cudaStream_t st);
 int launch_bias_sigmoid_sample(float* act, int ld, const float* bias, const float* u, int ldu, float* sample,
                                int lds, int units, int ncols, cudaStream_t st);
+// the same pass that also accumulates sum_dst[unit] = fold*sum_dst[unit] + fnew*sum over columns of the activation
+// (sum_sample == 0) or of the 0/1 sample (sum_sample != 0); store_act == 0 leaves act unwritten
+int launch_bias_sigmoid_sample_sum(float* act, int ld, const float* bias, const float* u, int ldu, float* sample,
+                                   int lds, int units, int ncols, float* sum_dst, int sum_sample, float fnew, float fold,
+                                   int store_act, cudaStream_t st);
+int launch_reduce_combine_add(float* dst, long long n_out, float fnew, float fold, int nsplit, const float* partial,
+                              cudaStream_t st);
 int launch_axpby(float* dst, const float* x, const float* y, float a, float b, long long n, cudaStream_t st);
 // momentum-free when M is null: (a, b) = (alpha, beta); with momentum (a, b, c) = (lr, momentum weight, l2 decay)
 int launch_learn_step(float* W, float* M, const float* dW, float a, float b, float c, long long n, cudaStream_t st);

@@ -207,7 +207,7 @@ static inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) 
 
 bool dd2dia_band_applicable(const cuvdia_plan* p, const float* A, int lda, const float* B, int ldb, int ncols) {
     return p->is_band && p->rf == 1 && al16(A) && al16(B) && lda % 4 == 0 && ldb % 4 == 0 && ncols >= 1 &&
-           p->nd >= 16;
+           p->nd >= 16 && tma_available();
 }
 
 int launch_dd2dia_band(cuvdia_plan* p, float* Cv, const float* A, int lda, const float* B, int ldb, int ncols,

@@ -154,7 +154,7 @@ static inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) 
 bool dd2dia_stream_applicable(const cuvdia_plan* p, const float* Cv, const float* A, int lda, const float* B, int ldb,
                               int ncols) {
     return p->is_band && p->rf == 1 && p->nd <= ds::KD && p->h >= 64 * ds::TR && ncols >= 1 && al16(A) && al16(B) &&
-           al16(Cv) && lda % 4 == 0 && ldb % 4 == 0 && p->stride % 4 == 0;
+           al16(Cv) && lda % 4 == 0 && ldb % 4 == 0 && p->stride % 4 == 0 && tma_available();
 }
 
 int launch_dd2dia_stream(cuvdia_plan* p, float* Cv, const float* A, int lda, const float* B, int ldb, int ncols,

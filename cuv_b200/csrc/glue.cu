@@ -56,6 +56,109 @@ int launch_bias_sigmoid_sample(float* act, int ld, const float* bias, const floa
     return check_launch("bias_sigmoid_sample_kernel");
 }
 
+// The same pass that also sums over the batch: a block owns 1024 (VEC) or 256 units and one slab of batch
+// columns, every thread keeps the running sums of its units over the slab's columns (ascending, four columns in
+// flight), and the slabs' partial sums are folded in slab order by the reductions' second stage, so the result is
+// reproducible run to run.  Summed is either the activation after the logistic or the 0/1 sample; this replaces a
+// separate reduce_to_col over a matrix this pass has just produced.  With store_act == 0 the activations are
+// not written back (callers that only consume the sample and its sum).
+template <bool VEC>
+__global__ void __launch_bounds__(256)
+bias_sigmoid_sample_sum_kernel(float* __restrict__ act, int ld, const float* __restrict__ bias,
+                               const float* __restrict__ u, int ldu, float* __restrict__ sample, int lds, int units,
+                               int ncols, int nslab, int sum_sample, int store_act, float* __restrict__ partial,
+                               float* __restrict__ dst, float fnew, float fold) {
+    constexpr int W = VEC ? 4 : 1;
+    const int i = (blockIdx.x * 256 + threadIdx.x) * W;
+    if (i >= units) return;
+    const int z = blockIdx.y;
+    const int c0 = (int)((long long)ncols * z / nslab), c1 = (int)((long long)ncols * (z + 1) / nslab);
+    float bv[W], acc[W];
+#pragma unroll
+    for (int v = 0; v < W; v++) { bv[v] = bias ? __ldg(bias + i + v) : 0.f; acc[v] = 0.f; }
+    auto one = [&](float (&a)[W], const float (&r)[W], int col) {
+        float s[W];
+#pragma unroll
+        for (int v = 0; v < W; v++) {
+            if (bias) a[v] += bv[v];
+            a[v] = sigm(a[v]);
+            s[v] = a[v] > r[v] ? 1.f : 0.f;                                  // random/random.cu:86-91
+            acc[v] += (sum_sample ? s[v] : a[v]);
+        }
+        if (VEC) {
+            if (store_act) *reinterpret_cast<float4*>(act + (size_t)col * ld + i) = make_float4(a[0], a[W > 1 ? 1 : 0], a[W > 2 ? 2 : 0], a[W > 3 ? 3 : 0]);
+            if (sample) *reinterpret_cast<float4*>(sample + (size_t)col * lds + i) = make_float4(s[0], s[W > 1 ? 1 : 0], s[W > 2 ? 2 : 0], s[W > 3 ? 3 : 0]);
+        } else {
+            if (store_act) act[(size_t)col * ld + i] = a[0];
+            if (sample) sample[(size_t)col * lds + i] = s[0];
+        }
+    };
+    auto load = [&](const float* base, int pitch, int col, float (&x)[W]) {
+        if (VEC) {
+            const float4 t = *reinterpret_cast<const float4*>(base + (size_t)col * pitch + i);
+            x[0] = t.x; x[W > 1 ? 1 : 0] = t.y; x[W > 2 ? 2 : 0] = t.z; x[W > 3 ? 3 : 0] = t.w;
+        } else {
+            x[0] = base[(size_t)col * pitch + i];
+        }
+    };
+    int col = c0;
+    for (; col + 4 <= c1; col += 4) {
+        float a[4][W], r[4][W];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            load(act, ld, col + q, a[q]);
+            if (u) load(u, ldu, col + q, r[q]);
+            else {
+#pragma unroll
+                for (int v = 0; v < W; v++) r[q][v] = 0.f;
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < 4; q++) one(a[q], r[q], col + q);
+    }
+    for (; col < c1; col++) {
+        float a[W], r[W];
+        load(act, ld, col, a);
+        if (u) load(u, ldu, col, r);
+        else {
+#pragma unroll
+            for (int v = 0; v < W; v++) r[v] = 0.f;
+        }
+        one(a, r, col);
+    }
+#pragma unroll
+    for (int v = 0; v < W; v++) {
+        if (nslab == 1) dst[i + v] = (fold != 0.f) ? fold * dst[i + v] + fnew * acc[v] : fnew * acc[v];
+        else partial[(size_t)z * units + i + v] = acc[v];
+    }
+}
+
+int launch_bias_sigmoid_sample_sum(float* act, int ld, const float* bias, const float* u, int ldu, float* sample,
+                                   int lds, int units, int ncols, float* sum_dst, int sum_sample, float fnew, float fold,
+                                   int store_act, cudaStream_t st) {
+    bool vec = units % 4 == 0 && ld % 4 == 0 && aligned16(act) && (!bias || aligned16(bias));
+    if (u) vec = vec && ldu % 4 == 0 && lds % 4 == 0 && aligned16(u) && aligned16(sample);
+    const int per_block = 256 * (vec ? 4 : 1);
+    const int gx = (units + per_block - 1) / per_block;
+    // enough blocks to fill the device several times over, but at least 8 columns per slab
+    int nslab = (int)std::min<long long>((8LL * sm_count() + gx - 1) / gx, std::max(1, ncols / 8));
+    nslab = std::max(1, std::min(nslab, 1024));
+    float* partial = nullptr;
+    if (nslab > 1) {
+        void* ws;
+        int rc = get_workspace(st, (size_t)nslab * units * sizeof(float), &ws);
+        if (rc) return rc;
+        partial = (float*)ws;
+    }
+    dim3 grid(gx, nslab);
+    if (vec) bias_sigmoid_sample_sum_kernel<true><<<grid, 256, 0, st>>>(act, ld, bias, u, ldu, sample, lds, units, ncols, nslab, sum_sample, store_act, partial, sum_dst, fnew, fold);
+    else     bias_sigmoid_sample_sum_kernel<false><<<grid, 256, 0, st>>>(act, ld, bias, u, ldu, sample, lds, units, ncols, nslab, sum_sample, store_act, partial, sum_dst, fnew, fold);
+    count_launch();
+    int rc = check_launch("bias_sigmoid_sample_sum_kernel");
+    if (rc || nslab == 1) return rc;
+    return launch_reduce_combine_add(sum_dst, units, fnew, fold, nslab, partial, st);
+}
+
 __global__ void __launch_bounds__(256)
 axpby_kernel(float* dst, const float* x, const float* y, float a, float b, long long n) {
     for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < n; t += (long long)gridDim.x * blockDim.x)

@@ -361,6 +361,8 @@ static EncodeTiledFn get_encode() {
     return fn;
 }
 
+bool tma_available() { return get_encode() != nullptr; }
+
 // 2-D fp32 tensor map: dim0 (contiguous) x dim1 with a pitch in elements, box0 x box1 tile, zero fill.
 int make_map_2d(CUtensorMap* m, const float* base, long long dim0, long long dim1, long long pitch, int box0, int box1) {
     EncodeTiledFn enc = get_encode();

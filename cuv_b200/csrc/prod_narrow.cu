@@ -383,7 +383,7 @@ static int launch_stream_t(const cuvdia_plan* p, const float* A, const float* B,
 
 // The streaming variant needs the whole band in one pass and enough rows to fill the GPU.
 bool prod_narrow_streams(const cuvdia_plan* p, bool trans) {
-    return p->nd <= pn::KD && (trans ? p->w : p->h) >= 64 * ps::TR;
+    return p->nd <= pn::KD && (trans ? p->w : p->h) >= 64 * ps::TR && tma_available();
 }
 
 int launch_prod_narrow(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,

@@ -311,7 +311,8 @@ static inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) 
 // Row factor 1, diagonals mostly in runs (the plan found on average at least four per pass), 16-byte
 // aligned operands.
 bool prod_runs_applicable(const cuvdia_plan* p, const float* A, const float* B, int ldb) {
-    return p->is_runs && p->d_passes != nullptr && al16(A) && al16(B) && p->stride % 4 == 0 && ldb % 4 == 0;
+    return p->is_runs && p->d_passes != nullptr && al16(A) && al16(B) && p->stride % 4 == 0 && ldb % 4 == 0 &&
+           tma_available();
 }
 
 template <bool TRANS, bool EXACT>

@@ -487,6 +487,15 @@ int launch_reduce_noalloc(float* dst, const float* src, long long n_contig, long
     return CUVDIA_ERR_INVALID;
 }
 
+// Second stage alone, for kernels elsewhere in the library that produce per-slab partial sums themselves.
+int launch_reduce_combine_add(float* dst, long long n_out, float fnew, float fold, int nsplit, const float* partial,
+                              cudaStream_t st) {
+    reduce_combine_kernel<CUVDIA_RF_ADD><<<(unsigned)((n_out + 255) / 256), 256, 0, st>>>(dst, n_out, fnew, fold, nsplit,
+                                                                                           partial, nullptr, 1.f);
+    count_launch();
+    return check_launch("reduce_combine_kernel");
+}
+
 int launch_reduce(float* dst, const float* src, long long n_contig, long long n_strided, bool over_strided,
                   int functor, float fnew, float fold, cudaStream_t st) {
 #define CASE(RF) case RF: return launch_reduce_t<RF>(dst, src, n_contig, n_strided, over_strided, fnew, fold, st)

@@ -21,7 +21,18 @@ import cuv_b200 as cb
 
 
 class SparseRBMStep:
-    def __init__(self, W, batch_local, batch_global=None, mode=cb.MODE_EXACT, device="cuda", fused=False):
+    """One rank's CD-1 step.  ``step()`` is a single call of the C ABI (``cuvdia_rbm_cd1_step_f32``); ``forward()`` +
+    ``gradients()`` issue the same kernels call by call (used when the calls are timed one by one, or when the inputs
+    arrive while the step runs).
+
+    ``bias_sums="glue"`` (default): the bias gradients come from the element-wise passes that already stream H0p, V1
+    and H1p, and only the sum over V0 is a reduction of its own.  ``"reduce"``: four ``reduce_to_col`` calls after
+    the products, as the trainer issues them (examples/rbm/base.py:76-83); ``fused=True`` additionally calls the
+    combined product + bias/logistic/compare entry point.  ``keep_v1p=False`` does not write the reconstruction's
+    probabilities back (only its sample is used afterwards)."""
+
+    def __init__(self, W, batch_local, batch_global=None, mode=cb.MODE_EXACT, device="cuda", fused=False,
+                 bias_sums="glue", keep_v1p=True):
         import torch
         self.W = W
         self.hid, self.vis = W.h, W.w
@@ -29,21 +40,31 @@ class SparseRBMStep:
         self.B = int(batch_global if batch_global is not None else batch_local)
         self.mode = mode
         self.fused = fused        # call the combined product + bias/logistic/compare entry point (same bits)
+        self.bias_sums = "reduce" if fused else bias_sums
+        self.keep_v1p = keep_v1p
         self.dev = device
         E = cb.colmajor_empty
         self.H0p, self.H0 = E(self.hid, self.nb, device), E(self.hid, self.nb, device)
         self.V1p, self.V1 = E(self.vis, self.nb, device), E(self.vis, self.nb, device)
         self.H1p = E(self.hid, self.nb, device)
-        # gradient with W's layout; padding cells are never written, keep them at zero
+        # gradient with W's layout; padding cells are never written, keep them at zero.  The diagonals' values and
+        # the two bias gradients (gc, then gb) share one buffer so that a single collective covers them all.
         self.G = cb.dev_dia_matrix_f(W.h, W.w, W.offsets, W.stride, W.row_fact, device=device)
-        self.G.vec.zero_()
+        n_g = self.G.vec.numel()
+        if n_g % 4 == 0:
+            self.grad_buf = torch.zeros(n_g + self.hid + self.vis, dtype=torch.float32, device=device)
+            self.G.vec = self.grad_buf[:n_g]
+            self.bias_grad = self.grad_buf[n_g:]
+        else:
+            self.grad_buf = None
+            self.G.vec.zero_()
+            self.bias_grad = torch.zeros(self.hid + self.vis, dtype=torch.float32, device=device)
         self.Gbd = cb.dev_block_descriptor_f(self.G)
-        # gc and gb share one buffer so that a single collective covers both
-        self.bias_grad = torch.zeros(self.hid + self.vis, dtype=torch.float32, device=device)
         self.gc, self.gb = self.bias_grad[:self.hid], self.bias_grad[self.hid:]
         self.b_vis = torch.zeros(self.vis, dtype=torch.float32, device=device)
         self.c_hid = torch.zeros(self.hid, dtype=torch.float32, device=device)
         self.timers = None        # optional dict name -> list of (start_event, end_event)
+        self._reducer = None
 
     def _timed(self, name, fn):
         if self.timers is None:
@@ -59,15 +80,31 @@ class SparseRBMStep:
     def step(self, V0, U_h, U_v):
         """One CD-1 gradient evaluation on this rank's batch columns; results in G.vec, gc, gb
         (partial sums when batch_global > batch_local)."""
+        if self.timers is None and self.bias_sums == "glue":
+            return self._step_c(V0, U_h, U_v)
         self.forward(V0, U_h, U_v)
         self.gradients(V0)
 
+    def _step_c(self, V0, U_h, U_v):
+        """The whole step as one call of the C ABI."""
+        import ctypes
+        from . import _capi
+        for t, rows, name in ((V0, self.vis, "V0"), (U_h, self.hid, "U_h"), (U_v, self.vis, "U_v")):
+            if cb._check_colmajor(t, name) != rows or t.shape != (rows, self.nb):
+                raise cb.CuvDiaError(_capi.ERR_INVALID, name + " must be a dense column-major [units x batch] matrix")
+        p = lambda t: t.data_ptr()
+        buf = _capi.RbmCd1Buffers(p(V0), p(U_h), p(U_v), p(self.b_vis), p(self.c_hid), p(self.H0p), p(self.H0),
+                                  p(self.V1p), p(self.V1), p(self.H1p), p(self.G.vec), p(self.gc), p(self.gb))
+        _capi.check(_capi.lib().cuvdia_rbm_cd1_step_f32(self.W._plan, cb._ptr(self.W.vec), ctypes.byref(buf), self.nb,
+                                                        self.B, self.mode, 1 if self.keep_v1p else 0, cb._stream()))
+
     def forward(self, V0, U_h, U_v, arrived=None):
-        """The three products with their bias/logistic/sampling passes.  ``arrived``: optional events
-        (V0, U_h, U_v) that the current stream waits for just before the first use of each input, so that a
-        step can start on V0 while the uniform numbers are still on their way."""
+        """The three products with their bias/logistic/sampling passes (and, with ``bias_sums="glue"``, the bias
+        gradients).  ``arrived``: optional events (V0, U_h, U_v) that the current stream waits for just before the
+        first use of each input, so that a step can start on V0 while the uniform numbers are still on their way."""
         W = self.W
         t = self._timed
+        inv = 1.0 / self.B
 
         def need(k):
             if arrived is not None:
@@ -83,6 +120,18 @@ class SparseRBMStep:
             t("prod_n", lambda: F(self.H1p, W, self.V1, "n", 1.0, 0.0, self.mode, self.c_hid))
             return
         need(0)
+        if self.bias_sums == "glue":
+            GS = cb.bias_sigmoid_sample_sum
+            t("reduce", lambda: cb.reduce_to_col(self.gb, V0, cb.RF_ADD, inv, 0.0))
+            t("prod_n", lambda: cb.prod(self.H0p, W, V0, "n", "n", 1.0, 0.0, self.mode))
+            need(1)
+            t("glue", lambda: GS(self.H0p, self.c_hid, U_h, self.H0, self.gc, False, inv, 0.0))
+            t("prod_t", lambda: cb.prod(self.V1p, W, self.H0, "t", "n", 1.0, 0.0, self.mode))
+            need(2)
+            t("glue", lambda: GS(self.V1p, self.b_vis, U_v, self.V1, self.gb, True, -inv, 1.0, self.keep_v1p))
+            t("prod_n", lambda: cb.prod(self.H1p, W, self.V1, "n", "n", 1.0, 0.0, self.mode))
+            t("glue", lambda: GS(self.H1p, self.c_hid, None, None, self.gc, False, -inv, 1.0))
+            return
         t("prod_n", lambda: cb.prod(self.H0p, W, V0, "n", "n", 1.0, 0.0, self.mode))
         need(1)
         t("glue", lambda: cb.bias_sigmoid_sample(self.H0p, self.c_hid, U_h, self.H0))
@@ -93,24 +142,29 @@ class SparseRBMStep:
         t("glue", lambda: cb.bias_sigmoid_sample(self.H1p, self.c_hid))
 
     def gradients(self, V0):
-        """Weight-gradient diagonals and bias gradients from the activations of forward()."""
+        """Weight-gradient diagonals (and, with ``bias_sums="reduce"``, the bias gradients) from the activations of
+        forward()."""
         inv = 1.0 / self.B
         t = self._timed
         t("dd2dia", lambda: cb.densedense_to_dia(self.G, self.Gbd, self.H0p, V0, inv, 0.0))
         t("dd2dia", lambda: cb.densedense_to_dia(self.G, self.Gbd, self.H1p, self.V1, -inv, 1.0))
+        if self.bias_sums == "glue":
+            return
         t("reduce", lambda: cb.reduce_to_col(self.gc, self.H0p, cb.RF_ADD, inv, 0.0))
         t("reduce", lambda: cb.reduce_to_col(self.gc, self.H1p, cb.RF_ADD, -inv, 1.0))
         t("reduce", lambda: cb.reduce_to_col(self.gb, V0, cb.RF_ADD, inv, 0.0))
         t("reduce", lambda: cb.reduce_to_col(self.gb, self.V1, cb.RF_ADD, -inv, 1.0))
 
     def allreduce(self, group=None):
-        """Sum the partial gradients over the ranks (NCCL over NVLink): the diagonals of G and the
-        two bias gradients."""
-        allreduce_gradients(self.G.vec, self.bias_grad, group)
+        """Sum the partial gradients over the ranks (NCCL over NVLink): the diagonals of G and the two bias
+        gradients, one collective issued through the C ABI on a communicator of the library's own."""
+        if self._reducer is None:
+            self._reducer = GradientAllReduce(self.dev, group)
+        self._reducer(self.G.vec, self.bias_grad)
 
     def capture(self, V0, U_h, U_v):
         """Records one step on the given (static) input tensors into a CUDA graph and returns it; ``graph.replay()``
-        then runs the 16 kernels of a step with a single launch.  The library allocates its scratch buffers on first
+        then runs the kernels of a step with a single launch.  The library allocates its scratch buffers on first
         use, so one ordinary step is run first; nothing is allocated while recording."""
         import torch
         timers, self.timers = self.timers, None          # events cannot be recorded into the graph this way
@@ -136,6 +190,41 @@ class SparseRBMStep:
         t("update", lambda: cb.learn_step_weight_decay(self.b_vis, self.gb, learnrate, decay))
 
 
+class GradientAllReduce:
+    """In-place sum of the partial gradients over the ranks through ``cuvdia_allreduce_grad``.  The NCCL
+    communicator is the library's own (``cuvdia_nccl_comm_create``): rank 0 draws the unique id and
+    ``torch.distributed`` only carries its 128 bytes to the other ranks."""
+
+    def __init__(self, device, group=None):
+        import ctypes
+        import torch
+        import torch.distributed as dist
+        from . import _capi
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        ident = torch.zeros(128, dtype=torch.uint8, device=device)
+        if self.rank == 0:
+            raw = ctypes.create_string_buffer(128)
+            _capi.check(_capi.lib().cuvdia_nccl_unique_id(raw))
+            ident.copy_(torch.frombuffer(bytearray(raw.raw), dtype=torch.uint8))
+        src = dist.get_global_rank(group, 0) if group is not None else 0
+        dist.broadcast(ident, src=src, group=group)
+        self.comm = ctypes.c_void_p()
+        with torch.cuda.device(torch.device(device)):
+            _capi.check(_capi.lib().cuvdia_nccl_comm_create(ctypes.byref(self.comm), self.world, self.rank,
+                                                            bytes(ident.cpu().numpy().tobytes())))
+
+    def __call__(self, g_vec, bias_grad):
+        from . import _capi
+        _capi.check(_capi.lib().cuvdia_allreduce_grad(self.comm, cb._ptr(g_vec), g_vec.numel(), cb._ptr(bias_grad),
+                                                      bias_grad.numel(), cb._stream()))
+
+    def close(self):
+        from . import _capi
+        comm, self.comm = self.comm, None
+        if comm:
+            _capi.check(_capi.lib().cuvdia_nccl_comm_destroy(comm))
+
+
 class HostFedRBM:
     """Runs SparseRBMStep on inputs that live in pinned host memory and returns the gradients to
     pinned host memory, with the transfers overlapped with compute: the host-to-device copies of step
@@ -154,7 +243,7 @@ class HostFedRBM:
         self.h2d, self.d2h = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
         self.ready = [[torch.cuda.Event() for _ in range(3)] for _ in range(2)]     # per slot: V0, U_h, U_v arrived
         self.consumed = [torch.cuda.Event() for _ in range(2)]
-        self.grads_done, self.fetched = torch.cuda.Event(), torch.cuda.Event()
+        self.grads_done, self.fetched, self.bias_fetched = torch.cuda.Event(), torch.cuda.Event(), torch.cuda.Event()
         self.n_sub = self.n_run = 0
         self._fetch_pending = False
 
@@ -178,6 +267,8 @@ class HostFedRBM:
         cur = torch.cuda.current_stream()
         slot = self.n_run % 2
         V0, U_h, U_v = self.inputs[slot]
+        if self._fetch_pending:
+            cur.wait_event(self.bias_fetched)     # forward() writes the bias gradients: their (small) read-back goes first
         self.step.forward(V0, U_h, U_v, arrived=self.ready[slot])       # each input is awaited where it is first used
         if self._fetch_pending:
             cur.wait_event(self.fetched)          # the previous gradients must have left before they are overwritten
@@ -190,8 +281,9 @@ class HostFedRBM:
             self.grads_done.record(cur)
             self.d2h.wait_event(self.grads_done)
             with torch.cuda.stream(self.d2h):
-                hG.copy_(self.step.G.vec, non_blocking=True)
                 hbias.copy_(self.step.bias_grad, non_blocking=True)
+                self.bias_fetched.record(self.d2h)
+                hG.copy_(self.step.G.vec, non_blocking=True)
                 self.fetched.record(self.d2h)
             self._fetch_pending = True
 
@@ -212,7 +304,9 @@ def shard_columns(batch_global, world, rank):
 
 def allreduce_gradients(g_vec, bias_grad, group=None):
     """In-place sum over the ranks of the per-rank partial gradients (every rank computed its
-    partials with the GLOBAL batch in the 1/B factor, so the sum is the full-batch gradient)."""
+    partials with the GLOBAL batch in the 1/B factor, so the sum is the full-batch gradient) with
+    ``torch.distributed``'s own collectives: the host-side ranks of the CPU tests (gloo) use this; on GPUs
+    ``SparseRBMStep.allreduce`` goes through the C ABI instead."""
     import torch.distributed as dist
     dist.all_reduce(g_vec, op=dist.ReduceOp.SUM, group=group)
     dist.all_reduce(bias_grad, op=dist.ReduceOp.SUM, group=group)
@@ -230,6 +324,7 @@ def algorithmic_work(h, w, nd, nnz, nb):
     glue_s, glue_n = 4 * 4, 4 * 2        # bytes per element: act r/w + u + sample, or act r/w
     byts = {"prod_n": prod_n, "prod_t": prod_t, "dd2dia": (dd0 + dd1) / 2.0,
             "reduce": (red(h, 0) + red(h, 1) + red(w, 0) + red(w, 1)) / 4.0,
+            "reduce_v0": red(w, 0),      # the one reduction left when the element-wise passes take the other sums
             "glue": (glue_s * h * nb + glue_s * w * nb + glue_n * h * nb) / 3.0}
     total_bytes = 2 * prod_n + prod_t + dd0 + dd1 + red(h, 0) + red(h, 1) + red(w, 0) + red(w, 1)
     flops = 5 * 2.0 * nnz * nb

@@ -44,6 +44,7 @@ void densedense_to_dia(dia_matrix<V, dev_memory_space, I>& C, const dev_block_de
     cuvdia_check(cuvdia_dd2dia_f32(C.plan(), C.vec().ptr(), A.ptr(), (int)A.shape()[0], B.ptr(), (int)B.shape()[0],
                                    (int)A.shape()[1], factAB, factC, 0));
     cuvSafeCall(cudaDeviceSynchronize());
+    cuvdia_check_plan(C.plan());
 }
 
 // host twin: CUV's own host code (the parity reference), not part of this library

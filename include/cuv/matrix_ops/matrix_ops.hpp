@@ -43,6 +43,7 @@ inline void prod(tensor<float, dev_memory_space, column_major>& C, const dia_mat
     cuvdia_check(cuvdia_prod_f32(A.plan(), A.vec().ptr(), B.ptr(), (int)B.shape()[0], C.ptr(), (int)C.shape()[0],
                                  (int)C.shape()[1], transA, transB, factAB, factC, dia_prod_mode(), 0));
     cuvSafeCall(cudaDeviceSynchronize());
+    cuvdia_check_plan(A.plan());
 }
 
 // ---- spmv(dst, A, v, transA, factAv, factC): vectors packed column-major in 1-D tensors ------------------
@@ -64,6 +65,7 @@ inline void spmv(tensor<float, dev_memory_space>& dst, const dia_matrix<float, d
     cuvdia_check(cuvdia_prod_f32(A.plan(), A.vec().ptr(), v.ptr(), (int)rows_b, dst.ptr(), (int)rows_c, (int)n, transA,
                                  'n', factAv, factC, dia_prod_mode(), 0));
     cuvSafeCall(cudaDeviceSynchronize());
+    cuvdia_check_plan(A.plan());
 }
 
 // ---- reductions ------------------------------------------------------------------------------------------

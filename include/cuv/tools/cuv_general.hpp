@@ -23,6 +23,19 @@ inline void cuvdia_check(int rc) {
         throw std::runtime_error(std::string(cuvdia_error_string(rc)) + ": " + cuvdia_last_error_message());
 }
 
+// After a blocking operation: a kernel of this plan that ran out of polls while waiting for an asynchronous copy
+// left its output incomplete and a code in the plan's health word.  CUV reports a failed operation by throwing
+// (checkCudaError, tools/cuv_general.cu:51-61); so does this.  The word is cleared first, so the next call starts clean.
+inline void cuvdia_check_plan(cuvdia_plan* plan) {
+    int status = 0;
+    cuvdia_check(cuvdia_plan_status(plan, &status));
+    if (status != 0) {
+        cuvdia_plan_status_clear(plan, 0);
+        throw std::runtime_error("a kernel gave up a bounded wait on an asynchronous copy (status " +
+                                 std::to_string(status) + "): the output is incomplete");
+    }
+}
+
 inline void initCUDA(int dev = 0) {
     if (cudaSetDevice(dev) != cudaSuccess) throw std::runtime_error("initCUDA: cannot select device");
 }

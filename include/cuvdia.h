@@ -16,6 +16,16 @@
  *    before anything is launched.
  *  - There is no CPU fallback: without a CUDA device every compute call fails with
  *    CUVDIA_ERR_CUDA.
+ *  - Concurrency: a plan carries scratch memory (the batch split of densedense_to_dia) and the library keeps
+ *    one workspace per (device, stream) for the split reductions; both grow on demand and are reused by the
+ *    next call.  Use a plan from one stream and one host thread at a time, and a stream from one host thread
+ *    at a time: two calls that share a plan or a stream's workspace and overlap on the GPU would overwrite each
+ *    other's partial results.  Different plans on different streams are independent.
+ *  - Waits inside the kernels (on asynchronous copies) are bounded.  A kernel that runs out of polls leaves its
+ *    output incomplete and a non-zero code in the plan's health word; the calls below are stream-ordered and do
+ *    not read that word, so callers of this C ABI poll cuvdia_plan_status() themselves (the C++ wrappers in
+ *    include/cuv and cuv_b200's check_status=True do so after their synchronisation and throw, as CUV's
+ *    blocking operations throw on failure, tools/cuv_general.cu:51-61).
  */
 #ifndef CUVDIA_H
 #define CUVDIA_H
@@ -60,6 +70,11 @@ CUVDIA_API const char* cuvdia_last_error_message(void);
 /* Number of kernels this library has launched in this process (all threads), for harnesses that
  * must prove the CUDA path ran. */
 CUVDIA_API unsigned long long cuvdia_launch_count(void);
+
+/* Frees the per-stream workspaces the library has allocated on the current device (the partial results of split
+ * reductions and of the element-wise pass with batch sums); blocks until the device is idle first.  They are
+ * re-created on demand.  No counterpart in CUV, whose allocations all belong to its tensors. */
+CUVDIA_API int cuvdia_release_workspaces(void);
 
 /* ---------------------------------------------------------------------------------------------
  * Plan: the structure of one DIA matrix (shape, diagonals, row factor) with the device-side
@@ -192,6 +207,20 @@ CUVDIA_API int cuvdia_reduce_noalloc_f32(float* dst, const float* src, long long
 CUVDIA_API int cuvdia_bias_sigmoid_sample_f32(float* act, int ld, const float* bias, const float* u, int ldu,
                                    float* sample, int lds, int units, int ncols, void* stream);
 
+/* The same element-wise pass that also accumulates the per-unit sum over the batch columns it streams:
+ *   sum_dst[unit] = factOld*sum_dst[unit] + factNew * sum_col x[unit, col]
+ * with x = act after the logistic (sum_of_sample == 0) or x = sample (sum_of_sample != 0; sample required).
+ * It replaces the reduce_to_col(dst, x, RF_ADD, factNew, factOld) that the RBM trainer issues afterwards for
+ * its bias gradients (examples/rbm/base.py:76-83; reduce_to_col: matrix_ops/matrix_ops.hpp:211-212) - the matrix
+ * is not read a second time.  factOld == 0: sum_dst is not read.  store_act == 0: act is not written back (for
+ * callers that only use the sample and its sum; sample required).  The batch is summed in a fixed order
+ * (reproducible run to run), not the host loop's sequential order: batch-sum tolerance as for cuvdia_reduce_f32.
+ * act, sample are bit-identical to cuvdia_bias_sigmoid_sample_f32.  Uses the per-stream workspace. */
+CUVDIA_API int cuvdia_bias_sigmoid_sample_sum_f32(float* act, int ld, const float* bias, const float* u, int ldu,
+                                                  float* sample, int lds, int units, int ncols, float* sum_dst,
+                                                  int sum_of_sample, float factNew, float factOld, int store_act,
+                                                  void* stream);
+
 /* prod followed by the element-wise tail of an RBM/MLP layer in one call:
  *   C <- sigmoid(factC*C + factAB*op(A)*B + bias[row]);   sample <- C > u ? 1 : 0   (u, sample may be NULL)
  * i.e. cuvdia_prod_f32 + cuvdia_bias_sigmoid_sample_f32, which is what upPass/downPass of
@@ -202,6 +231,57 @@ CUVDIA_API int cuvdia_prod_bias_sigmoid_sample_f32(const cuvdia_plan* plan, cons
                                                    int ldb, float* C, int ldc, int ncols, char transA, float factAB,
                                                    float factC, int mode, const float* bias, const float* u, int ldu,
                                                    float* sample, int lds, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * One contrastive-divergence (CD-1) step of a sparse RBM whose weight matrix W (hidden x visible,
+ * row_fact 1) is the plan's DIA matrix, queued on one stream.  No single CUV routine corresponds to
+ * it: it issues, in the trainer's order (examples/rbm/base.py:223-258 with one Gibbs step; upPass /
+ * downPass :48-54, gradient accumulation :76-83), the DIA forms of the calls made there:
+ *   gb  =  1/B sum_b V0                                               (reduce_to_col)
+ *   H0p = sigm(W V0 + c_hid),    H0 = H0p > U_h,   gc  =  1/B sum_b H0p   (prod 'n', one element-wise pass)
+ *   V1p = sigm(W^T H0 + b_vis),  V1 = V1p > U_v,   gb -=  1/B sum_b V1    (prod 't', one element-wise pass)
+ *   H1p = sigm(W V1 + c_hid),                      gc -=  1/B sum_b H1p   (prod 'n', one element-wise pass)
+ *   G   =  1/B (H0p V0^T)|dia;   G += -1/B (H1p V1^T)|dia                 (densedense_to_dia x2)
+ * All matrices are column-major with leading dimension = their row count (hidden: h, visible: w) and
+ * ncols batch columns.  B = batch_global >= ncols: a rank that holds only its share of the batch
+ * columns gets partial sums in G_vals, gc, gb, which cuvdia_allreduce_grad completes.  The uniform
+ * numbers are inputs, so the step is deterministic.  keep_v1p == 0: V1p is left holding the
+ * pre-activations (nothing after the sampling reads the probabilities).  Results are those of the
+ * separate entry points called in this order.  May allocate scratch on first use (not during capture).
+ * ------------------------------------------------------------------------------------------- */
+typedef struct cuvdia_rbm_cd1_buffers {
+    const float* V0;            /* visible data, w x ncols, values 0/1                     */
+    const float* U_h;           /* uniform numbers for the hidden sample, h x ncols        */
+    const float* U_v;           /* uniform numbers for the visible sample, w x ncols       */
+    const float* b_vis;         /* visible bias, w floats, or NULL for zero                */
+    const float* c_hid;         /* hidden bias, h floats, or NULL for zero                 */
+    float* H0p; float* H0;      /* h x ncols: hidden probabilities and sample (outputs)    */
+    float* V1p; float* V1;      /* w x ncols: reconstruction probabilities and sample      */
+    float* H1p;                 /* h x ncols: hidden probabilities of the reconstruction   */
+    float* G_vals;              /* num_dia*stride: weight gradient on W's diagonals        */
+    float* gc;                  /* h floats: hidden bias gradient                          */
+    float* gb;                  /* w floats: visible bias gradient                         */
+} cuvdia_rbm_cd1_buffers;
+
+CUVDIA_API int cuvdia_rbm_cd1_step_f32(cuvdia_plan* plan, const float* W_vals, const cuvdia_rbm_cd1_buffers* buffers,
+                                       int ncols, int batch_global, int mode, int keep_v1p, void* stream);
+
+/* Sum over the ranks of an NCCL communicator, in place, of the per-rank partial gradients of
+ * cuvdia_rbm_cd1_step_f32: the diagonals' value array and the bias gradients, as one collective when
+ * bias_grad == G_vals + n_g (one buffer) and as one NCCL group otherwise.  CUV has no multi-GPU path;
+ * this is the exchange step of the batch-column sharding.  nccl_comm is an ncclComm_t (the caller's, or
+ * one from cuvdia_nccl_comm_create) whose device is current.  NCCL is looked up at run time - the copy
+ * already loaded into the process if there is one, else libnccl.so.2 - so this library does not link
+ * against it; CUVDIA_ERR_UNSUPPORTED if none can be loaded.  Stream-ordered. */
+CUVDIA_API int cuvdia_allreduce_grad(void* nccl_comm, float* G_vals, long long n_g, float* bias_grad, long long n_bias,
+                                     void* stream);
+
+/* For callers without a communicator of their own: ncclGetUniqueId on one rank (128 bytes, to be sent
+ * to the others by whatever means the application has), then ncclCommInitRank on every rank with its
+ * device current (blocking, collective), and ncclCommDestroy. */
+CUVDIA_API int cuvdia_nccl_unique_id(char id128[128]);
+CUVDIA_API int cuvdia_nccl_comm_create(void** nccl_comm, int nranks, int rank, const char id128[128]);
+CUVDIA_API int cuvdia_nccl_comm_destroy(void* nccl_comm);
 
 /* dst = a*x + b*y element-wise over n floats (apply_binary_functor BF_AXPBY,
  * tensor_ops/tensor_ops.hpp:530-655, tensor_ops/functors.hpp:412-433); dst may alias x or y. */
@@ -242,14 +322,6 @@ CUVDIA_API int cuvdia_binary_f32(float* dst, const float* x, const float* y, int
  * sequence is thrust::sequence there, tensor_ops.cuh:251-252). */
 CUVDIA_API int cuvdia_fill_f32(float* dst, float value, long long n, void* stream);
 CUVDIA_API int cuvdia_sequence_f32(float* dst, long long n, void* stream);
-
-/* Benchmark aid, no counterpart in CUV: measures the device's FP32 ceiling with a register-resident
- * loop and returns it in TFLOP/s counting a multiply-add as 2 flops.  fused: 0 = a separate multiply
- * and add per step (the EXACT arithmetic), 1 = one fused multiply-add per step (the FAST arithmetic),
- * 2 = a packed-pair multiply (f32x2 instruction of sm_100) and two scalar adds (unfused), 3 = a packed
- * fused multiply-add.  Blocking;
- * allocates and frees 4 bytes. */
-CUVDIA_API int cuvdia_fp32_peak_tflops(int fused, float* tflops);
 
 #ifdef __cplusplus
 }

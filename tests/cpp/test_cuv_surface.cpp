@@ -327,6 +327,33 @@ static void test_reduce_3d() {
     }
 }
 
+// A kernel that gave up a bounded wait must surface as an exception from the next blocking call, as a failed
+// operation does in CUV (tools/cuv_general.cu:51-61); the self-test kernel leaves the code without any fault.
+static void test_given_up_wait_throws() {
+    const int n = 64, k = 8;
+    dia_matrix<float, dev_memory_space> A(n, n, 3, n);
+    std::vector<int> off = {-1, 0, 1};
+    A.set_offsets(off);
+    fill(A.vec(), 1.f);
+    tensor<float, dev_memory_space, column_major> B(n, k), C(n, k);
+    fill(B, 1.f);
+    prod(C, A, B);                                   // healthy call
+    CHECK((float)C(5, 0) == 3.f);
+    cuvdia_check(cuvdia_selftest_bounded_wait(A.plan(), 1000, 0));
+    bool thrown = false;
+    try { prod(C, A, B); } catch (const std::runtime_error& e) {
+        thrown = std::string(e.what()).find("gave up a bounded wait") != std::string::npos;
+    }
+    CHECK(thrown);
+    prod(C, A, B);                                   // the word was cleared: the next call is clean again
+    CHECK((float)C(5, 0) == 3.f);
+    cuvdia_check(cuvdia_selftest_bounded_wait(A.plan(), 1000, 0));
+    dev_block_descriptor<float> bd(A);
+    thrown = false;
+    try { densedense_to_dia(A, bd, C, B); } catch (const std::runtime_error&) { thrown = true; }
+    CHECK(thrown);
+}
+
 int main() {
     try {
         initCUDA(0);
@@ -338,6 +365,7 @@ int main() {
         test_tensor_ops();
         test_reduce_3d();
         test_learn_step();
+        test_given_up_wait_throws();
         exitCUDA();
     } catch (const std::exception& e) {
         std::printf("EXCEPTION: %s\n", e.what());

@@ -3,8 +3,10 @@ at these sizes): bit-exact comparison with the oracle on a slice of batch column
 identity that ties prod 'n' to prod 't', the trace identity that ties densedense_to_dia to prod,
 linearity, checksum-of-checksums for the reductions, and untouched padding cells.
 
-Shapes: config 3 in full (16384 x 16384, 512 diagonals, batch 1024) and the per-GPU shard of config 4
-at 8 GPUs (65536 x 65536, 1024 diagonals, batch 1024); config 1 in full (16384 x 4096, rf 4, 256
+Shapes: config 3 in full (16384 x 16384, 512 diagonals, batch 1024), the per-GPU shard of config 4
+at 8 GPUs (65536 x 65536, 1024 diagonals, batch 1024) and config 4 with the whole batch of 8192 on one GPU
+(the benchmark's one-GPU shape: 64 column tiles of the banded product, oracle slices on columns that fall
+into different tiles); config 1 in full (16384 x 4096, rf 4, 256
 diagonals, batch 512); config 0 and 2 run in full in test_gpu_parity.py."""
 import numpy as np
 import pytest
@@ -33,7 +35,7 @@ def band_problem(cb, n, nd, nb, seed):
     return W, offs, X, Y
 
 
-@pytest.mark.parametrize("n,nd,nb", [(16384, 512, 1024), (65536, 1024, 1024)])
+@pytest.mark.parametrize("n,nd,nb", [(16384, 512, 1024), (65536, 1024, 1024), (65536, 1024, 8192)])
 def test_band_full_size_properties(n, nd, nb):
     import torch
     import cuv_b200 as cb
@@ -46,13 +48,14 @@ def test_band_full_size_properties(n, nd, nb):
     assert torch.isfinite(WX).all() and torch.isfinite(WtY).all()
     # 1. a slice of batch columns against the oracle, bit for bit (both directions)
     Wh = ho.DiaHost(n, n, offs, n, 1, W.vec.cpu().numpy())
-    cols = [0, 1, nb // 2, nb - 1]
-    Xs, Ys = np.asfortranarray(cb.to_host(X)[:, cols]), np.asfortranarray(cb.to_host(Y)[:, cols])
+    cols = [0, 1, nb // 2, nb - 1] if nb <= 1024 else [0, 127, 128, nb // 2 - 1, nb - 1]
+    sl = lambda t: np.asfortranarray(t[:, cols].cpu().numpy())          # the slice is taken on the device
+    Xs, Ys = sl(X), sl(Y)
     want = np.zeros((n, len(cols)), dtype=np.float32, order="F")
     ho.prod(want, Wh, Xs, "n", nthreads=8)
-    assert_bits_equal(np.asfortranarray(cb.to_host(WX)[:, cols]), want, "prod 'n' slice at full size")
+    assert_bits_equal(sl(WX), want, "prod 'n' slice at full size")
     ho.prod(want, Wh, Ys, "t", nthreads=8)
-    assert_bits_equal(np.asfortranarray(cb.to_host(WtY)[:, cols]), want, "prod 't' slice at full size")
+    assert_bits_equal(sl(WtY), want, "prod 't' slice at full size")
     # 2. adjoint identity <W X, Y> == <X, W^T Y>
     # (the products have random signs, so the tolerance is relative to the sum of |terms|: fp32 rounding of
     # each of the n*nb outputs, about 6e-8 of its size, is all that separates the two sides)
@@ -77,11 +80,10 @@ def test_band_full_size_properties(n, nd, nb):
     # 4. factC: C <- 0.5*C + 1*W X applied to C = W X gives 1.5 * W X exactly (scaling by 0.5 and the sum are exact)
     C2 = WX.clone()
     cb.prod(C2, W, X, "n", "n", 1.0, 0.5, cb.MODE_EXACT)
-    ref = cb.colmajor_empty(n, 4)
-    refh = np.asfortranarray(cb.to_host(WX)[:, cols]).copy(order="F")
+    refh = sl(WX).copy(order="F")
     ho.prod(refh, Wh, Xs, "n", 1.0, 0.5, nthreads=8)
-    assert_bits_equal(np.asfortranarray(cb.to_host(C2)[:, cols]), refh, "factC path at full size")
-    del ref
+    assert_bits_equal(sl(C2), refh, "factC path at full size")
+    del C2
     # 5. reductions: checksum of checksums
     v = torch.empty(n, device="cuda")
     cb.reduce_to_col(v, WX)
@@ -93,7 +95,9 @@ def test_band_full_size_properties(n, nd, nb):
     # 6. FAST arithmetic stays within one rounding per term of EXACT
     WXf = cb.colmajor_empty(n, nb)
     cb.prod(WXf, W, X, "n", "n", 1.0, 0.0, cb.MODE_FAST)
-    assert float((WXf - WX).abs().max().item()) <= 1e-5 * float(WX.abs().max().item())
+    WXf.sub_(WX)
+    assert float(WXf.abs().max().item()) <= 1e-5 * float(WX.abs().max().item())
+    assert cb.plan_status(W) == 0 and cb.plan_status(G) == 0
 
 
 def test_config1_full_size_properties():

@@ -1,0 +1,93 @@
+"""The sharded CD-1 step on two GPUs: the CUDA kernels on each rank's batch columns plus the NCCL sum of the partial
+gradients (through the C ABI: cuvdia_rbm_cd1_step_f32, cuvdia_nccl_comm_create, cuvdia_allreduce_grad) against the
+unsharded step on one GPU and against the CPU oracle, all from ONE seeded input set sliced by shard_columns.
+Skipped when fewer than two GPUs are visible."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+from oracle import host_oracle as ho
+from oracle import rbm_oracle
+
+pytestmark = pytest.mark.gpu
+
+UNITS, ND, B, SEED = 2048, 128, 256, 1021
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _inputs():
+    offs = np.arange(-ND // 2, ND // 2, dtype=np.int32)
+    return rbm_oracle.make_inputs(SEED, UNITS, UNITS, offs, B, w_std=0.05, nthreads=4)
+
+
+def _rank_main(rank, world, port, out_dir):
+    import torch
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    import cuv_b200 as cb
+    from cuv_b200 import rbm
+    W, V0, U_h, U_v = _inputs()
+    c0, c1 = rbm.shard_columns(B, world, rank)
+    sl = lambda a: cb.to_device(np.asfortranarray(a[:, c0:c1]), dev)
+    Wd = cb.dev_dia_matrix_f(W.h, W.w, W.offsets, W.stride, W.rf, device=dev).set_vec(W.vals)
+    st = rbm.SparseRBMStep(Wd, c1 - c0, B, cb.MODE_EXACT, dev)
+    for _ in range(2):                       # twice: the collective leaves the same sum again on fresh partials
+        st.step(sl(V0), sl(U_h), sl(U_v))
+        st.allreduce()
+    torch.cuda.synchronize()
+    np.save(os.path.join(out_dir, "g%d.npy" % rank), st.G.vec.cpu().numpy())
+    np.save(os.path.join(out_dir, "b%d.npy" % rank), st.bias_grad.cpu().numpy())
+    np.save(os.path.join(out_dir, "h%d.npy" % rank), cb.to_host(st.H1p))
+    assert cb.plan_status(Wd) == 0
+    # the same sum over torch.distributed's own communicator: the two routes must agree bit for bit
+    st.step(sl(V0), sl(U_h), sl(U_v))
+    rbm.allreduce_gradients(st.G.vec, st.bias_grad)
+    torch.cuda.synchronize()
+    np.save(os.path.join(out_dir, "t%d.npy" % rank), st.G.vec.cpu().numpy())
+    st._reducer.close()
+    dist.destroy_process_group()
+
+
+def test_two_gpu_step_and_nccl_sum_equal_the_unsharded_step(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    import cuv_b200 as cb
+    from cuv_b200 import rbm
+    world = 2
+    mp.spawn(_rank_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    W, V0, U_h, U_v = _inputs()
+    g = [np.load(tmp_path / ("g%d.npy" % r)) for r in range(world)]
+    b = [np.load(tmp_path / ("b%d.npy" % r)) for r in range(world)]
+    assert np.array_equal(g[0], g[1]) and np.array_equal(b[0], b[1])         # every rank holds the same sum
+    assert np.array_equal(np.load(tmp_path / "t0.npy"), g[0])
+    # against the unsharded step on one GPU
+    Wd = cb.dev_dia_matrix_f(W.h, W.w, W.offsets, W.stride, W.rf).set_vec(W.vals)
+    full = rbm.SparseRBMStep(Wd, B, B, cb.MODE_EXACT)
+    full.step(cb.to_device(V0), cb.to_device(U_h), cb.to_device(U_v))
+    np.testing.assert_allclose(g[0], full.G.vec.cpu().numpy(), rtol=0, atol=2e-6)
+    np.testing.assert_allclose(b[0], full.bias_grad.cpu().numpy(), rtol=0, atol=2e-6)
+    H1p = np.concatenate([np.load(tmp_path / ("h%d.npy" % r)) for r in range(world)], axis=1)
+    assert np.array_equal(H1p, cb.to_host(full.H1p))                          # the shards are the full batch's columns
+    # against the CPU oracle's unsharded step
+    ref = rbm_oracle.cd1_step(W, V0, U_h, U_v, nthreads=8)
+    tol = 1e-4 * np.sqrt(B / 128.0)
+    m = ref["G"].valid_mask().reshape(-1)
+    pos = ho.DiaHost(W.h, W.w, W.offsets, W.stride, 1)
+    ho.densedense_to_dia(pos, ref["H0p"], V0, 1.0 / B, 0.0, nthreads=8)
+    assert np.all(np.abs(g[0][m] - ref["G"].vals[m]) <= tol * (np.abs(pos.vals[m]) + 1e-6))
+    assert np.all(g[0][~m] == 0)
+    np.testing.assert_allclose(b[0], np.concatenate([ref["gc"], ref["gb"]]), rtol=0, atol=tol)

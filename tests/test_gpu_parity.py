@@ -114,6 +114,46 @@ def test_prod_band_medium_both_ways(cb):
     prod_case(cb, rng, 2048, 2048, offs, 1, 160, "t", 1.0, 0.0)
 
 
+@pytest.mark.parametrize("trans", ["n", "t"])
+@pytest.mark.parametrize("n,nd,ncols", [(2048, 128, 96),      # tiled banded kernel
+                                        (65536, 12, 8),       # streaming kernel
+                                        (4096, 40, 16)])      # run-walking kernel
+def test_nonfinite_dense_values_beside_the_band(cb, trans, n, nd, ncols):
+    """Inf and NaN in the dense operand.  Outputs whose band contains the bad row are non-finite in CUV's host loop
+    (matrix_ops/spmv.cu:161-198) and here, with the same bits.  Outputs whose band lies well away from it are untouched
+    in both.  In between lies the one stated deviation of the TMA-fed kernels: they walk the band in fixed-size
+    chunks and give cells outside the band a zero coefficient instead of skipping them, so a non-finite dense value
+    within a chunk's reach of the band (at most 64 rows here) turns the output into NaN where CUV would not read
+    it.  The test pins exactly that: such outputs equal the oracle's or are NaN, nothing else."""
+    rng = np.random.default_rng(n + nd)
+    lo = -(nd // 2)
+    A = make_dia(rng, n, n, np.arange(lo, lo + nd, dtype=np.int32), 1)
+    B = F(rng.uniform(-1, 1, (n, ncols)))
+    bad_rows = [n // 3, (2 * n) // 3 + 1]
+    B[bad_rows[0], :] = np.inf
+    B[bad_rows[1], :] = np.nan
+    want = F(np.zeros((n, ncols)))
+    ho.prod(want, A, B, trans, nthreads=4)
+    got = run_prod(cb, A, B, F(np.zeros((n, ncols))), trans, 1.0, 0.0, cb.MODE_EXACT)
+    out = np.arange(n)
+    # output i reads dense rows i+lo .. i+lo+nd-1 ('n') or i-lo-nd+1 .. i-lo ('t')
+    first = out + lo if trans == "n" else out - lo - nd + 1
+    dist = np.full(n, 10 ** 9)
+    for r in bad_rows:
+        inside = (first <= r) & (r <= first + nd - 1)
+        d = np.where(inside, 0, np.minimum(np.abs(first - r), np.abs(first + nd - 1 - r)))
+        dist = np.minimum(dist, d)
+    hit, far = dist == 0, dist > 64
+    assert not np.isfinite(want[hit]).any() and np.isfinite(want[~hit]).all()
+    assert_bits_equal(got[far], want[far], "outputs away from the non-finite rows")
+    assert not np.isfinite(got[hit]).any()
+    assert np.array_equal(np.isnan(got[hit]), np.isnan(want[hit]))
+    assert_bits_equal(np.where(np.isnan(got[hit]), 0, got[hit]), np.where(np.isnan(want[hit]), 0, want[hit]), "inf outputs")
+    near = ~hit & ~far
+    same = (got[near].view(np.uint32) == want[near].view(np.uint32)) | ((got[near] == 0) & (want[near] == 0))
+    assert np.all(same | np.isnan(got[near]))
+
+
 def test_spmv_packed_vectors(cb):
     rng = np.random.default_rng(77)
     A = make_dia(rng, 64, 48, np.array([0, -3, 5], dtype=np.int32))
@@ -568,12 +608,20 @@ def test_bounded_wait_gives_up_with_a_status(cb):
     _capi.check(L.cuvdia_plan_status(D._plan, ctypes.byref(st)))
     assert st.value == 9
     assert L.cuvdia_selftest_bounded_wait(D._plan, 0, stream) == _capi.ERR_INVALID
-    _capi.check(L.cuvdia_plan_status_clear(D._plan, stream))
     B = np.asfortranarray(rng.standard_normal((300, 70)).astype(np.float32))
     want = np.zeros((300, 70), dtype=np.float32, order="F")
     ho.prod(want, A, B, "n")
     C = cb.colmajor_empty(300, 70)
-    cb.prod(C, D, dev_padded(cb, B), "n", "n", 1.0, 0.0, cb.MODE_EXACT)
+    # the blocking form of a call notices the code, clears it and raises, as CUV throws from a failed operation
+    with pytest.raises(cb.CuvDiaError, match="gave up a bounded wait"):
+        cb.prod(C, D, dev_padded(cb, B), "n", "n", 1.0, 0.0, cb.MODE_EXACT, check_status=True)
+    assert cb.plan_status(D) == 0
+    _capi.check(L.cuvdia_selftest_bounded_wait(D._plan, 2000, stream))
+    with pytest.raises(cb.CuvDiaError, match="gave up a bounded wait"):
+        cb.densedense_to_dia(D, None, cb.colmajor_empty(300, 8).zero_(), cb.colmajor_empty(300, 8).zero_(), 1.0, 1.0,
+                             check_status=True)
+    D.set_vec(A.vals)
+    cb.prod(C, D, dev_padded(cb, B), "n", "n", 1.0, 0.0, cb.MODE_EXACT, check_status=True)
     assert_bits_equal(cb.to_host(C), want, "prod after the self-test")
     _capi.check(L.cuvdia_plan_status(D._plan, ctypes.byref(st)))
     assert st.value == 0

@@ -9,21 +9,27 @@ from tests.helpers import assert_bits_equal
 pytestmark = pytest.mark.gpu
 
 
-def run_gpu_step(cb, W, V0, U_h, U_v, batch_global=None, mode=None, fused=True):
+def run_gpu_step(cb, W, V0, U_h, U_v, batch_global=None, mode=None, fused=False, **kw):
     from cuv_b200 import rbm
     Wd = cb.dev_dia_matrix_f(W.h, W.w, W.offsets, W.stride, W.rf).set_vec(W.vals)
-    st = rbm.SparseRBMStep(Wd, V0.shape[1], batch_global, cb.MODE_EXACT if mode is None else mode, fused=fused)
+    st = rbm.SparseRBMStep(Wd, V0.shape[1], batch_global, cb.MODE_EXACT if mode is None else mode, fused=fused, **kw)
     st.step(cb.to_device(V0), cb.to_device(U_h), cb.to_device(U_v))
     return st
 
 
-@pytest.mark.parametrize("units,nd,nb", [(1024, 32, 96), (2048, 128, 160)])
-def test_cd1_step_matches_oracle(units, nd, nb):
+# the step as one C call with the bias sums taken in the element-wise passes (default), and the trainer's literal
+# call sequence with four reductions, through the combined product + element-wise entry point
+STEP_VARIANTS = [dict(), dict(fused=True)]
+
+
+@pytest.mark.parametrize("variant", STEP_VARIANTS, ids=["c_step", "combined_calls"])
+@pytest.mark.parametrize("units,nd,nb", [(1024, 32, 96), (2048, 128, 160), (1000, 37, 50), (1001, 37, 50)])
+def test_cd1_step_matches_oracle(units, nd, nb, variant):
     import cuv_b200 as cb
-    offs = np.arange(-nd // 2, nd // 2, dtype=np.int32)
+    offs = np.arange(-(nd // 2), nd - nd // 2, dtype=np.int32)
     W, V0, U_h, U_v = rbm_oracle.make_inputs(1003, units, units, offs, nb, w_std=0.05)
     ref = rbm_oracle.cd1_step(W, V0, U_h, U_v, nthreads=8)
-    st = run_gpu_step(cb, W, V0, U_h, U_v)
+    st = run_gpu_step(cb, W, V0, U_h, U_v, **variant)
     np.testing.assert_allclose(cb.to_host(st.H0p), ref["H0p"], rtol=1e-5)           # activations: rel 1e-5
     assert np.array_equal(cb.to_host(st.H0), ref["H0"])                              # samples identical
     np.testing.assert_allclose(cb.to_host(st.V1p), ref["V1p"], rtol=1e-5)
@@ -129,7 +135,7 @@ def test_combined_entry_point_gives_the_bits_of_the_separate_calls(units, nd, nb
     offs = np.arange(-(nd // 2), nd - nd // 2, dtype=np.int32)
     W, V0, U_h, U_v = rbm_oracle.make_inputs(3000 + nd, units, units, offs, nb, w_std=0.05)
     a = run_gpu_step(cb, W, V0, U_h, U_v, fused=True)
-    b = run_gpu_step(cb, W, V0, U_h, U_v, fused=False)
+    b = run_gpu_step(cb, W, V0, U_h, U_v, fused=False, bias_sums="reduce")
     for name in ("H0p", "H0", "V1p", "V1", "H1p"):
         assert_bits_equal(cb.to_host(getattr(a, name)), cb.to_host(getattr(b, name)), name)
     assert_bits_equal(a.G.vec.cpu().numpy(), b.G.vec.cpu().numpy(), "G")
@@ -190,3 +196,143 @@ def test_step_replayed_from_a_cuda_graph():
     st.step(dV0, dUh, dUv)
     torch.cuda.synchronize()
     assert torch.equal(st.G.vec, replayed)
+
+
+@pytest.mark.parametrize("units,nb", [(1024, 96), (1000, 50), (4096, 7), (1027, 33), (8192, 1024)])
+def test_elementwise_pass_with_batch_sums(units, nb):
+    """bias + logistic + compare with the per-unit batch sum taken in the same pass: activations and samples are the
+    bits of the plain pass, the sums agree with a float64 sum (activations) or are exact (0/1 samples), accumulate
+    with factOld, and are identical run to run."""
+    import torch
+    import cuv_b200 as cb
+    g = torch.Generator(device="cuda"); g.manual_seed(units + nb)
+    mk = lambda lo, hi: cb.colmajor_empty(units, nb).uniform_(lo, hi, generator=g)
+    pre, U = mk(-3, 3), mk(0, 1)
+    bias = torch.empty(units, device="cuda").uniform_(-1, 1, generator=g)
+    act0, S0 = pre.clone(), cb.colmajor_empty(units, nb)
+    cb.bias_sigmoid_sample(act0, bias, U, S0)
+    tol = 1e-4 * np.sqrt(max(nb, 128) / 128.0)
+    for of_sample in (False, True):
+        act, S = pre.clone(), cb.colmajor_empty(units, nb)
+        dst = torch.full((units,), float("nan"), device="cuda")          # factOld == 0: never read
+        cb.bias_sigmoid_sample_sum(act, bias, U, S, dst, of_sample, 0.25, 0.0)
+        assert torch.equal(act, act0) and torch.equal(S, S0)
+        want = (S0 if of_sample else act0).double().sum(dim=1) * 0.25
+        if of_sample:
+            assert torch.equal(dst.double(), want)
+        else:
+            assert float(((dst.double() - want).abs() / want.abs().clamp_min(1e-6)).max()) <= tol
+        again = dst.clone()
+        cb.bias_sigmoid_sample_sum(pre.clone(), bias, U, S, again, of_sample, 0.25, 0.0)
+        assert torch.equal(again, dst)
+        acc = torch.ones(units, device="cuda")
+        cb.bias_sigmoid_sample_sum(pre.clone(), bias, U, S, acc, of_sample, -0.25, 2.0)
+        np.testing.assert_allclose(acc.cpu().numpy(), (2.0 - dst).cpu().numpy(), rtol=1e-6, atol=1e-6)
+    # store_act=False: samples and their sum as before, the activations left as they were
+    act, S = pre.clone(), cb.colmajor_empty(units, nb)
+    dst = torch.empty(units, device="cuda")
+    cb.bias_sigmoid_sample_sum(act, bias, U, S, dst, True, 1.0, 0.0, store_act=False)
+    assert torch.equal(act, pre) and torch.equal(S, S0) and torch.equal(dst.double(), S0.double().sum(dim=1))
+    # no sampling: activations only, no bias
+    act, act1 = pre.clone(), pre.clone()
+    cb.bias_sigmoid_sample(act1)
+    cb.bias_sigmoid_sample_sum(act, None, None, None, dst, False, 1.0, 0.0)
+    assert torch.equal(act, act1)
+    assert float(((dst.double() - act1.double().sum(dim=1)).abs() / act1.double().sum(dim=1)).max()) <= tol
+
+
+def test_c_step_equals_the_call_by_call_step():
+    """cuvdia_rbm_cd1_step_f32 queues exactly the launches of forward() + gradients(): same bits everywhere; the
+    bias sums taken in the element-wise passes agree with the four separate reductions within the batch-sum
+    tolerance, and keep_v1p=False changes nothing but V1p."""
+    import cuv_b200 as cb
+    from cuv_b200 import rbm
+    units, nd, nb = 2048, 96, 224
+    offs = np.arange(-nd // 2, nd // 2, dtype=np.int32)
+    W, V0, U_h, U_v = rbm_oracle.make_inputs(1011, units, units, offs, nb, w_std=0.05)
+    b = (np.random.default_rng(3).standard_normal(units) * 0.1).astype(np.float32)
+    c = (np.random.default_rng(4).standard_normal(units) * 0.1).astype(np.float32)
+    dV0, dUh, dUv = cb.to_device(V0), cb.to_device(U_h), cb.to_device(U_v)
+
+    def make(**kw):
+        Wd = cb.dev_dia_matrix_f(W.h, W.w, W.offsets, W.stride, W.rf).set_vec(W.vals)
+        st = rbm.SparseRBMStep(Wd, nb, 4 * nb, **kw)
+        st.b_vis.copy_(cb.to_device(b)); st.c_hid.copy_(cb.to_device(c))
+        return st
+    one = make(); one.step(dV0, dUh, dUv)
+    calls = make(); calls.forward(dV0, dUh, dUv); calls.gradients(dV0)
+    for name in ("H0p", "H0", "V1p", "V1", "H1p"):
+        assert_bits_equal(cb.to_host(getattr(one, name)), cb.to_host(getattr(calls, name)), name)
+    assert_bits_equal(one.G.vec.cpu().numpy(), calls.G.vec.cpu().numpy(), "G")
+    assert_bits_equal(one.bias_grad.cpu().numpy(), calls.bias_grad.cpu().numpy(), "bias gradients")
+    sep = make(bias_sums="reduce"); sep.step(dV0, dUh, dUv)
+    assert_bits_equal(one.G.vec.cpu().numpy(), sep.G.vec.cpu().numpy(), "G vs separate reductions")
+    tol = 1e-4 * np.sqrt(max(nb, 128) / 128.0)
+    np.testing.assert_allclose(one.bias_grad.cpu().numpy(), sep.bias_grad.cpu().numpy(), rtol=0, atol=tol)
+    lean = make(keep_v1p=False); lean.step(dV0, dUh, dUv)
+    for name in ("H0p", "H0", "V1", "H1p"):
+        assert_bits_equal(cb.to_host(getattr(lean, name)), cb.to_host(getattr(one, name)), name)
+    assert_bits_equal(lean.grad_buf.cpu().numpy(), one.grad_buf.cpu().numpy(), "gradients without V1p written")
+    ref = rbm_oracle.cd1_step(W, V0, U_h, U_v, batch_global=4 * nb, b=b, c=c, nthreads=8)
+    np.testing.assert_allclose(one.gc.cpu().numpy(), ref["gc"], rtol=0, atol=tol)
+    np.testing.assert_allclose(one.gb.cpu().numpy(), ref["gb"], rtol=0, atol=tol)
+
+
+def test_cd1_step_at_config3_size():
+    """BASELINE config 3 (16384 units, 512 diagonals, batch 1024) through the one-call step: the activations of a
+    16-column slice against the oracle (the oracle's step on those columns; samples identical because uniforms
+    that tie with a probability are moved away first), the bias gradients against float64 sums, and the weight
+    gradient through three diagonals computed by the oracle on all columns and the trace identity
+    sum(G * W) == (<H0p, W V0> - <H1p, W V1>) / B."""
+    import torch
+    import cuv_b200 as cb
+    from cuv_b200 import rbm
+    units, nd, nb = 16384, 512, 1024
+    offs = np.arange(-nd // 2, nd // 2, dtype=np.int32)
+    g = torch.Generator(device="cuda"); g.manual_seed(1003)
+    Wd = cb.dev_dia_matrix_f(units, units, offs, units, 1)
+    Wd.vec.normal_(0.0, 0.01, generator=g)
+    mask = torch.from_numpy(ho.DiaHost(units, units, offs, units, 1).valid_mask().reshape(-1)).cuda()
+    Wd.vec[~mask] = 0.0
+    V0 = cb.colmajor_empty(units, nb); V0.t().copy_((torch.rand((nb, units), device="cuda", generator=g) < 0.3).float())
+    U_h, U_v = cb.colmajor_empty(units, nb), cb.colmajor_empty(units, nb)
+    U_h.t().copy_(torch.rand((nb, units), device="cuda", generator=g))
+    U_v.t().copy_(torch.rand((nb, units), device="cuda", generator=g))
+    st = rbm.SparseRBMStep(Wd, nb, mode=cb.MODE_FAST)
+
+    def away(p, u):          # uniforms within 1e-4 of their probability move 1e-3 away (rbm_oracle.make_inputs does the same)
+        near = (p - u).abs() < 1e-4
+        u[near] = torch.where(p[near] >= 0.5, p[near] - 1e-3, p[near] + 1e-3)
+    st.step(V0, U_h, U_v); away(st.H0p, U_h)
+    st.step(V0, U_h, U_v); away(st.V1p, U_v)
+    st.step(V0, U_h, U_v)
+    cols = list(range(0, nb, nb // 16))
+    Wh = ho.DiaHost(units, units, offs, units, 1, Wd.vec.cpu().numpy())
+    sl = lambda t: np.asfortranarray(t[:, cols].cpu().numpy())
+    ref = rbm_oracle.cd1_step(Wh, sl(V0), sl(U_h), sl(U_v), batch_global=nb, nthreads=8)
+    np.testing.assert_allclose(sl(st.H0p), ref["H0p"], rtol=1e-5)
+    assert np.array_equal(sl(st.H0), ref["H0"])
+    np.testing.assert_allclose(sl(st.V1p), ref["V1p"], rtol=1e-5)
+    assert np.array_equal(sl(st.V1), ref["V1"])
+    np.testing.assert_allclose(sl(st.H1p), ref["H1p"], rtol=1e-5)
+    tol = 1e-4 * np.sqrt(nb / 128.0)
+    want_gc = (st.H0p.double().sum(dim=1) - st.H1p.double().sum(dim=1)) / nb
+    want_gb = (V0.double().sum(dim=1) - st.V1.double().sum(dim=1)) / nb
+    assert float((st.gc.double() - want_gc).abs().max()) <= tol
+    assert float((st.gb.double() - want_gb).abs().max()) <= tol
+    some = [0, nd // 2, nd - 1]
+    pos, neg = ho.DiaHost(units, units, offs[some], units, 1), ho.DiaHost(units, units, offs[some], units, 1)
+    full = lambda t: np.asfortranarray(t.cpu().numpy())
+    ho.densedense_to_dia(pos, full(st.H0p), full(V0), 1.0 / nb, 0.0, nthreads=8)
+    ho.densedense_to_dia(neg, full(st.H1p), full(st.V1), 1.0 / nb, 0.0, nthreads=8)
+    got = st.G.vec.cpu().numpy().reshape(nd, units)[some]
+    m = pos.valid_mask()
+    p_, n_ = pos.vals.reshape(len(some), units), neg.vals.reshape(len(some), units)
+    assert np.all(np.abs(got[m] - (p_[m] - n_[m])) <= tol * (np.abs(p_[m]) + 1e-6))
+    WV0, WV1 = cb.colmajor_empty(units, nb), cb.colmajor_empty(units, nb)
+    cb.prod(WV0, Wd, V0, "n"); cb.prod(WV1, Wd, st.V1, "n")
+    dot = lambda a, b_: float((a.double() * b_.double()).sum().item())
+    lhs = float((st.G.vec.double() * Wd.vec.double()).sum().item())
+    rhs = (dot(st.H0p, WV0) - dot(st.H1p, WV1)) / nb
+    scale = (dot(st.H0p, WV0.abs()) + dot(st.H1p, WV1.abs())) / nb
+    assert abs(lhs - rhs) <= 1e-5 * scale
