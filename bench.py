@@ -15,7 +15,8 @@ CUV's host code) on all host cores on a bounded batch slice of the same workload
 Other cases (single routines, used for profiling and for the per-configuration table):
 ``--case prod_n|prod_t|dd2dia|reduce|glue|update`` on the band shape given by --units/--num-dia/--batch, and
 ``--case cfg0|cfg1|cfg2|rbm_cfg3`` for the other BASELINE configurations, ``--case spmv_speed_n|spmv_speed_t|dd2dia_speed``
-for the reference's own speed fixtures (convolution-pattern matrices).
+for the reference's own speed fixtures (convolution-pattern matrices), ``--case wide_n|wide_dd`` for scattered
+diagonals that no shared-memory window covers (the plain kernels).
 """
 import argparse
 import json
@@ -299,10 +300,16 @@ def check_allreduce(cb, rbm, torch, dist, step, V0, U_h, U_v, W, units, nd, batc
     torch.cuda.synchronize()
     d2 = float((step.G.vec - full.G.vec).abs().max().item())
     d3 = float((step.bias_grad - full.bias_grad).abs().max().item())
-    ok = d1 <= 2e-6 and d2 <= 2e-6 and d3 <= 2e-6
+    # (1) is the same sum in another order over at most `world` terms; (2) compares tree sums of `batch` terms, each
+    # at most 1/batch in size, taken in different orders (two such sums per gradient cell on either side): the
+    # worst-case rounding is 4 * 2^-24 * (log2(batch) + 2), far inside the 1e-4*sqrt(batch/128) relative tolerance
+    # of batch-summed gradients
+    import math
+    tol = 4.0 * 2.0 ** -24 * (math.log2(batch) + 2)
+    ok = d1 <= tol and d2 <= tol and d3 <= tol
     del full, FV0, FUh, FUv
     torch.cuda.empty_cache()
-    return {"result": "ok" if ok else "MISMATCH", "tolerance_abs": 2e-6,
+    return {"result": "ok" if ok else "MISMATCH", "tolerance_abs": tol,
             "max_abs_diff_vs_sum_of_gathered_partials_3_diagonals": d1,
             "max_abs_diff_G_vs_unsharded_step_on_rank0": d2, "max_abs_diff_bias_grad_vs_unsharded_step_on_rank0": d3}
 
@@ -663,6 +670,12 @@ def measure_single(args, cfg):
     elif case == "cfg2":
         h = w = 4096; nb = 1024; rf = 1
         offs = np.sort(rng.choice(np.arange(-2047, 2048), 128, replace=False)).astype(np.int32); op = "dd2dia"
+    elif case in ("wide_n", "wide_dd"):
+        # scattered diagonals spread over tens of thousands of rows: no shared-memory window fits, the plain
+        # one-thread-per-row kernels run (prod_generic_kernel, dd2dia_generic_kernel)
+        h = w = 65536; nb = 128 if case == "wide_n" else 256; rf = 1
+        offs = np.sort(rng.choice(np.arange(-30000, 30001), 64, replace=False)).astype(np.int32)
+        op = "prod_n" if case == "wide_n" else "dd2dia"
     elif case == "membound_dd":
         # densedense_to_dia where HBM bounds it: 2^20 rows, 16 diagonals, 32 batch columns
         h = w = 1 << 20; nb = 32; rf = 1

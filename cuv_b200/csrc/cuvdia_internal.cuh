@@ -105,6 +105,9 @@ int ensure_plan_scratch(cuvdia_plan* p, size_t floats, cudaStream_t st);
 bool prod_band_applicable(const cuvdia_plan* p, const float* A, const float* B, int ldb, int ncols);
 int launch_prod_band(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
                      bool trans, float factAB, float factC, int mode, cudaStream_t st);
+bool prod_bandw_applicable(const cuvdia_plan* p, const float* A, const float* B, int ldb, int ncols);
+int launch_prod_bandw(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
+                      bool trans, float factAB, float factC, int mode, cudaStream_t st);
 bool prod_narrow_applicable(const cuvdia_plan* p, const float* A, const float* B, int ldb, int ncols);
 // true if launch_prod_narrow would take its TMA streaming variant (at most 16 diagonals, many rows)
 bool prod_narrow_streams(const cuvdia_plan* p, bool trans);

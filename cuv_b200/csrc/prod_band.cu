@@ -189,10 +189,16 @@ prod_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         constexpr unsigned RAW_TX = sizeof(float) * (TRANS ? RAW_FLOATS_T : RAW_FLOATS_N);
         constexpr unsigned BS_TX = sizeof(float) * BS_FLOATS;
         auto issue_raw = [&](int c) {
+#ifdef PB_X_SKIPRAW
+            if (c >= 1) { mbar_arrive(raw_full); return; }
+#endif
             mbar_expect_tx(raw_full, RAW_TX);
             tma_load_2d(raw, &mapA, TRANS ? win_row0(c) : t0, c * KC - P.rem - 7, raw_full);
         };
         auto issue_b = [&](int c) {
+#ifdef PB_X_SKIPB
+            if (c >= 2) { mbar_arrive(&bs_full[c & 1]); return; }
+#endif
             mbar_expect_tx(&bs_full[c & 1], BS_TX);
             tma_load_2d(Bs0 + (c & 1) * BSF, &mapB, win_row0(c), n0, &bs_full[c & 1]);
         };
@@ -202,11 +208,18 @@ prod_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
             if (nch > 1) issue_b(1);
         }
         for (int c = 0; c < nch; c++) {
+#ifdef PB_X_NOHANDOVER
+            if (c >= 2) return;
+#endif
             bool ok = warp_wait(raw_full, c & 1);
             if (ok && c >= 2) ok = warp_wait(&as_empty[c & 1], ((c >> 1) + 1) & 1);
             if (!ok) { if (lane == 0 && P.status) *P.status = 1; return; }
             // ---- skew: As[qq][r] = factAB * A[k][matrix row], zero where the cell is outside the matrix ----
             float* as = As0 + (c & 1) * AS_FLOATS;
+#ifdef PB_X_NOSKEW
+            if (c < 2)
+#endif
+            {
             const int y0 = c * KC - P.rem - 7;
             const int xb = win_row0(c);
             const int j = lane & 7;
@@ -242,6 +255,7 @@ prod_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
                         dst[it * NPROD_WARPS * TM] = in ? v : 0.f;
                     }
                 }
+            }
             }
             __syncwarp();
             if (lane == 0) { mbar_arrive(&as_full[c & 1]); mbar_arrive(raw_free); }
@@ -288,10 +302,18 @@ prod_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         }
     }
 
+#ifdef PB_X_STAGGER
+    if (warp >= 4) __nanosleep(PB_X_STAGGER);
+#endif
     for (int c = 0; c < nch; c++) {
         const int s = c & 1;
+#ifdef PB_X_NOHANDOVER
+        bool ok = c >= 2 ? true : warp_wait(&as_full[s], (c >> 1) & 1);
+        if (ok && c < 2) ok = warp_wait(&bs_full[s], (c >> 1) & 1);
+#else
         bool ok = warp_wait(&as_full[s], (c >> 1) & 1);
         if (ok) ok = warp_wait(&bs_full[s], (c >> 1) & 1);
+#endif
         if (!ok) { if (lane == 0 && P.status) *P.status = 1; return; }
         const float* bsp = Bs0 + s * BSF + cg * WR + (TRANS ? (r0 + KC - 4) : r0);
         const float* asp = As0 + s * AS_FLOATS + r0;
@@ -373,6 +395,26 @@ int make_map_2d(CUtensorMap* m, const float* base, long long dim0, long long dim
     cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_last_error("cuTensorMapEncodeTiled failed with code %d", (int)r); return CUVDIA_ERR_CUDA; }
+    return CUVDIA_OK;
+}
+
+// The same with a TMA shared-memory swizzle of 0 (none), 32, 64 or 128 bytes (the box's inner extent in bytes must not
+// exceed the swizzle span).
+int make_map_2d_swizzled(CUtensorMap* m, const float* base, long long dim0, long long dim1, long long pitch, int box0,
+                         int box1, int swizzle_bytes) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) { set_last_error("cuTensorMapEncodeTiled is not available from the driver"); return CUVDIA_ERR_CUDA; }
+    cuuint64_t dims[2] = {(cuuint64_t)dim0, (cuuint64_t)dim1};
+    cuuint64_t strides[1] = {(cuuint64_t)pitch * sizeof(float)};
+    cuuint32_t box[2] = {(cuuint32_t)box0, (cuuint32_t)box1};
+    cuuint32_t estr[2] = {1, 1};
+    const CUtensorMapSwizzle sw = swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                  : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                  : swizzle_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE;
+    CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { set_last_error("cuTensorMapEncodeTiled failed with code %d", (int)r); return CUVDIA_ERR_CUDA; }
     return CUVDIA_OK;

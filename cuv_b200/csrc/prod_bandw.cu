@@ -1,0 +1,355 @@
+// prod with a banded DIA operand (consecutive ascending diagonals, row_fact 1) and many batch columns:
+// the band walked as a streaming product.
+//
+// With offsets lo, lo+1, ..., lo+nd-1
+//     'n':  C[i,b] = sum_k A[k][i]       * B[i+lo+k, b]
+//     't':  C[j,b] = sum_k A[k][j-lo-k]  * B[j-lo-k, b].
+// A block owns 32 output rows and 1024 batch columns.  All of its rows walk the SAME dense rows of B,
+// X0, X0+1, ... in steps q = 0, 1, ...: output row r of the tile meets B row X0+q on diagonal
+// k = q - r - rem ('n') or k = nd-1+rem+r-q ('t'), so one step is the rank-1 update
+//     C[r, b] += As[q][r] * B[X0+q, b]
+// with the 32 coefficients As[q][.] of the step laid side by side - a product of a [32 x (nd+31)] coefficient
+// panel with [(nd+31) x 1024] rows of B, of which each output only uses the nd steps its diagonals cover
+// (the other 31 carry zero coefficients: the price of sharing B rows across the tile, 31/nd of the work).
+// B is therefore streamed through shared memory exactly once per tile, 16 rows at a time, by TMA tile
+// loads (cp.async.bulk.tensor, no multicast, 64-byte swizzle so that the 128-bit reads along a column are
+// free of bank conflicts) into a three-stage ring; there is no halo and no window to re-load.  One
+// producer warp issues the loads and re-lays ("skews") each slice of the band, as TMA delivers it, into the
+// coefficient panel As of the stage, applying factAB and zeroing cells outside the matrix (padding cells of
+// the diagonal storage may hold NaN and must never contribute).  Sixteen consumer warps (four per
+// scheduler) each own 32 rows x 64 columns, 16 rows x 4 columns per thread: per step four 128-bit loads of
+// coefficients (shared by half a warp), a quarter of four 128-bit loads of B, and 32 packed f32x2
+// multiply-adds.  About 100 registers per thread instead of the 160 of an 8 x 8 register tile is what lets
+// four warps per scheduler hide the shared-memory latency.  Every hand-over is an mbarrier with a bounded,
+// warp-uniform wait; consumers never meet a block barrier.
+// The transposed product walks the B rows in DESCENDING order (X0 is the highest row the tile needs), so that
+// for both products the diagonals an output meets ascend with the step: per output the terms are added in
+// diagonal storage order, and the EXACT mode (separate multiply and add) reproduces CUV's host loop
+// (matrix_ops/spmv.cu:161-198) bit for bit, except that skipped cells are added as +0 (a -0 accumulator
+// becomes +0) and a non-finite B value within a chunk's reach of an output's band meets a zeroed coefficient.
+#include <cuda.h>
+
+#include "cuvdia_internal.cuh"
+
+namespace cuvdia {
+
+int make_map_2d_swizzled(CUtensorMap* m, const float* base, long long dim0, long long dim1, long long pitch, int box0,
+                         int box1, int swizzle_bytes);
+
+namespace pw {
+constexpr int TM = 32;                 // output rows per block
+constexpr int NCW = 16;                // consumer warps, 64 columns each
+constexpr int TN = 64 * NCW;           // batch columns per block
+constexpr int KC = 16;                 // steps (B rows) per chunk
+constexpr int STAGES = 3;
+constexpr int NRAW = KC + TM - 1;      // diagonals a chunk touches
+constexpr int BOXC = 256;              // columns per TMA box of B
+constexpr int THREADS = 32 * (NCW + 4);   // warps are allocated four at a time: the producer warp brings three idle ones
+constexpr int REGS_CONSUMER = 112;        // register budgets after the warp groups re-balance the register file
+constexpr int REGS_PRODUCER = 64;
+constexpr int BS_FLOATS = KC * TN;     // one stage of B: [column][16 rows], 64 KB
+constexpr int AS_FLOATS = KC * TM;     // one stage of coefficients: [step][32 rows]
+constexpr int RAW_FLOATS = NRAW * TM;  // band slice as TMA delivers it ('n': 47 x 32; 't': 47 x 16 uses half)
+constexpr size_t SMEM = sizeof(float) * (STAGES * BS_FLOATS + STAGES * AS_FLOATS + 2 * RAW_FLOATS) + 256;
+constexpr unsigned SPIN_LIMIT = 1u << 26;
+}  // namespace pw
+
+__device__ __forceinline__ unsigned w_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void w_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(w_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void w_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(w_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void w_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(w_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool w_wait(unsigned long long* bar, unsigned parity) {
+    const unsigned addr = w_u32(bar);
+    for (unsigned it = 0; it < pw::SPIN_LIMIT; it++) {
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+// warp-uniform: either every lane sees the phase complete or the whole warp gives up
+__device__ __forceinline__ bool w_warp_wait(unsigned long long* bar, unsigned parity) {
+    return __all_sync(0xffffffffu, w_wait(bar, parity) ? 1 : 0) != 0;
+}
+__device__ __forceinline__ void w_tma_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(w_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(w_u32(bar)) : "memory");
+}
+
+template <bool EXACT>
+__device__ __forceinline__ void w_mac2(float2& acc, float2 a, float2 b) {
+    if (EXACT) {                       // separate roundings: packed multiply, two scalar adds (stays unfused)
+        const float2 p = __fmul2_rn(a, b);
+        acc.x = __fadd_rn(acc.x, p.x);
+        acc.y = __fadd_rn(acc.y, p.y);
+    } else {
+        acc = __ffma2_rn(a, b, acc);
+    }
+}
+
+struct BandWParams {
+    int h, w, nd, lo;
+    int rows_out, rows_b;     // h, w ('n') or w, h ('t')
+    int ncols, ldc;
+    int rem;                  // alignment shift (0..3) that keeps every TMA row coordinate a multiple of 4
+    int nchunks;
+    int last_groups;          // 4-step groups of the last chunk that contain steps of the band (1..4)
+    float fa, fc;
+    int vec_c;                // C allows 128-bit accesses
+    float* C;
+    int* status;
+};
+
+// Step q of the tile whose first output row is t0 meets B row
+//   'n': x = t0 + lo - rem + q            on diagonal k = q - r - rem            for output row t0 + r
+//   't': x = t0 - lo + rem + 31 - q       on diagonal k = q - (31 - r) - rem     for output row t0 + r
+// (rem makes x = 0 mod 4 at q = 0 mod 4 for 'n' and x = 3 mod 4 for 't', so 16-row boxes start on 16-byte
+// boundaries); in both cases the diagonals an output meets ascend with q.
+template <bool TRANS, bool EXACT>
+__global__ void __launch_bounds__(pw::THREADS, 1)
+prod_bandw_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                  const BandWParams P) {
+    using namespace pw;
+    extern __shared__ __align__(1024) float smem_f[];
+    float* const Bs0 = smem_f;                                   // [STAGES][TN][KC], swizzled by TMA
+    float* const As0 = smem_f + STAGES * BS_FLOATS;              // [STAGES][KC][TM]
+    float* const raw0 = As0 + STAGES * AS_FLOATS;                // [2][NRAW x TM]
+    unsigned long long* const bars = reinterpret_cast<unsigned long long*>(raw0 + 2 * RAW_FLOATS);
+    unsigned long long* const full = bars;                       // [STAGES] B landed (tx) + coefficients written
+    unsigned long long* const empty = bars + STAGES;             // [STAGES] one arrival per consumer warp
+    unsigned long long* const raw_full = bars + 2 * STAGES;      // [2]
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // column tiles vary fastest across the grid: blocks that run together share the band slice and neighbouring
+    // row tiles re-use each other's B rows out of L2
+    const int t0 = blockIdx.y * TM;
+    const int n0 = blockIdx.x * TN;
+    const int nch = P.nchunks;
+
+    if (tid == 0) {
+#pragma unroll
+        for (int s = 0; s < STAGES; s++) { w_init(&full[s], 2); w_init(&empty[s], NCW); }
+        w_init(&raw_full[0], 1);
+        w_init(&raw_full[1], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    // The kernel is compiled for 96 registers per thread (640 threads); the producer's warp group hands most of its
+    // share back and the four consumer warp groups take 112 each (16*32*112 + 4*32*64 registers = the whole file).
+    if (warp >= NCW) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_PRODUCER));
+        if (warp > NCW) return;
+        // =========================== producer warp ===========================
+        // first B row (TMA x coordinate) and first diagonal (y coordinate) of chunk c
+        auto b_row0 = [&](int c) { return TRANS ? (t0 - P.lo + P.rem + 31 - c * KC - (KC - 1)) : (t0 + P.lo - P.rem + c * KC); };
+        auto k0 = [&](int c) { return c * KC - (TM - 1) - P.rem; };
+        constexpr unsigned RAW_TX = sizeof(float) * NRAW * (TRANS ? KC : TM);
+        constexpr unsigned BS_TX = sizeof(float) * BS_FLOATS;
+        auto issue_raw = [&](int c) {
+            w_expect_tx(&raw_full[c & 1], RAW_TX);
+            // 'n': the tile's 32 rows of each diagonal;  't': the chunk's 16 matrix rows (= its B rows) of each diagonal
+            w_tma_2d(raw0 + (c & 1) * RAW_FLOATS, &mapA, TRANS ? b_row0(c) : t0, k0(c), &raw_full[c & 1]);
+        };
+        if (lane == 0) { issue_raw(0); if (nch > 1) issue_raw(1); }
+        for (int c = 0; c < nch; c++) {
+            const int s = c % STAGES;
+            bool ok = true;
+            if (c >= STAGES) ok = w_warp_wait(&empty[s], ((c / STAGES) - 1) & 1);
+            if (!ok) { if (lane == 0 && P.status) *P.status = 3; return; }
+            if (lane == 0) {
+                w_expect_tx(&full[s], BS_TX);
+#pragma unroll
+                for (int bx = 0; bx < TN / BOXC; bx++)
+                    w_tma_2d(Bs0 + s * BS_FLOATS + bx * (KC * BOXC), &mapB, b_row0(c), n0 + bx * BOXC, &full[s]);
+            }
+            ok = w_warp_wait(&raw_full[c & 1], (c >> 1) & 1);
+            if (!ok) { if (lane == 0 && P.status) *P.status = 3; return; }
+            // ---- skew: As[qq][r] = factAB * A[k][matrix row] with k = k0 + qq - r' + 31 (r' = r for 'n', 31 - r for
+            // 't'), zero where the cell lies outside the matrix.  Lane = output row r of the tile. ----
+            const float* raw = raw0 + (c & 1) * RAW_FLOATS;
+            float* as = As0 + s * AS_FLOATS;
+            const int kc0 = k0(c), xb = b_row0(c);
+            const int rr = TRANS ? (TM - 1 - lane) : lane;
+            // chunk-uniform: every cell the chunk touches lies inside the matrix
+            const bool interior = kc0 >= 0 && kc0 + NRAW <= P.nd && xb >= 0 && xb + KC <= P.rows_b &&
+                                  (TRANS || t0 + TM <= P.h);
+#pragma unroll 4
+            for (int qq = 0; qq < KC; qq++) {
+                const int kk = qq - rr + (TM - 1);                    // row of the slice: diagonal kc0 + kk
+                // 'n': slice is [diagonal][32 tile rows];  't': [diagonal][16 B rows], B row xb + (KC-1-qq) at step qq
+                float v = TRANS ? raw[kk * KC + (KC - 1 - qq)] : raw[kk * TM + lane];
+                if (!interior || P.fa != 1.f) {
+                    const int k = kc0 + kk;
+                    const int x = TRANS ? xb + (KC - 1 - qq) : xb + qq;                 // B row of the step
+                    // 'n': matrix cell (t0 + r, x): the column x must exist;  't': cell (x, t0 + r): the row x must exist
+                    const bool in = (unsigned)k < (unsigned)P.nd && (unsigned)x < (unsigned)P.rows_b &&
+                                    (TRANS || t0 + lane < P.h);
+                    if (P.fa != 1.f) v = __fmul_rn(P.fa, v);
+                    v = in ? v : 0.f;
+                }
+                as[qq * TM + lane] = v;
+            }
+            __syncwarp();
+            if (lane == 0) {
+                w_arrive(&full[s]);
+                if (c + 2 < nch) issue_raw(c + 2);
+            }
+            __syncwarp();
+        }
+        return;
+    }
+
+    // =========================== consumer warps ===========================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS_CONSUMER));
+    const int rg = lane >> 4, cg = lane & 15;
+    // this thread: rows t0 + 16*rg .. +15, columns n0 + 64*warp + cg + 16*cc (cc = 0..3)
+    const int colb = 64 * warp + cg;
+    const int sw = (cg >> 1) & 3;                 // 64-byte swizzle: 16-byte chunk j of column c sits at j ^ ((c >> 1) & 3)
+
+    float2 acc[8][4];                             // acc[jp][cc]: rows (2jp, 2jp+1) of column cc
+#pragma unroll
+    for (int jp = 0; jp < 8; jp++)
+#pragma unroll
+        for (int cc = 0; cc < 4; cc++) acc[jp][cc] = make_float2(0.f, 0.f);
+    if (P.fc != 0.f) {
+#pragma unroll
+        for (int cc = 0; cc < 4; cc++) {
+            const int col = n0 + colb + 16 * cc;
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                const int row = t0 + 16 * rg + j;
+                if (col < P.ncols && row < P.rows_out) {
+                    const float v = __fmul_rn(P.C[(size_t)col * P.ldc + row], P.fc);
+                    if (j & 1) acc[j >> 1][cc].y = v; else acc[j >> 1][cc].x = v;
+                }
+            }
+        }
+    }
+
+    for (int c = 0; c < nch; c++) {
+        const int s = c % STAGES;
+        if (!w_warp_wait(&full[s], (c / STAGES) & 1)) { if (lane == 0 && P.status) *P.status = 3; return; }
+        const float* bsp = Bs0 + s * BS_FLOATS + colb * KC;
+        const float* asp = As0 + s * AS_FLOATS + 16 * rg;
+        const int ng = c == nch - 1 ? P.last_groups : KC / 4;
+#pragma unroll
+        for (int g = 0; g < KC / 4; g++) {
+            if (g < ng) {
+                float4 bw[4];
+#pragma unroll
+                for (int cc = 0; cc < 4; cc++)
+                    bw[cc] = *reinterpret_cast<const float4*>(bsp + cc * 16 * KC + (((TRANS ? 3 - g : g) ^ sw) << 2));
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const float* ap = asp + (4 * g + u) * TM;
+                    const float4 a0 = *reinterpret_cast<const float4*>(ap);
+                    const float4 a1 = *reinterpret_cast<const float4*>(ap + 4);
+                    const float4 a2 = *reinterpret_cast<const float4*>(ap + 8);
+                    const float4 a3 = *reinterpret_cast<const float4*>(ap + 12);
+                    const float2 a[8] = {make_float2(a0.x, a0.y), make_float2(a0.z, a0.w), make_float2(a1.x, a1.y),
+                                         make_float2(a1.z, a1.w), make_float2(a2.x, a2.y), make_float2(a2.z, a2.w),
+                                         make_float2(a3.x, a3.y), make_float2(a3.z, a3.w)};
+#pragma unroll
+                    for (int cc = 0; cc < 4; cc++) {
+                        float b;
+                        // 'n': B rows ascend with the step;  't': the chunk's 16 rows were loaded ascending, walked descending
+                        if (!TRANS) b = u == 0 ? bw[cc].x : u == 1 ? bw[cc].y : u == 2 ? bw[cc].z : bw[cc].w;
+                        else        b = u == 0 ? bw[cc].w : u == 1 ? bw[cc].z : u == 2 ? bw[cc].y : bw[cc].x;
+                        const float2 bb = make_float2(b, b);
+#pragma unroll
+                        for (int jp = 0; jp < 8; jp++) w_mac2<EXACT>(acc[jp][cc], a[jp], bb);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) w_arrive(&empty[s]);
+    }
+
+    // ---- store ----
+#pragma unroll
+    for (int cc = 0; cc < 4; cc++) {
+        const int col = n0 + colb + 16 * cc;
+        if (col >= P.ncols) continue;
+        const int row0 = t0 + 16 * rg;
+        float* cp = P.C + (size_t)col * P.ldc + row0;
+        if (P.vec_c && row0 + 16 <= P.rows_out) {
+#pragma unroll
+            for (int v = 0; v < 4; v++)
+                *reinterpret_cast<float4*>(cp + 4 * v) =
+                    make_float4(acc[2 * v][cc].x, acc[2 * v][cc].y, acc[2 * v + 1][cc].x, acc[2 * v + 1][cc].y);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; j++)
+                if (row0 + j < P.rows_out) cp[j] = (j & 1) ? acc[j >> 1][cc].y : acc[j >> 1][cc].x;
+        }
+    }
+}
+
+// ---- host side ----------------------------------------------------------------------------------------
+
+static inline bool w_al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+bool prod_bandw_applicable(const cuvdia_plan* p, const float* A, const float* B, int ldb, int ncols) {
+    // 1024-column tiles: worth it when the batch fills them well and the band is wide enough to pay for the 31
+    // extra steps per tile
+    if (p->nd < 96) return false;
+    const int tiles = (ncols + pw::TN - 1) / pw::TN;
+    if ((long long)ncols * 4 < (long long)tiles * pw::TN * 3) return false;
+    return p->is_band && p->rf == 1 && w_al16(A) && w_al16(B) && p->stride % 4 == 0 && ldb % 4 == 0 && tma_available();
+}
+
+template <bool TRANS, bool EXACT>
+static int launch_bandw_t(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
+                          float fa, float fc, cudaStream_t st) {
+    using namespace pw;
+    CUtensorMap mapA, mapB;
+    int rc = make_map_2d_swizzled(&mapA, A, p->h, p->nd, p->stride, TRANS ? KC : TM, NRAW, 0);
+    if (rc) return rc;
+    rc = make_map_2d_swizzled(&mapB, B, TRANS ? p->h : p->w, ncols, ldb, KC, BOXC, 64);
+    if (rc) return rc;
+    BandWParams P;
+    P.h = p->h; P.w = p->w; P.nd = p->nd; P.lo = p->band_lo;
+    P.rows_out = TRANS ? p->w : p->h;
+    P.rows_b = TRANS ? p->h : p->w;
+    P.ncols = ncols; P.ldc = ldc;
+    // 'n': a chunk's first B row t0 + lo - rem + 16c, 't': t0 - lo + rem + 16 - 16c; both are 0 mod 4
+    P.rem = ((p->band_lo % 4) + 4) % 4;
+    const int steps = p->nd + (TM - 1) + P.rem;
+    P.nchunks = (steps + KC - 1) / KC;
+    P.last_groups = (steps - (P.nchunks - 1) * KC + 3) / 4;
+    P.fa = fa; P.fc = fc;
+    P.vec_c = (w_al16(C) && ldc % 4 == 0) ? 1 : 0;
+    P.C = C; P.status = p->d_status;
+    static bool attr_done[64] = {false};          // one flag set per template instantiation
+    rc = allow_dynamic_smem(prod_bandw_kernel<TRANS, EXACT>, SMEM, attr_done);
+    if (rc) return rc;
+    const int gx = (P.rows_out + TM - 1) / TM, gy = (ncols + TN - 1) / TN;
+    if (gx > 65535) { set_last_error("too many rows for the banded kernel"); return CUVDIA_ERR_UNSUPPORTED; }
+    prod_bandw_kernel<TRANS, EXACT><<<dim3(gy, gx), THREADS, SMEM, st>>>(mapA, mapB, P);
+    count_launch();
+    return check_launch("prod_bandw_kernel");
+}
+
+int launch_prod_bandw(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
+                      bool trans, float fa, float fc, int mode, cudaStream_t st) {
+    const bool exact = mode == CUVDIA_MODE_EXACT;
+    if (trans) return exact ? launch_bandw_t<true, true>(p, A, B, ldb, C, ldc, ncols, fa, fc, st)
+                            : launch_bandw_t<true, false>(p, A, B, ldb, C, ldc, ncols, fa, fc, st);
+    return exact ? launch_bandw_t<false, true>(p, A, B, ldb, C, ldc, ncols, fa, fc, st)
+                 : launch_bandw_t<false, false>(p, A, B, ldb, C, ldc, ncols, fa, fc, st);
+}
+
+}  // namespace cuvdia

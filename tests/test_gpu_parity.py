@@ -92,6 +92,22 @@ def test_prod_band_ragged_sizes(cb, trans):
         prod_case(cb, rng, h, w, offs, 1, ncols, trans, 1.0, 0.5)
 
 
+@pytest.mark.parametrize("trans", ["n", "t"])
+@pytest.mark.parametrize("h,w,lo,nd,ncols,fab,fc", [
+    (1000, 1000, -64, 128, 1024, 1.0, 0.0),      # square, centred band, one full column tile
+    (257, 301, -40, 97, 800, 0.75, 2.0),         # ragged rows, partly filled column tile, both factors
+    (301, 257, 3, 130, 1000, 1.0, 0.5),          # band above the main diagonal (alignment shift 3)
+    (640, 2000, 900, 200, 1024, 2.0, 0.0),       # wide matrix, band far from the main diagonal
+    (2000, 640, -1500, 256, 2048, 1.0, 0.0),     # tall matrix, two column tiles
+    (96, 96, -95, 191, 768, 1.0, 0.0),           # every diagonal of a small matrix: most cells outside it
+])
+def test_prod_band_wide_batches(cb, trans, h, w, lo, nd, ncols, fab, fc):
+    """Bands times many batch columns (the streaming banded kernel: 32-row tiles, 1024 columns per block)."""
+    rng = np.random.default_rng(h + 7 * nd + ncols + (trans == "t"))
+    offs = np.arange(lo, lo + nd, dtype=np.int32)
+    prod_case(cb, rng, h, w, offs, 1, ncols, trans, fab, fc)
+
+
 def test_prod_config0_shape(cb):
     """BASELINE config 0: 4096x4096, 64 sorted scattered diagonals, batch 128, factors 1/0."""
     rng = np.random.Generator(np.random.PCG64(1000))
@@ -116,6 +132,7 @@ def test_prod_band_medium_both_ways(cb):
 
 @pytest.mark.parametrize("trans", ["n", "t"])
 @pytest.mark.parametrize("n,nd,ncols", [(2048, 128, 96),      # tiled banded kernel
+                                        (2048, 128, 1024),    # streaming banded kernel (wide batches)
                                         (65536, 12, 8),       # streaming kernel
                                         (4096, 40, 16)])      # run-walking kernel
 def test_nonfinite_dense_values_beside_the_band(cb, trans, n, nd, ncols):
