@@ -18,7 +18,7 @@ from ._capi import (CuvDiaError, MODE_EXACT, MODE_FAST, RF_ADD, RF_MEAN, RF_ADD_
                     RF_ARGMIN, RF_MIN, RF_MULT, RF_LOGADDEXP, RF_ADDEXP)
 
 __all__ = ["dev_dia_matrix_f", "host_dia_matrix_f", "convert", "pull", "save_dia_mat", "load_dia_mat", "dev_block_descriptor_f", "prod", "spmv", "densedense_to_dia", "reduce_to_col",
-           "reduce_to_row", "bias_sigmoid_sample", "bias_sigmoid_sample_sum", "prod_bias_sigmoid_sample", "axpby", "learn_step_weight_decay",
+           "reduce_to_row", "avg_diagonals", "bias_sigmoid_sample", "bias_sigmoid_sample_sum", "prod_bias_sigmoid_sample", "axpby", "learn_step_weight_decay",
            "learn_step_weight_decay_momentum", "colmajor_empty", "to_device", "to_host",
            "launch_count", "plan_status", "raise_if_gave_up", "CuvDiaError", "MODE_EXACT", "MODE_FAST"]
 
@@ -337,10 +337,28 @@ def densedense_to_dia(C, Cbd, A, B, factAB=1.0, factC=0.0, check_status=False):
     return C
 
 
-def _reduce(dst, src, over_first_axis_kept, rf, factNew, factOld):
+def avg_diagonals(dst, A):
+    """dst[k] = mean over the cells of stored diagonal k that lie inside the matrix (matrix_ops/diagonals.hpp:12,
+    host definition matrix_ops/diagonals.cu:23-48)."""
+    if dst.numel() != A.num_dia or not dst.is_contiguous():
+        raise CuvDiaError(_capi.ERR_INVALID, "dia.num_dia()==dst.size()")
+    _capi.check(_capi.lib().cuvdia_avg_diagonals_f32(A._plan, _ptr(A.vec), _ptr(dst), _stream()))
+    return dst
+
+
+def _type_code(t):
     torch = _torch()
-    if not (src.is_cuda and src.dtype == torch.float32 and src.dim() == 2 and src.is_cuda and dst.is_cuda):
-        raise CuvDiaError(_capi.ERR_INVALID, "src must be a 2-D float32 CUDA tensor")
+    codes = {torch.float32: _capi.T_F32, torch.int32: _capi.T_I32, torch.uint8: _capi.T_U8}
+    if hasattr(torch, "uint32"):
+        codes[torch.uint32] = _capi.T_U32
+    if t.dtype not in codes:
+        raise CuvDiaError(_capi.ERR_UNSUPPORTED, "element type %s (float32, int32, uint32, uint8)" % t.dtype)
+    return codes[t.dtype]
+
+
+def _reduce(dst, src, over_first_axis_kept, rf, factNew, factOld):
+    if not (src.dim() == 2 and src.is_cuda and dst.is_cuda):
+        raise CuvDiaError(_capi.ERR_INVALID, "src must be a 2-D CUDA tensor")
     if src.stride(0) == 1 and (src.shape[1] == 1 or src.stride(1) == src.shape[0]):      # column-major
         n_contig, n_strided, keep_contig = src.shape[0], src.shape[1], over_first_axis_kept
     elif src.stride(1) == 1 and (src.shape[0] == 1 or src.stride(0) == src.shape[1]):    # row-major
@@ -349,14 +367,16 @@ def _reduce(dst, src, over_first_axis_kept, rf, factNew, factOld):
         raise CuvDiaError(_capi.ERR_INVALID, "src must be densely packed")
     if dst.numel() != (n_contig if keep_contig else n_strided) or not dst.is_contiguous():
         raise CuvDiaError(_capi.ERR_INVALID, "main_dim == v.size()")
-    _capi.check(_capi.lib().cuvdia_reduce_f32(_ptr(dst), _ptr(src), n_contig, n_strided, 1 if keep_contig else 0,
-                                              rf, factNew, factOld, _stream()))
+    _capi.check(_capi.lib().cuvdia_reduce(_ptr(dst), _type_code(dst), _ptr(src), _type_code(src), n_contig, n_strided,
+                                          1 if keep_contig else 0, rf, factNew, factOld, _stream()))
     return dst
 
 
 def reduce_to_col(dst, src, rf=RF_ADD, factNew=1.0, factOld=0.0):
     """dst[i] = factOld*dst[i] + factNew*rf_j(src[i, j]); dst.size == src.shape[0]
-    (matrix_ops/matrix_ops.hpp:211-212, matrix_ops_reduce.cu:348-362)."""
+    (matrix_ops/matrix_ops.hpp:211-212, matrix_ops_reduce.cu:348-362).  ``src`` / ``dst`` element types: the pairs
+    CUV instantiates (float32, int32, uint32, uint8 sources with float32 results; float32 sources with int32, uint32,
+    uint8 results; uint8 -> uint8 / uint32), with CUV's semantics for them (running value in the source type)."""
     return _reduce(dst, src, True, rf, factNew, factOld)
 
 

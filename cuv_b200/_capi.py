@@ -10,6 +10,7 @@ LIB_PATH = os.path.join(_HERE, "libcuvdia.so")
 
 OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_NOMEM = range(5)
 MODE_EXACT, MODE_FAST = 0, 1
+T_F32, T_I32, T_U32, T_U8 = range(4)
 (RF_ADD, RF_MEAN, RF_ADD_SQUARED, RF_MAX, RF_ARGMAX, RF_ARGMIN, RF_MIN, RF_MULT, RF_LOGADDEXP,
  RF_ADDEXP) = range(10)
 
@@ -31,7 +32,9 @@ SIGNATURES = {
     "cuvdia_prod_bias_sigmoid_sample_f32": (_i, [_vp, _vp, _vp, _i, _vp, _i, _i, _c, _f, _f, _i, _vp, _vp, _i, _vp, _i,
                                                  _vp]),
     "cuvdia_dd2dia_f32": (_i, [_vp, _vp, _vp, _i, _vp, _i, _i, _f, _f, _vp]),
+    "cuvdia_avg_diagonals_f32": (_i, [_vp, _vp, _vp, _vp]),
     "cuvdia_reduce_f32": (_i, [_vp, _vp, _ll, _ll, _i, _i, _f, _f, _vp]),
+    "cuvdia_reduce": (_i, [_vp, _i, _vp, _i, _ll, _ll, _i, _i, _f, _f, _vp]),
     "cuvdia_reduce_noalloc_f32": (_i, [_vp, _vp, _ll, _ll, _i, _i, _f, _f, _vp]),
     "cuvdia_bias_sigmoid_sample_f32": (_i, [_vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _vp]),
     "cuvdia_bias_sigmoid_sample_sum_f32": (_i, [_vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _vp, _i, _f, _f, _i, _vp]),

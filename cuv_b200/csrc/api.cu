@@ -302,6 +302,31 @@ int cuvdia_reduce_f32(float* dst, const float* src, long long n_contig, long lon
                          (cudaStream_t)stream);
 }
 
+int cuvdia_avg_diagonals_f32(const cuvdia_plan* p, const float* A_vals, float* dst, void* stream) {
+    CUVDIA_REQUIRE(p != nullptr && A_vals != nullptr && dst != nullptr);
+    CUVDIA_REQUIRE(p->rf == 1);                          // matrix_ops/diagonals.cu:28
+    CUVDIA_REQUIRE(plan_on_current_device(p));
+    return launch_avg_diagonals(p, A_vals, dst, (cudaStream_t)stream);
+}
+
+int cuvdia_reduce(void* dst, int dst_type, const void* src, int src_type, long long n_contig, long long n_strided,
+                  int over_strided, int functor, float factNew, float factOld, void* stream) {
+    if (dst_type == CUVDIA_T_F32 && src_type == CUVDIA_T_F32)
+        return cuvdia_reduce_f32((float*)dst, (const float*)src, n_contig, n_strided, over_strided, functor, factNew,
+                                 factOld, stream);
+    CUVDIA_REQUIRE(dst != nullptr);
+    CUVDIA_REQUIRE(src != nullptr);                      // matrix_ops_reduce.cu:160,192
+    CUVDIA_REQUIRE(n_contig > 0 && n_strided > 0);
+    CUVDIA_REQUIRE(n_contig * n_strided <= 2147483647LL);
+    CUVDIA_REQUIRE(functor >= CUVDIA_RF_ADD && functor <= CUVDIA_RF_ADDEXP);
+    if (functor == CUVDIA_RF_MEAN) {                     // matrix_ops_reduce.cu:309-310
+        CUVDIA_REQUIRE(factNew == 1.f);
+        CUVDIA_REQUIRE(factOld == 0.f);
+    }
+    return launch_reduce_typed(dst, dst_type, src, src_type, n_contig, n_strided, over_strided != 0, functor, factNew,
+                               factOld, (cudaStream_t)stream);
+}
+
 int cuvdia_bias_sigmoid_sample_f32(float* act, int ld, const float* bias, const float* u, int ldu, float* sample,
                                    int lds, int units, int ncols, void* stream) {
     CUVDIA_REQUIRE(act != nullptr);

@@ -131,6 +131,9 @@ int launch_dd2dia_band(cuvdia_plan* p, float* Cv, const float* A, int lda, const
                        float factAB, float factC, cudaStream_t st);
 int launch_reduce(float* dst, const float* src, long long n_contig, long long n_strided, bool over_strided,
                   int functor, float factNew, float factOld, cudaStream_t st);
+int launch_reduce_typed(void* dst, int dst_type, const void* src, int src_type, long long n_contig, long long n_strided,
+                        bool over_strided, int functor, float fnew, float fold, cudaStream_t st);
+int launch_avg_diagonals(const cuvdia_plan* p, const float* A, float* dst, cudaStream_t st);
 int launch_bias_sigmoid_sample(float* act, int ld, const float* bias, const float* u, int ldu, float* sample,
                                int lds, int units, int ncols, cudaStream_t st);
 // the same pass that also accumulates sum_dst[unit] = fold*sum_dst[unit] + fnew*sum over columns of the activation

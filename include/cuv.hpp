@@ -6,6 +6,7 @@
 #include "cuv/basics/tensor.hpp"
 #include "cuv/convert/convert.hpp"
 #include "cuv/matrix_ops/densedense_to_sparse.hpp"
+#include "cuv/matrix_ops/diagonals.hpp"
 #include "cuv/matrix_ops/matrix_ops.hpp"
 #include "cuv/tensor_ops/rprop.hpp"
 #include "cuv/tensor_ops/tensor_ops.hpp"

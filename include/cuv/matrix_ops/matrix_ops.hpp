@@ -69,13 +69,22 @@ inline void spmv(tensor<float, dev_memory_space>& dst, const dia_matrix<float, d
 }
 
 // ---- reductions ------------------------------------------------------------------------------------------
+// reduce_to_col / reduce_to_row keep CUV's signature (matrix_ops/matrix_ops.hpp:211-228): destination element type V2,
+// source element type V, factors of the SOURCE type.  The pairs CUV instantiates are available
+// (matrix_ops/matrix_ops_reduce.cu:395-413); any other pair fails with the library's "not supported" error.
 namespace detail {
-// src viewed as n_strided lines of n_contig contiguous floats.  A tensor of more than two dimensions is reduced
+template <class T> struct cuvdia_type;       // element type -> CUVDIA_T_* code
+template <> struct cuvdia_type<float> { static const int code = CUVDIA_T_F32; };
+template <> struct cuvdia_type<int> { static const int code = CUVDIA_T_I32; };
+template <> struct cuvdia_type<unsigned int> { static const int code = CUVDIA_T_U32; };
+template <> struct cuvdia_type<unsigned char> { static const int code = CUVDIA_T_U8; };
+
+// src viewed as n_strided lines of n_contig contiguous elements.  A tensor of more than two dimensions is reduced
 // like the matrix that keeps the surviving dimension and flattens the others (matrix_ops_reduce.cu:228-231,348-379):
 // reduce_to_col keeps the first dimension, reduce_to_row the last.  Returns whether the reduction runs over the
 // strided direction (the outputs are then the contiguous one).
-template <class M, class L>
-inline bool reduce_dims(const tensor<float, M, L>& m, bool keep_first, long long& n_contig, long long& n_strided) {
+template <class V, class M, class L>
+inline bool reduce_dims(const tensor<V, M, L>& m, bool keep_first, long long& n_contig, long long& n_strided) {
     const bool cm = std::is_same<L, column_major>::value;
     const long long kept = keep_first ? m.shape(0) : m.shape(m.ndim() - 1), others = m.size() / kept;
     const bool kept_is_contiguous = keep_first ? cm : !cm;
@@ -83,45 +92,53 @@ inline bool reduce_dims(const tensor<float, M, L>& m, bool keep_first, long long
     n_contig = others; n_strided = kept;
     return false;
 }
-void reduce_host(tensor<float, host_memory_space>& v, const float* m, long long n_contig, long long n_strided,
-                 bool over_strided, reduce_functor rf, float factNew, float factOld);   // reference host code
+// the reference host code (not part of this library; the test suite supplies it)
+void reduce_host(void* v, int v_type, const void* m, int m_type, long long n_contig, long long n_strided,
+                 bool over_strided, reduce_functor rf, float factNew, float factOld);
+
+template <class V2, class V, class L>
+inline void reduce_dev(tensor<V2, dev_memory_space>& dst, const tensor<V, dev_memory_space, L>& src, bool keep_first,
+                       reduce_functor rf, const V& factNew, const V& factOld) {
+    cuvAssert(src.ptr() != NULL);
+    long long nc, ns;
+    const bool over_strided = reduce_dims(src, keep_first, nc, ns);
+    cuvAssert((long long)dst.size() == (over_strided ? nc : ns));
+    cuvdia_check(cuvdia_reduce(dst.ptr(), cuvdia_type<V2>::code, src.ptr(), cuvdia_type<V>::code, nc, ns,
+                               over_strided ? 1 : 0, (int)rf, (float)factNew, (float)factOld, 0));
+    cuvSafeCall(cudaDeviceSynchronize());
+}
+template <class V2, class V, class L>
+inline void reduce_hst(tensor<V2, host_memory_space>& dst, const tensor<V, host_memory_space, L>& src, bool keep_first,
+                       reduce_functor rf, const V& factNew, const V& factOld) {
+    long long nc, ns;
+    const bool over_strided = reduce_dims(src, keep_first, nc, ns);
+    cuvAssert((long long)dst.size() == (over_strided ? nc : ns));
+    reduce_host(dst.ptr(), cuvdia_type<V2>::code, src.ptr(), cuvdia_type<V>::code, nc, ns, over_strided, rf,
+                (float)factNew, (float)factOld);
+}
 }  // namespace detail
 
 // dst[i] = factOld*dst[i] + factNew*rf_j(src(i,j)), dst.size() == src.shape(0)
-template <class L>
-void reduce_to_col(tensor<float, dev_memory_space>& dst, const tensor<float, dev_memory_space, L>& src,
-                   reduce_functor rf = RF_ADD, const float& factNew = 1.f, const float& factOld = 0.f) {
-    cuvAssert(src.ptr() != NULL);
-    long long nc, ns;
-    const bool over_strided = detail::reduce_dims(src, true, nc, ns);
-    cuvAssert((long long)dst.size() == (over_strided ? nc : ns));
-    cuvdia_check(cuvdia_reduce_f32(dst.ptr(), src.ptr(), nc, ns, over_strided ? 1 : 0, (int)rf, factNew, factOld, 0));
-    cuvSafeCall(cudaDeviceSynchronize());
+template <class V2, class V, class L>
+void reduce_to_col(tensor<V2, dev_memory_space>& dst, const tensor<V, dev_memory_space, L>& src, reduce_functor rf = RF_ADD,
+                   const V& factNew = 1, const V& factOld = 0) {
+    detail::reduce_dev(dst, src, true, rf, factNew, factOld);
 }
 // dst[j] = factOld*dst[j] + factNew*rf_i(src(i,j)), dst.size() == src.shape(last)
-template <class L>
-void reduce_to_row(tensor<float, dev_memory_space>& dst, const tensor<float, dev_memory_space, L>& src,
-                   reduce_functor rf = RF_ADD, const float& factNew = 1.f, const float& factOld = 0.f) {
-    cuvAssert(src.ptr() != NULL);
-    long long nc, ns;
-    const bool over_strided = detail::reduce_dims(src, false, nc, ns);
-    cuvAssert((long long)dst.size() == (over_strided ? nc : ns));
-    cuvdia_check(cuvdia_reduce_f32(dst.ptr(), src.ptr(), nc, ns, over_strided ? 1 : 0, (int)rf, factNew, factOld, 0));
-    cuvSafeCall(cudaDeviceSynchronize());
+template <class V2, class V, class L>
+void reduce_to_row(tensor<V2, dev_memory_space>& dst, const tensor<V, dev_memory_space, L>& src, reduce_functor rf = RF_ADD,
+                   const V& factNew = 1, const V& factOld = 0) {
+    detail::reduce_dev(dst, src, false, rf, factNew, factOld);
 }
-template <class L>
-void reduce_to_col(tensor<float, host_memory_space>& dst, const tensor<float, host_memory_space, L>& src,
-                   reduce_functor rf = RF_ADD, const float& factNew = 1.f, const float& factOld = 0.f) {
-    long long nc, ns;
-    const bool over_strided = detail::reduce_dims(src, true, nc, ns);
-    detail::reduce_host(dst, src.ptr(), nc, ns, over_strided, rf, factNew, factOld);
+template <class V2, class V, class L>
+void reduce_to_col(tensor<V2, host_memory_space>& dst, const tensor<V, host_memory_space, L>& src, reduce_functor rf = RF_ADD,
+                   const V& factNew = 1, const V& factOld = 0) {
+    detail::reduce_hst(dst, src, true, rf, factNew, factOld);
 }
-template <class L>
-void reduce_to_row(tensor<float, host_memory_space>& dst, const tensor<float, host_memory_space, L>& src,
-                   reduce_functor rf = RF_ADD, const float& factNew = 1.f, const float& factOld = 0.f) {
-    long long nc, ns;
-    const bool over_strided = detail::reduce_dims(src, false, nc, ns);
-    detail::reduce_host(dst, src.ptr(), nc, ns, over_strided, rf, factNew, factOld);
+template <class V2, class V, class L>
+void reduce_to_row(tensor<V2, host_memory_space>& dst, const tensor<V, host_memory_space, L>& src, reduce_functor rf = RF_ADD,
+                   const V& factNew = 1, const V& factOld = 0) {
+    detail::reduce_hst(dst, src, false, rf, factNew, factOld);
 }
 
 }  // namespace cuv

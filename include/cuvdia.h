@@ -157,6 +157,13 @@ CUVDIA_API int cuvdia_prod_f32(const cuvdia_plan* plan, const float* A_vals,
 CUVDIA_API int cuvdia_dd2dia_f32(cuvdia_plan* plan, float* C_vals, const float* A, int lda,
                       const float* B, int ldb, int ncols, float factAB, float factC, void* stream);
 
+/* dst[k] = mean of stored diagonal k over the cells that lie inside the matrix (num_dia floats, device memory).
+ * Replaces cuv::avg_diagonals(tensor&, const dia_matrix&) (matrix_ops/diagonals.hpp:12) with the definition of its
+ * host code (matrix_ops/diagonals.cu:23-48; row_fact must be 1, :28).  CUV's device version (:13-22) averages the
+ * whole stored array of each diagonal, padding included; the host definition is followed.  A diagonal with no cell
+ * inside the matrix gives NaN.  The sum is taken in a fixed tree order (batch-sum tolerance). */
+CUVDIA_API int cuvdia_avg_diagonals_f32(const cuvdia_plan* plan, const float* A_vals, float* dst, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * dst = factOld*dst + factNew*functor(src) along one axis of a matrix.
  * Replaces cuv::reduce_to_col / cuv::reduce_to_row (matrix_ops/matrix_ops.hpp:211-212,227-228;
@@ -172,6 +179,30 @@ CUVDIA_API int cuvdia_dd2dia_f32(cuvdia_plan* plan, float* C_vals, const float* 
  * ------------------------------------------------------------------------------------------- */
 CUVDIA_API int cuvdia_reduce_f32(float* dst, const float* src, long long n_contig, long long n_strided,
                       int over_strided, int functor, float factNew, float factOld, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * The reduction between the other element types CUV instantiates (matrix_ops/matrix_ops_reduce.cu:395-413):
+ * (source, destination) = (int, float), (unsigned, float), (unsigned char, float), (float, int),
+ * (float, unsigned), (float, unsigned char), (unsigned char, unsigned char), (unsigned char, unsigned);
+ * (float, float) forwards to cuvdia_reduce_f32; any other pair returns CUVDIA_ERR_UNSUPPORTED, as CUV has no
+ * instantiation for it.  Semantics are those of CUV's code, which keeps the running value in the SOURCE type
+ * and folds in the DESTINATION type (matrix_ops_reduce.cu:217-292, reduce_switch :304-343):
+ *   ADD/MEAN r = (S)((D)r + (D)x);  ADD_SQUARED r = (S)((D)r + (D)(x*x));  MAX/MIN/ARGMAX/ARGMIN compare in S;
+ *   dst = factOld*dst + factNew*r with both factors converted to S first (unsigned char: 0.5 becomes 0) and the
+ *   expression evaluated by C++'s usual arithmetic conversions before it is stored as D; ARG* store the index;
+ *   MEAN divides by the line length in D.
+ * Integer running values wrap to the width of S (8 or 32 bits), so the result does not depend on the summation
+ * order and is bit-identical to CUV's sequential host loop wherever C++ defines that loop (no float -> integer
+ * conversion out of range, no signed overflow, sums routed through float below 2^24).  MULT, LOGADDEXP and
+ * ADDEXP are float -> float only (CUVDIA_ERR_UNSUPPORTED otherwise).  Layout arguments as cuvdia_reduce_f32.
+ * ------------------------------------------------------------------------------------------- */
+#define CUVDIA_T_F32 0
+#define CUVDIA_T_I32 1
+#define CUVDIA_T_U32 2
+#define CUVDIA_T_U8  3
+CUVDIA_API int cuvdia_reduce(void* dst, int dst_type, const void* src, int src_type, long long n_contig,
+                             long long n_strided, int over_strided, int functor, float factNew, float factOld,
+                             void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * The same reduction as cuvdia_reduce_f32 for callers that must not allocate device memory.

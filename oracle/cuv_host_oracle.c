@@ -24,6 +24,7 @@
  * reduce over the strided axis).  Each output's summation order is unchanged
  * by the split, so results are bit-identical to one thread.
  */
+#include <limits.h>
 #include <math.h>
 #include <float.h>
 #include <pthread.h>
@@ -347,6 +348,101 @@ ORACLE_API int oracle_reduce(float *dst, const float *src, long n_contig, long n
     red_ctx c = { dst, src, n_contig, n_strided, over_strided, rf, factNew, factOld };
     parallel_ranges(red_range, &c, over_strided ? n_contig : n_strided, nthreads);
     return 0;
+}
+
+/* avg_diagonals, host version (matrix_ops/diagonals.cu:23-48): mean of each stored diagonal over the cells
+ * inside the matrix, summed sequentially in float; row_fact must be 1 (:28). */
+ORACLE_API int oracle_avg_diagonals(float *dst, const float *vals, const int *offsets, int nd, int h, int w, int stride,
+                                    int rf)
+{
+    if (rf != 1) return -1;
+    for (int i = 0; i < nd; i++) {
+        float sum = 0;
+        const int k = offsets[i];
+        const int i_start = k < 0 ? -k : 0, j_start = k > 0 ? k : 0;
+        const int N = (h - i_start) < (w - j_start) ? (h - i_start) : (w - j_start);
+        const float *d = vals + (long)i * stride + i_start;
+        for (int j = 0; j < N; j++) sum += *d++;
+        dst[i] = sum / N;
+    }
+    return 0;
+}
+
+/* ------------------------------------------------------------------------ */
+/* reduce_to_col / reduce_to_row between other element types                  */
+/* ------------------------------------------------------------------------ */
+
+/* CUV instantiates the reductions for nine (source S, destination D) pairs
+ * (matrix_ops/matrix_ops_reduce.cu:395-413).  The host loop (:217-292) keeps
+ * the running value in the SOURCE type (`values` is tensor<unconstV>, :244),
+ * starts it at reduce_functor_traits::init_value() (functors.hpp:599-644:
+ * 0, or the lowest / highest value of S for max / min and their arg forms),
+ * folds with the functors reduce_switch picks (:304-343)
+ *    ADD, MEAN     r = bf_plus<D,D,S>(r, x)       = (D)r + (D)x      (functors.hpp:374)
+ *    ADD_SQUARED   r = bf_add_square<D,D,S>(r, x) = (D)r + (D)(x*x)  (:392)
+ *    MAX, MIN      r = bf_max / bf_min<S,S,S>                        (:401-404)
+ *    ARGMAX/ARGMIN reduce_argmax / reduce_argmin<S, index>           (:574-592)
+ * (the functor's D result is stored back into the S running value), and ends
+ * with  *v = factOld * *v + factNew * r  or  *v = factNew * r  with factors of
+ * type S (:277-283), the index for the arg forms (:285-287), and for MEAN a
+ * division of v by the line length in D (:312).  The macro below is that loop,
+ * sequential, one instance per pair; C's conversions are C++'s. */
+#define DEFINE_REDUCE_TYPED(NAME, S, D, S_LOWEST, S_HIGHEST)                                              \
+static void NAME(D *dst, const S *src, long n_contig, long n_strided, int over_strided, int rf,          \
+                 float factNew_f, float factOld_f)                                                        \
+{                                                                                                         \
+    const S factNew = (S)factNew_f, factOld = (S)factOld_f;                                               \
+    const long n_out = over_strided ? n_contig : n_strided, n_red = over_strided ? n_strided : n_contig;  \
+    for (long o = 0; o < n_out; o++) {                                                                    \
+        S r = (rf == RF_MAX || rf == RF_ARGMAX) ? (S_LOWEST) : (rf == RF_MIN || rf == RF_ARGMIN) ? (S_HIGHEST) : (S)0; \
+        unsigned idx = 0;                                                                                 \
+        for (long j = 0; j < n_red; j++) {                                                                \
+            const S x = over_strided ? src[j * n_contig + o] : src[o * n_contig + j];                     \
+            switch (rf) {                                                                                 \
+            case RF_ADD: case RF_MEAN: { const D t = (D)r; r = (S)(D)(t + (D)x); } break;                 \
+            case RF_ADD_SQUARED: { const D t = (D)r; r = (S)(D)(t + (D)(x * x)); } break;                 \
+            case RF_MAX: r = r > x ? r : x; break;                                                        \
+            case RF_MIN: r = r < x ? r : x; break;                                                        \
+            case RF_ARGMAX: if (x > r) { r = x; idx = (unsigned)j; } break;                               \
+            case RF_ARGMIN: if (x < r) { r = x; idx = (unsigned)j; } break;                               \
+            }                                                                                             \
+        }                                                                                                 \
+        if (rf == RF_ARGMAX || rf == RF_ARGMIN) { dst[o] = (D)idx; continue; }                            \
+        if (factOld != 0) dst[o] = factOld * dst[o] + factNew * r;                                        \
+        else dst[o] = factNew * r;                                                                        \
+        if (rf == RF_MEAN) dst[o] = dst[o] / (D)n_red;                                                    \
+    }                                                                                                     \
+}
+
+DEFINE_REDUCE_TYPED(red_i32_f32, int, float, INT_MIN, INT_MAX)
+DEFINE_REDUCE_TYPED(red_u32_f32, unsigned, float, 0u, UINT_MAX)
+DEFINE_REDUCE_TYPED(red_u8_f32, unsigned char, float, 0, 255)
+DEFINE_REDUCE_TYPED(red_f32_i32, float, int, -FLT_MAX, FLT_MAX)
+DEFINE_REDUCE_TYPED(red_f32_u32, float, unsigned, -FLT_MAX, FLT_MAX)
+DEFINE_REDUCE_TYPED(red_f32_u8, float, unsigned char, -FLT_MAX, FLT_MAX)
+DEFINE_REDUCE_TYPED(red_u8_u8, unsigned char, unsigned char, 0, 255)
+DEFINE_REDUCE_TYPED(red_u8_u32, unsigned char, unsigned, 0, 255)
+
+/* Type codes: 0 float, 1 int, 2 unsigned int, 3 unsigned char.  Returns -1 for a pair CUV does not instantiate,
+ * a functor outside ADD/MEAN/ADD_SQUARED/MAX/MIN/ARGMAX/ARGMIN, or MEAN with factors other than (1, 0). */
+ORACLE_API int oracle_reduce_typed(void *dst, int dst_type, const void *src, int src_type, long n_contig,
+                                   long n_strided, int over_strided, int rf, float factNew, float factOld)
+{
+    if (!(rf == RF_ADD || rf == RF_MEAN || rf == RF_ADD_SQUARED || rf == RF_MAX || rf == RF_MIN || rf == RF_ARGMAX ||
+          rf == RF_ARGMIN)) return -1;
+    if (rf == RF_MEAN && !(factNew == 1.f && factOld == 0.f)) return -1;
+#define PAIR(ST, DT, FN, S, D) if (src_type == ST && dst_type == DT) { \
+        FN((D *)dst, (const S *)src, n_contig, n_strided, over_strided, rf, factNew, factOld); return 0; }
+    PAIR(1, 0, red_i32_f32, int, float)
+    PAIR(2, 0, red_u32_f32, unsigned, float)
+    PAIR(3, 0, red_u8_f32, unsigned char, float)
+    PAIR(0, 1, red_f32_i32, float, int)
+    PAIR(0, 2, red_f32_u32, float, unsigned)
+    PAIR(0, 3, red_f32_u8, float, unsigned char)
+    PAIR(3, 3, red_u8_u8, unsigned char, unsigned char)
+    PAIR(3, 2, red_u8_u32, unsigned char, unsigned)
+#undef PAIR
+    return -1;
 }
 
 /* ------------------------------------------------------------------------ */

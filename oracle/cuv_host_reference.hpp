@@ -12,6 +12,9 @@ int oracle_dd2dia(float* Cvals, const int* offsets, int nd, int h, int w, int st
                   const float* B, int ldb, int ncols, float factAB, float factC, int literal_host, int nthreads);
 int oracle_reduce(float* dst, const float* src, long n_contig, long n_strided, int over_strided, int rf, float factNew,
                   float factOld, int nthreads);
+int oracle_avg_diagonals(float* dst, const float* vals, const int* offsets, int nd, int h, int w, int stride, int rf);
+int oracle_reduce_typed(void* dst, int dst_type, const void* src, int src_type, long n_contig, long n_strided,
+                        int over_strided, int rf, float factNew, float factOld);
 void oracle_learn_step_weight_decay(float* W, const float* dW, long n, float learnrate, float decay);
 void oracle_learn_step_weight_decay_momentum(float* W, float* M, const float* dW, long n, float lr, float mw, float l2,
                                              int device_formula);
@@ -52,11 +55,23 @@ void densedense_to_dia(dia_matrix<V, host_memory_space, I>& C, const host_block_
                             A.ptr(), A.shape()[0], B.ptr(), B.shape()[0], A.shape()[1], factAB, factC, 0, 1) == 0);
 }
 
+template <>
+inline void avg_diagonals(tensor<float, host_memory_space>& dst, const dia_matrix<float, host_memory_space>& dia) {
+    cuvAssert(dia.num_dia() == (int)dst.size());
+    cuvAssert(oracle_avg_diagonals(dst.ptr(), dia.vec().ptr(), dia.get_offsets().ptr(), dia.num_dia(), dia.h(), dia.w(),
+                                   dia.stride(), dia.row_fact()) == 0);
+}
+
 namespace detail {
-inline void reduce_host(tensor<float, host_memory_space>& v, const float* m, long long n_contig, long long n_strided,
+inline void reduce_host(void* v, int v_type, const void* m, int m_type, long long n_contig, long long n_strided,
                         bool over_strided, reduce_functor rf, float factNew, float factOld) {
-    cuvAssert((long long)v.size() == (over_strided ? n_contig : n_strided));
-    cuvAssert(oracle_reduce(v.ptr(), m, n_contig, n_strided, over_strided ? 1 : 0, (int)rf, factNew, factOld, 1) == 0);
+    if (v_type == CUVDIA_T_F32 && m_type == CUVDIA_T_F32) {
+        cuvAssert(oracle_reduce((float*)v, (const float*)m, n_contig, n_strided, over_strided ? 1 : 0, (int)rf, factNew,
+                                factOld, 1) == 0);
+    } else {
+        cuvAssert(oracle_reduce_typed(v, v_type, m, m_type, n_contig, n_strided, over_strided ? 1 : 0, (int)rf, factNew,
+                                      factOld) == 0);
+    }
 }
 inline void learn_step_host(float* W, const float* dW, unsigned long long n, float learnrate, float decay) {
     oracle_learn_step_weight_decay(W, dW, (long)n, learnrate, decay);

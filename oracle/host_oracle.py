@@ -51,6 +51,9 @@ def lib():
         L.oracle_reduce.argtypes = [_f32p, _f32p, ctypes.c_long, ctypes.c_long, ctypes.c_int, ctypes.c_int,
                                     ctypes.c_float, ctypes.c_float, ctypes.c_int]
         L.oracle_bias_sigmoid_sample.restype = None
+        L.oracle_avg_diagonals.argtypes = [_f32p, _f32p, _i32p] + [ctypes.c_int] * 5
+        L.oracle_reduce_typed.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_long,
+                                          ctypes.c_long, ctypes.c_int, ctypes.c_int, ctypes.c_float, ctypes.c_float]
         L.oracle_bias_sigmoid_sample.argtypes = [_f32p, _f32p, _f32p, _f32p, ctypes.c_long, ctypes.c_long,
                                                  ctypes.c_int]
         L.oracle_learn_step_weight_decay.restype = None
@@ -162,6 +165,36 @@ def reduce_to_col(dst, src, rf=RF_ADD, factNew=1.0, factOld=0.0, nthreads=1):
 def reduce_to_row(dst, src, rf=RF_ADD, factNew=1.0, factOld=0.0, nthreads=1):
     """Column-major src: dst[j] = reduce over i of src[i, j] (matrix_ops_reduce.cu:364-379)."""
     return reduce(dst, src, False, rf, factNew, factOld, nthreads)
+
+
+def avg_diagonals(dst, A):
+    """dst[k] = mean of stored diagonal k over the cells inside the matrix (matrix_ops/diagonals.cu:23-48)."""
+    assert dst.dtype == np.float32 and dst.size == A.offsets.size
+    if lib().oracle_avg_diagonals(_fp(dst), _fp(A.vals), A.offsets.ctypes.data_as(_i32p), A.offsets.size, A.h, A.w,
+                                  A.stride, A.rf):
+        raise RuntimeError("oracle_avg_diagonals: row_fact must be 1")
+    return dst
+
+
+TYPE_CODES = {np.dtype(np.float32): 0, np.dtype(np.int32): 1, np.dtype(np.uint32): 2, np.dtype(np.uint8): 3}
+
+
+def reduce_typed(dst, src, over_strided, rf=RF_ADD, factNew=1.0, factOld=0.0):
+    """The reduction between the element types CUV instantiates besides float -> float
+    (matrix_ops/matrix_ops_reduce.cu:395-413), with the host loop's semantics: running value in the SOURCE type,
+    fold in the DESTINATION type, factors converted to the source type.  ``src`` column-major 2-D, ``dst`` 1-D."""
+    _colmajor_any(src)
+    n_contig, n_strided = src.shape
+    assert dst.size == (n_contig if over_strided else n_strided) and dst.flags.c_contiguous
+    rc = lib().oracle_reduce_typed(dst.ctypes.data, TYPE_CODES[dst.dtype], src.ctypes.data, TYPE_CODES[src.dtype],
+                                   n_contig, n_strided, 1 if over_strided else 0, rf, factNew, factOld)
+    if rc:
+        raise RuntimeError("oracle_reduce_typed: pair of types or functor not instantiated by CUV")
+    return dst
+
+
+def _colmajor_any(a):
+    assert a.ndim == 2 and a.flags.f_contiguous, "column-major 2-D array expected"
 
 
 def bias_sigmoid_sample(act, bias=None, u=None, nthreads=1):

@@ -183,6 +183,12 @@ static void test_dia_mat() {
         for (int i = 0; i < n; i++) for (int j = 0; j < m; j++) bad += (float)w(i, j) != (float)w3(i, j) || (float)w(i, j) != (float)w2(i, j);
         CHECK(bad == 0);
         for (int s = 0; s < 3; s++) CHECK(w3.get_offset(s) == off[s] && w2.get_offset(s) == off[s]);
+        // avg_diagonals (:134-142; the call is commented out in CUV's test): device == host definition
+        tensor<float, host_memory_space> avg_h(w.num_dia());
+        tensor<float, dev_memory_space> avg_d(w.num_dia());
+        avg_diagonals(avg_h, w);
+        avg_diagonals(avg_d, w2);
+        for (int s = 0; s < 3; s++) CHECK(std::fabs((float)avg_h[s] - (float)avg_d[s]) <= 1e-5f * std::fabs((float)avg_h[s]) + 1e-7f);
     }
 }
 
@@ -221,6 +227,42 @@ template <class L> static void reduce_sweep(const char* layout) {
         for (int i = 0; i < n; i++) bad += !(std::fabs((float)vh[i] - (float)vd[i]) <= 1e-4f * std::fabs((float)vh[i]));
         CHECK(bad == 0);
     }
+}
+
+// reduce_to_col / reduce_to_row between the other element types CUV instantiates (matrix_ops_reduce.cu:395-413;
+// CUV's own test of a typed pair: src/tests/matrix_op.cpp:574-628 compares device with host): device == host, exactly.
+template <class V, class V2> static void reduce_typed_pair(const char* what, int modulus) {
+    const int n = 200, m = 60;
+    tensor<V, host_memory_space, column_major> h(n, m);
+    unsigned s = 777;
+    for (int i = 0; i < n * m; i++) { s = s * 1664525u + 1013904223u; h[i] = (V)(((s >> 10) % modulus)); }
+    tensor<V, dev_memory_space, column_major> d(n, m);
+    convert(d, h);
+    const reduce_functor rfs[] = {RF_ADD, RF_MAX, RF_MIN, RF_ARGMAX, RF_ARGMIN};
+    for (reduce_functor rf : rfs)
+        for (int to_col = 0; to_col < 2; to_col++) {
+            const int len = to_col ? n : m;
+            tensor<V2, host_memory_space> vh(len);
+            tensor<V2, dev_memory_space> vd(len);
+            if (to_col) { reduce_to_col(vh, h, rf); reduce_to_col(vd, d, rf); }
+            else { reduce_to_row(vh, h, rf); reduce_to_row(vd, d, rf); }
+            tensor<V2, host_memory_space> back(len);
+            back = vd;
+            int bad = 0;
+            for (int i = 0; i < len; i++) bad += !((V2)vh[i] == (V2)back[i]);
+            if (bad) std::printf("typed reduce %s rf=%d to_col=%d: %d mismatches\n", what, (int)rf, to_col, bad);
+            CHECK(bad == 0);
+        }
+}
+static void test_reduce_typed() {
+    reduce_typed_pair<int, float>("int -> float", 1000);
+    reduce_typed_pair<unsigned int, float>("unsigned -> float", 1000);
+    reduce_typed_pair<unsigned char, float>("uchar -> float", 2);          // line totals stay inside 8 bits
+    reduce_typed_pair<float, int>("float -> int", 100);
+    reduce_typed_pair<float, unsigned int>("float -> unsigned", 100);
+    reduce_typed_pair<float, unsigned char>("float -> uchar", 2);
+    reduce_typed_pair<unsigned char, unsigned char>("uchar -> uchar", 2);
+    reduce_typed_pair<unsigned char, unsigned int>("uchar -> unsigned", 2);
 }
 
 static void test_tensor_ops() {
@@ -363,6 +405,7 @@ int main() {
         reduce_sweep<column_major>("column_major");
         reduce_sweep<row_major>("row_major");
         test_tensor_ops();
+        test_reduce_typed();
         test_reduce_3d();
         test_learn_step();
         test_given_up_wait_throws();

@@ -607,6 +607,92 @@ def test_dd2dia_streaming_narrow_band(cb, lo, nd):
     dd_case(cb, rng, 36008, 40004, offs, 1, 21, 0.01, 0.9, dist="uniform")
 
 
+def test_avg_diagonals(cb):
+    """Mean of every stored diagonal over its cells inside the matrix (host definition, matrix_ops/diagonals.cu:23-48):
+    padding cells (NaN here) never enter; unsorted offsets; tall, wide and large matrices."""
+    import torch
+    rng = np.random.default_rng(11)
+    for h, w, offs in [(32, 16, [0, 1, -1]), (57, 150, [5, -40, 149, 0, -56]), (4096, 4096, list(range(-70, 58)))]:
+        A = make_dia(rng, h, w, np.array(offs, dtype=np.int32), 1)
+        want = np.zeros(len(offs), dtype=np.float32)
+        ho.avg_diagonals(want, A)
+        got = torch.full((len(offs),), 7.0, device="cuda")
+        cb.avg_diagonals(got, to_dev_dia(A))
+        np.testing.assert_allclose(got.cpu().numpy(), want, rtol=1e-4, atol=1e-6)
+    # the dia_mat.cpp fixture (src/tests/dia_mat.cpp:134-142 with the call restored): diagonal k of a matrix filled with k
+    A = ho.DiaHost(32, 16, np.array([0, 1, -1], dtype=np.int32), 32, 1)
+    A.vals[:] = np.repeat(np.array([3.0, 5.0, -2.0], dtype=np.float32), 32)
+    got = torch.empty(3, device="cuda")
+    cb.avg_diagonals(got, to_dev_dia(A))
+    assert got.cpu().numpy().tolist() == [3.0, 5.0, -2.0]
+    with pytest.raises(cb.CuvDiaError):
+        cb.avg_diagonals(got, to_dev_dia(make_dia(rng, 32, 16, np.array([0, 1, -1], dtype=np.int32), 2)))
+
+
+TYPED_PAIRS = [("int32", "float32"), ("uint32", "float32"), ("uint8", "float32"), ("float32", "int32"),
+               ("float32", "uint32"), ("float32", "uint8"), ("uint8", "uint8"), ("uint8", "uint32")]
+
+
+def typed_source(rng, dtype, shape, small):
+    """Values for which C++ defines every conversion of CUV's host loop and every sum stays exact in float (below
+    2^24): non-negative, and small where they are squared or summed through an 8-bit value."""
+    if dtype == "uint8":
+        return np.asfortranarray(rng.integers(0, 3 if small else 256, shape).astype(np.uint8))
+    if dtype == "int32":
+        return np.asfortranarray(rng.integers(-50, 50, shape).astype(np.int32) if small else
+                                 rng.integers(-1000, 1000, shape).astype(np.int32))
+    if dtype == "uint32":
+        return np.asfortranarray(rng.integers(0, 60 if small else 3000, shape).astype(np.uint32))
+    return np.asfortranarray((rng.uniform(0, 2.99 if small else 200.0, shape)).astype(np.float32))
+
+
+@pytest.mark.parametrize("src_t,dst_t", TYPED_PAIRS)
+@pytest.mark.parametrize("shape", [(270, 33), (37, 4100), (1030, 1030)])
+def test_reduce_between_element_types(cb, src_t, dst_t, shape):
+    """The eight other (source, destination) pairs CUV instantiates (matrix_ops/matrix_ops_reduce.cu:395-413), both
+    axes, bit for bit against the restated host loop: running value in the source type, fold in the destination type,
+    factors converted to the source type, indices for the arg forms."""
+    import torch
+    import zlib
+    rng = np.random.default_rng(zlib.crc32(("%s %s %s" % (src_t, dst_t, shape)).encode()))
+    tdt = {"float32": torch.float32, "int32": torch.int32, "uint32": torch.uint32, "uint8": torch.uint8}
+    cases = [(ho.RF_ADD, 1.0, 0.0, True), (ho.RF_ADD, 2.0, 3.0, True), (ho.RF_MEAN, 1.0, 0.0, True),
+             (ho.RF_ADD_SQUARED, 1.0, 0.0, True), (ho.RF_MAX, 1.0, 0.0, False), (ho.RF_MIN, 1.0, 1.0, False),
+             (ho.RF_ARGMAX, 1.0, 0.0, False), (ho.RF_ARGMIN, 1.0, 0.0, False)]
+    for rf, fn, fo, summed in cases:
+        # sums that travel through an 8-bit value must stay below 256 for the host loop to be defined
+        eight_bit = summed and ("uint8" in (src_t, dst_t))
+        for over_strided in (True, False):
+            n_red = shape[1] if over_strided else shape[0]
+            small = eight_bit or rf == ho.RF_ADD_SQUARED
+            src = typed_source(rng, src_t, shape, small)
+            if eight_bit:
+                # keep each line's total (and factNew * total + factOld * old) inside 8 bits: about 20 non-zero
+                # elements of at most 2 per line
+                keep = rng.random(shape) < min(1.0, 20.0 / n_red)
+                src = np.asfortranarray(np.where(keep, src, 0).astype(src.dtype))
+            n_out = shape[0] if over_strided else shape[1]
+            old = rng.integers(0, 3, n_out).astype(dst_t)
+            want = old.copy()
+            ho.reduce_typed(want, src, over_strided, rf, fn, fo)
+            dsrc = torch.from_numpy(np.ascontiguousarray(src.T)).cuda().t()
+            ddst = torch.from_numpy(old.copy()).cuda()
+            assert ddst.dtype == tdt[dst_t]
+            (cb.reduce_to_col if over_strided else cb.reduce_to_row)(ddst, dsrc, rf, fn, fo)
+            got = ddst.cpu().numpy()
+            assert np.array_equal(got, want), "%s -> %s rf=%d over_strided=%s: %d of %d differ" % (
+                src_t, dst_t, rf, over_strided, int((got != want).sum()), got.size)
+
+
+def test_reduce_element_type_errors(cb):
+    import torch
+    src = torch.zeros((8, 8), dtype=torch.int32, device="cuda").t()
+    with pytest.raises(cb.CuvDiaError, match="no instantiation"):
+        cb.reduce_to_col(torch.zeros(8, dtype=torch.int32, device="cuda"), src)
+    with pytest.raises(cb.CuvDiaError, match="float -> float only"):
+        cb.reduce_to_col(torch.zeros(8, dtype=torch.float32, device="cuda"), src, cb.RF_LOGADDEXP)
+
+
 def test_bounded_wait_gives_up_with_a_status(cb):
     """A wait that nothing will ever satisfy runs out after its poll limit, leaves a code in the plan's health word
     and returns; the device stays usable (the next product is bit-exact) and the word can be cleared."""

@@ -187,3 +187,46 @@ def test_learn_step_weight_decay_oracle():
     ho.learn_step_weight_decay_momentum(w1, m1, g, 0.1, 0.9, 0.05, device_formula=True)
     ho.learn_step_weight_decay_momentum(w2, m2, g, 0.1, 0.9, 0.05, device_formula=False)
     assert np.array_equal(m1, -lr * (g + decay * w)) and np.array_equal(m2, -lr * (g - decay * w))
+
+
+def test_typed_reductions_follow_the_host_loop():
+    """Known answers for the reductions between other element types, worked out by hand from CUV's host loop
+    (matrix_ops/matrix_ops_reduce.cu:217-292): the running value has the SOURCE type, the fold computes in the
+    DESTINATION type, factors are converted to the source type."""
+    import numpy as np
+    from oracle import host_oracle as ho
+    m8 = np.asfortranarray(np.array([[0, 30, 60, 90], [120, 150, 180, 210], [240, 14, 44, 74]], dtype=np.uint8))
+    d = np.zeros(3, dtype=np.float32)
+    assert ho.reduce_typed(d, m8, True).tolist() == [180.0, 660 % 256, 372 % 256]      # 8-bit running value wraps
+    d = np.zeros(3, dtype=np.uint32)
+    assert ho.reduce_typed(d, m8, True, ho.RF_MAX).tolist() == [90, 210, 240]
+    d = np.zeros(4, dtype=np.uint8)
+    assert ho.reduce_typed(d, m8, False, ho.RF_ARGMAX).tolist() == [2, 1, 1, 1]
+    d = np.full(4, 7, dtype=np.uint8)
+    assert ho.reduce_typed(d, m8, False, ho.RF_ARGMIN).tolist() == [0, 2, 2, 2]
+    mf = np.asfortranarray(np.array([[1.7, 2.2, -3.9], [0.5, 100.9, 7.0]], dtype=np.float32))
+    d = np.array([10, 20], dtype=np.int32)
+    # float -> int: every element is truncated before it is added; factors stay float: 0.5*old + 2*sum, then truncated
+    assert ho.reduce_typed(d, mf, True, ho.RF_ADD, 2.0, 0.5).tolist() == [int(0.5 * 10 + 2 * 0), int(0.5 * 20 + 2 * 107)]
+    mi = np.asfortranarray(np.array([[3, -4], [5, 6]], dtype=np.int32))
+    d = np.array([1.5, 2.5], dtype=np.float32)
+    # int -> float: factors are converted to int first (2.9 -> 2, 0.9 -> 0: the old value is dropped)
+    assert ho.reduce_typed(d, mi, True, ho.RF_ADD, 2.9, 0.9).tolist() == [-2.0, 22.0]
+    assert ho.reduce_typed(np.zeros(2, dtype=np.float32), mi, True, ho.RF_ADD_SQUARED).tolist() == [25.0, 61.0]
+    assert ho.reduce_typed(np.zeros(2, dtype=np.float32), mi, False, ho.RF_MEAN).tolist() == [4.0, 1.0]
+    with pytest.raises(RuntimeError):
+        ho.reduce_typed(np.zeros(2, dtype=np.int32), mi, True)          # int -> int is not instantiated by CUV
+
+
+def test_avg_diagonals_fixture():
+    """src/tests/dia_mat.cpp:134-142 (the call is commented out there): each diagonal's mean over its cells inside
+    the matrix; a 4 x 3 matrix whose diagonals hold 1..n along their valid range."""
+    import numpy as np
+    from oracle import host_oracle as ho
+    A = ho.DiaHost(4, 3, np.array([0, 1, -2], dtype=np.int32), 4, 1)
+    A.vals[:] = np.nan
+    A.vals[0:3] = [1, 2, 3]            # diagonal 0: cells (0,0) (1,1) (2,2)
+    A.vals[4:6] = [4, 6]               # diagonal +1: cells (0,1) (1,2)
+    A.vals[10:12] = [10, 20]           # diagonal -2: cells (2,0) (3,1), stored at rows 2, 3
+    out = np.zeros(3, dtype=np.float32)
+    assert ho.avg_diagonals(out, A).tolist() == [2.0, 5.0, 15.0]
