@@ -45,8 +45,15 @@ constexpr int STAGES = 3;
 constexpr int NRAW = KC + TM - 1;      // diagonals a chunk touches
 constexpr int BOXC = 256;              // columns per TMA box of B
 constexpr int THREADS = 32 * (NCW + 4);   // warps are allocated four at a time: the producer warp brings three idle ones
-constexpr int REGS_CONSUMER = 112;        // register budgets after the warp groups re-balance the register file
-constexpr int REGS_PRODUCER = 64;
+// Register budgets after the warp groups re-balance the block's register pool.  The pool is what the block was
+// launched with (THREADS x the kernel's register count, REGS_LAUNCH); what the consumers take must have been given
+// back by the producer's warp group, or the request would wait for ever.  The host side checks the kernel's actual
+// register count against REGS_LAUNCH before it ever launches.
+constexpr int REGS_LAUNCH = 96;
+constexpr int REGS_CONSUMER = 112;
+constexpr int REGS_PRODUCER = 32;
+static_assert(NCW * 32 * REGS_CONSUMER + 4 * 32 * REGS_PRODUCER <= THREADS * REGS_LAUNCH,
+              "the re-balanced register budgets must fit into the pool the block is launched with");
 constexpr int BS_FLOATS = KC * TN;     // one stage of B: [column][16 rows], 64 KB
 constexpr int AS_FLOATS = KC * TM;     // one stage of coefficients: [step][32 rows]
 constexpr int RAW_FLOATS = NRAW * TM;  // band slice as TMA delivers it ('n': 47 x 32; 't': 47 x 16 uses half)
@@ -146,8 +153,8 @@ prod_bandw_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
     }
     __syncthreads();
 
-    // The kernel is compiled for 96 registers per thread (640 threads); the producer's warp group hands most of its
-    // share back and the four consumer warp groups take 112 each (16*32*112 + 4*32*64 registers = the whole file).
+    // The kernel is compiled for 96 registers per thread (640 threads: a pool of 61440); the producer's warp group
+    // hands back all but 32 per thread and the four consumer warp groups take 112 each (16*32*112 + 4*32*32 = 61440).
     if (warp >= NCW) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_PRODUCER));
         if (warp > NCW) return;
@@ -302,13 +309,30 @@ prod_bandw_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
 
 static inline bool w_al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// The register re-balancing inside the kernel is only safe if every instantiation was compiled with exactly the
+// register count its budgets were derived from (a smaller pool would leave the consumers waiting for registers).
+static bool bandw_register_pool_ok() {
+    static int cached = -1;
+    if (cached < 0) {
+        cudaFuncAttributes a;
+        bool ok = true;
+        ok = ok && cudaFuncGetAttributes(&a, prod_bandw_kernel<false, false>) == cudaSuccess && a.numRegs == pw::REGS_LAUNCH;
+        ok = ok && cudaFuncGetAttributes(&a, prod_bandw_kernel<false, true>) == cudaSuccess && a.numRegs == pw::REGS_LAUNCH;
+        ok = ok && cudaFuncGetAttributes(&a, prod_bandw_kernel<true, false>) == cudaSuccess && a.numRegs == pw::REGS_LAUNCH;
+        ok = ok && cudaFuncGetAttributes(&a, prod_bandw_kernel<true, true>) == cudaSuccess && a.numRegs == pw::REGS_LAUNCH;
+        cached = ok ? 1 : 0;
+    }
+    return cached == 1;
+}
+
 bool prod_bandw_applicable(const cuvdia_plan* p, const float* A, const float* B, int ldb, int ncols) {
     // 1024-column tiles: worth it when the batch fills them well and the band is wide enough to pay for the 31
     // extra steps per tile
     if (p->nd < 96) return false;
     const int tiles = (ncols + pw::TN - 1) / pw::TN;
     if ((long long)ncols * 4 < (long long)tiles * pw::TN * 3) return false;
-    return p->is_band && p->rf == 1 && w_al16(A) && w_al16(B) && p->stride % 4 == 0 && ldb % 4 == 0 && tma_available();
+    return p->is_band && p->rf == 1 && w_al16(A) && w_al16(B) && p->stride % 4 == 0 && ldb % 4 == 0 && tma_available() &&
+           bandw_register_pool_ok();
 }
 
 template <bool TRANS, bool EXACT>
