@@ -28,13 +28,8 @@ __global__ void dd2dia_combine_kernel(float* __restrict__ Cv, const int* __restr
                                       const float* __restrict__ partial);
 
 namespace db {
-#ifndef DB_KB
-#define DB_KB 32
-#endif
-#ifndef DB_STAGES
-#define DB_STAGES 3
-#endif
-constexpr int TI = 128, TJ = 128, KB = DB_KB, STAGES = DB_STAGES, THREADS = 256;
+// 32 batch columns per stage and 3 stages were the best of the (16, 32, 64) x (2, 3, 4) combinations that fit
+constexpr int TI = 128, TJ = 128, KB = 32, STAGES = 3, THREADS = 256;
 constexpr int TILE_FLOATS = TI * KB;                 // one operand tile of one stage
 constexpr size_t SMEM = sizeof(float) * 2 * TILE_FLOATS * STAGES + 128;
 constexpr unsigned SPIN_LIMIT = 1u << 26;

@@ -12,12 +12,11 @@ int launch_prod(const cuvdia_plan* p, const float* A, const float* B, int ldb, f
     const bool runs = prod_runs_applicable(p, A, B, ldb);
     if (prod_narrow_applicable(p, A, B, ldb, ncols) && (prod_narrow_streams(p, trans) || !runs))
         rc = launch_prod_narrow(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);
-#ifndef CUVDIA_X_NO_BANDW
-    else if (prod_bandw_applicable(p, A, B, ldb, ncols))
-        rc = launch_prod_bandw(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);
-#endif
     else if (prod_band_applicable(p, A, B, ldb, ncols))
         rc = launch_prod_band(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);
+    // steep bands (row factor 2, 4, 8) times many columns: the streaming banded kernel
+    else if (prod_bandw_applicable(p, A, B, ldb, ncols))
+        rc = launch_prod_bandw(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);
     else if (runs)
         rc = launch_prod_runs(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);
     else if (prod_window_applicable(p, trans, ncols))

@@ -1,12 +1,14 @@
-// prod with a banded DIA operand (consecutive ascending diagonals, row_fact 1) and many batch columns:
-// the band walked as a streaming product.
+// prod with a banded DIA operand (consecutive ascending diagonals) whose row factor is larger than 1 (a "steep"
+// band: diagonal k holds the cells (i, i/rf + lo + k); the local receptive fields of a layer that shrinks by rf),
+// times many batch columns: the band walked as a streaming product.
 //
-// With offsets lo, lo+1, ..., lo+nd-1
-//     'n':  C[i,b] = sum_k A[k][i]       * B[i+lo+k, b]
-//     't':  C[j,b] = sum_k A[k][j-lo-k]  * B[j-lo-k, b].
-// A block owns 32 output rows and 1024 batch columns.  All of its rows walk the SAME dense rows of B,
+// With offsets lo, lo+1, ..., lo+nd-1 and rf = row_fact (matrix_ops/spmv.cu:161-198)
+//     'n':  C[i,b] = sum_k A[k][i] * B[i/rf + lo + k, b]
+//     't':  C[j,b] = sum_k sum_{l<rf} A[k][rf*(j-lo-k) + l] * B[rf*(j-lo-k) + l, b]
+// (for rf = 1 the register-tiled kernel of prod_band.cu was measured faster - 52.6 against 50.0 TFLOP/s at 1024
+// diagonals - and is used instead).  A block owns 32 output rows and 1024 batch columns.  All of its rows walk the SAME dense rows of B,
 // X0, X0+1, ... in steps q = 0, 1, ...: output row r of the tile meets B row X0+q on diagonal
-// k = q - r - rem ('n') or k = nd-1+rem+r-q ('t'), so one step is the rank-1 update
+// k = q - r/rf - rem ('n') or k = q/rf - (31 - r) - rem ('t'), so one step is the rank-1 update
 //     C[r, b] += As[q][r] * B[X0+q, b]
 // with the 32 coefficients As[q][.] of the step laid side by side - a product of a [32 x (nd+31)] coefficient
 // panel with [(nd+31) x 1024] rows of B, of which each output only uses the nd steps its diagonals cover
@@ -106,7 +108,8 @@ __device__ __forceinline__ void w_mac2(float2& acc, float2 a, float2 b) {
 }
 
 struct BandWParams {
-    int h, w, nd, lo;
+    int h, w, nd, lo, rf;
+    int gpc;                  // groups of rf B rows per chunk: KC / rf ('t')
     int rows_out, rows_b;     // h, w ('n') or w, h ('t')
     int ncols, ldc;
     int rem;                  // alignment shift (0..3) that keeps every TMA row coordinate a multiple of 4
@@ -119,11 +122,14 @@ struct BandWParams {
 };
 
 // Step q of the tile whose first output row is t0 meets B row
-//   'n': x = t0 + lo - rem + q            on diagonal k = q - r - rem            for output row t0 + r
-//   't': x = t0 - lo + rem + 31 - q       on diagonal k = q - (31 - r) - rem     for output row t0 + r
-// (rem makes x = 0 mod 4 at q = 0 mod 4 for 'n' and x = 3 mod 4 for 't', so 16-row boxes start on 16-byte
-// boundaries); in both cases the diagonals an output meets ascend with q.
-template <bool TRANS, bool EXACT>
+//   'n': x = t0/rf + lo - rem + q                       on diagonal k = q - r/rf - rem         for output row t0 + r
+//   't': x = rf*(t0 + 31 - lo + rem - q/rf) + q%rf      on diagonal k = q/rf - (31 - r) - rem  for output row t0 + r
+// (rem keeps the first row of every 16-row box a multiple of 4, i.e. on a 16-byte boundary).  In both cases the
+// diagonals an output meets ascend with q, and for 't' the rf rows of one diagonal's group come in ascending order:
+// the order of CUV's host loops.  RFT is the row factor the transposed consumer is compiled for (2, 4 or 8; it
+// fixes which element of a 128-bit B vector belongs to which step); 'n' is compiled once (RFT = 1) and takes any
+// row factor that divides 8.
+template <bool TRANS, bool EXACT, int RFT>
 __global__ void __launch_bounds__(pw::THREADS, 1)
 prod_bandw_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                   const BandWParams P) {
@@ -160,8 +166,11 @@ prod_bandw_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
         if (warp > NCW) return;
         // =========================== producer warp ===========================
         // first B row (TMA x coordinate) and first diagonal (y coordinate) of chunk c
-        auto b_row0 = [&](int c) { return TRANS ? (t0 - P.lo + P.rem + 31 - c * KC - (KC - 1)) : (t0 + P.lo - P.rem + c * KC); };
-        auto k0 = [&](int c) { return c * KC - (TM - 1) - P.rem; };
+        const int rf = P.rf;
+        auto b_row0 = [&](int c) {
+            return TRANS ? rf * (t0 + (TM - 1) - P.lo + P.rem - (c + 1) * P.gpc + 1) : (t0 / rf + P.lo - P.rem + c * KC);
+        };
+        auto k0 = [&](int c) { return (TRANS ? c * P.gpc : c * KC) - (TM - 1) - P.rem; };
         constexpr unsigned RAW_TX = sizeof(float) * NRAW * (TRANS ? KC : TM);
         constexpr unsigned BS_TX = sizeof(float) * BS_FLOATS;
         auto issue_raw = [&](int c) {
@@ -183,26 +192,31 @@ prod_bandw_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
             }
             ok = w_warp_wait(&raw_full[c & 1], (c >> 1) & 1);
             if (!ok) { if (lane == 0 && P.status) *P.status = 3; return; }
-            // ---- skew: As[qq][r] = factAB * A[k][matrix row] with k = k0 + qq - r' + 31 (r' = r for 'n', 31 - r for
-            // 't'), zero where the cell lies outside the matrix.  Lane = output row r of the tile. ----
+            // ---- skew: As[qq][r] = factAB * A[k][matrix row] for the diagonal k that output row r meets at step qq, zero
+            // where the cell lies outside the matrix.  Lane = output row r of the tile.
+            //   'n': k = k0 + 31 + qq - r/rf,  slice [diagonal][32 tile rows]
+            //   't': k = k0 + qq/rf + r,       slice [diagonal][16 B rows]; step qq reads box row rf*(gpc-1-qq/rf) + qq%rf ----
             const float* raw = raw0 + (c & 1) * RAW_FLOATS;
             float* as = As0 + s * AS_FLOATS;
             const int kc0 = k0(c), xb = b_row0(c);
-            const int rr = TRANS ? (TM - 1 - lane) : lane;
-            // chunk-uniform: every cell the chunk touches lies inside the matrix
+            // chunk-uniform: every cell the chunk touches lies inside the matrix ('t': whole groups of rf rows)
             const bool interior = kc0 >= 0 && kc0 + NRAW <= P.nd && xb >= 0 && xb + KC <= P.rows_b &&
                                   (TRANS || t0 + TM <= P.h);
+            const int rdiv = lane / rf;
 #pragma unroll 4
             for (int qq = 0; qq < KC; qq++) {
-                const int kk = qq - rr + (TM - 1);                    // row of the slice: diagonal kc0 + kk
-                // 'n': slice is [diagonal][32 tile rows];  't': [diagonal][16 B rows], B row xb + (KC-1-qq) at step qq
-                float v = TRANS ? raw[kk * KC + (KC - 1 - qq)] : raw[kk * TM + lane];
+                const int gq = qq / rf;                               // 't': group of rf rows within the chunk
+                const int brow = TRANS ? rf * (P.gpc - 1 - gq) + (qq - gq * rf) : qq;     // row of the B box this step reads
+                const int kk = TRANS ? gq + lane : qq - rdiv + (TM - 1);                  // row of the slice: diagonal kc0 + kk
+                float v = TRANS ? raw[kk * KC + brow] : raw[kk * TM + lane];
                 if (!interior || P.fa != 1.f) {
                     const int k = kc0 + kk;
-                    const int x = TRANS ? xb + (KC - 1 - qq) : xb + qq;                 // B row of the step
-                    // 'n': matrix cell (t0 + r, x): the column x must exist;  't': cell (x, t0 + r): the row x must exist
-                    const bool in = (unsigned)k < (unsigned)P.nd && (unsigned)x < (unsigned)P.rows_b &&
-                                    (TRANS || t0 + lane < P.h);
+                    const int x = xb + brow;                                             // B row of the step
+                    bool in = (unsigned)k < (unsigned)P.nd;
+                    // 'n': cell (t0 + r, x): row and column must exist;  't': cell (x, t0 + r): the whole group of rf
+                    // rows must lie inside the matrix (matrix_ops/spmv.cu:168: N counts whole groups only)
+                    if (!TRANS) in = in && (unsigned)x < (unsigned)P.w && t0 + lane < P.h;
+                    else { const int m = x >= 0 ? x / rf : -1; in = in && m >= 0 && (long long)(m + 1) * rf <= P.h; }
                     if (P.fa != 1.f) v = __fmul_rn(P.fa, v);
                     v = in ? v : 0.f;
                 }
@@ -245,9 +259,15 @@ prod_bandw_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
         }
     }
 
+    // 16-byte chunk of a column's 16 rows that the steps of group g read: 'n' ascending; 't' the groups of RFT rows
+    // descend through the box (RFT 8: two chunks per group, ascending inside it)
+    auto bchunk = [](int g) { return !TRANS ? g : RFT == 8 ? ((g & 2) ^ 2) + (g & 1) : 3 - g; };
+    // a warp whose 64 columns all lie beyond the batch keeps the hand-over going and leaves the arithmetic out
+    const bool has_columns = n0 + 64 * warp < P.ncols;
     for (int c = 0; c < nch; c++) {
         const int s = c % STAGES;
         if (!w_warp_wait(&full[s], (c / STAGES) & 1)) { if (lane == 0 && P.status) *P.status = 3; return; }
+        if (!has_columns) { if (lane == 0) w_arrive(&empty[s]); continue; }
         const float* bsp = Bs0 + s * BS_FLOATS + colb * KC;
         const float* asp = As0 + s * AS_FLOATS + 16 * rg;
         const int ng = c == nch - 1 ? P.last_groups : KC / 4;
@@ -257,7 +277,7 @@ prod_bandw_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
                 float4 bw[4];
 #pragma unroll
                 for (int cc = 0; cc < 4; cc++)
-                    bw[cc] = *reinterpret_cast<const float4*>(bsp + cc * 16 * KC + (((TRANS ? 3 - g : g) ^ sw) << 2));
+                    bw[cc] = *reinterpret_cast<const float4*>(bsp + cc * 16 * KC + ((bchunk(g) ^ sw) << 2));
 #pragma unroll
                 for (int u = 0; u < 4; u++) {
                     const float* ap = asp + (4 * g + u) * TM;
@@ -270,10 +290,10 @@ prod_bandw_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
                                          make_float2(a3.x, a3.y), make_float2(a3.z, a3.w)};
 #pragma unroll
                     for (int cc = 0; cc < 4; cc++) {
-                        float b;
-                        // 'n': B rows ascend with the step;  't': the chunk's 16 rows were loaded ascending, walked descending
-                        if (!TRANS) b = u == 0 ? bw[cc].x : u == 1 ? bw[cc].y : u == 2 ? bw[cc].z : bw[cc].w;
-                        else        b = u == 0 ? bw[cc].w : u == 1 ? bw[cc].z : u == 2 ? bw[cc].y : bw[cc].x;
+                        // which element of the vector step u reads: 'n' ascending; 't' groups of RFT rows descending,
+                        // ascending inside a group (RFT 2: z w x y, RFT 4 and 8: x y z w)
+                        const int e = (TRANS && RFT == 2) ? (u ^ 2) : u;
+                        const float b = e == 0 ? bw[cc].x : e == 1 ? bw[cc].y : e == 2 ? bw[cc].z : bw[cc].w;
                         const float2 bb = make_float2(b, b);
 #pragma unroll
                         for (int jp = 0; jp < 8; jp++) w_mac2<EXACT>(acc[jp][cc], a[jp], bb);
@@ -311,31 +331,34 @@ static inline bool w_al16(const void* p) { return (reinterpret_cast<uintptr_t>(p
 
 // The register re-balancing inside the kernel is only safe if every instantiation was compiled with exactly the
 // register count its budgets were derived from (a smaller pool would leave the consumers waiting for registers).
+template <bool TRANS, bool EXACT, int RFT>
+static bool bandw_pool_ok_one() {
+    cudaFuncAttributes a;
+    return cudaFuncGetAttributes(&a, prod_bandw_kernel<TRANS, EXACT, RFT>) == cudaSuccess && a.numRegs == pw::REGS_LAUNCH;
+}
 static bool bandw_register_pool_ok() {
     static int cached = -1;
     if (cached < 0) {
-        cudaFuncAttributes a;
-        bool ok = true;
-        ok = ok && cudaFuncGetAttributes(&a, prod_bandw_kernel<false, false>) == cudaSuccess && a.numRegs == pw::REGS_LAUNCH;
-        ok = ok && cudaFuncGetAttributes(&a, prod_bandw_kernel<false, true>) == cudaSuccess && a.numRegs == pw::REGS_LAUNCH;
-        ok = ok && cudaFuncGetAttributes(&a, prod_bandw_kernel<true, false>) == cudaSuccess && a.numRegs == pw::REGS_LAUNCH;
-        ok = ok && cudaFuncGetAttributes(&a, prod_bandw_kernel<true, true>) == cudaSuccess && a.numRegs == pw::REGS_LAUNCH;
+        const bool ok = bandw_pool_ok_one<false, false, 1>() && bandw_pool_ok_one<false, true, 1>() &&
+                        bandw_pool_ok_one<true, false, 2>() && bandw_pool_ok_one<true, true, 2>() &&
+                        bandw_pool_ok_one<true, false, 4>() && bandw_pool_ok_one<true, true, 4>() &&
+                        bandw_pool_ok_one<true, false, 8>() && bandw_pool_ok_one<true, true, 8>();
         cached = ok ? 1 : 0;
     }
     return cached == 1;
 }
 
 bool prod_bandw_applicable(const cuvdia_plan* p, const float* A, const float* B, int ldb, int ncols) {
-    // 1024-column tiles: worth it when the batch fills them well and the band is wide enough to pay for the 31
-    // extra steps per tile
-    if (p->nd < 96) return false;
-    const int tiles = (ncols + pw::TN - 1) / pw::TN;
-    if ((long long)ncols * 4 < (long long)tiles * pw::TN * 3) return false;
-    return p->is_band && p->rf == 1 && w_al16(A) && w_al16(B) && p->stride % 4 == 0 && ldb % 4 == 0 && tma_available() &&
+    // Row factors 2, 4, 8 (a chunk of 16 B rows must hold whole groups of rf rows, and the first B row of a tile,
+    // t0/rf, must stay a multiple of 4); enough diagonals to pay for the up to 31 extra steps of a tile; and enough
+    // batch columns to keep at least four of the sixteen consumer warps busy.
+    if (!(p->rf == 2 || p->rf == 4 || p->rf == 8)) return false;
+    if (p->nd < 32 || ncols < 256) return false;
+    return p->is_band && w_al16(A) && w_al16(B) && p->stride % 4 == 0 && ldb % 4 == 0 && tma_available() &&
            bandw_register_pool_ok();
 }
 
-template <bool TRANS, bool EXACT>
+template <bool TRANS, bool EXACT, int RFT>
 static int launch_bandw_t(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
                           float fa, float fc, cudaStream_t st) {
     using namespace pw;
@@ -345,24 +368,26 @@ static int launch_bandw_t(const cuvdia_plan* p, const float* A, const float* B, 
     rc = make_map_2d_swizzled(&mapB, B, TRANS ? p->h : p->w, ncols, ldb, KC, BOXC, 64);
     if (rc) return rc;
     BandWParams P;
-    P.h = p->h; P.w = p->w; P.nd = p->nd; P.lo = p->band_lo;
+    P.h = p->h; P.w = p->w; P.nd = p->nd; P.lo = p->band_lo; P.rf = p->rf;
+    P.gpc = KC / p->rf;
     P.rows_out = TRANS ? p->w : p->h;
     P.rows_b = TRANS ? p->h : p->w;
     P.ncols = ncols; P.ldc = ldc;
-    // 'n': a chunk's first B row t0 + lo - rem + 16c, 't': t0 - lo + rem + 16 - 16c; both are 0 mod 4
-    P.rem = ((p->band_lo % 4) + 4) % 4;
-    const int steps = p->nd + (TM - 1) + P.rem;
+    // the first B row of a chunk must be a multiple of 4:  'n': t0/rf + lo - rem + 16c;  't': rf*(t0 + 32 - lo + rem) - 16(c+1)
+    const int g = TRANS ? (p->rf >= 4 ? 1 : 2) : 4;
+    P.rem = ((p->band_lo % g) + g) % g;
+    const int steps = TRANS ? p->rf * (p->nd + (TM - 1) + P.rem) : p->nd + (TM - 1) / p->rf + P.rem;
     P.nchunks = (steps + KC - 1) / KC;
     P.last_groups = (steps - (P.nchunks - 1) * KC + 3) / 4;
     P.fa = fa; P.fc = fc;
     P.vec_c = (w_al16(C) && ldc % 4 == 0) ? 1 : 0;
     P.C = C; P.status = p->d_status;
     static bool attr_done[64] = {false};          // one flag set per template instantiation
-    rc = allow_dynamic_smem(prod_bandw_kernel<TRANS, EXACT>, SMEM, attr_done);
+    rc = allow_dynamic_smem(prod_bandw_kernel<TRANS, EXACT, RFT>, SMEM, attr_done);
     if (rc) return rc;
     const int gx = (P.rows_out + TM - 1) / TM, gy = (ncols + TN - 1) / TN;
     if (gx > 65535) { set_last_error("too many rows for the banded kernel"); return CUVDIA_ERR_UNSUPPORTED; }
-    prod_bandw_kernel<TRANS, EXACT><<<dim3(gy, gx), THREADS, SMEM, st>>>(mapA, mapB, P);
+    prod_bandw_kernel<TRANS, EXACT, RFT><<<dim3(gy, gx), THREADS, SMEM, st>>>(mapA, mapB, P);
     count_launch();
     return check_launch("prod_bandw_kernel");
 }
@@ -370,10 +395,13 @@ static int launch_bandw_t(const cuvdia_plan* p, const float* A, const float* B, 
 int launch_prod_bandw(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
                       bool trans, float fa, float fc, int mode, cudaStream_t st) {
     const bool exact = mode == CUVDIA_MODE_EXACT;
-    if (trans) return exact ? launch_bandw_t<true, true>(p, A, B, ldb, C, ldc, ncols, fa, fc, st)
-                            : launch_bandw_t<true, false>(p, A, B, ldb, C, ldc, ncols, fa, fc, st);
-    return exact ? launch_bandw_t<false, true>(p, A, B, ldb, C, ldc, ncols, fa, fc, st)
-                 : launch_bandw_t<false, false>(p, A, B, ldb, C, ldc, ncols, fa, fc, st);
+#define GO(TR, RFT) return exact ? launch_bandw_t<TR, true, RFT>(p, A, B, ldb, C, ldc, ncols, fa, fc, st) \
+                                 : launch_bandw_t<TR, false, RFT>(p, A, B, ldb, C, ldc, ncols, fa, fc, st)
+    if (!trans) GO(false, 1);
+    if (p->rf == 2) GO(true, 2);
+    if (p->rf == 4) GO(true, 4);
+    GO(true, 8);
+#undef GO
 }
 
 }  // namespace cuvdia

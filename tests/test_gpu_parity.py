@@ -108,6 +108,22 @@ def test_prod_band_wide_batches(cb, trans, h, w, lo, nd, ncols, fab, fc):
     prod_case(cb, rng, h, w, offs, 1, ncols, trans, fab, fc)
 
 
+@pytest.mark.parametrize("trans", ["n", "t"])
+@pytest.mark.parametrize("h,w,rf,lo,nd,ncols,fab,fc", [
+    (1024, 256, 4, -64, 128, 512, 1.0, 0.5),     # config 1's pattern at a quarter of the size
+    (1024, 512, 2, -50, 100, 1024, 1.0, 0.0),    # row factor 2, one full column tile
+    (2048, 256, 8, -30, 64, 300, 0.75, 2.0),     # row factor 8, a partly filled tile, both factors
+    (1023, 256, 4, -7, 40, 256, 1.0, 0.0),       # height not a multiple of the row factor: the last group is cut
+    (520, 300, 2, 101, 150, 640, 2.0, 0.0),      # band above the main diagonal, odd first offset
+    (128, 64, 4, -63, 127, 256, 1.0, 0.0),       # every diagonal of a small matrix
+])
+def test_prod_steep_band_wide_batches(cb, trans, h, w, rf, lo, nd, ncols, fab, fc):
+    """Bands with a row factor above 1 times many batch columns (the streaming banded kernel)."""
+    rng = np.random.default_rng(h + 7 * nd + ncols + rf + (trans == "t"))
+    offs = np.arange(lo, lo + nd, dtype=np.int32)
+    prod_case(cb, rng, h, w, offs, rf, ncols, trans, fab, fc)
+
+
 def test_prod_config0_shape(cb):
     """BASELINE config 0: 4096x4096, 64 sorted scattered diagonals, batch 128, factors 1/0."""
     rng = np.random.Generator(np.random.PCG64(1000))
