@@ -5,8 +5,9 @@
 // With offsets lo, lo+1, ..., lo+nd-1 and rf = row_fact (matrix_ops/spmv.cu:161-198)
 //     'n':  C[i,b] = sum_k A[k][i] * B[i/rf + lo + k, b]
 //     't':  C[j,b] = sum_k sum_{l<rf} A[k][rf*(j-lo-k) + l] * B[rf*(j-lo-k) + l, b]
-// (for rf = 1 the register-tiled kernel of prod_band.cu was measured faster - 52.6 against 50.0 TFLOP/s at 1024
-// diagonals - and is used instead).  A block owns 32 output rows and 1024 batch columns.  All of its rows walk the SAME dense rows of B,
+// (for rf = 1 the register-tiled kernel of prod_band.cu was measured faster - 53.5 against 49.7 TFLOP/s at 1024
+// diagonals - and is used instead).  A block owns 32 output rows and 1024 batch columns (512 in the variant
+// with 8 rows per thread, which is taken when 512-column tiles waste fewer columns of the batch).  All of its rows walk the SAME dense rows of B,
 // X0, X0+1, ... in steps q = 0, 1, ...: output row r of the tile meets B row X0+q on diagonal
 // k = q - r/rf - rem ('n') or k = q/rf - (31 - r) - rem ('t'), so one step is the rank-1 update
 //     C[r, b] += As[q][r] * B[X0+q, b]
@@ -15,14 +16,14 @@
 // (the other 31 carry zero coefficients: the price of sharing B rows across the tile, 31/nd of the work).
 // B is therefore streamed through shared memory exactly once per tile, 16 rows at a time, by TMA tile
 // loads (cp.async.bulk.tensor, no multicast, 64-byte swizzle so that the 128-bit reads along a column are
-// free of bank conflicts) into a three-stage ring; there is no halo and no window to re-load.  One
-// producer warp issues the loads and re-lays ("skews") each slice of the band, as TMA delivers it, into the
-// coefficient panel As of the stage, applying factAB and zeroing cells outside the matrix (padding cells of
-// the diagonal storage may hold NaN and must never contribute).  Sixteen consumer warps (four per
-// scheduler) each own 32 rows x 64 columns, 16 rows x 4 columns per thread: per step four 128-bit loads of
-// coefficients (shared by half a warp), a quarter of four 128-bit loads of B, and 32 packed f32x2
-// multiply-adds.  About 100 registers per thread instead of the 160 of an 8 x 8 register tile is what lets
-// four warps per scheduler hide the shared-memory latency.  Every hand-over is an mbarrier with a bounded,
+// free of bank conflicts) into a ring of three or four stages; there is no halo and no window to re-load.
+// Four producer warps (one of them issues the loads) re-lay ("skew") each slice of the band, as TMA delivers
+// it, into the coefficient panel As of the stage, applying factAB and zeroing cells outside the matrix (padding
+// cells of the diagonal storage may hold NaN and must never contribute); with a single producer warp the
+// consumers waited for coefficients more than they computed (config 1: 259 us, with four 184 us).  Sixteen
+// consumer warps (four per scheduler) each own 32 rows x 64 columns, 16 rows x 4 columns per thread: per step
+// four 128-bit loads of coefficients (shared by half a warp), a quarter of four 128-bit loads of B, and 32
+// packed f32x2 multiply-adds.  Every hand-over is an mbarrier with a bounded,
 // warp-uniform wait; consumers never meet a block barrier.
 // The transposed product walks the B rows in DESCENDING order (X0 is the highest row the tile needs), so that
 // for both products the diagonals an output meets ascend with the step: per output the terms are added in
@@ -40,10 +41,9 @@ int make_map_2d_swizzled(CUtensorMap* m, const float* base, long long dim0, long
 
 namespace pw {
 constexpr int TM = 32;                 // output rows per block
-constexpr int NCW = 16;                // consumer warps, 64 columns each
-constexpr int TN = 64 * NCW;           // batch columns per block
+constexpr int NCW = 16;                // consumer warps
 constexpr int KC = 16;                 // steps (B rows) per chunk
-constexpr int STAGES = 3;
+constexpr int NPW = 4;                 // producer warps (one warp group): one issues the loads, all four re-lay the band slice
 constexpr int NRAW = KC + TM - 1;      // diagonals a chunk touches
 constexpr int BOXC = 256;              // columns per TMA box of B
 constexpr int THREADS = 32 * (NCW + 4);   // warps are allocated four at a time: the producer warp brings three idle ones
@@ -56,10 +56,19 @@ constexpr int REGS_CONSUMER = 112;
 constexpr int REGS_PRODUCER = 32;
 static_assert(NCW * 32 * REGS_CONSUMER + 4 * 32 * REGS_PRODUCER <= THREADS * REGS_LAUNCH,
               "the re-balanced register budgets must fit into the pool the block is launched with");
-constexpr int BS_FLOATS = KC * TN;     // one stage of B: [column][16 rows], 64 KB
 constexpr int AS_FLOATS = KC * TM;     // one stage of coefficients: [step][32 rows]
 constexpr int RAW_FLOATS = NRAW * TM;  // band slice as TMA delivers it ('n': 47 x 32; 't': 47 x 16 uses half)
-constexpr size_t SMEM = sizeof(float) * (STAGES * BS_FLOATS + STAGES * AS_FLOATS + 2 * RAW_FLOATS) + 256;
+// RPT = output rows per thread (4 columns each).  16: a warp owns 32 rows x 64 columns, the block 32 x 1024.
+// 8: a warp owns 16 rows x 64 columns, two warp rows, the block 32 x 512 - twice the warps for the same outputs,
+// for batches that do not fill 1024-column tiles.
+template <int RPT> struct Tile {
+    static constexpr int WARP_ROWS = TM / (2 * RPT);
+    static constexpr int WARP_COLS = NCW / WARP_ROWS;
+    static constexpr int TN = 64 * WARP_COLS;              // batch columns per block
+    static constexpr int BS_FLOATS = KC * TN;              // one stage of B: [column][16 rows]
+    static constexpr int STAGES = RPT == 16 ? 3 : 4;       // 3 x 64 KB or 4 x 32 KB of B in flight
+    static constexpr size_t SMEM = sizeof(float) * (STAGES * BS_FLOATS + STAGES * AS_FLOATS + 2 * RAW_FLOATS) + 256;
+};
 constexpr unsigned SPIN_LIMIT = 1u << 26;
 }  // namespace pw
 
@@ -110,6 +119,7 @@ __device__ __forceinline__ void w_mac2(float2& acc, float2 a, float2 b) {
 struct BandWParams {
     int h, w, nd, lo, rf;
     int gpc;                  // groups of rf B rows per chunk: KC / rf ('t')
+    int rf_shift;             // log2(rf)
     int rows_out, rows_b;     // h, w ('n') or w, h ('t')
     int ncols, ldc;
     int rem;                  // alignment shift (0..3) that keeps every TMA row coordinate a multiple of 4
@@ -129,11 +139,13 @@ struct BandWParams {
 // the order of CUV's host loops.  RFT is the row factor the transposed consumer is compiled for (2, 4 or 8; it
 // fixes which element of a 128-bit B vector belongs to which step); 'n' is compiled once (RFT = 1) and takes any
 // row factor that divides 8.
-template <bool TRANS, bool EXACT, int RFT>
+template <bool TRANS, bool EXACT, int RFT, int RPT>
 __global__ void __launch_bounds__(pw::THREADS, 1)
 prod_bandw_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                   const BandWParams P) {
     using namespace pw;
+    constexpr int TN = Tile<RPT>::TN, BS_FLOATS = Tile<RPT>::BS_FLOATS, WARP_COLS = Tile<RPT>::WARP_COLS;
+    constexpr int STAGES = Tile<RPT>::STAGES;
     extern __shared__ __align__(1024) float smem_f[];
     float* const Bs0 = smem_f;                                   // [STAGES][TN][KC], swizzled by TMA
     float* const As0 = smem_f + STAGES * BS_FLOATS;              // [STAGES][KC][TM]
@@ -142,6 +154,7 @@ prod_bandw_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
     unsigned long long* const full = bars;                       // [STAGES] B landed (tx) + coefficients written
     unsigned long long* const empty = bars + STAGES;             // [STAGES] one arrival per consumer warp
     unsigned long long* const raw_full = bars + 2 * STAGES;      // [2]
+    unsigned long long* const raw_free = bars + 2 * STAGES + 2;  // [2] one arrival per producer warp
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // column tiles vary fastest across the grid: blocks that run together share the band slice and neighbouring
@@ -152,23 +165,27 @@ prod_bandw_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
 
     if (tid == 0) {
 #pragma unroll
-        for (int s = 0; s < STAGES; s++) { w_init(&full[s], 2); w_init(&empty[s], NCW); }
+        for (int s = 0; s < STAGES; s++) { w_init(&full[s], 1 + NPW); w_init(&empty[s], NCW); }
         w_init(&raw_full[0], 1);
         w_init(&raw_full[1], 1);
+        w_init(&raw_free[0], NPW);
+        w_init(&raw_free[1], NPW);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
 
-    // The kernel is compiled for 96 registers per thread (640 threads: a pool of 61440); the producer's warp group
+    // The kernel is compiled for 96 registers per thread (640 threads: a pool of 61440); the producers' warp group
     // hands back all but 32 per thread and the four consumer warp groups take 112 each (16*32*112 + 4*32*32 = 61440).
     if (warp >= NCW) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_PRODUCER));
-        if (warp > NCW) return;
-        // =========================== producer warp ===========================
+        // =========================== producer warps ===========================
+        // Warp pw of the four re-lays steps pw, pw+4, pw+8, pw+12 of every chunk; lane 0 of warp 0 issues the loads.
+        const int pw_ = warp - NCW;
+        const bool issuer = pw_ == 0 && lane == 0;
         // first B row (TMA x coordinate) and first diagonal (y coordinate) of chunk c
-        const int rf = P.rf;
+        const int rf = P.rf, rsh = P.rf_shift;               // rf is 1, 2, 4 or 8: divisions become shifts
         auto b_row0 = [&](int c) {
-            return TRANS ? rf * (t0 + (TM - 1) - P.lo + P.rem - (c + 1) * P.gpc + 1) : (t0 / rf + P.lo - P.rem + c * KC);
+            return TRANS ? rf * (t0 + (TM - 1) - P.lo + P.rem - (c + 1) * P.gpc + 1) : ((t0 >> rsh) + P.lo - P.rem + c * KC);
         };
         auto k0 = [&](int c) { return (TRANS ? c * P.gpc : c * KC) - (TM - 1) - P.rem; };
         constexpr unsigned RAW_TX = sizeof(float) * NRAW * (TRANS ? KC : TM);
@@ -178,13 +195,13 @@ prod_bandw_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
             // 'n': the tile's 32 rows of each diagonal;  't': the chunk's 16 matrix rows (= its B rows) of each diagonal
             w_tma_2d(raw0 + (c & 1) * RAW_FLOATS, &mapA, TRANS ? b_row0(c) : t0, k0(c), &raw_full[c & 1]);
         };
-        if (lane == 0) { issue_raw(0); if (nch > 1) issue_raw(1); }
+        if (issuer) { issue_raw(0); if (nch > 1) issue_raw(1); }
         for (int c = 0; c < nch; c++) {
             const int s = c % STAGES;
             bool ok = true;
             if (c >= STAGES) ok = w_warp_wait(&empty[s], ((c / STAGES) - 1) & 1);
             if (!ok) { if (lane == 0 && P.status) *P.status = 3; return; }
-            if (lane == 0) {
+            if (issuer) {
                 w_expect_tx(&full[s], BS_TX);
 #pragma unroll
                 for (int bx = 0; bx < TN / BOXC; bx++)
@@ -195,18 +212,21 @@ prod_bandw_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
             // ---- skew: As[qq][r] = factAB * A[k][matrix row] for the diagonal k that output row r meets at step qq, zero
             // where the cell lies outside the matrix.  Lane = output row r of the tile.
             //   'n': k = k0 + 31 + qq - r/rf,  slice [diagonal][32 tile rows]
-            //   't': k = k0 + qq/rf + r,       slice [diagonal][16 B rows]; step qq reads box row rf*(gpc-1-qq/rf) + qq%rf ----
+            //   't': k = k0 + qq/rf + r,       slice [diagonal][16 B rows]; step qq reads box row rf*(gpc-1-qq/rf) + qq%rf
+            // For 't' every lane starts at a different step (qq rotated by the lane), so that the 32 reads of one
+            // instruction fall into 16 different banks instead of 2. ----
             const float* raw = raw0 + (c & 1) * RAW_FLOATS;
             float* as = As0 + s * AS_FLOATS;
             const int kc0 = k0(c), xb = b_row0(c);
             // chunk-uniform: every cell the chunk touches lies inside the matrix ('t': whole groups of rf rows)
             const bool interior = kc0 >= 0 && kc0 + NRAW <= P.nd && xb >= 0 && xb + KC <= P.rows_b &&
                                   (TRANS || t0 + TM <= P.h);
-            const int rdiv = lane / rf;
-#pragma unroll 4
-            for (int qq = 0; qq < KC; qq++) {
-                const int gq = qq / rf;                               // 't': group of rf rows within the chunk
-                const int brow = TRANS ? rf * (P.gpc - 1 - gq) + (qq - gq * rf) : qq;     // row of the B box this step reads
+            const int rdiv = lane >> rsh;
+#pragma unroll
+            for (int it = 0; it < KC / NPW; it++) {
+                const int qq = TRANS ? ((pw_ + NPW * it + lane) & (KC - 1)) : pw_ + NPW * it;
+                const int gq = qq >> rsh;                             // 't': group of rf rows within the chunk
+                const int brow = TRANS ? rf * (P.gpc - 1 - gq) + (qq - (gq << rsh)) : qq;  // row of the B box this step reads
                 const int kk = TRANS ? gq + lane : qq - rdiv + (TM - 1);                  // row of the slice: diagonal kc0 + kk
                 float v = TRANS ? raw[kk * KC + brow] : raw[kk * TM + lane];
                 if (!interior || P.fa != 1.f) {
@@ -216,16 +236,18 @@ prod_bandw_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
                     // 'n': cell (t0 + r, x): row and column must exist;  't': cell (x, t0 + r): the whole group of rf
                     // rows must lie inside the matrix (matrix_ops/spmv.cu:168: N counts whole groups only)
                     if (!TRANS) in = in && (unsigned)x < (unsigned)P.w && t0 + lane < P.h;
-                    else { const int m = x >= 0 ? x / rf : -1; in = in && m >= 0 && (long long)(m + 1) * rf <= P.h; }
+                    else { const int m = x >= 0 ? (x >> rsh) : -1; in = in && m >= 0 && (long long)(m + 1) * rf <= P.h; }
                     if (P.fa != 1.f) v = __fmul_rn(P.fa, v);
                     v = in ? v : 0.f;
                 }
                 as[qq * TM + lane] = v;
             }
             __syncwarp();
-            if (lane == 0) {
-                w_arrive(&full[s]);
-                if (c + 2 < nch) issue_raw(c + 2);
+            if (lane == 0) { w_arrive(&full[s]); w_arrive(&raw_free[c & 1]); }
+            // the slice buffer may be refilled once all four warps have read it (a bounded wait, like every other)
+            if (issuer && c + 2 < nch) {
+                if (!w_wait(&raw_free[c & 1], (c >> 1) & 1)) { if (P.status) *P.status = 3; }
+                else issue_raw(c + 2);
             }
             __syncwarp();
         }
@@ -235,13 +257,15 @@ prod_bandw_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
     // =========================== consumer warps ===========================
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS_CONSUMER));
     const int rg = lane >> 4, cg = lane & 15;
-    // this thread: rows t0 + 16*rg .. +15, columns n0 + 64*warp + cg + 16*cc (cc = 0..3)
-    const int colb = 64 * warp + cg;
+    const int wr = warp / WARP_COLS, wc = warp % WARP_COLS;
+    // this thread: rows t0 + row0 .. + RPT-1, columns n0 + 64*wc + cg + 16*cc (cc = 0..3)
+    const int row0 = (2 * wr + rg) * RPT;
+    const int colb = 64 * wc + cg;
     const int sw = (cg >> 1) & 3;                 // 64-byte swizzle: 16-byte chunk j of column c sits at j ^ ((c >> 1) & 3)
 
-    float2 acc[8][4];                             // acc[jp][cc]: rows (2jp, 2jp+1) of column cc
+    float2 acc[RPT / 2][4];                       // acc[jp][cc]: rows (2jp, 2jp+1) of column cc
 #pragma unroll
-    for (int jp = 0; jp < 8; jp++)
+    for (int jp = 0; jp < RPT / 2; jp++)
 #pragma unroll
         for (int cc = 0; cc < 4; cc++) acc[jp][cc] = make_float2(0.f, 0.f);
     if (P.fc != 0.f) {
@@ -249,8 +273,8 @@ prod_bandw_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
         for (int cc = 0; cc < 4; cc++) {
             const int col = n0 + colb + 16 * cc;
 #pragma unroll
-            for (int j = 0; j < 16; j++) {
-                const int row = t0 + 16 * rg + j;
+            for (int j = 0; j < RPT; j++) {
+                const int row = t0 + row0 + j;
                 if (col < P.ncols && row < P.rows_out) {
                     const float v = __fmul_rn(P.C[(size_t)col * P.ldc + row], P.fc);
                     if (j & 1) acc[j >> 1][cc].y = v; else acc[j >> 1][cc].x = v;
@@ -263,13 +287,13 @@ prod_bandw_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
     // descend through the box (RFT 8: two chunks per group, ascending inside it)
     auto bchunk = [](int g) { return !TRANS ? g : RFT == 8 ? ((g & 2) ^ 2) + (g & 1) : 3 - g; };
     // a warp whose 64 columns all lie beyond the batch keeps the hand-over going and leaves the arithmetic out
-    const bool has_columns = n0 + 64 * warp < P.ncols;
+    const bool has_columns = n0 + 64 * wc < P.ncols;
     for (int c = 0; c < nch; c++) {
         const int s = c % STAGES;
         if (!w_warp_wait(&full[s], (c / STAGES) & 1)) { if (lane == 0 && P.status) *P.status = 3; return; }
         if (!has_columns) { if (lane == 0) w_arrive(&empty[s]); continue; }
         const float* bsp = Bs0 + s * BS_FLOATS + colb * KC;
-        const float* asp = As0 + s * AS_FLOATS + 16 * rg;
+        const float* asp = As0 + s * AS_FLOATS + row0;
         const int ng = c == nch - 1 ? P.last_groups : KC / 4;
 #pragma unroll
         for (int g = 0; g < KC / 4; g++) {
@@ -281,13 +305,13 @@ prod_bandw_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
 #pragma unroll
                 for (int u = 0; u < 4; u++) {
                     const float* ap = asp + (4 * g + u) * TM;
-                    const float4 a0 = *reinterpret_cast<const float4*>(ap);
-                    const float4 a1 = *reinterpret_cast<const float4*>(ap + 4);
-                    const float4 a2 = *reinterpret_cast<const float4*>(ap + 8);
-                    const float4 a3 = *reinterpret_cast<const float4*>(ap + 12);
-                    const float2 a[8] = {make_float2(a0.x, a0.y), make_float2(a0.z, a0.w), make_float2(a1.x, a1.y),
-                                         make_float2(a1.z, a1.w), make_float2(a2.x, a2.y), make_float2(a2.z, a2.w),
-                                         make_float2(a3.x, a3.y), make_float2(a3.z, a3.w)};
+                    float2 a[RPT / 2];
+#pragma unroll
+                    for (int v = 0; v < RPT / 4; v++) {
+                        const float4 av = *reinterpret_cast<const float4*>(ap + 4 * v);
+                        a[2 * v] = make_float2(av.x, av.y);
+                        a[2 * v + 1] = make_float2(av.z, av.w);
+                    }
 #pragma unroll
                     for (int cc = 0; cc < 4; cc++) {
                         // which element of the vector step u reads: 'n' ascending; 't' groups of RFT rows descending,
@@ -296,7 +320,7 @@ prod_bandw_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
                         const float b = e == 0 ? bw[cc].x : e == 1 ? bw[cc].y : e == 2 ? bw[cc].z : bw[cc].w;
                         const float2 bb = make_float2(b, b);
 #pragma unroll
-                        for (int jp = 0; jp < 8; jp++) w_mac2<EXACT>(acc[jp][cc], a[jp], bb);
+                        for (int jp = 0; jp < RPT / 2; jp++) w_mac2<EXACT>(acc[jp][cc], a[jp], bb);
                     }
                 }
             }
@@ -310,17 +334,17 @@ prod_bandw_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
     for (int cc = 0; cc < 4; cc++) {
         const int col = n0 + colb + 16 * cc;
         if (col >= P.ncols) continue;
-        const int row0 = t0 + 16 * rg;
-        float* cp = P.C + (size_t)col * P.ldc + row0;
-        if (P.vec_c && row0 + 16 <= P.rows_out) {
+        const int orow = t0 + row0;
+        float* cp = P.C + (size_t)col * P.ldc + orow;
+        if (P.vec_c && orow + RPT <= P.rows_out) {
 #pragma unroll
-            for (int v = 0; v < 4; v++)
+            for (int v = 0; v < RPT / 4; v++)
                 *reinterpret_cast<float4*>(cp + 4 * v) =
                     make_float4(acc[2 * v][cc].x, acc[2 * v][cc].y, acc[2 * v + 1][cc].x, acc[2 * v + 1][cc].y);
         } else {
 #pragma unroll
-            for (int j = 0; j < 16; j++)
-                if (row0 + j < P.rows_out) cp[j] = (j & 1) ? acc[j >> 1][cc].y : acc[j >> 1][cc].x;
+            for (int j = 0; j < RPT; j++)
+                if (orow + j < P.rows_out) cp[j] = (j & 1) ? acc[j >> 1][cc].y : acc[j >> 1][cc].x;
         }
     }
 }
@@ -333,8 +357,9 @@ static inline bool w_al16(const void* p) { return (reinterpret_cast<uintptr_t>(p
 // register count its budgets were derived from (a smaller pool would leave the consumers waiting for registers).
 template <bool TRANS, bool EXACT, int RFT>
 static bool bandw_pool_ok_one() {
-    cudaFuncAttributes a;
-    return cudaFuncGetAttributes(&a, prod_bandw_kernel<TRANS, EXACT, RFT>) == cudaSuccess && a.numRegs == pw::REGS_LAUNCH;
+    cudaFuncAttributes a, b;
+    return cudaFuncGetAttributes(&a, prod_bandw_kernel<TRANS, EXACT, RFT, 16>) == cudaSuccess && a.numRegs == pw::REGS_LAUNCH &&
+           cudaFuncGetAttributes(&b, prod_bandw_kernel<TRANS, EXACT, RFT, 8>) == cudaSuccess && b.numRegs == pw::REGS_LAUNCH;
 }
 static bool bandw_register_pool_ok() {
     static int cached = -1;
@@ -358,10 +383,12 @@ bool prod_bandw_applicable(const cuvdia_plan* p, const float* A, const float* B,
            bandw_register_pool_ok();
 }
 
-template <bool TRANS, bool EXACT, int RFT>
+template <bool TRANS, bool EXACT, int RFT, int RPT>
 static int launch_bandw_t(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
                           float fa, float fc, cudaStream_t st) {
     using namespace pw;
+    constexpr int TN = Tile<RPT>::TN;
+    constexpr size_t SMEM = Tile<RPT>::SMEM;
     CUtensorMap mapA, mapB;
     int rc = make_map_2d_swizzled(&mapA, A, p->h, p->nd, p->stride, TRANS ? KC : TM, NRAW, 0);
     if (rc) return rc;
@@ -370,6 +397,7 @@ static int launch_bandw_t(const cuvdia_plan* p, const float* A, const float* B, 
     BandWParams P;
     P.h = p->h; P.w = p->w; P.nd = p->nd; P.lo = p->band_lo; P.rf = p->rf;
     P.gpc = KC / p->rf;
+    P.rf_shift = p->rf == 8 ? 3 : p->rf == 4 ? 2 : p->rf == 2 ? 1 : 0;
     P.rows_out = TRANS ? p->w : p->h;
     P.rows_b = TRANS ? p->h : p->w;
     P.ncols = ncols; P.ldc = ldc;
@@ -383,11 +411,11 @@ static int launch_bandw_t(const cuvdia_plan* p, const float* A, const float* B, 
     P.vec_c = (w_al16(C) && ldc % 4 == 0) ? 1 : 0;
     P.C = C; P.status = p->d_status;
     static bool attr_done[64] = {false};          // one flag set per template instantiation
-    rc = allow_dynamic_smem(prod_bandw_kernel<TRANS, EXACT, RFT>, SMEM, attr_done);
+    rc = allow_dynamic_smem(prod_bandw_kernel<TRANS, EXACT, RFT, RPT>, SMEM, attr_done);
     if (rc) return rc;
     const int gx = (P.rows_out + TM - 1) / TM, gy = (ncols + TN - 1) / TN;
     if (gx > 65535) { set_last_error("too many rows for the banded kernel"); return CUVDIA_ERR_UNSUPPORTED; }
-    prod_bandw_kernel<TRANS, EXACT, RFT><<<dim3(gy, gx), THREADS, SMEM, st>>>(mapA, mapB, P);
+    prod_bandw_kernel<TRANS, EXACT, RFT, RPT><<<dim3(gy, gx), THREADS, SMEM, st>>>(mapA, mapB, P);
     count_launch();
     return check_launch("prod_bandw_kernel");
 }
@@ -395,8 +423,15 @@ static int launch_bandw_t(const cuvdia_plan* p, const float* A, const float* B, 
 int launch_prod_bandw(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
                       bool trans, float fa, float fc, int mode, cudaStream_t st) {
     const bool exact = mode == CUVDIA_MODE_EXACT;
-#define GO(TR, RFT) return exact ? launch_bandw_t<TR, true, RFT>(p, A, B, ldb, C, ldc, ncols, fa, fc, st) \
-                                 : launch_bandw_t<TR, false, RFT>(p, A, B, ldb, C, ldc, ncols, fa, fc, st)
+    // 512-column tiles (8 rows per thread, twice the warps) when they waste fewer columns than 1024-column tiles
+    const bool narrow = (ncols + 511) / 512 * 512 < (ncols + 1023) / 1024 * 1024;
+#define GO(TR, RFT)                                                                                              \
+    do {                                                                                                         \
+        if (narrow) return exact ? launch_bandw_t<TR, true, RFT, 8>(p, A, B, ldb, C, ldc, ncols, fa, fc, st)     \
+                                 : launch_bandw_t<TR, false, RFT, 8>(p, A, B, ldb, C, ldc, ncols, fa, fc, st);   \
+        return exact ? launch_bandw_t<TR, true, RFT, 16>(p, A, B, ldb, C, ldc, ncols, fa, fc, st)                \
+                     : launch_bandw_t<TR, false, RFT, 16>(p, A, B, ldb, C, ldc, ncols, fa, fc, st);              \
+    } while (0)
     if (!trans) GO(false, 1);
     if (p->rf == 2) GO(true, 2);
     if (p->rf == 4) GO(true, 4);

@@ -45,7 +45,9 @@ prod_window_kernel(const WindowParams P) {
     const int c0 = blockIdx.y * CB;
     const int rf = P.rf;
     // first B row of the window (a multiple of rf for 't', so groups of rf rows stay together)
-    const int lo = TRANS ? max(0, o0 - P.off_max) * rf : max(0, o0 / rf + P.off_min);
+    // ('n' with 16-byte staging: rounded down to a multiple of 4 so that every copy is aligned)
+    const int lo = TRANS ? max(0, o0 - P.off_max) * rf
+                         : (P.natural ? (max(0, o0 / rf + P.off_min) & ~3) : max(0, o0 / rf + P.off_min));
     const int rows_b = TRANS ? P.h : P.w;
     const int wrows = TRANS ? P.wq * rf : P.wq;
     // ---- stage the window: element (row lo+rr, column c0+c) -> win[c*pitch + pos(rr)] ----
@@ -55,8 +57,10 @@ prod_window_kernel(const WindowParams P) {
     // With a row factor that is a multiple of 4 the transposed product needs no de-interleaving: the rf rows of
     // a group are contiguous and 16-byte aligned, so the window keeps memory order, is staged with 16-byte copies
     // and read with 128-bit loads (consecutive threads read consecutive groups: no bank conflicts).
+    // The plain product with row factor 1 reads the window in memory order anyway; with aligned operands it is staged
+    // with 16-byte copies too (a quarter of the copy instructions).
     const bool natural = TRANS && P.natural;
-    if (natural) {
+    if (P.natural) {
         for (int c = 0; c < CB; c++) {
             const int col = c0 + c;
             const float* src = P.B + (size_t)min(col, P.ncols - 1) * P.ldb;
@@ -232,11 +236,13 @@ static int launch_window_t(const cuvdia_plan* p, const float* A, const float* B,
     P.h = p->h; P.w = p->w; P.nd = p->nd; P.S = p->stride; P.rf = p->rf;
     P.ldb = ldb; P.ldc = ldc; P.ncols = ncols; P.off_min = p->off_min; P.off_max = p->off_max;
     long long wq = 0;
-    const long long wrows = window_rows(p, TRANS, T * tiles, &wq);
-    P.wq = (int)wq;
+    long long wrows = window_rows(p, TRANS, T * tiles, &wq);
     P.tiles = tiles;
-    P.natural = (TRANS && p->rf % 4 == 0 && p->stride % 4 == 0 && ldb % 4 == 0 &&
-                 (reinterpret_cast<uintptr_t>(A) & 15) == 0 && (reinterpret_cast<uintptr_t>(B) & 15) == 0) ? 1 : 0;
+    const bool b_aligned = ldb % 4 == 0 && (reinterpret_cast<uintptr_t>(B) & 15) == 0;
+    if (TRANS) P.natural = (p->rf % 4 == 0 && p->stride % 4 == 0 && b_aligned && (reinterpret_cast<uintptr_t>(A) & 15) == 0) ? 1 : 0;
+    else       P.natural = (p->rf == 1 && b_aligned) ? 1 : 0;
+    if (!TRANS && P.natural) { wq += 3; wrows += 3; }    // the window starts up to 3 rows early, on a 16-byte boundary
+    P.wq = (int)wq;
     // odd pitch: columns start in different banks; the memory-order window needs 16-byte aligned columns instead
     P.pitch = P.natural ? (int)((wrows + 3) / 4 * 4) : (int)(wrows | 1);
     P.fa = fa; P.fc = fc; P.A = A; P.offs = p->d_offsets; P.B = B; P.C = C;
@@ -256,7 +262,7 @@ static int launch_window_t(const cuvdia_plan* p, const float* A, const float* B,
 // its window (twice the copy's wavefronts, for the latency of the fetch) and one wavefront per term, column and
 // warp; the blocks of the grid are spread over the SMs.  Returns false if no window fits.
 static bool window_config(const cuvdia_plan* p, bool trans, int ncols, int* T, int* CB, int* tiles) {
-    const int cands[4][2] = {{256, 16}, {256, 8}, {128, 8}, {128, 4}};
+    const int cands[7][2] = {{1024, 4}, {512, 8}, {512, 4}, {256, 16}, {256, 8}, {128, 8}, {128, 4}};
     const long long rows_out = trans ? p->w : p->h;
     const long long terms = (long long)p->nd * (trans ? p->rf : 1);        // terms per output row
     const int sms = std::max(1, sm_count());
@@ -267,10 +273,11 @@ static bool window_config(const cuvdia_plan* p, bool trans, int ncols, int* T, i
         const size_t limit = (pass == 0 && trans) ? (size_t)100 * 1024 : pw::SMEM_LIMIT;
         for (auto& c : cands) {
             if (c[1] > 8 && ncols < 64) continue;
+            if (c[0] > 256 && (trans || p->rf != 1)) continue;      // the large blocks serve the plain product only
             for (int nt = 1; nt <= 8; nt *= 2) {
                 if (nt > 1 && (long long)c[0] * nt > rows_out) break;
                 const long long wrows = window_rows(p, trans, c[0] * nt, nullptr);
-                const size_t smem = (size_t)(wrows + 4) * c[1] * sizeof(float);      // covers either pitch
+                const size_t smem = (size_t)(wrows + 8) * c[1] * sizeof(float);      // covers either pitch
                 if (smem > limit) continue;
                 const long long blocks = ((rows_out + (long long)c[0] * nt - 1) / ((long long)c[0] * nt)) *
                                          ((ncols + c[1] - 1) / c[1]);
@@ -304,6 +311,9 @@ int launch_prod_window(const cuvdia_plan* p, const float* A, const float* B, int
     const bool exact = mode == CUVDIA_MODE_EXACT;
 #define GO(TR, EX, TT, CC) return launch_window_t<TR, EX, TT, CC>(p, A, B, ldb, C, ldc, ncols, fa, fc, tiles, st)
 #define PICK(TR, EX)                                    \
+    if (T == 1024 && CB == 4) GO(TR, EX, 1024, 4);      \
+    if (T == 512 && CB == 8) GO(TR, EX, 512, 8);        \
+    if (T == 512 && CB == 4) GO(TR, EX, 512, 4);        \
     if (T == 256 && CB == 16) GO(TR, EX, 256, 16);      \
     if (T == 256 && CB == 8) GO(TR, EX, 256, 8);        \
     if (T == 128 && CB == 8) GO(TR, EX, 128, 8);        \
