@@ -13,7 +13,7 @@ and bias gradients.  Inputs are synthetic with the configuration's shapes and di
 CUV's host code) on all host cores on a bounded batch slice of the same workload.
 
 Other cases (single routines, used for profiling and for the per-configuration table):
-``--case prod_n|prod_t|dd2dia|reduce|glue|update`` on the band shape given by --units/--num-dia/--batch, and
+``--case prod_n|prod_t|dd2dia|reduce|glue|glue_sum|update`` on the band shape given by --units/--num-dia/--batch, and
 ``--case cfg0|cfg1|cfg2|rbm_cfg3`` for the other BASELINE configurations, ``--case spmv_speed_n|spmv_speed_t|dd2dia_speed``
 for the reference's own speed fixtures (convolution-pattern matrices), ``--case wide_n|wide_dd`` for scattered
 diagonals that no shared-memory window covers (the plain kernels).
@@ -705,6 +705,7 @@ def measure_single(args, cfg):
     X, Y = cb.colmajor_empty(h, nb), cb.colmajor_empty(w, nb)
     X.uniform_(-1, 1); Y.uniform_(-1, 1)
     vec = torch.empty(h, device="cuda")
+    vec2 = torch.empty(h, device="cuda")
     nnz, nd = A.nnz, offs.size
     if op == "prod_n":
         fa, fc = (2.0, 1.3) if case.startswith("spmv_speed") else (1.0, 0.0)
@@ -727,6 +728,11 @@ def measure_single(args, cfg):
         S = cb.colmajor_empty(h, nb)
         fn = lambda: cb.bias_sigmoid_sample(X, vec, Y[:h] if w >= h else X, S)
         byts, flops = 16 * h * nb, 4.0 * h * nb
+    elif op == "glue_sum":
+        # the element-wise pass that also takes the per-unit batch sum (16 bytes per element + the sums)
+        S = cb.colmajor_empty(h, nb)
+        fn = lambda: cb.bias_sigmoid_sample_sum(X, vec, Y[:h] if w >= h else X, S, vec2, False, 1.0 / nb, 0.0)
+        byts, flops = 16 * h * nb + 4 * h, 5.0 * h * nb
     elif op == "update":
         # the weight update of the step over the diagonals' whole value array (12 bytes per value)
         Gd = torch.empty_like(A.vec).uniform_(-1, 1)
@@ -749,6 +755,8 @@ def measure_single(args, cfg):
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
+            fn()                      # the library's per-stream workspace is allocated on first use: not while recording
+            side.synchronize()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=side):
                 for _ in range(reps):
