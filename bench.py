@@ -691,6 +691,13 @@ def measure_single(args, cfg):
         h, w, nb, rf = px * px, 16 * px * px, 14, 1
         offs = np.array([i * px + j for _ in range(nm) for i in range(fs) for j in range(fs)], dtype=np.int32)
         op = "prod_n" if case == "spmv_speed_n" else "prod_t"
+    elif case == "conv_dd":
+        # densedense_to_dia on the convolution-pattern matrix of the spmv speed fixture (65536 x 1048576, 1024 diagonals in
+        # 128 runs of 8, 14 images): the weight gradient of that layer
+        px, fs, nm = 256, 8, 16
+        h, w, nb, rf = px * px, 16 * px * px, 14, 1
+        offs = np.array([i * px + j for _ in range(nm) for i in range(fs) for j in range(fs)], dtype=np.int32)
+        op = "dd2dia"
     elif case == "dd2dia_speed":
         # the reference's densedense_to_dia speed fixture (src/tests/densedense_to_dia_speed.cpp:65-106): a 28x28
         # image, two output maps, 8x8 filters stored as offsets i*28 + j once per map, 96 images
@@ -718,7 +725,7 @@ def measure_single(args, cfg):
         fn = lambda: cb.prod(Y, A, X, "t", "n", fa, fc, mode)
         byts, flops = 4 * (nnz + nd + h * nb + w * nb * (2 if fc else 1)), 2.0 * nnz * nb
     elif op == "dd2dia":
-        fa, fc = (0.01, 0.9) if case == "cfg2" else (1.0, 0.0) if case == "dd2dia_speed" else (1.0 / nb, 0.0)
+        fa, fc = (0.01, 0.9) if case == "cfg2" else (1.0, 0.0) if case in ("dd2dia_speed", "conv_dd") else (1.0 / nb, 0.0)
         fn = lambda: cb.densedense_to_dia(A, None, X, Y, fa, fc)
         byts, flops = 4 * (h * nb + w * nb + nd + nnz * (2 if fc else 1)), 2.0 * nnz * nb
     elif op == "reduce":

@@ -17,7 +17,7 @@ from . import _capi
 from ._capi import (CuvDiaError, MODE_EXACT, MODE_FAST, RF_ADD, RF_MEAN, RF_ADD_SQUARED, RF_MAX, RF_ARGMAX,
                     RF_ARGMIN, RF_MIN, RF_MULT, RF_LOGADDEXP, RF_ADDEXP)
 
-__all__ = ["dev_dia_matrix_f", "host_dia_matrix_f", "convert", "pull", "save_dia_mat", "load_dia_mat", "dev_block_descriptor_f", "prod", "spmv", "densedense_to_dia", "reduce_to_col",
+__all__ = ["dev_dia_matrix_f", "host_dia_matrix_f", "filter_factory", "convert", "pull", "save_dia_mat", "load_dia_mat", "dev_block_descriptor_f", "prod", "spmv", "densedense_to_dia", "reduce_to_col",
            "reduce_to_row", "avg_diagonals", "bias_sigmoid_sample", "bias_sigmoid_sample_sum", "prod_bias_sigmoid_sample", "axpby", "learn_step_weight_decay",
            "learn_step_weight_decay_momentum", "colmajor_empty", "to_device", "to_host",
            "launch_count", "plan_status", "raise_if_gave_up", "CuvDiaError", "MODE_EXACT", "MODE_FAST"]
@@ -232,6 +232,50 @@ def convert(dst, src):
 def pull(mat):
     """Device DIA matrix -> dense host matrix (``pull`` of src/cuv_python/export_dia_mat.cpp:158-167)."""
     return convert(None, convert(host_dia_matrix_f(mat.h, mat.w, mat.offsets, mat.stride, mat.row_fact), mat))
+
+
+class filter_factory:
+    """``filter_factory`` (basics/filter_factory.hpp:6-84): the DIA matrix of a layer of ``fs`` x ``fs`` convolution
+    filters between ``input_maps`` and ``output_maps`` images of ``px`` x ``py`` pixels - runs of ``fs`` consecutive
+    diagonals one image line apart, one block of ``fs*fs`` diagonals per map distance - and the way back from such a
+    matrix to one filter.  Host-side index arithmetic only."""
+
+    def __init__(self, px, py, fs, input_maps, output_maps):
+        self.px, self.py, self.fs = int(px), int(py), int(fs)
+        self.input_maps, self.output_maps = int(input_maps), int(output_maps)
+
+    def offsets(self):
+        """Diagonal numbers in storage order (basics/filter_factory.hpp:58-71)."""
+        px, py, fs = self.px, self.py, self.fs
+        m, i, j = np.meshgrid(np.arange(self.output_maps + self.input_maps - 1), np.arange(fs), np.arange(fs), indexing="ij")
+        shift = -(px + 1) * (fs // 2) - (self.input_maps - 1) * px * py
+        return (i * px + j + m * px * py + shift).reshape(-1).astype(np.int32)
+
+    def get_dia(self, device="cuda"):
+        """A new device matrix (``device=None``: host matrix) of ``px*py*input_maps`` x ``px*py*output_maps``."""
+        h, w = self.px * self.py * self.input_maps, self.px * self.py * self.output_maps
+        if device is None:
+            return host_dia_matrix_f(h, w, self.offsets(), max(h, w), 1)
+        return dev_dia_matrix_f(h, w, self.offsets(), max(h, w), 1, device=device)
+
+    def extract_filter(self, dia, filternumber):
+        """The coefficients that column ``filternumber`` receives from each input map, as CUV lays them out: an
+        ``(fs*fs, input_maps)`` row-major array filled flat, map after map (basics/filter_factory.hpp:22-41)."""
+        host = dia if isinstance(dia, host_dia_matrix_f) else convert(
+            host_dia_matrix_f(dia.h, dia.w, dia.offsets, dia.stride, dia.row_fact), dia)
+        out = np.zeros(self.fs * self.fs * self.input_maps, dtype=np.float32)
+        map_size = host.h // self.input_maps
+        for m in range(self.input_maps):
+            found = 0
+            for i in range(map_size):
+                row = i + m * map_size
+                if not host.has(row, filternumber):
+                    continue
+                out[m * self.fs * self.fs + found] = host(row, filternumber)
+                found += 1
+                if found >= out.size:
+                    break
+        return out.reshape(self.fs * self.fs, self.input_maps)
 
 
 class dev_block_descriptor_f:

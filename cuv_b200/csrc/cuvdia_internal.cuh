@@ -123,6 +123,10 @@ bool dd2dia_stream_applicable(const cuvdia_plan* p, const float* Cv, const float
                               int ncols);
 int launch_dd2dia_stream(cuvdia_plan* p, float* Cv, const float* A, int lda, const float* B, int ldb, int ncols,
                          float factAB, float factC, cudaStream_t st);
+bool dd2dia_runs_applicable(const cuvdia_plan* p, const float* Cv, const float* A, int lda, const float* B, int ldb,
+                            int ncols);
+int launch_dd2dia_runs(cuvdia_plan* p, float* Cv, const float* A, int lda, const float* B, int ldb, int ncols,
+                       float factAB, float factC, cudaStream_t st);
 bool dd2dia_window_applicable(const cuvdia_plan* p, const float* A, int lda, const float* B, int ldb, int ncols);
 int launch_dd2dia_window(cuvdia_plan* p, float* Cv, const float* A, int lda, const float* B, int ldb, int ncols,
                          float factAB, float factC, cudaStream_t st);

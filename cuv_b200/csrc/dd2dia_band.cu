@@ -50,6 +50,19 @@ __device__ __forceinline__ bool dmbar_wait(unsigned long long* bar, unsigned par
     return false;
 }
 
+__device__ __forceinline__ void dmbar_wait_short(unsigned long long* bar, unsigned parity) {
+    const unsigned addr = dsmem_u32(bar);
+    for (unsigned it = 0; it < (1u << 22); it++) {
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return;
+    }
+}
+
 struct DdBandParams {
     int h, w, nd, lo, S, ncols;
     int rem;            // lo mod 4 (non-negative): keeps the TMA row coordinate of B 16-byte aligned
@@ -155,6 +168,10 @@ dd2dia_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
         const int s = c % STAGES;
         if (!dmbar_wait(&full[s], (c / STAGES) & 1)) {
             if (P.status) *P.status = 2;
+            // the issuing thread waits once more, bounded, for the copies it started (this chunk's and the ones ahead
+            // of it), so that none lands in shared memory the block has given back
+            if (tid == 0)
+                for (int c2 = c; c2 < nch && c2 < c + STAGES; c2++) dmbar_wait_short(&full[c2 % STAGES], (c2 / STAGES) & 1);
             return;
         }
         const float* xs = Xs0 + s * TILE_FLOATS + 4 * R;

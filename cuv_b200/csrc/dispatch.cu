@@ -36,6 +36,9 @@ int launch_dd2dia(cuvdia_plan* p, float* Cv, const float* A, int lda, const floa
         return launch_dd2dia_stream(p, Cv, A, lda, B, ldb, ncols, factAB, factC, st);
     if (dd2dia_band_applicable(p, A, lda, B, ldb, ncols))
         return launch_dd2dia_band(p, Cv, A, lda, B, ldb, ncols, factAB, factC, st);
+    // runs of consecutive diagonals (convolution patterns): every run a narrow band of its own
+    if (dd2dia_runs_applicable(p, Cv, A, lda, B, ldb, ncols))
+        return launch_dd2dia_runs(p, Cv, A, lda, B, ldb, ncols, factAB, factC, st);
     if (dd2dia_window_applicable(p, A, lda, B, ldb, ncols))
         return launch_dd2dia_window(p, Cv, A, lda, B, ldb, ncols, factAB, factC, st);
     return launch_dd2dia_generic(p, Cv, A, lda, B, ldb, ncols, factAB, factC, st);

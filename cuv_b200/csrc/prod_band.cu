@@ -49,6 +49,7 @@ template <bool TRANS> __host__ __device__ constexpr size_t smem_bytes() {
 // 52.3 TFLOP/s with 4), half of it for the exact one (three instructions per multiply-add pair: 30.0 against 29.5)
 template <bool EXACT> __host__ __device__ constexpr int group_unroll() { return EXACT ? 4 : 8; }
 constexpr unsigned SPIN_LIMIT = 1u << 26;   // bounded wait on a TMA completion barrier
+constexpr unsigned DRAIN_LIMIT = 1u << 22;  // second, shorter wait for copies still in flight when a warp gives up
 }  // namespace pb
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -72,6 +73,20 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
         if (done) return true;
     }
     return false;
+}
+// After a wait has run out: one more bounded wait for a copy this thread issued, so that it does not land in shared
+// memory the block has already given back.
+__device__ __forceinline__ void mbar_drain(unsigned long long* bar, unsigned parity) {
+    const unsigned addr = smem_u32(bar);
+    for (unsigned it = 0; it < pb::DRAIN_LIMIT; it++) {
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return;
+    }
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
     asm volatile(
@@ -184,13 +199,25 @@ prod_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         const bool issuer = pw == 0 && lane == 0;
         constexpr unsigned RAW_TX = sizeof(float) * (TRANS ? RAW_FLOATS_T : RAW_FLOATS_N);
         constexpr unsigned BS_TX = sizeof(float) * BS_FLOATS;
+        int armed_raw = -1, armed_b0 = -1, armed_b1 = -1;      // issuer: last chunk whose copy was started, per barrier
         auto issue_raw = [&](int c) {
             mbar_expect_tx(raw_full, RAW_TX);
             tma_load_2d(raw, &mapA, TRANS ? win_row0(c) : t0, c * KC - P.rem - 7, raw_full);
+            armed_raw = c;
         };
         auto issue_b = [&](int c) {
             mbar_expect_tx(&bs_full[c & 1], BS_TX);
             tma_load_2d(Bs0 + (c & 1) * BSF, &mapB, win_row0(c), n0, &bs_full[c & 1]);
+            if (c & 1) armed_b1 = c; else armed_b0 = c;
+        };
+        // a producer that gives up: the issuing thread first waits, bounded again, for the copies it started
+        auto give_up = [&]() {
+            if (lane == 0 && P.status) *P.status = 1;
+            if (issuer) {
+                if (armed_raw >= 0) mbar_drain(raw_full, armed_raw & 1);
+                if (armed_b0 >= 0) mbar_drain(&bs_full[0], (armed_b0 >> 1) & 1);
+                if (armed_b1 >= 0) mbar_drain(&bs_full[1], (armed_b1 >> 1) & 1);
+            }
         };
         if (issuer) {
             issue_raw(0);
@@ -200,7 +227,7 @@ prod_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         for (int c = 0; c < nch; c++) {
             bool ok = warp_wait(raw_full, c & 1);
             if (ok && c >= 2) ok = warp_wait(&as_empty[c & 1], ((c >> 1) + 1) & 1);
-            if (!ok) { if (lane == 0 && P.status) *P.status = 1; return; }
+            if (!ok) { give_up(); return; }
             // ---- skew: As[qq][r] = factAB * A[k][matrix row], zero where the cell is outside the matrix ----
             float* as = As0 + (c & 1) * AS_FLOATS;
             const int y0 = c * KC - P.rem - 7;

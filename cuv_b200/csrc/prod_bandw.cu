@@ -70,6 +70,7 @@ template <int RPT> struct Tile {
     static constexpr size_t SMEM = sizeof(float) * (STAGES * BS_FLOATS + STAGES * AS_FLOATS + 2 * RAW_FLOATS) + 256;
 };
 constexpr unsigned SPIN_LIMIT = 1u << 26;
+constexpr unsigned DRAIN_LIMIT = 1u << 22;  // second, shorter wait for copies still in flight when a warp gives up
 }  // namespace pw
 
 __device__ __forceinline__ unsigned w_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -94,6 +95,20 @@ __device__ __forceinline__ bool w_wait(unsigned long long* bar, unsigned parity)
         if (done) return true;
     }
     return false;
+}
+// After a wait has run out: one more bounded wait for a copy this thread issued, so that it does not land in shared
+// memory the block has already given back.
+__device__ __forceinline__ void w_drain(unsigned long long* bar, unsigned parity) {
+    const unsigned addr = w_u32(bar);
+    for (unsigned it = 0; it < pw::DRAIN_LIMIT; it++) {
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return;
+    }
 }
 // warp-uniform: either every lane sees the phase complete or the whole warp gives up
 __device__ __forceinline__ bool w_warp_wait(unsigned long long* bar, unsigned parity) {
@@ -190,25 +205,37 @@ prod_bandw_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
         auto k0 = [&](int c) { return (TRANS ? c * P.gpc : c * KC) - (TM - 1) - P.rem; };
         constexpr unsigned RAW_TX = sizeof(float) * NRAW * (TRANS ? KC : TM);
         constexpr unsigned BS_TX = sizeof(float) * BS_FLOATS;
+        int armed_raw = -1, armed_b = -1;                   // issuer: last chunk whose copies were started
         auto issue_raw = [&](int c) {
             w_expect_tx(&raw_full[c & 1], RAW_TX);
             // 'n': the tile's 32 rows of each diagonal;  't': the chunk's 16 matrix rows (= its B rows) of each diagonal
             w_tma_2d(raw0 + (c & 1) * RAW_FLOATS, &mapA, TRANS ? b_row0(c) : t0, k0(c), &raw_full[c & 1]);
+            armed_raw = c;
+        };
+        // a producer that gives up: the issuing thread first waits, bounded again, for the copies it started (the
+        // band slices of the last two chunks and the B stages of the last STAGES chunks)
+        auto give_up = [&]() {
+            if (lane == 0 && P.status) *P.status = 3;
+            if (issuer) {
+                for (int c2 = max(0, armed_raw - 1); c2 <= armed_raw; c2++) w_drain(&raw_full[c2 & 1], (c2 >> 1) & 1);
+                for (int c2 = max(0, armed_b - STAGES + 1); c2 <= armed_b; c2++) w_drain(&full[c2 % STAGES], (c2 / STAGES) & 1);
+            }
         };
         if (issuer) { issue_raw(0); if (nch > 1) issue_raw(1); }
         for (int c = 0; c < nch; c++) {
             const int s = c % STAGES;
             bool ok = true;
             if (c >= STAGES) ok = w_warp_wait(&empty[s], ((c / STAGES) - 1) & 1);
-            if (!ok) { if (lane == 0 && P.status) *P.status = 3; return; }
+            if (!ok) { give_up(); return; }
             if (issuer) {
+                armed_b = c;
                 w_expect_tx(&full[s], BS_TX);
 #pragma unroll
                 for (int bx = 0; bx < TN / BOXC; bx++)
                     w_tma_2d(Bs0 + s * BS_FLOATS + bx * (KC * BOXC), &mapB, b_row0(c), n0 + bx * BOXC, &full[s]);
             }
             ok = w_warp_wait(&raw_full[c & 1], (c >> 1) & 1);
-            if (!ok) { if (lane == 0 && P.status) *P.status = 3; return; }
+            if (!ok) { give_up(); return; }
             // ---- skew: As[qq][r] = factAB * A[k][matrix row] for the diagonal k that output row r meets at step qq, zero
             // where the cell lies outside the matrix.  Lane = output row r of the tile.
             //   'n': k = k0 + 31 + qq - r/rf,  slice [diagonal][32 tile rows]

@@ -1,6 +1,7 @@
 // Umbrella header of the CUV surface for the DIA sparse path.
 #pragma once
 #include "cuv/basics/dia_matrix.hpp"
+#include "cuv/basics/filter_factory.hpp"
 #include "cuv/basics/sparse_matrix_io.hpp"
 #include "cuv/basics/tags.hpp"
 #include "cuv/basics/tensor.hpp"

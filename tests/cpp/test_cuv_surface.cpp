@@ -265,6 +265,27 @@ static void test_reduce_typed() {
     reduce_typed_pair<unsigned char, unsigned int>("uchar -> unsigned", 2);
 }
 
+// filter_factory (basics/filter_factory.hpp:43-76): the diagonals of a convolution layer, and a filter read back.
+static void test_filter_factory() {
+    filter_factory<float, host_memory_space> ff(12, 12, 3, 1, 1);
+    dia_matrix<float, host_memory_space>* m = ff.get_dia();
+    CHECK(m->h() == 144 && m->w() == 144 && m->num_dia() == 9 && m->stride() == 144);
+    CHECK(m->get_offset(0) == -13 && m->get_offset(4) == 0 && m->get_offset(8) == 13);
+    fill(m->vec(), 0.f);
+    const std::vector<int> off = ff.offsets();
+    for (int t = 0; t < 9; t++) m->set(100 - off[t], 100, (float)(t + 1));
+    tensor<float, host_memory_space, row_major>* f = ff.extract_filter(*m, 100);
+    bool ok = f->size() == 9;
+    for (int t = 0; t < 9 && ok; t++) ok = (float)(*f)[t] == (float)(9 - t);
+    CHECK(ok);
+    delete f;
+    delete m;
+    filter_factory<float, dev_memory_space> fd(16, 16, 5, 2, 3);
+    dia_matrix<float, dev_memory_space>* md = fd.get_dia();
+    CHECK(md->num_dia() == 100 && md->h() == 512 && md->w() == 768);
+    delete md;
+}
+
 static void test_tensor_ops() {
     tensor<float, host_memory_space> a(100), b(100);
     sequence(a); fill(b, 2.f);
@@ -405,6 +426,7 @@ int main() {
         reduce_sweep<column_major>("column_major");
         reduce_sweep<row_major>("row_major");
         test_tensor_ops();
+        test_filter_factory();
         test_reduce_typed();
         test_reduce_3d();
         test_learn_step();

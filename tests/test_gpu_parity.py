@@ -375,6 +375,21 @@ def test_dd2dia_convolution_pattern(cb):
     dd_case(cb, rng, h, w, offs, 1, 72, -1.0 / 72, 1.0, dist="uniform")
 
 
+def test_dd2dia_runs_of_diagonals(cb):
+    """Runs of consecutive diagonals as narrow bands of their own (the run-aware kernel): the reference's speed fixture
+    (src/tests/densedense_to_dia_speed.cpp:65-106: a 28 x 28 image, 8 x 8 filters, two output maps whose diagonal numbers
+    repeat), runs of unequal length with every alignment of their first offset, several row tiles with a ragged end,
+    and both factors."""
+    rng = np.random.default_rng(43)
+    offs = np.array([i * 28 + j for _ in range(2) for i in range(8) for j in range(8)], dtype=np.int32)
+    dd_case(cb, rng, 784, 1568, offs, 1, 96, 1.0, 0.0)
+    runs = [(-301, 8), (-150, 7), (-9, 8), (2, 5), (43, 8), (60, 8), (201, 6), (350, 8), (-1290, 8), (1301, 8), (-37, 8),
+            (500, 8), (521, 4), (-700, 8), (-650, 8), (777, 8)]
+    offs = np.concatenate([np.arange(lo, lo + n) for lo, n in runs]).astype(np.int32)
+    dd_case(cb, rng, 1300, 1411, offs, 1, 37, -0.5, 1.0, dist="uniform")
+    dd_case(cb, rng, 1300, 1411, offs, 1, 16, 2.0, 0.0)
+
+
 def test_reference_fixture_dd2dia(cb, golden):
     g = golden                                           # src/tests/densedense_to_dia.cpp:109-137,166-197
     h, w, rf, S = int(g["dd2dia_h"]), int(g["dd2dia_w"]), int(g["dd2dia_rf"]), int(g["dd2dia_stride"])
