@@ -353,9 +353,10 @@ def run_ours(args, cfg):
     local_work = rbm.algorithmic_work(units, units, nd, W.nnz, nb)
 
     def one_step():
-        step.step(V0, U_h, U_v)                # one call of the C ABI: cuvdia_rbm_cd1_step_f32
         if world > 1:
-            step.allreduce()                   # cuvdia_allreduce_grad
+            step.step_allreduce(V0, U_h, U_v)  # one call of the C ABI: cuvdia_rbm_cd1_step_allreduce_f32
+        else:
+            step.step(V0, U_h, U_v)            # one call of the C ABI: cuvdia_rbm_cd1_step_f32
 
     def barrier():
         torch.cuda.synchronize()
@@ -518,9 +519,11 @@ def run_ours(args, cfg):
         n_ar = step.G.vec.numel() + step.bias_grad.numel()
         per_op["allreduce"] = {"ms": ar_ms, "bytes": 4 * n_ar,
                                "bus_GB/s": 4 * n_ar * 2.0 * (world - 1) / world / (ar_ms * 1e-3) / 1e9,
-                               "how": "one ncclAllReduce over the diagonals' values and both bias gradients (one buffer), "
-                                      "issued through cuvdia_allreduce_grad after the step; not overlapped: the last "
-                                      "densedense_to_dia finishes whole rows of all diagonals, not diagonal slabs"}
+                               "how": "timed alone here: one ncclAllReduce over the diagonals' values and both bias gradients "
+                                      "(one buffer) through cuvdia_allreduce_grad.  In the timed step "
+                                      "(cuvdia_rbm_cd1_step_allreduce_f32) the last densedense_to_dia is cut in two launches by "
+                                      "column tiles and the diagonals the first one completes are all-reduced on a side stream "
+                                      "under the second"}
     tflops = prod_flops / (prod_ms * 1e-3) / 1e12
     if pos["bound"] == "fp32":
         roof = {"bound": "fp32", "achieved": tflops, "peak": fp32_peak, "unit": "TFLOP/s", "frac": tflops / fp32_peak,

@@ -39,6 +39,7 @@ SIGNATURES = {
     "cuvdia_bias_sigmoid_sample_f32": (_i, [_vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _vp]),
     "cuvdia_bias_sigmoid_sample_sum_f32": (_i, [_vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _vp, _i, _f, _f, _i, _vp]),
     "cuvdia_rbm_cd1_step_f32": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "cuvdia_rbm_cd1_step_allreduce_f32": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp]),
     "cuvdia_allreduce_grad": (_i, [_vp, _vp, _ll, _vp, _ll, _vp]),
     "cuvdia_nccl_unique_id": (_i, [ctypes.c_char_p]),
     "cuvdia_nccl_comm_create": (_i, [ctypes.POINTER(_vp), _i, _i, ctypes.c_char_p]),

@@ -127,6 +127,7 @@ int cuvdia_plan_create(cuvdia_plan** out, int h, int w, int num_dia, int stride,
     p->h = h; p->w = w; p->nd = num_dia; p->stride = stride; p->rf = row_fact;
     p->offsets.assign(offsets_host, offsets_host + num_dia);
     p->d_offsets = nullptr; p->scratch = nullptr; p->scratch_floats = 0; p->d_status = nullptr; p->d_passes = nullptr; p->d_sorted = nullptr;
+    p->side_stream = nullptr; p->ev_first = nullptr; p->ev_side = nullptr;
     p->is_band = true;
     for (int k = 1; k < num_dia; k++) if (p->offsets[k] != p->offsets[0] + k) { p->is_band = false; break; }
     p->band_lo = p->offsets[0];
@@ -201,6 +202,9 @@ int cuvdia_plan_destroy(cuvdia_plan* p) {
     if (p->d_status) cudaFree(p->d_status);
     if (p->d_passes) cudaFree(p->d_passes);
     if (p->d_sorted) cudaFree(p->d_sorted);
+    if (p->ev_first) cudaEventDestroy(p->ev_first);
+    if (p->ev_side) cudaEventDestroy(p->ev_side);
+    if (p->side_stream) cudaStreamDestroy(p->side_stream);
     delete p;
     return CUVDIA_OK;
 }

@@ -83,6 +83,9 @@ struct cuvdia_plan {
     // largest number of dense rows that 16 ([0]) and 32 ([1]) neighbours in that order span
     int* d_sorted;
     int group_window_max[2];
+    // side stream (highest priority) and events of the step that overlaps its all-reduce; created on first use
+    cudaStream_t side_stream;
+    cudaEvent_t ev_first, ev_side;
 };
 
 namespace cuvdia {
@@ -133,6 +136,11 @@ int launch_dd2dia_window(cuvdia_plan* p, float* Cv, const float* A, int lda, con
 bool dd2dia_band_applicable(const cuvdia_plan* p, const float* A, int lda, const float* B, int ldb, int ncols);
 int launch_dd2dia_band(cuvdia_plan* p, float* Cv, const float* A, int lda, const float* B, int ldb, int ncols,
                        float factAB, float factC, cudaStream_t st);
+// the banded densedense_to_dia cut in two launches by column tiles (see dd2dia_band.cu)
+int dd2dia_band_cut(const cuvdia_plan* p, int ncols, int* first_diagonals, bool force);
+int dd2dia_band_nsplit(const cuvdia_plan* p, int ncols);
+int launch_dd2dia_band_range(cuvdia_plan* p, float* Cv, const float* A, int lda, const float* B, int ldb, int ncols,
+                             float factAB, float factC, int tile0, int tile1, cudaStream_t st);
 int launch_reduce(float* dst, const float* src, long long n_contig, long long n_strided, bool over_strided,
                   int functor, float factNew, float factOld, cudaStream_t st);
 int launch_reduce_typed(void* dst, int dst_type, const void* src, int src_type, long long n_contig, long long n_strided,

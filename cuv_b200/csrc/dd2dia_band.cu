@@ -67,6 +67,7 @@ struct DdBandParams {
     int h, w, nd, lo, S, ncols;
     int rem;            // lo mod 4 (non-negative): keeps the TMA row coordinate of B 16-byte aligned
     int nsplit;
+    int tile0, ntiles;  // this launch covers column tiles tile0 .. tile0 + gridDim.x - 1 of the ntiles of a row block
     float fa, fc;
     float* G;
     float* partial;     // [nsplit][nd*S] when nsplit > 1
@@ -119,7 +120,8 @@ dd2dia_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
     // the column tiles of one row block are neighbours in the grid: they share the A tile, and
     // adjacent row blocks share most B tiles, so both operands come from HBM about once
     const int i0 = blockIdx.y * TI;
-    const int j0 = i0 + P.lo - P.rem + (int)blockIdx.x * TJ;
+    const int tile = P.tile0 + (int)blockIdx.x;
+    const int j0 = i0 + P.lo - P.rem + tile * TJ;
     const int z = blockIdx.z;
     const int nch_all = (P.ncols + KB - 1) / KB;
     const int ch0 = (int)((long long)nch_all * z / P.nsplit), ch1 = (int)((long long)nch_all * (z + 1) / P.nsplit);
@@ -129,8 +131,8 @@ dd2dia_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
     // first tile of a row block the quadrant rows 64.. x columns ..63 never is; in the last one the quadrant
     // rows ..63 x columns 64.. is not either when the band ends at or before the tile's main diagonal, and when it
     // ends 63 or more diagonals before it only the quadrant rows 64.. x columns ..63 is left.
-    const int dlast = P.nd + P.rem - TJ * (int)blockIdx.x;        // cells of this tile need jc - ir < dlast
-    const int skip = blockIdx.x == 0 ? 1 : (blockIdx.x == gridDim.x - 1 && dlast <= 1) ? (dlast <= -63 ? 3 : 2) : 0;
+    const int dlast = P.nd + P.rem - TJ * tile;                   // cells of this tile need jc - ir < dlast
+    const int skip = tile == 0 ? 1 : (tile == P.ntiles - 1 && dlast <= 1) ? (dlast <= -63 ? 3 : 2) : 0;
 
     constexpr unsigned TX_BYTES = sizeof(float) * 2 * TILE_FLOATS;
     auto issue = [&](int c) {
@@ -222,8 +224,69 @@ bool dd2dia_band_applicable(const cuvdia_plan* p, const float* A, int lda, const
            p->nd >= 16 && tma_available();
 }
 
+// Column tiles per row block, and how a call may be cut in two launches so that the diagonals' array is finished
+// slab by slab: tile t writes diagonals 128t - rem - 127 .. 128t - rem + 127, so after tiles 0 .. T-1 the diagonals
+// 0 .. 128(T-1) - rem are complete (they are contiguous in memory: a band is stored in ascending order).
+static int band_tiles(const cuvdia_plan* p) {
+    const int rem = ((p->band_lo % 4) + 4) % 4;
+    return (p->nd + db::TI - 1 + rem + db::TJ - 1) / db::TJ;
+}
+
+// Finds a cut T (tiles 0..T-1, then T..gy-1) that needs no more waves of blocks than the uncut grid and finishes as
+// close to half of the diagonals as possible with its first launch; 0 if the call should stay one launch (batch split
+// in use, too few tiles, or every cut costs a wave; with `force` the waves are not looked at and two tiles are enough).
+// *first_diagonals = diagonals complete after the first launch.
+int dd2dia_band_cut(const cuvdia_plan* p, int ncols, int* first_diagonals, bool force) {
+    const int rem = ((p->band_lo % 4) + 4) % 4;
+    const int gx = (p->h + db::TI - 1) / db::TI, gy = band_tiles(p);
+    const long long slots = 2LL * sm_count();
+    auto waves = [&](long long ctas) { return (ctas + slots - 1) / slots; };
+    if (gy < (force ? 3 : 4)) return 0;
+    int best = 0, best_dist = 1 << 30;
+    for (int T = 2; T < gy; T++) {
+        if (!force && waves((long long)gx * T) + waves((long long)gx * (gy - T)) > waves((long long)gx * gy)) continue;
+        const int done = db::TJ * (T - 1) - rem + 1;
+        if (done <= 0) continue;
+        const int dist = abs(2 * done - p->nd);
+        if (dist < best_dist) { best_dist = dist; best = T; *first_diagonals = std::min(done, p->nd); }
+    }
+    (void)ncols;
+    return best;
+}
+
+static int launch_dd2dia_band_tiles(cuvdia_plan* p, float* Cv, const float* A, int lda, const float* B, int ldb, int ncols,
+                                    float fa, float fc, int tile0, int tile1, int nsplit, cudaStream_t st);
+
 int launch_dd2dia_band(cuvdia_plan* p, float* Cv, const float* A, int lda, const float* B, int ldb, int ncols,
                        float fa, float fc, cudaStream_t st) {
+    return launch_dd2dia_band_tiles(p, Cv, A, lda, B, ldb, ncols, fa, fc, 0, -1, 0, st);
+}
+
+// The batch split a whole call would use (1 = none).
+int dd2dia_band_nsplit(const cuvdia_plan* p, int ncols) {
+    using namespace db;
+    const int gx = (p->h + TI - 1) / TI, gy = band_tiles(p);
+    const int slots = 2 * sm_count();
+    const int nch_all = (ncols + KB - 1) / KB;
+    int nsplit = 1;
+    double best = 0.0;
+    for (int s = 1; s <= 8 && s <= std::max(1, nch_all / 4); s++) {
+        const long long ctas = (long long)gx * gy * s;
+        const long long waves = (ctas + slots - 1) / slots;
+        const double eff = (double)ctas / (double)(waves * slots);
+        if (eff > best + 0.05) { best = eff; nsplit = s; }
+    }
+    return nsplit;
+}
+
+// Column tiles tile0 .. tile1-1 (tile1 < 0: all) of every row block; force_nsplit > 0 overrides the batch split.
+int launch_dd2dia_band_range(cuvdia_plan* p, float* Cv, const float* A, int lda, const float* B, int ldb, int ncols,
+                             float fa, float fc, int tile0, int tile1, cudaStream_t st) {
+    return launch_dd2dia_band_tiles(p, Cv, A, lda, B, ldb, ncols, fa, fc, tile0, tile1, 1, st);
+}
+
+static int launch_dd2dia_band_tiles(cuvdia_plan* p, float* Cv, const float* A, int lda, const float* B, int ldb, int ncols,
+                                    float fa, float fc, int tile0, int tile1, int force_nsplit, cudaStream_t st) {
     using namespace db;
     CUtensorMap mapA, mapB;
     int rc = make_map_2d(&mapA, A, p->h, ncols, lda, TI, KB);
@@ -235,19 +298,12 @@ int launch_dd2dia_band(cuvdia_plan* p, float* Cv, const float* A, int lda, const
     P.rem = ((p->band_lo % 4) + 4) % 4;
     P.fa = fa; P.fc = fc; P.G = Cv; P.status = p->d_status;
     const int gx = (p->h + TI - 1) / TI;
-    const int gy = (p->nd + TI - 1 + P.rem + TJ - 1) / TJ;       // column tiles that cover the band of one row block
+    const int gy = band_tiles(p);                                // column tiles that cover the band of one row block
+    if (tile1 < 0) tile1 = gy;
     // split the batch when the tiles alone leave SMs idle or quantise badly into waves
-    const int slots = 2 * sm_count();
-    const int nch_all = (ncols + KB - 1) / KB;
-    int nsplit = 1;
-    double best = 0.0;
-    for (int s = 1; s <= 8 && s <= std::max(1, nch_all / 4); s++) {
-        const long long ctas = (long long)gx * gy * s;
-        const long long waves = (ctas + slots - 1) / slots;
-        const double eff = (double)ctas / (double)(waves * slots);
-        if (eff > best + 0.05) { best = eff; nsplit = s; }
-    }
+    const int nsplit = force_nsplit > 0 ? force_nsplit : dd2dia_band_nsplit(p, ncols);
     P.nsplit = nsplit;
+    P.tile0 = tile0; P.ntiles = gy;
     P.partial = nullptr;
     if (nsplit > 1) {
         rc = ensure_plan_scratch(p, (size_t)nsplit * p->nd * p->stride, st);
@@ -258,7 +314,7 @@ int launch_dd2dia_band(cuvdia_plan* p, float* Cv, const float* A, int lda, const
     rc = allow_dynamic_smem(dd2dia_band_kernel, SMEM, attr_done);
     if (rc) return rc;
     if (gx > 65535 || nsplit > 65535) { set_last_error("matrix too tall for the banded densedense_to_dia"); return CUVDIA_ERR_UNSUPPORTED; }
-    dd2dia_band_kernel<<<dim3(gy, gx, nsplit), THREADS, SMEM, st>>>(mapA, mapB, P);
+    dd2dia_band_kernel<<<dim3(tile1 - tile0, gx, nsplit), THREADS, SMEM, st>>>(mapA, mapB, P);
     count_launch();
     rc = check_launch("dd2dia_band_kernel");
     if (rc) return rc;

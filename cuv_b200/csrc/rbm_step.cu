@@ -89,46 +89,20 @@ using namespace cuvdia;
 
 extern "C" {
 
+// The step up to and including the first densedense_to_dia (everything but the call that completes G).
+static int rbm_step_head(cuvdia_plan* p, const float* W_vals, const cuvdia_rbm_cd1_buffers* b, int ncols, int batch_global,
+                         int mode, int keep_v1p, cudaStream_t st, float* inv_out);
+
 int cuvdia_rbm_cd1_step_f32(cuvdia_plan* p, const float* W_vals, const cuvdia_rbm_cd1_buffers* b, int ncols,
                             int batch_global, int mode, int keep_v1p, void* stream) {
-    CUVDIA_REQUIRE(p != nullptr && W_vals != nullptr && b != nullptr);
-    CUVDIA_REQUIRE(p->rf == 1);                        // the trainer's weight matrix (row factors belong to other layers)
-    CUVDIA_REQUIRE(ncols > 0 && batch_global >= ncols);
-    CUVDIA_REQUIRE(mode == CUVDIA_MODE_EXACT || mode == CUVDIA_MODE_FAST);
-    CUVDIA_REQUIRE(b->V0 && b->U_h && b->U_v);
-    CUVDIA_REQUIRE(b->H0p && b->H0 && b->V1p && b->V1 && b->H1p);
-    CUVDIA_REQUIRE(b->G_vals && b->gc && b->gb);
-    int dev = -1;
-    CUVDIA_REQUIRE(cudaGetDevice(&dev) == cudaSuccess && dev == p->device);
-    cudaStream_t st = (cudaStream_t)stream;
-    const int hid = p->h, vis = p->w;
-    const float inv = (float)(1.0 / (double)batch_global);
-    int rc;
-#define STEP(call) do { rc = (call); if (rc) return rc; } while (0)
-    STEP(launch_reduce(b->gb, b->V0, vis, ncols, true, CUVDIA_RF_ADD, inv, 0.f, st));
-    STEP(launch_prod(p, W_vals, b->V0, vis, b->H0p, hid, ncols, false, 1.f, 0.f, mode, nullptr, st));
-    STEP(launch_bias_sigmoid_sample_sum(b->H0p, hid, b->c_hid, b->U_h, hid, b->H0, hid, hid, ncols, b->gc, 0, inv, 0.f, 1, st));
-    STEP(launch_prod(p, W_vals, b->H0, hid, b->V1p, vis, ncols, true, 1.f, 0.f, mode, nullptr, st));
-    STEP(launch_bias_sigmoid_sample_sum(b->V1p, vis, b->b_vis, b->U_v, vis, b->V1, vis, vis, ncols, b->gb, 1, -inv, 1.f,
-                                        keep_v1p ? 1 : 0, st));
-    STEP(launch_prod(p, W_vals, b->V1, vis, b->H1p, hid, ncols, false, 1.f, 0.f, mode, nullptr, st));
-    STEP(launch_bias_sigmoid_sample_sum(b->H1p, hid, b->c_hid, nullptr, 0, nullptr, 0, hid, ncols, b->gc, 0, -inv, 1.f, 1, st));
-    STEP(launch_dd2dia(p, b->G_vals, b->H0p, hid, b->V0, vis, ncols, inv, 0.f, st));
-    STEP(launch_dd2dia(p, b->G_vals, b->H1p, hid, b->V1, vis, ncols, -inv, 1.f, st));
-#undef STEP
-    return CUVDIA_OK;
+    float inv = 0.f;
+    int rc = rbm_step_head(p, W_vals, b, ncols, batch_global, mode, keep_v1p, (cudaStream_t)stream, &inv);
+    if (rc) return rc;
+    return launch_dd2dia(p, b->G_vals, b->H1p, p->h, b->V1, p->w, ncols, -inv, 1.f, (cudaStream_t)stream);
 }
 
-int cuvdia_allreduce_grad(void* nccl_comm, float* G_vals, long long n_g, float* bias_grad, long long n_bias,
-                          void* stream) {
-    CUVDIA_REQUIRE(nccl_comm != nullptr);
-    CUVDIA_REQUIRE(n_g >= 0 && n_bias >= 0);
-    CUVDIA_REQUIRE(n_g == 0 || G_vals != nullptr);
-    CUVDIA_REQUIRE(n_bias == 0 || bias_grad != nullptr);
-    const NcclApi* n = need_nccl();
-    if (!n) return CUVDIA_ERR_UNSUPPORTED;
-    ncclComm_t comm = (ncclComm_t)nccl_comm;
-    cudaStream_t st = (cudaStream_t)stream;
+static int allreduce_two(const NcclApi* n, ncclComm_t comm, float* G_vals, long long n_g, float* bias_grad, long long n_bias,
+                         cudaStream_t st) {
     if (n_g > 0 && n_bias > 0 && bias_grad == G_vals + n_g) {
         // one buffer: one collective
         CUVDIA_NCCL(n, n->AllReduce(G_vals, G_vals, (size_t)(n_g + n_bias), kNcclFloat32, kNcclSum, comm, st));
@@ -142,6 +116,102 @@ int cuvdia_allreduce_grad(void* nccl_comm, float* G_vals, long long n_g, float* 
     if (r2) return nccl_fail(n, r2, "ncclAllReduce(bias gradients)");
     if (r3) return nccl_fail(n, r3, "ncclGroupEnd");
     return CUVDIA_OK;
+}
+
+int cuvdia_rbm_cd1_step_allreduce_f32(cuvdia_plan* p, const float* W_vals, const cuvdia_rbm_cd1_buffers* b, int ncols,
+                                      int batch_global, int mode, int keep_v1p, int overlap, void* nccl_comm,
+                                      void* stream) {
+    CUVDIA_REQUIRE(nccl_comm != nullptr);
+    CUVDIA_REQUIRE(overlap >= 0 && overlap <= 2);
+    const NcclApi* n = need_nccl();
+    if (!n) return CUVDIA_ERR_UNSUPPORTED;
+    ncclComm_t comm = (ncclComm_t)nccl_comm;
+    cudaStream_t st = (cudaStream_t)stream;
+    float inv = 0.f;
+    int rc = rbm_step_head(p, W_vals, b, ncols, batch_global, mode, keep_v1p, st, &inv);
+    if (rc) return rc;
+    const long long n_g = (long long)p->nd * p->stride, n_bias = (long long)p->h + p->w;
+    float* bias = b->gc;                                  // gc then gb: one array when gb follows gc
+    const bool bias_one = b->gb == b->gc + p->h;
+    // Cut the call that completes G in two launches by column tiles when that costs no wave of blocks: the diagonals
+    // the first launch completes are summed over the ranks on a side stream while the second launch computes.
+    int first_diagonals = 0;
+    const int cut = (overlap > 0 && bias_one && dd2dia_band_applicable(p, b->H1p, p->h, b->V1, p->w, ncols) &&
+                     !dd2dia_stream_applicable(p, b->G_vals, b->H1p, p->h, b->V1, p->w, ncols) &&
+                     (overlap == 2 || dd2dia_band_nsplit(p, ncols) == 1))
+                        ? dd2dia_band_cut(p, ncols, &first_diagonals, overlap == 2) : 0;
+    if (cut <= 0) {
+        rc = launch_dd2dia(p, b->G_vals, b->H1p, p->h, b->V1, p->w, ncols, -inv, 1.f, st);
+        if (rc) return rc;
+        if (bias_one) return allreduce_two(n, comm, b->G_vals, n_g, bias, n_bias, st);
+        rc = allreduce_two(n, comm, b->G_vals, n_g, b->gc, p->h, st);
+        if (rc) return rc;
+        CUVDIA_NCCL(n, n->AllReduce(b->gb, b->gb, (size_t)p->w, kNcclFloat32, kNcclSum, comm, st));
+        return CUVDIA_OK;
+    }
+    if (!p->side_stream) {
+        int lo = 0, hi = 0;
+        CUVDIA_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));       // hi = numerically lowest = highest priority
+        CUVDIA_CUDA(cudaStreamCreateWithPriority(&p->side_stream, cudaStreamNonBlocking, hi));
+        CUVDIA_CUDA(cudaEventCreateWithFlags(&p->ev_first, cudaEventDisableTiming));
+        CUVDIA_CUDA(cudaEventCreateWithFlags(&p->ev_side, cudaEventDisableTiming));
+    }
+    rc = launch_dd2dia_band_range(p, b->G_vals, b->H1p, p->h, b->V1, p->w, ncols, -inv, 1.f, 0, cut, st);
+    if (rc) return rc;
+    CUVDIA_CUDA(cudaEventRecord(p->ev_first, st));
+    CUVDIA_CUDA(cudaStreamWaitEvent(p->side_stream, p->ev_first, 0));
+    const long long n_first = (long long)first_diagonals * p->stride;
+    CUVDIA_NCCL(n, n->AllReduce(b->G_vals, b->G_vals, (size_t)n_first, kNcclFloat32, kNcclSum, comm, p->side_stream));
+    rc = launch_dd2dia_band_range(p, b->G_vals, b->H1p, p->h, b->V1, p->w, ncols, -inv, 1.f, cut, -1, st);
+    if (rc) return rc;
+    // the rest of the diagonals and, behind them in the same buffer or on its own, the bias gradients
+    const bool tail_one = bias == b->G_vals + n_g;
+    CUVDIA_NCCL(n, n->AllReduce(b->G_vals + n_first, b->G_vals + n_first, (size_t)(n_g - n_first + (tail_one ? n_bias : 0)),
+                                kNcclFloat32, kNcclSum, comm, st));
+    if (!tail_one) CUVDIA_NCCL(n, n->AllReduce(bias, bias, (size_t)n_bias, kNcclFloat32, kNcclSum, comm, st));
+    CUVDIA_CUDA(cudaEventRecord(p->ev_side, p->side_stream));
+    CUVDIA_CUDA(cudaStreamWaitEvent(st, p->ev_side, 0));
+    return CUVDIA_OK;
+}
+
+static int rbm_step_head(cuvdia_plan* p, const float* W_vals, const cuvdia_rbm_cd1_buffers* b, int ncols, int batch_global,
+                         int mode, int keep_v1p, cudaStream_t st, float* inv_out) {
+    CUVDIA_REQUIRE(p != nullptr && W_vals != nullptr && b != nullptr);
+    CUVDIA_REQUIRE(p->rf == 1);                        // the trainer's weight matrix (row factors belong to other layers)
+    CUVDIA_REQUIRE(ncols > 0 && batch_global >= ncols);
+    CUVDIA_REQUIRE(mode == CUVDIA_MODE_EXACT || mode == CUVDIA_MODE_FAST);
+    CUVDIA_REQUIRE(b->V0 && b->U_h && b->U_v);
+    CUVDIA_REQUIRE(b->H0p && b->H0 && b->V1p && b->V1 && b->H1p);
+    CUVDIA_REQUIRE(b->G_vals && b->gc && b->gb);
+    int dev = -1;
+    CUVDIA_REQUIRE(cudaGetDevice(&dev) == cudaSuccess && dev == p->device);
+    const int hid = p->h, vis = p->w;
+    const float inv = (float)(1.0 / (double)batch_global);
+    *inv_out = inv;
+    int rc;
+#define STEP(call) do { rc = (call); if (rc) return rc; } while (0)
+    STEP(launch_reduce(b->gb, b->V0, vis, ncols, true, CUVDIA_RF_ADD, inv, 0.f, st));
+    STEP(launch_prod(p, W_vals, b->V0, vis, b->H0p, hid, ncols, false, 1.f, 0.f, mode, nullptr, st));
+    STEP(launch_bias_sigmoid_sample_sum(b->H0p, hid, b->c_hid, b->U_h, hid, b->H0, hid, hid, ncols, b->gc, 0, inv, 0.f, 1, st));
+    STEP(launch_prod(p, W_vals, b->H0, hid, b->V1p, vis, ncols, true, 1.f, 0.f, mode, nullptr, st));
+    STEP(launch_bias_sigmoid_sample_sum(b->V1p, vis, b->b_vis, b->U_v, vis, b->V1, vis, vis, ncols, b->gb, 1, -inv, 1.f,
+                                        keep_v1p ? 1 : 0, st));
+    STEP(launch_prod(p, W_vals, b->V1, vis, b->H1p, hid, ncols, false, 1.f, 0.f, mode, nullptr, st));
+    STEP(launch_bias_sigmoid_sample_sum(b->H1p, hid, b->c_hid, nullptr, 0, nullptr, 0, hid, ncols, b->gc, 0, -inv, 1.f, 1, st));
+    STEP(launch_dd2dia(p, b->G_vals, b->H0p, hid, b->V0, vis, ncols, inv, 0.f, st));
+#undef STEP
+    return CUVDIA_OK;
+}
+
+int cuvdia_allreduce_grad(void* nccl_comm, float* G_vals, long long n_g, float* bias_grad, long long n_bias,
+                          void* stream) {
+    CUVDIA_REQUIRE(nccl_comm != nullptr);
+    CUVDIA_REQUIRE(n_g >= 0 && n_bias >= 0);
+    CUVDIA_REQUIRE(n_g == 0 || G_vals != nullptr);
+    CUVDIA_REQUIRE(n_bias == 0 || bias_grad != nullptr);
+    const NcclApi* n = need_nccl();
+    if (!n) return CUVDIA_ERR_UNSUPPORTED;
+    return allreduce_two(n, (ncclComm_t)nccl_comm, G_vals, n_g, bias_grad, n_bias, (cudaStream_t)stream);
 }
 
 int cuvdia_nccl_unique_id(char id128[128]) {

@@ -85,7 +85,19 @@ class SparseRBMStep:
         self.forward(V0, U_h, U_v)
         self.gradients(V0)
 
-    def _step_c(self, V0, U_h, U_v):
+    def step_allreduce(self, V0, U_h, U_v, group=None, overlap=1):
+        """step() followed by allreduce() as one call of the C ABI (``cuvdia_rbm_cd1_step_allreduce_f32``): the
+        all-reduce of the diagonals that the step's last kernel completes first runs while that kernel finishes the
+        rest.  Same results as the two separate calls.  ``overlap``: 0 never, 1 when cutting the kernel's grid in two
+        costs no wave of blocks, 2 whenever the tiled kernel applies."""
+        if self._reducer is None:
+            self._reducer = GradientAllReduce(self.dev, group)
+        if self.timers is not None or self.bias_sums != "glue":
+            self.step(V0, U_h, U_v)
+            return self.allreduce(group)
+        self._step_c(V0, U_h, U_v, comm=self._reducer.comm, overlap=overlap)
+
+    def _step_c(self, V0, U_h, U_v, comm=None, overlap=1):
         """The whole step as one call of the C ABI."""
         import ctypes
         from . import _capi
@@ -95,6 +107,11 @@ class SparseRBMStep:
         p = lambda t: t.data_ptr()
         buf = _capi.RbmCd1Buffers(p(V0), p(U_h), p(U_v), p(self.b_vis), p(self.c_hid), p(self.H0p), p(self.H0),
                                   p(self.V1p), p(self.V1), p(self.H1p), p(self.G.vec), p(self.gc), p(self.gb))
+        if comm is not None:
+            _capi.check(_capi.lib().cuvdia_rbm_cd1_step_allreduce_f32(
+                self.W._plan, cb._ptr(self.W.vec), ctypes.byref(buf), self.nb, self.B, self.mode,
+                1 if self.keep_v1p else 0, int(overlap), comm, cb._stream()))
+            return
         _capi.check(_capi.lib().cuvdia_rbm_cd1_step_f32(self.W._plan, cb._ptr(self.W.vec), ctypes.byref(buf), self.nb,
                                                         self.B, self.mode, 1 if self.keep_v1p else 0, cb._stream()))
 

@@ -307,6 +307,21 @@ CUVDIA_API int cuvdia_rbm_cd1_step_f32(cuvdia_plan* plan, const float* W_vals, c
 CUVDIA_API int cuvdia_allreduce_grad(void* nccl_comm, float* G_vals, long long n_g, float* bias_grad, long long n_bias,
                                      void* stream);
 
+/* cuvdia_rbm_cd1_step_f32 and cuvdia_allreduce_grad in one call, with part of the collective hidden under the
+ * step's last kernel: when G is a band computed by the tiled kernel and cutting that call in two launches by column
+ * tiles costs no wave of blocks, the diagonals the first launch completes (a contiguous slab of G_vals) are summed over
+ * the ranks on a side stream of the plan (highest priority) while the second launch computes; the rest of G_vals and
+ * the bias gradients follow on `stream`, which then waits for the side stream.  Otherwise it is exactly the two
+ * separate calls.  overlap: 0 = never cut (the two separate calls), 1 = cut when it is free, 2 = cut whenever the
+ * tiled kernel computes G with at least three column tiles (also with a batch that would otherwise be split: the cut
+ * launches are not split).  Results equal those of the two separate calls up to the batch-sum tolerance, and bit for
+ * bit when the uncut call would not split the batch (the same sums).  gc and gb should be one array (gb == gc + h), as
+ * should G_vals and gc (gc == G_vals + num_dia*stride), for one collective per part.  Every rank must make the same
+ * sequence of calls with the same arguments.  No counterpart in CUV. */
+CUVDIA_API int cuvdia_rbm_cd1_step_allreduce_f32(cuvdia_plan* plan, const float* W_vals,
+                                                 const cuvdia_rbm_cd1_buffers* buffers, int ncols, int batch_global,
+                                                 int mode, int keep_v1p, int overlap, void* nccl_comm, void* stream);
+
 /* For callers without a communicator of their own: ncclGetUniqueId on one rank (128 bytes, to be sent
  * to the others by whatever means the application has), then ncclCommInitRank on every rank with its
  * device current (blocking, collective), and ncclCommDestroy. */

@@ -56,6 +56,29 @@ def _rank_main(rank, world, port, out_dir):
     rbm.allreduce_gradients(st.G.vec, st.bias_grad)
     torch.cuda.synchronize()
     np.save(os.path.join(out_dir, "t%d.npy" % rank), st.G.vec.cpu().numpy())
+    # and the one-call form that hides part of the collective under the step's last kernel
+    st.grad_buf.zero_()
+    st.step_allreduce(sl(V0), sl(U_h), sl(U_v))
+    torch.cuda.synchronize()
+    np.save(os.path.join(out_dir, "o%d.npy" % rank), st.grad_buf.cpu().numpy())
+    assert cb.plan_status(Wd) == 0
+    # the cut itself (forced: at this size it would cost a wave of blocks) on a band of five column tiles
+    offs5 = np.arange(-256, 256, dtype=np.int32)
+    W5, V5, Uh5, Uv5 = rbm_oracle.make_inputs(SEED + 1, UNITS, UNITS, offs5, B, w_std=0.02, nthreads=4)
+    W5d = cb.dev_dia_matrix_f(W5.h, W5.w, W5.offsets, W5.stride, W5.rf, device=dev).set_vec(W5.vals)
+    s5 = rbm.SparseRBMStep(W5d, c1 - c0, B, cb.MODE_EXACT, dev)
+    s5._reducer = st._reducer
+    s5.grad_buf.fill_(float("nan"))          # cells outside the diagonals' ranges are never written: they stay NaN
+    s5.step(sl(V5), sl(Uh5), sl(Uv5))
+    s5.allreduce()
+    torch.cuda.synchronize()
+    plain = s5.grad_buf.cpu().numpy().copy()
+    for _ in range(2):
+        s5.grad_buf.fill_(float("nan"))
+        s5.step_allreduce(sl(V5), sl(Uh5), sl(Uv5), overlap=2)
+        torch.cuda.synchronize()
+        np.save(os.path.join(out_dir, "c%d.npy" % rank), np.stack([plain, s5.grad_buf.cpu().numpy()]))
+    assert cb.plan_status(W5d) == 0
     st._reducer.close()
     dist.destroy_process_group()
 
@@ -74,6 +97,12 @@ def test_two_gpu_step_and_nccl_sum_equal_the_unsharded_step(tmp_path):
     b = [np.load(tmp_path / ("b%d.npy" % r)) for r in range(world)]
     assert np.array_equal(g[0], g[1]) and np.array_equal(b[0], b[1])         # every rank holds the same sum
     assert np.array_equal(np.load(tmp_path / "t0.npy"), g[0])
+    for r in range(world):                                                    # the overlapped form: the same bits
+        assert np.array_equal(np.load(tmp_path / ("o%d.npy" % r)), np.concatenate([g[r], b[r]]))
+    for r in range(world):                                                    # ... also when the last kernel is cut in two
+        plain, cut = np.load(tmp_path / ("c%d.npy" % r))
+        m5 = np.isfinite(plain)
+        assert np.array_equal(np.isfinite(cut), m5) and np.array_equal(cut[m5], plain[m5])
     # against the unsharded step on one GPU
     Wd = cb.dev_dia_matrix_f(W.h, W.w, W.offsets, W.stride, W.rf).set_vec(W.vals)
     full = rbm.SparseRBMStep(Wd, B, B, cb.MODE_EXACT)
