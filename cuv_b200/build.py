@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libcuvdia.so")
-SOURCES = ["api.cu", "dispatch.cu", "prod_generic.cu", "prod_band.cu", "prod_bandw.cu", "prod_window.cu", "prod_narrow.cu", "prod_runs.cu", "dd2dia_generic.cu", "dd2dia_band.cu", "dd2dia_stream.cu", "dd2dia_window.cu", "reduce.cu", "diagonals.cu", "reduce_typed.cu", "glue.cu", "rbm_step.cu", "selftest.cu"]
+SOURCES = ["api.cu", "dispatch.cu", "prod_generic.cu", "prod_band.cu", "prod_bandw.cu", "prod_window.cu", "prod_windown.cu", "prod_narrow.cu", "prod_runs.cu", "dd2dia_generic.cu", "dd2dia_band.cu", "dd2dia_stream.cu", "dd2dia_window.cu", "reduce.cu", "diagonals.cu", "reduce_typed.cu", "glue.cu", "rbm_step.cu", "selftest.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--fmad=false",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "-I", os.path.join(ROOT, "include"), "-I", CSRC]
 

@@ -126,7 +126,7 @@ int cuvdia_plan_create(cuvdia_plan** out, int h, int w, int num_dia, int stride,
     if (!p) { set_last_error("host allocation failed"); return CUVDIA_ERR_NOMEM; }
     p->h = h; p->w = w; p->nd = num_dia; p->stride = stride; p->rf = row_fact;
     p->offsets.assign(offsets_host, offsets_host + num_dia);
-    p->d_offsets = nullptr; p->scratch = nullptr; p->scratch_floats = 0; p->d_status = nullptr; p->d_passes = nullptr; p->d_sorted = nullptr;
+    p->d_offsets = nullptr; p->scratch = nullptr; p->scratch_floats = 0; p->d_status = nullptr; p->d_passes = nullptr; p->d_sorted = nullptr; p->d_witems = nullptr;
     p->side_stream = nullptr; p->ev_first = nullptr; p->ev_side = nullptr;
     p->is_band = true;
     for (int k = 1; k < num_dia; k++) if (p->offsets[k] != p->offsets[0] + k) { p->is_band = false; break; }
@@ -160,20 +160,22 @@ int cuvdia_plan_create(cuvdia_plan** out, int h, int w, int num_dia, int stride,
     std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return p->offsets[a] < p->offsets[b]; });
     std::vector<int> sorted(2 * (size_t)num_dia);
     for (int k = 0; k < num_dia; k++) { sorted[k] = order[k]; sorted[num_dia + k] = p->offsets[order[k]]; }
-    for (int v = 0; v < 2; v++) {
-        const int kg = v == 0 ? 16 : 32;
-        p->group_window_max[v] = 0;
-        for (int g = 0; g < num_dia; g += kg) {
-            const int last = std::min(num_dia, g + kg) - 1;
-            p->group_window_max[v] = std::max(p->group_window_max[v], sorted[num_dia + last] - sorted[num_dia + g] + 1);
-        }
-    }
-    p->d_sorted = nullptr;
+    std::vector<int> witems;
+    window_items(h, w, num_dia, row_fact, sorted.data() + num_dia, &witems);
+    p->n_witems = (int)(witems.size() / 3);
+    p->witem_diagonals = 0;
+    for (int t = 0; t < p->n_witems; t++) p->witem_diagonals += witems[3 * t + 2];
+    p->d_sorted = nullptr; p->d_witems = nullptr;
     cudaError_t e = cudaGetDevice(&p->device);
     if (e == cudaSuccess) e = cudaMalloc(&p->d_offsets, sizeof(int) * (size_t)num_dia);
     if (e == cudaSuccess) e = cudaMalloc(&p->d_sorted, sizeof(int) * sorted.size());
     if (e == cudaSuccess)
         e = cudaMemcpy(p->d_sorted, sorted.data(), sizeof(int) * sorted.size(), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess && p->n_witems > 0) {
+        e = cudaMalloc(&p->d_witems, sizeof(int) * witems.size());
+        if (e == cudaSuccess)
+            e = cudaMemcpy(p->d_witems, witems.data(), sizeof(int) * witems.size(), cudaMemcpyHostToDevice);
+    }
     if (e == cudaSuccess && p->is_runs) {
         e = cudaMalloc(&p->d_passes, sizeof(int) * passes.size());
         if (e == cudaSuccess)
@@ -188,6 +190,7 @@ int cuvdia_plan_create(cuvdia_plan** out, int h, int w, int num_dia, int stride,
         if (p->d_status) cudaFree(p->d_status);
         if (p->d_passes) cudaFree(p->d_passes);
         if (p->d_sorted) cudaFree(p->d_sorted);
+        if (p->d_witems) cudaFree(p->d_witems);
         delete p;
         return cuda_fail(e, "cuvdia_plan_create");
     }
@@ -202,6 +205,7 @@ int cuvdia_plan_destroy(cuvdia_plan* p) {
     if (p->d_status) cudaFree(p->d_status);
     if (p->d_passes) cudaFree(p->d_passes);
     if (p->d_sorted) cudaFree(p->d_sorted);
+    if (p->d_witems) cudaFree(p->d_witems);
     if (p->ev_first) cudaEventDestroy(p->ev_first);
     if (p->ev_side) cudaEventDestroy(p->ev_side);
     if (p->side_stream) cudaStreamDestroy(p->side_stream);

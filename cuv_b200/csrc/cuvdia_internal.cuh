@@ -82,7 +82,11 @@ struct cuvdia_plan {
     // the diagonals in ascending order of their offsets: nd storage slots followed by nd offsets (device), and the
     // largest number of dense rows that 16 ([0]) and 32 ([1]) neighbours in that order span
     int* d_sorted;
-    int group_window_max[2];
+    // the windowed densedense_to_dia's list of (row tile, group of neighbouring diagonals) pairs, three ints each
+    // (device), their number and the diagonals they hold in total
+    int* d_witems;
+    int n_witems;
+    long long witem_diagonals;
     // side stream (highest priority) and events of the step that overlaps its all-reduce; created on first use
     cudaStream_t side_stream;
     cudaEvent_t ev_first, ev_side;
@@ -119,6 +123,10 @@ int launch_prod_narrow(const cuvdia_plan* p, const float* A, const float* B, int
 bool prod_runs_applicable(const cuvdia_plan* p, const float* A, const float* B, int ldb);
 int launch_prod_runs(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
                      bool trans, float factAB, float factC, int mode, cudaStream_t st);
+// the staged-window kernel for row factor 1 with a lean inner loop (prod_windown.cu)
+bool prod_windown_applicable(const cuvdia_plan* p, bool trans, const float* A, const float* B, int ldb, int ncols);
+int launch_prod_windown(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
+                        bool trans, float factAB, float factC, int mode, cudaStream_t st);
 bool prod_window_applicable(const cuvdia_plan* p, bool trans, int ncols);
 int launch_prod_window(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
                        bool trans, float factAB, float factC, int mode, cudaStream_t st);
@@ -136,6 +144,8 @@ int launch_dd2dia_window(cuvdia_plan* p, float* Cv, const float* A, int lda, con
 bool dd2dia_band_applicable(const cuvdia_plan* p, const float* A, int lda, const float* B, int ldb, int ncols);
 int launch_dd2dia_band(cuvdia_plan* p, float* Cv, const float* A, int lda, const float* B, int ldb, int ncols,
                        float factAB, float factC, cudaStream_t st);
+// the (row tile, diagonal group) pairs of the windowed densedense_to_dia (see dd2dia_window.cu)
+void window_items(int h, int w, int nd, int rf, const int* sorted_off, std::vector<int>* items);
 // the banded densedense_to_dia cut in two launches by column tiles (see dd2dia_band.cu)
 int dd2dia_band_cut(const cuvdia_plan* p, int ncols, int* first_diagonals, bool force);
 int dd2dia_band_nsplit(const cuvdia_plan* p, int ncols);

@@ -19,6 +19,8 @@ int launch_prod(const cuvdia_plan* p, const float* A, const float* B, int ldb, f
         rc = launch_prod_bandw(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);
     else if (runs)
         rc = launch_prod_runs(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);
+    else if (prod_windown_applicable(p, trans, A, B, ldb, ncols))
+        rc = launch_prod_windown(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);
     else if (prod_window_applicable(p, trans, ncols))
         rc = launch_prod_window(p, A, B, ldb, C, ldc, ncols, trans, factAB, factC, mode, st);
     else

@@ -39,7 +39,7 @@ template <bool TRANS, bool EXACT, int T, int CB>
 __global__ void __launch_bounds__(T)
 prod_window_kernel(const WindowParams P) {
     extern __shared__ __align__(16) float win[];        // [CB][pitch]
-    __shared__ int s_off[pw::OFFS];
+    __shared__ int s_off[pw::OFFS + 8];
     const int tid = threadIdx.x;
     const int o0 = blockIdx.x * T * P.tiles;            // first output row of the block
     const int c0 = blockIdx.y * CB;
@@ -101,41 +101,62 @@ prod_window_kernel(const WindowParams P) {
         if (P.fc != 0.f && row_ok && c0 + c < P.ncols) acc[c] = __fmul_rn(P.C[(size_t)(c0 + c) * P.ldc + o], P.fc);
     }
     const int oq = TRANS ? o : (row_ok ? o / rf : 0);
+    const int oqs = row_ok ? oq : -(1 << 29);            // 'n': a row past the end makes every term fall outside the matrix
     for (int kb = 0; kb < P.nd; kb += pw::OFFS) {
         const int kn = min(pw::OFFS, P.nd - kb);
         __syncthreads();                               // window staged / previous offsets consumed
-        for (int t = tid; t < kn; t += T) s_off[t] = P.offs[kb + t];
+        // places past the pass's last diagonal hold an offset that no row can use
+        for (int t = tid; t < kn + 8; t += T) s_off[t] = t < kn ? P.offs[kb + t] : -(1 << 29);
         __syncthreads();
         if (!TRANS) {
             // term of diagonal k: A[k][o] * B[o/rf + off_k].  The coefficients of the next eight diagonals are
-            // fetched while the current eight are consumed.
+            // fetched while the current eight are consumed.  A term whose cell lies outside the matrix (spmv.cu:185-189)
+            // carries a negative window position and is skipped; rows past the end of the matrix and the places past
+            // the last diagonal of a pass are such terms too (oqs and the padded offsets see to that), so that the
+            // loop needs no other test.
             constexpr int U = 8;
             float a[U], an[U];
             int pos[U], posn[U];
-            bool ok[U], okn[U];
-            auto fetch = [&](int kk, float (&av)[U], int (&pv)[U], bool (&ov)[U]) {
+            const float* Ao = P.A + (size_t)kb * P.S + o;
+            auto fetch = [&](int kk, float (&av)[U], int (&pv)[U]) {
 #pragma unroll
                 for (int u = 0; u < U; u++) {
-                    const int k = kk + u;
-                    const int j = oq + (k < kn ? s_off[k] : 0);
-                    ov[u] = row_ok && k < kn && j >= 0 && j < P.w;          // spmv.cu:185-189
-                    pv[u] = ov[u] ? j - lo : 0;
-                    av[u] = ov[u] ? __ldg(P.A + (size_t)(kb + k) * P.S + o) : 0.f;
+                    const int j = oqs + s_off[kk + u];
+                    const bool ok = (unsigned)j < (unsigned)P.w;
+                    pv[u] = ok ? j - lo : -1;
+                    av[u] = ok ? __ldg(Ao + (size_t)(kk + u) * P.S) : 0.f;
                 }
             };
-            fetch(0, an, posn, okn);
+            fetch(0, an, posn);
             for (int kk = 0; kk < kn; kk += U) {
 #pragma unroll
-                for (int u = 0; u < U; u++) { a[u] = an[u]; pos[u] = posn[u]; ok[u] = okn[u]; }
-                if (kk + U < kn) fetch(kk + U, an, posn, okn);
+                for (int u = 0; u < U; u++) { a[u] = an[u]; pos[u] = posn[u]; }
+                if (kk + U < kn) fetch(kk + U, an, posn);
 #pragma unroll
                 for (int u = 0; u < U; u++) {
-                    if (!ok[u]) continue;
+                    if (pos[u] < 0) continue;
                     const float av = (P.fa != 1.f) ? __fmul_rn(P.fa, a[u]) : a[u];
+                    const float* wp = win + pos[u];
+                    if (CB % 2 == 0) {
+                        // two columns at a time: one packed multiply (or packed fused multiply-add)
 #pragma unroll
-                    for (int c = 0; c < CB; c++) {
-                        const float x = win[c * P.pitch + pos[u]];
-                        acc[c] = EXACT ? __fadd_rn(acc[c], __fmul_rn(av, x)) : fmaf(av, x, acc[c]);
+                        for (int c = 0; c < CB; c += 2) {
+                            const float2 x = make_float2(wp[c * P.pitch], wp[(c + 1) * P.pitch]);
+                            if (EXACT) {
+                                const float2 pr = __fmul2_rn(make_float2(av, av), x);
+                                acc[c] = __fadd_rn(acc[c], pr.x);
+                                acc[c + 1] = __fadd_rn(acc[c + 1], pr.y);
+                            } else {
+                                const float2 r = __ffma2_rn(make_float2(av, av), x, make_float2(acc[c], acc[c + 1]));
+                                acc[c] = r.x; acc[c + 1] = r.y;
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < CB; c++) {
+                            const float x = wp[c * P.pitch];
+                            acc[c] = EXACT ? __fadd_rn(acc[c], __fmul_rn(av, x)) : fmaf(av, x, acc[c]);
+                        }
                     }
                 }
             }

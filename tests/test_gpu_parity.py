@@ -325,7 +325,10 @@ def test_prod_runs_ragged_and_repeated(cb, trans):
 
 # ---- densedense_to_dia -------------------------------------------------------------------------------
 
-def dd_case(cb, rng, h, w, offsets, rf, ncols, fab, fc, stride=None, dist="rbm"):
+def dd_case(cb, rng, h, w, offsets, rf, ncols, fab, fc, stride=None, dist="rbm", addend_scale=False):
+    """One densedense_to_dia call against the host loop.  addend_scale: where factC * C_old and factAB * sum nearly
+    cancel, no summation order can promise an error relative to the small result; such cells are also accepted within
+    a few units in the last place of the addends' magnitudes."""
     C = make_dia(rng, h, w, offsets, rf, stride)
     if dist == "rbm":
         X = F((rng.uniform(0, 1, (h, ncols)) < 0.5).astype(np.float32))
@@ -344,7 +347,13 @@ def dd_case(cb, rng, h, w, offsets, rf, ncols, fab, fc, stride=None, dist="rbm")
     m = C.valid_mask().reshape(-1)
     assert_bits_equal(got[~m], C.vals[~m], "cells outside the diagonals' ranges must be untouched")
     tol = 1e-4 * np.sqrt(max(ncols, 128) / 128.0)
-    np.testing.assert_allclose(got[m], want.vals[m], rtol=tol, atol=tol * 1e-3)
+    if addend_scale:
+        mag = ho.DiaHost(h, w, C.offsets, C.stride, rf, np.abs(np.nan_to_num(C.vals)))
+        ho.densedense_to_dia(mag, np.abs(X), np.abs(H), abs(fab), abs(fc), nthreads=4)
+        err = np.abs(got[m] - want.vals[m])
+        assert np.all(err <= tol * np.abs(want.vals[m]) + 8 * 2.0 ** -24 * mag.vals[m])
+    else:
+        np.testing.assert_allclose(got[m], want.vals[m], rtol=tol, atol=tol * 1e-3)
     D2 = to_dev_dia(C)
     cb.densedense_to_dia(D2, bd, Xd, Hd, fab, fc)
     assert_bits_equal(D2.vec.cpu().numpy()[m], got[m], "run-to-run reproducibility")
@@ -362,6 +371,21 @@ def test_dd2dia_scattered_windowed(cb, rf, h, w, nd, ncols, fab, fc):
     rng = np.random.default_rng(300 + rf + nd)
     offs = scattered_offsets(rng, nd, -(h // rf) + 1, w - 1, sort=False)
     dd_case(cb, rng, h, w, offs, rf, ncols, fab, fc)
+
+
+@pytest.mark.parametrize("h,w,ncols", [(4096, 4096, 200), (2500, 3000, 70)])
+def test_dd2dia_scattered_groups_outside_the_matrix(cb, h, w, ncols):
+    """Tiles of 512 rows and offsets spread over the whole matrix: for most tiles some of the diagonals lie wholly
+    outside the matrix and are never scheduled, the groups of neighbours start at a different diagonal for every tile,
+    and two clusters of offsets far apart cut a group short.  Every cell inside the matrix still gets its sum, every
+    other cell stays as it was."""
+    rng = np.random.default_rng(h + ncols)
+    spread = scattered_offsets(rng, 96, -h + 1, w - 1, sort=False)
+    clusters = np.concatenate([np.arange(-1500, -1500 + 3 * 7, 3), np.arange(900, 900 + 2 * 9, 2)]).astype(np.int32)
+    offs = np.unique(np.concatenate([spread, clusters])).astype(np.int32)
+    rng.shuffle(offs)
+    dd_case(cb, rng, h, w, offs, 1, ncols, 0.01, 0.9, addend_scale=True)
+    dd_case(cb, rng, h, w, offs, 1, ncols, 1.0, 0.0, dist="uniform")
 
 
 def test_dd2dia_convolution_pattern(cb):
