@@ -258,27 +258,39 @@ def binding_bound(byts, flops, ms, hbm_peak, fp32_peak):
             "hbm_frac": t_mem / t, "fp32_frac": t_fp / t}
 
 
-def shard_inputs(cb, torch, units, nb, dev, shard):
-    """The batch columns of shard ``shard`` of the global batch: V0 ~ Bernoulli(0.3), U_h, U_v ~ U[0,1).  Every
-    shard has its own seed, so any rank can rebuild any other rank's columns (the unsharded check does)."""
+DRAW_SEED = 20260711
+
+
+def shard_inputs(cb, torch, units, nb, dev, shard, uniforms=True):
+    """The batch columns of shard ``shard`` of the global batch: V0 ~ Bernoulli(0.3) from the shard's own seed, so any
+    rank can rebuild any other rank's columns (the unsharded check does); U_h, U_v = the uniform numbers in [0, 1) that
+    the device-drawn step draws for those columns in step 0 (cuvdia_uniform_f32), so the step that reads them from
+    memory and the step that draws them compute the same thing."""
     gen = torch.Generator(device=dev)
     gen.manual_seed(2000 + shard)
     V0 = cb.colmajor_empty(units, nb, dev)
     tmp = torch.rand((nb, units), device=dev, generator=gen)
     V0.t().copy_((tmp < 0.3).float())
+    del tmp
+    if not uniforms:
+        return V0, None, None
     U_h, U_v = cb.colmajor_empty(units, nb, dev), cb.colmajor_empty(units, nb, dev)
-    U_h.t().copy_(torch.rand((nb, units), device=dev, generator=gen))
-    U_v.t().copy_(torch.rand((nb, units), device=dev, generator=gen))
+    cb.fill_rnd_uniform(U_h, DRAW_SEED, 0, shard * nb, 0)
+    cb.fill_rnd_uniform(U_v, DRAW_SEED, 0, shard * nb, 1)
     return V0, U_h, U_v
 
 
-def check_allreduce(cb, rbm, torch, dist, step, V0, U_h, U_v, W, units, nd, batch, world, rank, dev, mode):
+def check_allreduce(cb, rbm, torch, dist, step, V0, U_h, U_v, W, units, nd, batch, world, rank, dev, mode, drawn):
     """Outside every timed region: (1) three diagonals (first, middle, last) of the all-reduced gradient against the
     rank-order sum of the per-rank partial values gathered to rank 0; (2) on rank 0, the whole all-reduced gradient and
     the bias gradients against the unsharded step on the full batch (all shards rebuilt from their seeds)."""
     stride = W.stride
     some = [0, nd // 2, nd - 1]
-    step.step(V0, U_h, U_v)
+    nb = batch // world
+    if drawn:
+        step.step_drawn(V0, DRAW_SEED, 0, rank * nb)
+    else:
+        step.step(V0, U_h, U_v)
     part = torch.cat([step.G.vec[k * stride:(k + 1) * stride] for k in some]).clone()
     parts = [torch.empty_like(part) for _ in range(world)] if rank == 0 else None
     dist.gather(part, parts, dst=0)
@@ -291,12 +303,16 @@ def check_allreduce(cb, rbm, torch, dist, step, V0, U_h, U_v, W, units, nd, batc
     for q in parts[1:]:
         want += q
     d1 = float((got - want).abs().max().item())
-    full_in = [shard_inputs(cb, torch, units, batch // world, dev, s) for s in range(world)]
+    full_in = [shard_inputs(cb, torch, units, nb, dev, s, uniforms=not drawn) for s in range(world)]
     cat = lambda k: torch.cat([f[k].t() for f in full_in], dim=0).t()        # column blocks side by side
-    FV0, FUh, FUv = cat(0), cat(1), cat(2)
+    FV0 = cat(0)
+    FUh, FUv = (None, None) if drawn else (cat(1), cat(2))
     del full_in
     full = rbm.SparseRBMStep(W, batch, batch, mode, dev)
-    full.step(FV0, FUh, FUv)
+    if drawn:
+        full.step_drawn(FV0, DRAW_SEED, 0, 0)      # the unsharded run draws what the shards drew (col0 = rank * nb)
+    else:
+        full.step(FV0, FUh, FUv)
     torch.cuda.synchronize()
     d2 = float((step.G.vec - full.G.vec).abs().max().item())
     d3 = float((step.bias_grad - full.bias_grad).abs().max().item())
@@ -345,6 +361,8 @@ def run_ours(args, cfg):
     gen.manual_seed(1004)                      # identical weights on every rank
     W = cb.dev_dia_matrix_f(units, units, band_offsets(nd), units, 1, device=dev)
     W.vec.normal_(0.0, 0.01, generator=gen)
+    drawn = args.uniforms == "drawn"
+    col0 = rank * nb
     V0, U_h, U_v = shard_inputs(cb, torch, units, nb, dev, rank)        # this rank's batch columns
     step = rbm.SparseRBMStep(W, nb, batch, mode, dev, keep_v1p=False)
     # The metric counts the GLOBAL problem's algorithmic bytes at every N (strong scaling: value_N / value_1 is the
@@ -352,11 +370,17 @@ def run_ours(args, cfg):
     work = rbm.algorithmic_work(units, units, nd, W.nnz, batch)
     local_work = rbm.algorithmic_work(units, units, nd, W.nnz, nb)
 
-    def one_step():
-        if world > 1:
-            step.step_allreduce(V0, U_h, U_v)  # one call of the C ABI: cuvdia_rbm_cd1_step_allreduce_f32
+    def one_step(i=0, drawn=drawn):
+        # one call of the C ABI: cuvdia_rbm_cd1_step[_drawn][_allreduce]_f32
+        if drawn:
+            if world > 1:
+                step.step_drawn_allreduce(V0, DRAW_SEED, i, col0)
+            else:
+                step.step_drawn(V0, DRAW_SEED, i, col0)
+        elif world > 1:
+            step.step_allreduce(V0, U_h, U_v)
         else:
-            step.step(V0, U_h, U_v)            # one call of the C ABI: cuvdia_rbm_cd1_step_f32
+            step.step(V0, U_h, U_v)
 
     def barrier():
         torch.cuda.synchronize()
@@ -380,19 +404,36 @@ def run_ours(args, cfg):
     launches0 = cb.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
-        one_step()
+    for i in range(args.steps):
+        one_step(i)
     e1.record()
     barrier()
     launches = cb.launch_count() - launches0
     clocks = sampler.stop()
     ms_total = max_over_ranks(e0.elapsed_time(e1))
     ms_step = ms_total / args.steps
+    host_uniforms = None
+    if drawn:
+        # for the record: the same step with the uniform numbers read from tensors resident in HBM
+        for _ in range(2):
+            one_step(0, False)
+        barrier()
+        h0, h1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        h0.record()
+        for _ in range(args.steps):
+            one_step(0, False)
+        h1.record()
+        barrier()
+        host_uniforms = {"ms_per_step": max_over_ranks(h0.elapsed_time(h1)) / args.steps}
 
     # ---- the same kernels call by call with an event pair around each (outside the timed region) ----
     step.timers = {}
-    for _ in range(3):
-        step.step(V0, U_h, U_v)
+    for i in range(3):
+        if drawn:
+            step.forward(V0, None, None, draw=(DRAW_SEED, i, col0))
+            step.gradients(V0)
+        else:
+            step.step(V0, U_h, U_v)
     torch.cuda.synchronize()
     op_ms = {k: statistics.mean(event_ms(v)) for k, v in step.timers.items()}
     step.timers = None
@@ -413,67 +454,81 @@ def run_ours(args, cfg):
         hG = torch.empty(step.G.vec.numel(), dtype=torch.float32, pin_memory=True) if rank == 0 else None
         hb = torch.empty(step.bias_grad.numel(), dtype=torch.float32, pin_memory=True) if rank == 0 else None
 
-        fed = rbm.HostFedRBM(step, allreduce=world > 1)
+        def measure_e2e(drawn_inputs):
+            fed = rbm.HostFedRBM(step, allreduce=world > 1, draw=(DRAW_SEED, col0) if drawn_inputs else None)
+            host_in = (hV0,) if drawn_inputs else (hV0, hUh, hUv)
 
-        def e2e_steps(k):
-            # copies of step i+1 overlap the compute of step i; every step's inputs cross PCIe inside the region
-            fed.submit(hV0, hUh, hUv)
-            for i in range(k):
-                if i + 1 < k:
-                    fed.submit(hV0, hUh, hUv)
+            def e2e_steps(k):
+                # copies of step i+1 overlap the compute of step i; every step's inputs cross PCIe inside the region
+                fed.submit(*host_in)
+                for i in range(k):
+                    if i + 1 < k:
+                        fed.submit(*host_in)
+                    fed.run(hG, hb) if rank == 0 else fed.run()
+                fed.wait()
+
+            e2e_steps(2)
+            barrier()
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            e2e_steps(args.steps)
+            a1.record()
+            barrier()
+            e2e_ms = max_over_ranks(a0.elapsed_time(a1)) / args.steps
+            # For the record, the same loop with the pipeline already primed: the region starts when the first step's
+            # inputs are on the device and contains one input copy (for the following step) and one read-back per step.
+            fed.submit(*host_in)
+            fed.wait()
+            barrier()
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record()
+            for i in range(args.steps):
+                fed.submit(*host_in)
                 fed.run(hG, hb) if rank == 0 else fed.run()
             fed.wait()
-
-        e2e_steps(2)
-        barrier()
-        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a0.record()
-        e2e_steps(args.steps)
-        a1.record()
-        barrier()
-        e2e_ms = max_over_ranks(a0.elapsed_time(a1)) / args.steps
-        # For the record, the same loop with the pipeline already primed: the region starts when the first step's
-        # inputs are on the device and contains one input copy (for the following step) and one read-back per step.
-        fed.submit(hV0, hUh, hUv)
-        fed.wait()
-        barrier()
-        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s0.record()
-        for i in range(args.steps):
-            fed.submit(hV0, hUh, hUv)
-            fed.run(hG, hb) if rank == 0 else fed.run()
-        fed.wait()
-        s1.record()
-        barrier()
-        steady_ms = max_over_ranks(s0.elapsed_time(s1)) / args.steps
-        fed.run()                                        # consume the copy that is still queued
-        torch.cuda.synchronize()
-        # the host link alone: one step's three input matrices copied with no kernel running - first on this rank
-        # alone (rank 0), then on all ranks at once (what a step's input copies share when several GPUs hang off
-        # one host)
-        def copy_inputs_ms():
-            l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            l0.record()
-            for dst, src in zip(fed.inputs[0], (hV0, hUh, hUv)):
-                dst.t().copy_(src, non_blocking=True)
-            l1.record()
+            s1.record()
+            barrier()
+            steady_ms = max_over_ranks(s0.elapsed_time(s1)) / args.steps
+            fed.run()                                        # consume the copy that is still queued
             torch.cuda.synchronize()
-            return l0.elapsed_time(l1)
-        in_bytes = 3 * units * nb * 4
-        alone_ms = copy_inputs_ms() if rank == 0 else 0.0
-        barrier()
-        all_ms = max_over_ranks(copy_inputs_ms())
-        barrier()
-        e2e = {"value": work["bytes"] / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
-               "h2d_bytes_per_step": int(world * in_bytes),
-               "d2h_bytes_per_step": int((step.G.vec.numel() + step.bias_grad.numel()) * 4),
-               "ms_per_step": e2e_ms,
-               "ms_per_step_pipeline_primed": steady_ms,
-               "host_link_GB/s_one_rank_alone": max_over_ranks(in_bytes / (alone_ms * 1e-3) / 1e9 if rank == 0 else 0.0),
-               "host_link_GB/s_all_ranks_at_once": world * in_bytes / (all_ms * 1e-3) / 1e9,
-               "ms_input_copies_all_ranks_at_once": all_ms,
-               "how": "pinned host inputs (V0, U_h, U_v) copied to the device every step on a copy stream, overlapped "
-                      "with the previous step's compute; gradients read back to pinned host memory every step"}
+            # the host link alone: one step's input matrices copied with no kernel running - first on this rank
+            # alone (rank 0), then on all ranks at once (what a step's input copies share when several GPUs hang off
+            # one host)
+            def copy_inputs_ms():
+                l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                l0.record()
+                for dst, src in zip(fed.inputs[0], host_in):
+                    dst.t().copy_(src, non_blocking=True)
+                l1.record()
+                torch.cuda.synchronize()
+                return l0.elapsed_time(l1)
+            in_bytes = len(host_in) * units * nb * 4
+            alone_ms = copy_inputs_ms() if rank == 0 else 0.0
+            barrier()
+            all_ms = max_over_ranks(copy_inputs_ms())
+            barrier()
+            del fed
+            torch.cuda.empty_cache()
+            return {"value": work["bytes"] / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+                    "h2d_bytes_per_step": int(world * in_bytes),
+                    "d2h_bytes_per_step": int((step.G.vec.numel() + step.bias_grad.numel()) * 4),
+                    "ms_per_step": e2e_ms,
+                    "ms_per_step_pipeline_primed": steady_ms,
+                    "host_link_GB/s_one_rank_alone": max_over_ranks(in_bytes / (alone_ms * 1e-3) / 1e9 if rank == 0 else 0.0),
+                    "host_link_GB/s_all_ranks_at_once": world * in_bytes / (all_ms * 1e-3) / 1e9,
+                    "ms_input_copies_all_ranks_at_once": all_ms,
+                    "how": ("pinned host input V0 copied to the device every step on a copy stream, overlapped with the "
+                            "previous step's compute; the uniform numbers of the two samples are drawn on the device "
+                            "inside the element-wise passes (cuvdia_bias_sigmoid_draw_sum_f32), as the reference draws "
+                            "them on the device (rnd_binarize, random/random.cu:139-156); gradients read back to pinned "
+                            "host memory every step") if drawn_inputs else
+                           ("pinned host inputs (V0, U_h, U_v) copied to the device every step on a copy stream, "
+                            "overlapped with the previous step's compute; gradients read back to pinned host memory "
+                            "every step")}
+
+        e2e = measure_e2e(drawn)
+        if drawn:
+            host_uniforms["e2e"] = measure_e2e(False)
 
     # the products once more in the other arithmetic, for the record (outside every timed region)
     other = cb.MODE_EXACT if mode == cb.MODE_FAST else cb.MODE_FAST
@@ -486,7 +541,7 @@ def run_ours(args, cfg):
 
     ar_check = None
     if world > 1:
-        ar_check = check_allreduce(cb, rbm, torch, dist, step, V0, U_h, U_v, W, units, nd, batch, world, rank, dev, mode)
+        ar_check = check_allreduce(cb, rbm, torch, dist, step, V0, U_h, U_v, W, units, nd, batch, world, rank, dev, mode, drawn)
 
     status = cb.plan_status(W) if rank == 0 else 0
 
@@ -555,6 +610,10 @@ def run_ours(args, cfg):
                                                      "the dense operand of every product is 0/1)" if args.mode == "fast" else
                                                      " (separate multiply and add, reference order)"), "l2": "inputs larger than L2 (each activation matrix %.0f MB)"
                    % (units * nb * 4 / 1e6),
+                   "uniforms": ("drawn on the device inside the sampling passes, a pure function of (seed, step, row, "
+                                "global column) that the CPU oracle restates bit for bit; the step that reads them from "
+                                "precomputed tensors is timed beside it under host_uniforms") if drawn else
+                               "precomputed tensors U_h, U_v (inputs of the step)",
                    "algorithmic_bytes_per_step": work["bytes"],
                    "bytes_counted": "the global problem's routines as the reference issues them (3 prod, 2 "
                                     "densedense_to_dia, 4 reduce_to_col), the same number at every N"},
@@ -573,6 +632,8 @@ def run_ours(args, cfg):
         line["allreduce_check_detail"] = ar_check
     if e2e:
         line["e2e"] = e2e
+    if host_uniforms:
+        line["host_uniforms"] = host_uniforms
     if world == 1 and not args.no_extra:
         # The step's big kernels are bound by FP32 issue.  Beside them, the same routines on a shape that HBM
         # bounds (2^20 rows, 16 diagonals, 32 columns; operands larger than L2), as a fraction of the HBM peak.
@@ -834,6 +895,9 @@ def main():
     ap.add_argument("--batch", type=int)
     ap.add_argument("--cpu-sample-cols", type=int, default=512,
                     help="batch columns of the workload the CPU oracle is timed on (its time is scaled to the full batch)")
+    ap.add_argument("--uniforms", default="drawn", choices=["drawn", "host"],
+                    help="RBM step: uniform numbers of the samples drawn on the device (default) or read from "
+                         "precomputed tensors that the end-to-end run copies from the host every step")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the HBM-bound side measurement of the default run")

@@ -464,6 +464,34 @@ def bias_sigmoid_sample_sum(act, bias, u, sample, sum_dst, sum_of_sample=False, 
     return sample
 
 
+def fill_rnd_uniform(dst, seed, step=0, col0=0, which=0):
+    """dst[i, j] = the uniform number in [0, 1) of element (i, col0 + j) of draw ``which`` in step ``step``
+    (``fill_rnd_uniform``, random/random.cu:167-177, as a pure function of its arguments: see
+    ``cuvdia_uniform_f32`` in include/cuvdia.h)."""
+    import ctypes
+    ld = _check_colmajor(dst, "dst")
+    d = _capi.Draw(int(seed), int(step), int(col0))
+    _capi.check(_capi.lib().cuvdia_uniform_f32(_ptr(dst), ld, int(dst.shape[0]), int(dst.shape[1]), ctypes.byref(d),
+                                               int(which), _stream()))
+    return dst
+
+
+def bias_sigmoid_draw_sum(act, bias, sample, sum_dst, seed, step=0, col0=0, which=0, sum_of_sample=False, factNew=1.0,
+                          factOld=0.0, store_act=True):
+    """:func:`bias_sigmoid_sample_sum` with the uniform numbers drawn inside the pass (``rnd_binarize`` fused in,
+    random/random.cu:139-156): the bits of that call on ``u = fill_rnd_uniform(..)`` with the same arguments."""
+    import ctypes
+    ld = _check_colmajor(act, "act")
+    lds = _check_colmajor(sample, "sample")
+    if sum_dst.numel() != act.shape[0] or not sum_dst.is_contiguous():
+        raise CuvDiaError(_capi.ERR_INVALID, "main_dim == v.size()")
+    d = _capi.Draw(int(seed), int(step), int(col0))
+    _capi.check(_capi.lib().cuvdia_bias_sigmoid_draw_sum_f32(
+        _ptr(act), ld, _ptr(bias), _ptr(sample), lds, int(act.shape[0]), int(act.shape[1]), _ptr(sum_dst),
+        1 if sum_of_sample else 0, factNew, factOld, 1 if store_act else 0, ctypes.byref(d), int(which), _stream()))
+    return sample
+
+
 def axpby(dst, x, y, a, b):
     """dst = a*x + b*y (apply_binary_functor BF_AXPBY, tensor_ops/tensor_ops.hpp:530-655)."""
     if not (dst.numel() == x.numel() == y.numel()):

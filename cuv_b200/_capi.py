@@ -39,6 +39,10 @@ SIGNATURES = {
     "cuvdia_bias_sigmoid_sample_f32": (_i, [_vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _vp]),
     "cuvdia_bias_sigmoid_sample_sum_f32": (_i, [_vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _vp, _i, _f, _f, _i, _vp]),
     "cuvdia_rbm_cd1_step_f32": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "cuvdia_uniform_f32": (_i, [_vp, _i, _i, _i, _vp, _i, _vp]),
+    "cuvdia_bias_sigmoid_draw_sum_f32": (_i, [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _i, _f, _f, _i, _vp, _i, _vp]),
+    "cuvdia_rbm_cd1_step_drawn_f32": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
+    "cuvdia_rbm_cd1_step_drawn_allreduce_f32": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _vp]),
     "cuvdia_rbm_cd1_step_allreduce_f32": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp]),
     "cuvdia_allreduce_grad": (_i, [_vp, _vp, _ll, _vp, _ll, _vp]),
     "cuvdia_nccl_unique_id": (_i, [ctypes.c_char_p]),
@@ -51,6 +55,11 @@ SIGNATURES = {
     "cuvdia_fill_f32": (_i, [_vp, _f, _ll, _vp]),
     "cuvdia_sequence_f32": (_i, [_vp, _ll, _vp]),
 }
+
+
+class Draw(ctypes.Structure):
+    """``cuvdia_draw`` of include/cuvdia.h."""
+    _fields_ = [("seed", ctypes.c_ulonglong), ("step", ctypes.c_ulonglong), ("col0", ctypes.c_longlong)]
 
 
 class RbmCd1Buffers(ctypes.Structure):

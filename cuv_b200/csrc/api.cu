@@ -361,6 +361,28 @@ int cuvdia_bias_sigmoid_sample_sum_f32(float* act, int ld, const float* bias, co
                                           factNew, factOld, store_act ? 1 : 0, (cudaStream_t)stream);
 }
 
+int cuvdia_uniform_f32(float* dst, int ld, int rows, int ncols, const cuvdia_draw* draw, int which, void* stream) {
+    CUVDIA_REQUIRE(dst != nullptr && draw != nullptr);
+    CUVDIA_REQUIRE(rows > 0 && ncols >= 0 && ld >= rows);
+    CUVDIA_REQUIRE(which >= 0 && which < 65536);
+    CUVDIA_REQUIRE(draw->col0 >= 0 && draw->step < (1ull << 32));
+    if (ncols == 0) return CUVDIA_OK;
+    return launch_uniform(dst, ld, rows, ncols, make_draw(draw, (unsigned)which), (cudaStream_t)stream);
+}
+
+int cuvdia_bias_sigmoid_draw_sum_f32(float* act, int ld, const float* bias, float* sample, int lds, int units, int ncols,
+                                     float* sum_dst, int sum_of_sample, float factNew, float factOld, int store_act,
+                                     const cuvdia_draw* draw, int which, void* stream) {
+    CUVDIA_REQUIRE(act != nullptr && sample != nullptr && sum_dst != nullptr && draw != nullptr);
+    CUVDIA_REQUIRE(units > 0 && ncols > 0);
+    CUVDIA_REQUIRE(ld >= units && lds >= units);
+    CUVDIA_REQUIRE(which >= 0 && which < 65536);
+    CUVDIA_REQUIRE(draw->col0 >= 0 && draw->step < (1ull << 32));
+    const DrawParams dp = make_draw(draw, (unsigned)which);
+    return launch_bias_sigmoid_sample_sum(act, ld, bias, nullptr, 0, sample, lds, units, ncols, sum_dst, sum_of_sample ? 1 : 0,
+                                          factNew, factOld, store_act ? 1 : 0, (cudaStream_t)stream, &dp);
+}
+
 int cuvdia_axpby_f32(float* dst, const float* x, const float* y, float a, float b, long long n, void* stream) {
     CUVDIA_REQUIRE(dst != nullptr && x != nullptr && y != nullptr);
     CUVDIA_REQUIRE(n >= 0);

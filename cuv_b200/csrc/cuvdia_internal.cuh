@@ -93,6 +93,18 @@ struct cuvdia_plan {
 };
 
 namespace cuvdia {
+// Which uniform numbers a pass draws: key (the seed's two halves), the draw within the step, the step, and the global
+// index of the first batch column the call sees (see glue.cu).
+struct DrawParams {
+    unsigned k0, k1, which, step;
+    long long col0;
+};
+inline DrawParams make_draw(const cuvdia_draw* d, unsigned which) {
+    DrawParams r;
+    r.k0 = (unsigned)(d->seed & 0xffffffffull); r.k1 = (unsigned)(d->seed >> 32);
+    r.which = which; r.step = (unsigned)d->step; r.col0 = d->col0;
+    return r;
+}
 // Optional element-wise tail of prod: C <- sigmoid(C + bias[row]); S <- C > U ? 1 : 0.
 struct ProdEpilogue {
     const float* bias;       // may be null
@@ -160,9 +172,12 @@ int launch_bias_sigmoid_sample(float* act, int ld, const float* bias, const floa
                                int lds, int units, int ncols, cudaStream_t st);
 // the same pass that also accumulates sum_dst[unit] = fold*sum_dst[unit] + fnew*sum over columns of the activation
 // (sum_sample == 0) or of the 0/1 sample (sum_sample != 0); store_act == 0 leaves act unwritten
+// draw != null: the uniform numbers are drawn in the kernel (u is not read)
 int launch_bias_sigmoid_sample_sum(float* act, int ld, const float* bias, const float* u, int ldu, float* sample,
                                    int lds, int units, int ncols, float* sum_dst, int sum_sample, float fnew, float fold,
-                                   int store_act, cudaStream_t st);
+                                   int store_act, cudaStream_t st, const DrawParams* draw = nullptr);
+// dst[row, col] = the uniform number of (row, d.col0 + col) of draw d.which in step d.step
+int launch_uniform(float* dst, int ld, int rows, int ncols, const DrawParams& d, cudaStream_t st);
 int launch_reduce_combine_add(float* dst, long long n_out, float fnew, float fold, int nsplit, const float* partial,
                               cudaStream_t st);
 int launch_axpby(float* dst, const float* x, const float* y, float a, float b, long long n, cudaStream_t st);

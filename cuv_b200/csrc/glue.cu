@@ -6,6 +6,57 @@ namespace cuvdia {
 
 __device__ __forceinline__ float sigm(float x) { return 1.f / (1.f + expf(-x)); }   // tensor_ops/functors.hpp:122
 
+// ---- uniform numbers drawn where they are used -------------------------------------------------------------------
+// CUV binarises an activation by comparing it with a uniform number drawn on the device (rnd_binarize,
+// random/random.cu:86-91,139-156: one generator state per thread).  Here the number of element (row, column) of draw
+// `which` in step `step` is a pure function of those four and a 64-bit seed - the counter-based generator
+// Philox4x32-10 (Salmon, Moraes, Dror, Shaw: "Parallel random numbers: as easy as 1, 2, 3", SC 2011) - so a pass can
+// draw it in registers instead of reading it from memory, any sharding of the batch columns draws the same numbers
+// as the unsharded run, and a CPU restatement reproduces them bit for bit.  One call gives four 32-bit words: the
+// numbers of rows 4q .. 4q+3 of one column; counter = (q, column, which + 65536 * (column >> 32), step), key = seed.
+// A word x becomes the float (x >> 8) * 2^-24 in [0, 1): exact, and P(u < p) = p to within 2^-24.
+__device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
+#pragma unroll
+    for (int r = 0; r < 10; r++) {
+        const unsigned hi0 = __umulhi(0xD2511F53u, c.x), lo0 = 0xD2511F53u * c.x;
+        const unsigned hi1 = __umulhi(0xCD9E8D57u, c.z), lo1 = 0xCD9E8D57u * c.z;
+        c = make_uint4(hi1 ^ c.y ^ k.x, lo1, hi0 ^ c.w ^ k.y, lo0);
+        k.x += 0x9E3779B9u; k.y += 0xBB67AE85u;
+    }
+    return c;
+}
+
+__device__ __forceinline__ float u01(unsigned x) { return (float)(x >> 8) * (1.f / 16777216.f); }
+
+// the four uniform numbers of rows 4q .. 4q+3 of global column gcol
+__device__ __forceinline__ float4 draw4(const DrawParams& d, int q, long long gcol) {
+    const uint4 r = philox4x32_10(make_uint4((unsigned)q, (unsigned)gcol, d.which + 65536u * (unsigned)(gcol >> 32), d.step),
+                                  make_uint2(d.k0, d.k1));
+    return make_float4(u01(r.x), u01(r.y), u01(r.z), u01(r.w));
+}
+
+__global__ void __launch_bounds__(256)
+uniform_kernel(float* __restrict__ dst, int ld, int rows, int ncols, const DrawParams d) {
+    const int groups = (rows + 3) / 4;
+    const long long total = (long long)groups * ncols;
+    for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total;
+         t += (long long)gridDim.x * blockDim.x) {
+        const int col = (int)(t / groups), q = (int)(t - (long long)col * groups);
+        const float4 u = draw4(d, q, d.col0 + col);
+        float* o = dst + (size_t)col * ld + 4 * q;
+        const float v[4] = {u.x, u.y, u.z, u.w};
+        for (int e = 0; e < 4 && 4 * q + e < rows; e++) o[e] = v[e];
+    }
+}
+
+int launch_uniform(float* dst, int ld, int rows, int ncols, const DrawParams& d, cudaStream_t st) {
+    const long long total = (long long)((rows + 3) / 4) * ncols;
+    const int blocks = (int)std::max<long long>(1, std::min<long long>((total + 255) / 256, 16LL * sm_count()));
+    uniform_kernel<<<blocks, 256, 0, st>>>(dst, ld, rows, ncols, d);
+    count_launch();
+    return check_launch("uniform_kernel");
+}
+
 template <bool VEC>
 __global__ void __launch_bounds__(256)
 bias_sigmoid_sample_kernel(float* __restrict__ act, int ld, const float* __restrict__ bias,
@@ -62,12 +113,13 @@ int launch_bias_sigmoid_sample(float* act, int ld, const float* bias, const floa
 // reproducible run to run.  Summed is either the activation after the logistic or the 0/1 sample; this replaces a
 // separate reduce_to_col over a matrix this pass has just produced.  With store_act == 0 the activations are
 // not written back (callers that only consume the sample and its sum).
-template <bool VEC>
+// DRAW: the uniform numbers are not read from u but drawn in registers (see draw4 above).
+template <bool VEC, bool DRAW>
 __global__ void __launch_bounds__(256)
 bias_sigmoid_sample_sum_kernel(float* __restrict__ act, int ld, const float* __restrict__ bias,
                                const float* __restrict__ u, int ldu, float* __restrict__ sample, int lds, int units,
                                int ncols, int nslab, int sum_sample, int store_act, float* __restrict__ partial,
-                               float* __restrict__ dst, float fnew, float fold) {
+                               float* __restrict__ dst, float fnew, float fold, const DrawParams dp) {
     constexpr int W = VEC ? 4 : 1;
     const int i = (blockIdx.x * 256 + threadIdx.x) * W;
     if (i >= units) return;
@@ -101,13 +153,19 @@ bias_sigmoid_sample_sum_kernel(float* __restrict__ act, int ld, const float* __r
             x[0] = base[(size_t)col * pitch + i];
         }
     };
+    auto draw = [&](int col, float (&x)[W]) {
+        const float4 t = draw4(dp, i >> 2, dp.col0 + col);
+        if (VEC) { x[0] = t.x; x[W > 1 ? 1 : 0] = t.y; x[W > 2 ? 2 : 0] = t.z; x[W > 3 ? 3 : 0] = t.w; }
+        else { const int e = i & 3; x[0] = e == 0 ? t.x : e == 1 ? t.y : e == 2 ? t.z : t.w; }
+    };
     int col = c0;
     for (; col + 4 <= c1; col += 4) {
         float a[4][W], r[4][W];
 #pragma unroll
         for (int q = 0; q < 4; q++) {
             load(act, ld, col + q, a[q]);
-            if (u) load(u, ldu, col + q, r[q]);
+            if (DRAW) draw(col + q, r[q]);
+            else if (u) load(u, ldu, col + q, r[q]);
             else {
 #pragma unroll
                 for (int v = 0; v < W; v++) r[q][v] = 0.f;
@@ -119,7 +177,8 @@ bias_sigmoid_sample_sum_kernel(float* __restrict__ act, int ld, const float* __r
     for (; col < c1; col++) {
         float a[W], r[W];
         load(act, ld, col, a);
-        if (u) load(u, ldu, col, r);
+        if (DRAW) draw(col, r);
+        else if (u) load(u, ldu, col, r);
         else {
 #pragma unroll
             for (int v = 0; v < W; v++) r[v] = 0.f;
@@ -135,9 +194,12 @@ bias_sigmoid_sample_sum_kernel(float* __restrict__ act, int ld, const float* __r
 
 int launch_bias_sigmoid_sample_sum(float* act, int ld, const float* bias, const float* u, int ldu, float* sample,
                                    int lds, int units, int ncols, float* sum_dst, int sum_sample, float fnew, float fold,
-                                   int store_act, cudaStream_t st) {
+                                   int store_act, cudaStream_t st, const DrawParams* draw) {
     bool vec = units % 4 == 0 && ld % 4 == 0 && aligned16(act) && (!bias || aligned16(bias));
-    if (u) vec = vec && ldu % 4 == 0 && lds % 4 == 0 && aligned16(u) && aligned16(sample);
+    if (u) vec = vec && ldu % 4 == 0 && aligned16(u);
+    if (sample) vec = vec && lds % 4 == 0 && aligned16(sample);
+    DrawParams dp = {};
+    if (draw) dp = *draw;
     const int per_block = 256 * (vec ? 4 : 1);
     const int gx = (units + per_block - 1) / per_block;
     // enough blocks to fill the device several times over, but at least 8 columns per slab
@@ -151,8 +213,10 @@ int launch_bias_sigmoid_sample_sum(float* act, int ld, const float* bias, const 
         partial = (float*)ws;
     }
     dim3 grid(gx, nslab);
-    if (vec) bias_sigmoid_sample_sum_kernel<true><<<grid, 256, 0, st>>>(act, ld, bias, u, ldu, sample, lds, units, ncols, nslab, sum_sample, store_act, partial, sum_dst, fnew, fold);
-    else     bias_sigmoid_sample_sum_kernel<false><<<grid, 256, 0, st>>>(act, ld, bias, u, ldu, sample, lds, units, ncols, nslab, sum_sample, store_act, partial, sum_dst, fnew, fold);
+#define BSS_GO(V, D) bias_sigmoid_sample_sum_kernel<V, D><<<grid, 256, 0, st>>>(act, ld, bias, u, ldu, sample, lds, units, ncols, nslab, sum_sample, store_act, partial, sum_dst, fnew, fold, dp)
+    if (draw) { if (vec) BSS_GO(true, true); else BSS_GO(false, true); }
+    else      { if (vec) BSS_GO(true, false); else BSS_GO(false, false); }
+#undef BSS_GO
     count_launch();
     int rc = check_launch("bias_sigmoid_sample_sum_kernel");
     if (rc || nslab == 1) return rc;

@@ -91,12 +91,24 @@ extern "C" {
 
 // The step up to and including the first densedense_to_dia (everything but the call that completes G).
 static int rbm_step_head(cuvdia_plan* p, const float* W_vals, const cuvdia_rbm_cd1_buffers* b, int ncols, int batch_global,
-                         int mode, int keep_v1p, cudaStream_t st, float* inv_out);
+                         int mode, int keep_v1p, cudaStream_t st, float* inv_out, const cuvdia_draw* draw = nullptr);
+static int rbm_step_allreduce(cuvdia_plan* p, const float* W_vals, const cuvdia_rbm_cd1_buffers* b, int ncols,
+                              int batch_global, int mode, int keep_v1p, int overlap, void* nccl_comm, void* stream,
+                              const cuvdia_draw* draw);
 
 int cuvdia_rbm_cd1_step_f32(cuvdia_plan* p, const float* W_vals, const cuvdia_rbm_cd1_buffers* b, int ncols,
                             int batch_global, int mode, int keep_v1p, void* stream) {
     float inv = 0.f;
     int rc = rbm_step_head(p, W_vals, b, ncols, batch_global, mode, keep_v1p, (cudaStream_t)stream, &inv);
+    if (rc) return rc;
+    return launch_dd2dia(p, b->G_vals, b->H1p, p->h, b->V1, p->w, ncols, -inv, 1.f, (cudaStream_t)stream);
+}
+
+int cuvdia_rbm_cd1_step_drawn_f32(cuvdia_plan* p, const float* W_vals, const cuvdia_rbm_cd1_buffers* b, int ncols,
+                                  int batch_global, int mode, int keep_v1p, const cuvdia_draw* draw, void* stream) {
+    CUVDIA_REQUIRE(draw != nullptr);
+    float inv = 0.f;
+    int rc = rbm_step_head(p, W_vals, b, ncols, batch_global, mode, keep_v1p, (cudaStream_t)stream, &inv, draw);
     if (rc) return rc;
     return launch_dd2dia(p, b->G_vals, b->H1p, p->h, b->V1, p->w, ncols, -inv, 1.f, (cudaStream_t)stream);
 }
@@ -121,6 +133,19 @@ static int allreduce_two(const NcclApi* n, ncclComm_t comm, float* G_vals, long 
 int cuvdia_rbm_cd1_step_allreduce_f32(cuvdia_plan* p, const float* W_vals, const cuvdia_rbm_cd1_buffers* b, int ncols,
                                       int batch_global, int mode, int keep_v1p, int overlap, void* nccl_comm,
                                       void* stream) {
+    return rbm_step_allreduce(p, W_vals, b, ncols, batch_global, mode, keep_v1p, overlap, nccl_comm, stream, nullptr);
+}
+
+int cuvdia_rbm_cd1_step_drawn_allreduce_f32(cuvdia_plan* p, const float* W_vals, const cuvdia_rbm_cd1_buffers* b, int ncols,
+                                            int batch_global, int mode, int keep_v1p, const cuvdia_draw* draw, int overlap,
+                                            void* nccl_comm, void* stream) {
+    CUVDIA_REQUIRE(draw != nullptr);
+    return rbm_step_allreduce(p, W_vals, b, ncols, batch_global, mode, keep_v1p, overlap, nccl_comm, stream, draw);
+}
+
+static int rbm_step_allreduce(cuvdia_plan* p, const float* W_vals, const cuvdia_rbm_cd1_buffers* b, int ncols,
+                              int batch_global, int mode, int keep_v1p, int overlap, void* nccl_comm, void* stream,
+                              const cuvdia_draw* draw) {
     CUVDIA_REQUIRE(nccl_comm != nullptr);
     CUVDIA_REQUIRE(overlap >= 0 && overlap <= 2);
     const NcclApi* n = need_nccl();
@@ -128,7 +153,7 @@ int cuvdia_rbm_cd1_step_allreduce_f32(cuvdia_plan* p, const float* W_vals, const
     ncclComm_t comm = (ncclComm_t)nccl_comm;
     cudaStream_t st = (cudaStream_t)stream;
     float inv = 0.f;
-    int rc = rbm_step_head(p, W_vals, b, ncols, batch_global, mode, keep_v1p, st, &inv);
+    int rc = rbm_step_head(p, W_vals, b, ncols, batch_global, mode, keep_v1p, st, &inv, draw);
     if (rc) return rc;
     const long long n_g = (long long)p->nd * p->stride, n_bias = (long long)p->h + p->w;
     float* bias = b->gc;                                  // gc then gb: one array when gb follows gc
@@ -175,12 +200,17 @@ int cuvdia_rbm_cd1_step_allreduce_f32(cuvdia_plan* p, const float* W_vals, const
 }
 
 static int rbm_step_head(cuvdia_plan* p, const float* W_vals, const cuvdia_rbm_cd1_buffers* b, int ncols, int batch_global,
-                         int mode, int keep_v1p, cudaStream_t st, float* inv_out) {
+                         int mode, int keep_v1p, cudaStream_t st, float* inv_out, const cuvdia_draw* draw) {
     CUVDIA_REQUIRE(p != nullptr && W_vals != nullptr && b != nullptr);
     CUVDIA_REQUIRE(p->rf == 1);                        // the trainer's weight matrix (row factors belong to other layers)
     CUVDIA_REQUIRE(ncols > 0 && batch_global >= ncols);
     CUVDIA_REQUIRE(mode == CUVDIA_MODE_EXACT || mode == CUVDIA_MODE_FAST);
-    CUVDIA_REQUIRE(b->V0 && b->U_h && b->U_v);
+    CUVDIA_REQUIRE(b->V0 != nullptr);
+    if (draw) { CUVDIA_REQUIRE(draw->col0 >= 0 && draw->step < (1ull << 32)); }
+    else      { CUVDIA_REQUIRE(b->U_h && b->U_v); }
+    // draw 0: the hidden sample, draw 1: the visible sample (U_h and U_v are not read)
+    DrawParams d_h = {}, d_v = {};
+    if (draw) { d_h = make_draw(draw, 0); d_v = make_draw(draw, 1); }
     CUVDIA_REQUIRE(b->H0p && b->H0 && b->V1p && b->V1 && b->H1p);
     CUVDIA_REQUIRE(b->G_vals && b->gc && b->gb);
     int dev = -1;
@@ -192,10 +222,11 @@ static int rbm_step_head(cuvdia_plan* p, const float* W_vals, const cuvdia_rbm_c
 #define STEP(call) do { rc = (call); if (rc) return rc; } while (0)
     STEP(launch_reduce(b->gb, b->V0, vis, ncols, true, CUVDIA_RF_ADD, inv, 0.f, st));
     STEP(launch_prod(p, W_vals, b->V0, vis, b->H0p, hid, ncols, false, 1.f, 0.f, mode, nullptr, st));
-    STEP(launch_bias_sigmoid_sample_sum(b->H0p, hid, b->c_hid, b->U_h, hid, b->H0, hid, hid, ncols, b->gc, 0, inv, 0.f, 1, st));
+    STEP(launch_bias_sigmoid_sample_sum(b->H0p, hid, b->c_hid, draw ? nullptr : b->U_h, hid, b->H0, hid, hid, ncols, b->gc, 0, inv,
+                                        0.f, 1, st, draw ? &d_h : nullptr));
     STEP(launch_prod(p, W_vals, b->H0, hid, b->V1p, vis, ncols, true, 1.f, 0.f, mode, nullptr, st));
-    STEP(launch_bias_sigmoid_sample_sum(b->V1p, vis, b->b_vis, b->U_v, vis, b->V1, vis, vis, ncols, b->gb, 1, -inv, 1.f,
-                                        keep_v1p ? 1 : 0, st));
+    STEP(launch_bias_sigmoid_sample_sum(b->V1p, vis, b->b_vis, draw ? nullptr : b->U_v, vis, b->V1, vis, vis, ncols, b->gb, 1, -inv,
+                                        1.f, keep_v1p ? 1 : 0, st, draw ? &d_v : nullptr));
     STEP(launch_prod(p, W_vals, b->V1, vis, b->H1p, hid, ncols, false, 1.f, 0.f, mode, nullptr, st));
     STEP(launch_bias_sigmoid_sample_sum(b->H1p, hid, b->c_hid, nullptr, 0, nullptr, 0, hid, ncols, b->gc, 0, -inv, 1.f, 1, st));
     STEP(launch_dd2dia(p, b->G_vals, b->H0p, hid, b->V0, vis, ncols, inv, 0.f, st));

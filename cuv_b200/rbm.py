@@ -97,16 +97,41 @@ class SparseRBMStep:
             return self.allreduce(group)
         self._step_c(V0, U_h, U_v, comm=self._reducer.comm, overlap=overlap)
 
-    def _step_c(self, V0, U_h, U_v, comm=None, overlap=1):
+    def step_drawn(self, V0, seed, step=0, col0=0):
+        """step() with the uniform numbers of the two samples drawn on the device (``cuvdia_rbm_cd1_step_drawn_f32``):
+        the bits of ``step(V0, U_h, U_v)`` on ``U_h = cb.fill_rnd_uniform(.., which=0)`` and ``U_v = .. which=1`` with
+        the same ``seed``, ``step`` and ``col0`` (global index of this rank's first batch column).  Nothing but V0 has
+        to reach the device."""
+        return self._step_c(V0, None, None, draw=(seed, step, col0))
+
+    def step_drawn_allreduce(self, V0, seed, step=0, col0=0, group=None, overlap=1):
+        """step_drawn() and the all-reduce of the gradients as one call of the C ABI."""
+        if self._reducer is None:
+            self._reducer = GradientAllReduce(self.dev, group)
+        return self._step_c(V0, None, None, comm=self._reducer.comm, overlap=overlap, draw=(seed, step, col0))
+
+    def _step_c(self, V0, U_h, U_v, comm=None, overlap=1, draw=None):
         """The whole step as one call of the C ABI."""
         import ctypes
         from . import _capi
-        for t, rows, name in ((V0, self.vis, "V0"), (U_h, self.hid, "U_h"), (U_v, self.vis, "U_v")):
+        inputs = ((V0, self.vis, "V0"),) if draw is not None else ((V0, self.vis, "V0"), (U_h, self.hid, "U_h"), (U_v, self.vis, "U_v"))
+        for t, rows, name in inputs:
             if cb._check_colmajor(t, name) != rows or t.shape != (rows, self.nb):
                 raise cb.CuvDiaError(_capi.ERR_INVALID, name + " must be a dense column-major [units x batch] matrix")
-        p = lambda t: t.data_ptr()
+        p = lambda t: t.data_ptr() if t is not None else None
         buf = _capi.RbmCd1Buffers(p(V0), p(U_h), p(U_v), p(self.b_vis), p(self.c_hid), p(self.H0p), p(self.H0),
                                   p(self.V1p), p(self.V1), p(self.H1p), p(self.G.vec), p(self.gc), p(self.gb))
+        if draw is not None:
+            d = _capi.Draw(int(draw[0]), int(draw[1]), int(draw[2]))
+            if comm is not None:
+                _capi.check(_capi.lib().cuvdia_rbm_cd1_step_drawn_allreduce_f32(
+                    self.W._plan, cb._ptr(self.W.vec), ctypes.byref(buf), self.nb, self.B, self.mode,
+                    1 if self.keep_v1p else 0, ctypes.byref(d), int(overlap), comm, cb._stream()))
+            else:
+                _capi.check(_capi.lib().cuvdia_rbm_cd1_step_drawn_f32(
+                    self.W._plan, cb._ptr(self.W.vec), ctypes.byref(buf), self.nb, self.B, self.mode,
+                    1 if self.keep_v1p else 0, ctypes.byref(d), cb._stream()))
+            return
         if comm is not None:
             _capi.check(_capi.lib().cuvdia_rbm_cd1_step_allreduce_f32(
                 self.W._plan, cb._ptr(self.W.vec), ctypes.byref(buf), self.nb, self.B, self.mode,
@@ -115,10 +140,11 @@ class SparseRBMStep:
         _capi.check(_capi.lib().cuvdia_rbm_cd1_step_f32(self.W._plan, cb._ptr(self.W.vec), ctypes.byref(buf), self.nb,
                                                         self.B, self.mode, 1 if self.keep_v1p else 0, cb._stream()))
 
-    def forward(self, V0, U_h, U_v, arrived=None):
+    def forward(self, V0, U_h, U_v, arrived=None, draw=None):
         """The three products with their bias/logistic/sampling passes (and, with ``bias_sums="glue"``, the bias
         gradients).  ``arrived``: optional events (V0, U_h, U_v) that the current stream waits for just before the
-        first use of each input, so that a step can start on V0 while the uniform numbers are still on their way."""
+        first use of each input, so that a step can start on V0 while the uniform numbers are still on their way.
+        ``draw=(seed, step, col0)``: the uniform numbers are drawn inside the element-wise passes (U_h, U_v unused)."""
         W = self.W
         t = self._timed
         inv = 1.0 / self.B
@@ -137,6 +163,20 @@ class SparseRBMStep:
             t("prod_n", lambda: F(self.H1p, W, self.V1, "n", 1.0, 0.0, self.mode, self.c_hid))
             return
         need(0)
+        if draw is not None:
+            if self.bias_sums != "glue" or self.fused:
+                raise ValueError("drawn samples come with the bias sums taken in the element-wise passes")
+            GS, DS = cb.bias_sigmoid_sample_sum, cb.bias_sigmoid_draw_sum
+            seed, stepno, col0 = draw
+            t("reduce", lambda: cb.reduce_to_col(self.gb, V0, cb.RF_ADD, inv, 0.0))
+            t("prod_n", lambda: cb.prod(self.H0p, W, V0, "n", "n", 1.0, 0.0, self.mode))
+            t("glue", lambda: DS(self.H0p, self.c_hid, self.H0, self.gc, seed, stepno, col0, 0, False, inv, 0.0))
+            t("prod_t", lambda: cb.prod(self.V1p, W, self.H0, "t", "n", 1.0, 0.0, self.mode))
+            t("glue", lambda: DS(self.V1p, self.b_vis, self.V1, self.gb, seed, stepno, col0, 1, True, -inv, 1.0,
+                                 self.keep_v1p))
+            t("prod_n", lambda: cb.prod(self.H1p, W, self.V1, "n", "n", 1.0, 0.0, self.mode))
+            t("glue", lambda: GS(self.H1p, self.c_hid, None, None, self.gc, False, -inv, 1.0))
+            return
         if self.bias_sums == "glue":
             GS = cb.bias_sigmoid_sample_sum
             t("reduce", lambda: cb.reduce_to_col(self.gb, V0, cb.RF_ADD, inv, 0.0))
@@ -250,13 +290,18 @@ class HostFedRBM:
     device-to-host read of step i's gradients runs on a third stream while step i+1's products
     compute."""
 
-    def __init__(self, step, allreduce=False):
+    def __init__(self, step, allreduce=False, draw=None):
+        """``draw=(seed, col0)``: the uniform numbers are drawn on the device (step number = count of steps run), so
+        only V0 is copied per step and ``submit`` takes one tensor."""
         import torch
-        self.step, self.allreduce = step, allreduce
+        self.step, self.allreduce, self.draw = step, allreduce, draw
         dev = step.dev
         E = cb.colmajor_empty
-        self.inputs = [(E(step.vis, step.nb, dev), E(step.hid, step.nb, dev), E(step.vis, step.nb, dev))
-                       for _ in range(2)]
+        if draw is not None:
+            self.inputs = [(E(step.vis, step.nb, dev),) for _ in range(2)]
+        else:
+            self.inputs = [(E(step.vis, step.nb, dev), E(step.hid, step.nb, dev), E(step.vis, step.nb, dev))
+                           for _ in range(2)]
         self.h2d, self.d2h = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
         self.ready = [[torch.cuda.Event() for _ in range(3)] for _ in range(2)]     # per slot: V0, U_h, U_v arrived
         self.consumed = [torch.cuda.Event() for _ in range(2)]
@@ -264,7 +309,7 @@ class HostFedRBM:
         self.n_sub = self.n_run = 0
         self._fetch_pending = False
 
-    def submit(self, hV0, hU_h, hU_v):
+    def submit(self, hV0, hU_h=None, hU_v=None):
         """Queue the copy of one step's inputs (pinned host tensors holding the column-major matrices,
         i.e. shape (batch, units) contiguous)."""
         import torch
@@ -272,7 +317,7 @@ class HostFedRBM:
         if self.n_sub >= 2:
             self.h2d.wait_event(self.consumed[slot])
         with torch.cuda.stream(self.h2d):
-            for k, (dst, src) in enumerate(zip(self.inputs[slot], (hV0, hU_h, hU_v))):
+            for k, (dst, src) in enumerate(zip(self.inputs[slot], (hV0, hU_h, hU_v))):      # one tensor when drawn
                 dst.t().copy_(src, non_blocking=True)
                 self.ready[slot][k].record(self.h2d)
         self.n_sub += 1
@@ -283,10 +328,14 @@ class HostFedRBM:
         import torch
         cur = torch.cuda.current_stream()
         slot = self.n_run % 2
-        V0, U_h, U_v = self.inputs[slot]
+        V0 = self.inputs[slot][0]
         if self._fetch_pending:
             cur.wait_event(self.bias_fetched)     # forward() writes the bias gradients: their (small) read-back goes first
-        self.step.forward(V0, U_h, U_v, arrived=self.ready[slot])       # each input is awaited where it is first used
+        if self.draw is not None:
+            self.step.forward(V0, None, None, arrived=self.ready[slot], draw=(self.draw[0], self.n_run, self.draw[1]))
+        else:
+            U_h, U_v = self.inputs[slot][1:]
+            self.step.forward(V0, U_h, U_v, arrived=self.ready[slot])   # each input is awaited where it is first used
         if self._fetch_pending:
             cur.wait_event(self.fetched)          # the previous gradients must have left before they are overwritten
         self.step.gradients(V0)

@@ -297,6 +297,44 @@ typedef struct cuvdia_rbm_cd1_buffers {
 CUVDIA_API int cuvdia_rbm_cd1_step_f32(cuvdia_plan* plan, const float* W_vals, const cuvdia_rbm_cd1_buffers* buffers,
                                        int ncols, int batch_global, int mode, int keep_v1p, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Uniform numbers drawn on the device.  CUV binarises an activation against a uniform number that the
+ * device draws (rnd_binarize / fill_rnd_uniform, random/random.cu:86-95,139-177; one generator state
+ * per thread, so the numbers depend on the launch geometry).  Here the number of element (row, column)
+ * is a pure function of (seed, step, which, row, global column): the counter-based generator
+ * Philox4x32-10 (Salmon et al., SC 2011) with counter (row / 4, column, which, step) and key = seed,
+ * word row % 4 of its output, as the float (word >> 8) * 2^-24 in [0, 1).  A sampling pass can
+ * therefore draw its numbers in registers - nothing is read from memory and a host-fed trainer has
+ * nothing to upload but its data - every sharding of the batch columns (col0 = global index of the
+ * caller's first column) draws what the unsharded run draws, and a CPU restatement gives the same
+ * bits (oracle/cuv_host_oracle.c).  step < 2^32, 0 <= which < 65536.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct cuvdia_draw {
+    unsigned long long seed;    /* key of the generator                                      */
+    unsigned long long step;    /* distinguishes the steps of a run                          */
+    long long col0;             /* global index of the first batch column the call sees      */
+} cuvdia_draw;
+
+/* dst[row, col] = that uniform number, rows x ncols, column-major with leading dimension ld
+ * (fill_rnd_uniform, random/random.cu:167-177, made reproducible). */
+CUVDIA_API int cuvdia_uniform_f32(float* dst, int ld, int rows, int ncols, const cuvdia_draw* draw, int which,
+                                  void* stream);
+
+/* cuvdia_bias_sigmoid_sample_sum_f32 with the uniform numbers drawn in the kernel instead of read from u:
+ * bit for bit what that call gives on u = cuvdia_uniform_f32(draw, which) (rnd_binarize fused into the pass,
+ * random/random.cu:139-156). */
+CUVDIA_API int cuvdia_bias_sigmoid_draw_sum_f32(float* act, int ld, const float* bias, float* sample, int lds, int units,
+                                                int ncols, float* sum_dst, int sum_of_sample, float factNew,
+                                                float factOld, int store_act, const cuvdia_draw* draw, int which,
+                                                void* stream);
+
+/* cuvdia_rbm_cd1_step_f32 with the hidden (which = 0) and visible (which = 1) samples drawn on the device:
+ * buffers->U_h and U_v are not read and may be NULL.  Bit for bit the step on U_h = cuvdia_uniform_f32(draw, 0),
+ * U_v = cuvdia_uniform_f32(draw, 1). */
+CUVDIA_API int cuvdia_rbm_cd1_step_drawn_f32(cuvdia_plan* plan, const float* W_vals, const cuvdia_rbm_cd1_buffers* buffers,
+                                             int ncols, int batch_global, int mode, int keep_v1p,
+                                             const cuvdia_draw* draw, void* stream);
+
 /* Sum over the ranks of an NCCL communicator, in place, of the per-rank partial gradients of
  * cuvdia_rbm_cd1_step_f32: the diagonals' value array and the bias gradients, as one collective when
  * bias_grad == G_vals + n_g (one buffer) and as one NCCL group otherwise.  CUV has no multi-GPU path;
@@ -321,6 +359,12 @@ CUVDIA_API int cuvdia_allreduce_grad(void* nccl_comm, float* G_vals, long long n
 CUVDIA_API int cuvdia_rbm_cd1_step_allreduce_f32(cuvdia_plan* plan, const float* W_vals,
                                                  const cuvdia_rbm_cd1_buffers* buffers, int ncols, int batch_global,
                                                  int mode, int keep_v1p, int overlap, void* nccl_comm, void* stream);
+
+/* The same with the samples drawn on the device (see cuvdia_rbm_cd1_step_drawn_f32). */
+CUVDIA_API int cuvdia_rbm_cd1_step_drawn_allreduce_f32(cuvdia_plan* plan, const float* W_vals,
+                                                       const cuvdia_rbm_cd1_buffers* buffers, int ncols,
+                                                       int batch_global, int mode, int keep_v1p, const cuvdia_draw* draw,
+                                                       int overlap, void* nccl_comm, void* stream);
 
 /* For callers without a communicator of their own: ncclGetUniqueId on one rank (128 bytes, to be sent
  * to the others by whatever means the application has), then ncclCommInitRank on every rank with its

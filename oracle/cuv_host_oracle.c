@@ -505,3 +505,43 @@ ORACLE_API void oracle_learn_step_weight_decay_momentum(float *W, float *M, cons
         M[i] = m;
     }
 }
+
+/* ---- uniform numbers of the sampling step ---------------------------------------------------------
+ * CUV draws the number an activation is binarised against on the device (rnd_binarize, random/random.cu:86-91,
+ * 139-156), one generator state per thread, so its stream depends on the launch geometry and no host code
+ * reproduces it.  The product path defines the number of element (row, column) of draw `which` in step `step`
+ * as word row % 4 of Philox4x32-10 (Salmon, Moraes, Dror, Shaw, "Parallel random numbers: as easy as 1, 2, 3",
+ * SC 2011) on counter (row / 4, column, which + 65536 * (column >> 32), step) with key (seed low, seed high),
+ * mapped to [0, 1) as (word >> 8) * 2^-24.  This is the published algorithm restated: ten rounds of
+ * (hi1 ^ c1 ^ k0, lo1, hi0 ^ c3 ^ k1, lo0) with (hi0, lo0) = 0xD2511F53 * c0, (hi1, lo1) = 0xCD9E8D57 * c2, the key
+ * raised by (0x9E3779B9, 0xBB67AE85) between rounds.  Pinned by the known-answer vectors of the generator's
+ * authors in tests/test_oracle_golden.py. */
+ORACLE_API void oracle_philox4x32_10(const unsigned *ctr, const unsigned *key, unsigned *out)
+{
+    unsigned c0 = ctr[0], c1 = ctr[1], c2 = ctr[2], c3 = ctr[3], k0 = key[0], k1 = key[1];
+    for (int r = 0; r < 10; r++) {
+        const unsigned long long p0 = 0xD2511F53ull * c0, p1 = 0xCD9E8D57ull * c2;
+        const unsigned n0 = (unsigned)(p1 >> 32) ^ c1 ^ k0, n1 = (unsigned)p1;
+        const unsigned n2 = (unsigned)(p0 >> 32) ^ c3 ^ k1, n3 = (unsigned)p0;
+        c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+        k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+    }
+    out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+}
+
+ORACLE_API void oracle_uniform(float *dst, long ld, long rows, long ncols, unsigned long long seed,
+                               unsigned long long step, long long col0, int which)
+{
+    const unsigned key[2] = {(unsigned)(seed & 0xffffffffull), (unsigned)(seed >> 32)};
+    for (long c = 0; c < ncols; c++) {
+        const long long gcol = col0 + c;
+        for (long q = 0; 4 * q < rows; q++) {
+            const unsigned ctr[4] = {(unsigned)q, (unsigned)gcol, (unsigned)which + 65536u * (unsigned)(gcol >> 32),
+                                     (unsigned)step};
+            unsigned w[4];
+            oracle_philox4x32_10(ctr, key, w);
+            for (int e = 0; e < 4 && 4 * q + e < rows; e++)
+                dst[c * ld + 4 * q + e] = (float)(w[e] >> 8) * (1.f / 16777216.f);
+        }
+    }
+}

@@ -61,6 +61,11 @@ def lib():
         L.oracle_learn_step_weight_decay_momentum.restype = None
         L.oracle_learn_step_weight_decay_momentum.argtypes = [_f32p, _f32p, _f32p, ctypes.c_long, ctypes.c_float,
                                                               ctypes.c_float, ctypes.c_float, ctypes.c_int]
+        L.oracle_philox4x32_10.restype = None
+        L.oracle_philox4x32_10.argtypes = [ctypes.c_void_p] * 3
+        L.oracle_uniform.restype = None
+        L.oracle_uniform.argtypes = [_f32p, ctypes.c_long, ctypes.c_long, ctypes.c_long, ctypes.c_ulonglong,
+                                     ctypes.c_ulonglong, ctypes.c_longlong, ctypes.c_int]
         _lib = L
     return _lib
 
@@ -206,6 +211,23 @@ def bias_sigmoid_sample(act, bias=None, u=None, nthreads=1):
         sample = np.empty_like(act, order="F")
     lib().oracle_bias_sigmoid_sample(_fp(act), _fp(bias), _fp(u), _fp(sample), act.shape[0], act.shape[1], nthreads)
     return sample
+
+
+def philox4x32_10(counter, key):
+    """The generator's block function: four counter words and two key words -> four output words."""
+    c = np.asarray(counter, dtype=np.uint32).copy()
+    k = np.asarray(key, dtype=np.uint32).copy()
+    out = np.zeros(4, dtype=np.uint32)
+    lib().oracle_philox4x32_10(c.ctypes.data, k.ctypes.data, out.ctypes.data)
+    return out
+
+
+def uniform(rows, ncols, seed, step=0, col0=0, which=0):
+    """The uniform numbers of draw ``which`` in step ``step`` for the batch columns col0 .. col0 + ncols - 1, as a
+    column-major float32 matrix (what the product path's sampling passes draw on the device)."""
+    dst = np.empty((rows, ncols), dtype=np.float32, order="F")
+    lib().oracle_uniform(_fp(dst), rows, rows, ncols, seed, step, col0, which)
+    return dst
 
 
 def learn_step_weight_decay(W, dW, learnrate, decay=0.0):

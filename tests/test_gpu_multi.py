@@ -79,6 +79,12 @@ def _rank_main(rank, world, port, out_dir):
         torch.cuda.synchronize()
         np.save(os.path.join(out_dir, "c%d.npy" % rank), np.stack([plain, s5.grad_buf.cpu().numpy()]))
     assert cb.plan_status(W5d) == 0
+    # the step that draws its uniform numbers on the device: every rank passes the global index of its first column
+    st.grad_buf.zero_()
+    st.step_drawn_allreduce(sl(V0), 77, 5, c0)
+    torch.cuda.synchronize()
+    np.save(os.path.join(out_dir, "d%d.npy" % rank), st.grad_buf.cpu().numpy())
+    np.save(os.path.join(out_dir, "s%d.npy" % rank), cb.to_host(st.V1))
     st._reducer.close()
     dist.destroy_process_group()
 
@@ -111,6 +117,14 @@ def test_two_gpu_step_and_nccl_sum_equal_the_unsharded_step(tmp_path):
     np.testing.assert_allclose(b[0], full.bias_grad.cpu().numpy(), rtol=0, atol=2e-6)
     H1p = np.concatenate([np.load(tmp_path / ("h%d.npy" % r)) for r in range(world)], axis=1)
     assert np.array_equal(H1p, cb.to_host(full.H1p))                          # the shards are the full batch's columns
+    # the drawn-sample step: the shards draw what the unsharded run draws, and the oracle restates those numbers
+    full.step_drawn(cb.to_device(V0), 77, 5, 0)
+    d = [np.load(tmp_path / ("d%d.npy" % r)) for r in range(world)]
+    assert np.array_equal(d[0], d[1])
+    np.testing.assert_allclose(d[0], full.grad_buf.cpu().numpy(), rtol=0, atol=2e-6)
+    V1 = np.concatenate([np.load(tmp_path / ("s%d.npy" % r)) for r in range(world)], axis=1)
+    assert np.array_equal(V1, cb.to_host(full.V1))
+    assert np.array_equal(V1, (cb.to_host(full.V1p) > ho.uniform(UNITS, B, 77, 5, 0, which=1)).astype(np.float32))
     # against the CPU oracle's unsharded step
     ref = rbm_oracle.cd1_step(W, V0, U_h, U_v, nthreads=8)
     tol = 1e-4 * np.sqrt(B / 128.0)

@@ -336,3 +336,42 @@ def test_cd1_step_at_config3_size():
     rhs = (dot(st.H0p, WV0) - dot(st.H1p, WV1)) / nb
     scale = (dot(st.H0p, WV0.abs()) + dot(st.H1p, WV1.abs())) / nb
     assert abs(lhs - rhs) <= 1e-5 * scale
+
+
+@pytest.mark.parametrize("rows,ncols,ld_pad", [(1024, 33, 0), (1001, 7, 3), (6, 5, 0)])
+def test_device_drawn_uniforms_equal_the_oracle(rows, ncols, ld_pad):
+    """cuvdia_uniform_f32 against the CPU restatement of the generator, bit for bit, with a column offset (what a
+    rank that holds a shard of the batch passes) and a padded leading dimension."""
+    import cuv_b200 as cb
+    buf = cb.colmajor_empty(rows + ld_pad, ncols)
+    buf.fill_(-1.0)
+    cb.fill_rnd_uniform(buf[:rows], seed=0x1234567890abcdef, step=3, col0=2 ** 33 + 5, which=1)
+    want = ho.uniform(rows, ncols, seed=0x1234567890abcdef, step=3, col0=2 ** 33 + 5, which=1)
+    assert_bits_equal(cb.to_host(buf[:rows]), want, "uniform numbers")
+    if ld_pad:
+        assert (buf[rows:] == -1.0).all()
+
+
+@pytest.mark.parametrize("units,nd,nb", [(1024, 64, 96), (1001, 37, 50)])
+def test_step_with_drawn_samples_equals_the_step_on_those_numbers(units, nd, nb):
+    """The step that draws its uniform numbers inside the element-wise passes gives, bit for bit, the step that reads
+    them from memory when those tensors hold the same numbers - which the oracle produces too - so every parity check
+    of the precomputed-number step carries over; with a column shard (col0) as a rank of a sharded run passes it."""
+    import cuv_b200 as cb
+    from cuv_b200 import rbm
+    offs = np.arange(-(nd // 2), nd - nd // 2, dtype=np.int32)
+    W, V0, _, _ = rbm_oracle.make_inputs(1009, units, units, offs, nb, w_std=0.05)
+    seed, step, col0 = 99, 4, 1000
+    U_h = ho.uniform(units, nb, seed, step, col0, which=0)
+    U_v = ho.uniform(units, nb, seed, step, col0, which=1)
+    ref = run_gpu_step(cb, W, V0, U_h, U_v, mode=cb.MODE_FAST)
+    Wd = cb.dev_dia_matrix_f(W.h, W.w, W.offsets, W.stride, W.rf).set_vec(W.vals)
+    st = rbm.SparseRBMStep(Wd, nb, None, cb.MODE_FAST)
+    st.step_drawn(cb.to_device(V0), seed, step, col0)
+    for name in ("H0p", "H0", "V1p", "V1", "H1p"):
+        assert_bits_equal(cb.to_host(getattr(st, name)), cb.to_host(getattr(ref, name)), name)
+    assert_bits_equal(st.G.vec.cpu().numpy(), ref.G.vec.cpu().numpy(), "G")
+    assert_bits_equal(st.bias_grad.cpu().numpy(), ref.bias_grad.cpu().numpy(), "bias gradients")
+    # and the samples are the oracle's comparison of the GPU's probabilities with the oracle's numbers
+    assert np.array_equal(cb.to_host(st.H0), (cb.to_host(st.H0p) > U_h).astype(np.float32))
+    assert np.array_equal(cb.to_host(st.V1), (cb.to_host(st.V1p) > U_v).astype(np.float32))

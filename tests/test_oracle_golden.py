@@ -230,3 +230,24 @@ def test_avg_diagonals_fixture():
     A.vals[10:12] = [10, 20]           # diagonal -2: cells (2,0) (3,1), stored at rows 2, 3
     out = np.zeros(3, dtype=np.float32)
     assert ho.avg_diagonals(out, A).tolist() == [2.0, 5.0, 15.0]
+
+
+def test_philox_known_answers():
+    """The generator behind the product path's device-drawn uniform numbers, against the known-answer vectors its
+    authors publish for Philox4x32 with 10 rounds (counter, key -> output), and the mapping to [0, 1)."""
+    kat = [
+        ((0, 0, 0, 0), (0, 0), (0x6627e8d5, 0xe169c58d, 0xbc57ac4c, 0x9b00dbd8)),
+        ((0xffffffff,) * 4, (0xffffffff,) * 2, (0x408f276d, 0x41c83b0e, 0xa20bc7c6, 0x6d5451fd)),
+        ((0x243f6a88, 0x85a308d3, 0x13198a2e, 0x03707344), (0xa4093822, 0x299f31d0),
+         (0xd16cfe09, 0x94fdcceb, 0x5001e420, 0x24126ea1)),
+    ]
+    for ctr, key, want in kat:
+        assert tuple(int(x) for x in ho.philox4x32_10(ctr, key)) == want
+    # element (row, column) of draw `which` in step `step`: word row % 4 of the block with counter
+    # (row / 4, column, which, step), as (word >> 8) * 2^-24
+    u = ho.uniform(7, 3, seed=0x299f31d0a4093822, step=0x03707344, col0=0x85a308d3 - 1, which=0)
+    blk = ho.philox4x32_10((1, 0x85a308d3, 0, 0x03707344), (0xa4093822, 0x299f31d0))
+    assert u[4, 1] == np.float32(int(blk[0]) >> 8) * np.float32(2.0 ** -24)
+    assert u[6, 1] == np.float32(int(blk[2]) >> 8) * np.float32(2.0 ** -24)
+    big = ho.uniform(1000, 40, seed=7, step=1, which=1)
+    assert 0.0 <= big.min() and big.max() < 1.0 and abs(big.mean() - 0.5) < 0.01
