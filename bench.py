@@ -804,6 +804,11 @@ def measure_single(args, cfg):
         S = cb.colmajor_empty(h, nb)
         fn = lambda: cb.bias_sigmoid_sample_sum(X, vec, Y[:h] if w >= h else X, S, vec2, False, 1.0 / nb, 0.0)
         byts, flops = 16 * h * nb + 4 * h, 5.0 * h * nb
+    elif op == "glue_draw":
+        # the same pass with the uniform numbers drawn in registers (12 bytes per element + the sums)
+        S = cb.colmajor_empty(h, nb)
+        fn = lambda: cb.bias_sigmoid_draw_sum(X, vec, S, vec2, 1234, 0, 0, 0, False, 1.0 / nb, 0.0)
+        byts, flops = 12 * h * nb + 4 * h, 5.0 * h * nb
     elif op == "update":
         # the weight update of the step over the diagonals' whole value array (12 bytes per value)
         Gd = torch.empty_like(A.vec).uniform_(-1, 1)

@@ -220,7 +220,6 @@ prod_windown_tma_kernel(const __grid_constant__ CUtensorMap mapA, const WindowTm
     const int ngroups = (P.nd + U - 1) / U;
     const int nstages = ngroups * P.tiles;              // coefficient stages the block consumes, tile after tile
 
-    for (int k = tid; k < ngroups * U; k += T + 32) s_p4[k] = 4 * (o0 + (k < P.nd ? P.offs[k] : P.off_min) - lo);
     if (tid == 0) {
         for (int s = 0; s < P.nseg; s++) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(wn_smem_u32(&wbar[s])));
 #pragma unroll
@@ -231,13 +230,19 @@ prod_windown_tma_kernel(const __grid_constant__ CUtensorMap mapA, const WindowTm
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    for (int g = tid; g < ngroups; g += T + 32) {
-        int mn = s_p4[g * U], mx = mn;
+    // From here on the producer warp and the consumers go separate ways: the copies are under way while the consumers
+    // build their tables (which need the offsets from global memory) and meet at a barrier of their own.
+    if (warp != T / 32) {
+        for (int k = tid; k < ngroups * U; k += T) s_p4[k] = 4 * (o0 + (k < P.nd ? P.offs[k] : P.off_min) - lo);
+        asm volatile("bar.sync 1, %0;" ::"n"(T) : "memory");
+        for (int g = tid; g < ngroups; g += T) {
+            int mn = s_p4[g * U], mx = mn;
 #pragma unroll
-        for (int u = 1; u < U; u++) { mn = min(mn, s_p4[g * U + u]); mx = max(mx, s_p4[g * U + u]); }
-        s_gmin[g] = mn >> 2; s_gmax[g] = mx >> 2;
+            for (int u = 1; u < U; u++) { mn = min(mn, s_p4[g * U + u]); mx = max(mx, s_p4[g * U + u]); }
+            s_gmin[g] = mn >> 2; s_gmax[g] = mx >> 2;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(T) : "memory");
     }
-    __syncthreads();
 
     if (warp == T / 32) {
         // ================= producer warp =================
