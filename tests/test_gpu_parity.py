@@ -124,6 +124,44 @@ def test_prod_steep_band_wide_batches(cb, trans, h, w, rf, lo, nd, ncols, fab, f
     prod_case(cb, rng, h, w, offs, rf, ncols, trans, fab, fc)
 
 
+@pytest.mark.parametrize("trans", ["n", "t"])
+@pytest.mark.parametrize("h,w,nd,spread,ncols,fab,fc", [
+    (1500, 1404, 70, None, 40, 1.0, 0.0),       # ragged last row tile, 70 diagonals (not a multiple of 8), five column groups
+    (1500, 1403, 70, None, 40, 1.5, 0.5),       # w not a multiple of 4: the last rows of a column are copied by hand
+    (3000, 3000, 33, 600, 64, 1.0, 0.0),        # offsets within +-600: the small window (two blocks per SM)
+    (2200, 2200, 1100, None, 32, 1.0, 0.0),     # more than 1024 diagonals: the variant that fetches its coefficients
+    (700, 5000, 64, None, 36, 2.0, 1.0),        # much wider than tall: most of the window lies beyond the outputs' rows
+])
+def test_prod_scattered_staged_window(cb, trans, h, w, nd, spread, ncols, fab, fc):
+    """Scattered diagonals with row factor 1 on operands that allow TMA (16-byte aligned, leading dimensions that are
+    multiples of 4, NaN in the padding rows of B and in the padding cells of the diagonals): the staged-window kernels of
+    prod_windown.cu, bit for bit against the host loop."""
+    rng = np.random.default_rng(h + w + nd + (trans == "t"))
+    lo, hi = (-spread, spread) if spread else (-h + 1, w - 1)
+    offs = scattered_offsets(rng, nd, lo, hi, sort=(nd % 2 == 0))
+    A = make_dia(rng, h, w, offs, 1, stride=(h + 3) // 4 * 4)
+    rb, rc = (h, w) if trans == "t" else (w, h)
+    B = F(rng.uniform(-1, 1, (rb, ncols)))
+    C0 = F(rng.uniform(-1, 1, (rc, ncols)))
+    if fc == 0:
+        C0[:] = np.nan
+    want = C0.copy(order="F")
+    ho.prod(want, A, B, trans, fab, fc, nthreads=8)
+    D = to_dev_dia(A)
+    for mode in (cb.MODE_EXACT, cb.MODE_FAST):
+        Cd = cb.to_device(C0)
+        cb.prod(Cd, D, dev_padded(cb, B), trans, "n", fab, fc, mode)
+        got = cb.to_host(Cd)
+        if mode == cb.MODE_EXACT:
+            assert_bits_equal(got, want, "staged-window prod %s" % trans)
+        else:
+            Aabs = ho.DiaHost(h, w, A.offsets, A.stride, 1, np.abs(np.nan_to_num(A.vals)))
+            mag = F(np.abs(np.nan_to_num(C0)) * abs(fc))
+            ho.prod(mag, Aabs, F(np.abs(B)), trans, abs(fab), 1.0, nthreads=8)
+            assert np.all(np.abs(got.astype(np.float64) - want) <= 1e-5 * mag + 1e-30)
+    assert cb.plan_status(D) == 0
+
+
 def test_prod_config0_shape(cb):
     """BASELINE config 0: 4096x4096, 64 sorted scattered diagonals, batch 128, factors 1/0."""
     rng = np.random.Generator(np.random.PCG64(1000))
