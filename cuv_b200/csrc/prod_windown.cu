@@ -297,6 +297,12 @@ prod_windown_tma_kernel(const __grid_constant__ CUtensorMap mapA, const WindowTm
             }
             issue_coef(n);
         }
+        // A segment that none of the block's (row, diagonal) pairs touches is waited for by no consumer: the warp
+        // that started the copies stays until each of them has landed (bounded), so that the block cannot end - and
+        // its shared memory be handed on - with a copy still on its way.
+        if (lane == 0)
+            for (int sg = 0; sg < P.nseg; sg++)
+                if (!wn_wait(&wbar[sg], 0, SPIN_LIMIT)) { *P.status = 8; break; }
         return;
     }
 

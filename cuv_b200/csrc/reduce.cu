@@ -394,17 +394,18 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH
 
 // Device address of the static scratch on the current device (looked up on the first call per device).
 static int noalloc_scratch_ptr(void** out) {
-    static void* cached[64] = {nullptr};
+    // two host threads may make the first call on a device at once: both look the address up and store the same value
+    static std::atomic<void*> cached[64];
     int dev = 0;
     CUVDIA_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) { set_last_error("device index %d out of range", dev); return CUVDIA_ERR_UNSUPPORTED; }
-    if (!cached[dev]) {
-        void* p = nullptr;
+    void* p = cached[dev].load(std::memory_order_acquire);
+    if (!p) {
         cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
         if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_noalloc_scratch)");
-        cached[dev] = p;
+        cached[dev].store(p, std::memory_order_release);
     }
-    *out = cached[dev];
+    *out = p;
     return CUVDIA_OK;
 }
 

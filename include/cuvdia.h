@@ -221,6 +221,8 @@ CUVDIA_API int cuvdia_reduce(void* dst, int dst_type, const void* src, int src_t
  *    clearing: each call writes every slot it later reads).  Two calls that overlap on the GPU -
  *    different streams or different host threads - race on it; run them in one stream or
  *    serialise them.
+ *  - It always takes the general split kernels; for very short lines, where cuvdia_reduce_f32 has
+ *    sub-warp and grouped variants, it is slower than that entry point (same results).
  * Arguments, semantics and results are those of cuvdia_reduce_f32.
  * ------------------------------------------------------------------------------------------- */
 CUVDIA_API int cuvdia_reduce_noalloc_f32(float* dst, const float* src, long long n_contig, long long n_strided,

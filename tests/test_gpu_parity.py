@@ -162,6 +162,16 @@ def test_prod_scattered_staged_window(cb, trans, h, w, nd, spread, ncols, fab, f
     assert cb.plan_status(D) == 0
 
 
+def test_prod_staged_window_with_untouched_segments(cb):
+    """Two clusters of diagonals far apart: the middle of the staged window is copied but touched by no term (the warp
+    that issues the copies waits for them all the same)."""
+    rng = np.random.default_rng(4242)
+    h = w = 4096
+    offs = np.concatenate([np.arange(-2040, -2040 + 3 * 11, 3), np.arange(2000, 2000 + 2 * 13, 2)]).astype(np.int32)
+    prod_case(cb, rng, h, w, offs, 1, 48, "n", 1.0, 0.0)
+    prod_case(cb, rng, h, w, offs, 1, 48, "t", 0.5, 2.0)
+
+
 def test_prod_config0_shape(cb):
     """BASELINE config 0: 4096x4096, 64 sorted scattered diagonals, batch 128, factors 1/0."""
     rng = np.random.Generator(np.random.PCG64(1000))
