@@ -249,7 +249,7 @@ def workload_name(case, cfg):
 # ---------------------------------------------------------------------------------------------------
 
 def binding_bound(byts, flops, ms, hbm_peak, fp32_peak):
-    """SURVEY-style roofline position of one routine: t_min = max(bytes / HBM peak, flops / FP32 peak); the larger
+    """Roofline position of one routine: t_min = max(bytes / HBM peak, flops / FP32 peak); the larger
     term names the bound and frac = t_min / t_measured."""
     t_mem, t_fp = byts / (hbm_peak * 1e9), flops / (fp32_peak * 1e12)
     t = ms * 1e-3
