@@ -451,7 +451,11 @@ def run_ours(args, cfg):
         hV0 = torch.empty((nb, units), dtype=torch.float32, pin_memory=True)
         hUh, hUv = torch.empty_like(hV0, pin_memory=True), torch.empty_like(hV0, pin_memory=True)
         hV0.copy_(V0.t()); hUh.copy_(U_h.t()); hUv.copy_(U_v.t())
-        hG = torch.empty(step.G.vec.numel(), dtype=torch.float32, pin_memory=True) if rank == 0 else None
+        # the gradients go back to the host every step: after the all-reduce every rank holds them all, so each rank
+        # sends its own 1/N of the diagonals' array over its own link (rank 0 also the bias gradients)
+        n_g = step.G.vec.numel()
+        g_lo, g_hi = (n_g * rank) // world, (n_g * (rank + 1)) // world
+        hG = torch.empty(g_hi - g_lo, dtype=torch.float32, pin_memory=True)
         hb = torch.empty(step.bias_grad.numel(), dtype=torch.float32, pin_memory=True) if rank == 0 else None
 
         def measure_e2e(drawn_inputs):
@@ -464,7 +468,7 @@ def run_ours(args, cfg):
                 for i in range(k):
                     if i + 1 < k:
                         fed.submit(*host_in)
-                    fed.run(hG, hb) if rank == 0 else fed.run()
+                    fed.run(hG, hb, (g_lo, g_hi))
                 fed.wait()
 
             e2e_steps(2)
@@ -484,7 +488,7 @@ def run_ours(args, cfg):
             s0.record()
             for i in range(args.steps):
                 fed.submit(*host_in)
-                fed.run(hG, hb) if rank == 0 else fed.run()
+                fed.run(hG, hb, (g_lo, g_hi))
             fed.wait()
             s1.record()
             barrier()
@@ -521,10 +525,10 @@ def run_ours(args, cfg):
                             "previous step's compute; the uniform numbers of the two samples are drawn on the device "
                             "inside the element-wise passes (cuvdia_bias_sigmoid_draw_sum_f32), as the reference draws "
                             "them on the device (rnd_binarize, random/random.cu:139-156); gradients read back to pinned "
-                            "host memory every step") if drawn_inputs else
+                            "host memory every step, every rank its 1/N of the diagonals over its own link") if drawn_inputs else
                            ("pinned host inputs (V0, U_h, U_v) copied to the device every step on a copy stream, "
                             "overlapped with the previous step's compute; gradients read back to pinned host memory "
-                            "every step")}
+                            "every step, every rank its 1/N of the diagonals over its own link")}
 
         e2e = measure_e2e(drawn)
         if drawn:

@@ -322,9 +322,11 @@ class HostFedRBM:
                 self.ready[slot][k].record(self.h2d)
         self.n_sub += 1
 
-    def run(self, hG=None, hbias=None):
+    def run(self, hG=None, hbias=None, g_range=None):
         """Compute the oldest submitted step; if host buffers are given, queue the read-back of its
-        gradients into them."""
+        gradients into them.  ``g_range=(lo, hi)``: hG receives only the values lo .. hi-1 of the diagonals' array -
+        after the all-reduce every rank holds the whole gradient, so each rank can send its own share to the host over
+        its own link (hbias may then be None on all ranks but one)."""
         import torch
         cur = torch.cuda.current_stream()
         slot = self.n_run % 2
@@ -347,9 +349,11 @@ class HostFedRBM:
             self.grads_done.record(cur)
             self.d2h.wait_event(self.grads_done)
             with torch.cuda.stream(self.d2h):
-                hbias.copy_(self.step.bias_grad, non_blocking=True)
+                if hbias is not None:
+                    hbias.copy_(self.step.bias_grad, non_blocking=True)
                 self.bias_fetched.record(self.d2h)
-                hG.copy_(self.step.G.vec, non_blocking=True)
+                src = self.step.G.vec if g_range is None else self.step.G.vec[g_range[0]:g_range[1]]
+                hG[:src.numel()].copy_(src, non_blocking=True)
                 self.fetched.record(self.d2h)
             self._fetch_pending = True
 
