@@ -46,21 +46,22 @@ struct WindowNParams {
     const float* A; const int* offs; const float* B; float* C;
 };
 
-template <bool TRANS, bool EXACT, int PITCH>
+// CBK: batch columns per block (8, or 4 for windows of more than 6400 rows).
+template <bool TRANS, bool EXACT, int PITCH, int CBK>
 __global__ void __launch_bounds__(pwn::T)
 prod_windown_kernel(const WindowNParams P) {
     using namespace pwn;
-    extern __shared__ __align__(16) float win[];        // [CB][PITCH]
+    extern __shared__ __align__(16) float win[];        // [CBK][PITCH]
     __shared__ int s_j[OFFS + U];                       // per diagonal of the pass: tile's first row + offset
     const int tid = threadIdx.x;
     const int o0 = blockIdx.x * T * P.tiles;            // first output row of the block
-    const int c0 = blockIdx.y * CB;
+    const int c0 = blockIdx.y * CBK;
     const int lo = max(0, TRANS ? o0 - P.off_max : o0 + P.off_min) & ~3;      // first staged B row, on a 16-byte boundary
     const int rows_b = TRANS ? P.h : P.w, rows_out = TRANS ? P.w : P.h;
     // ---- stage the window: element (row lo+rr, column c0+c) -> win[c*PITCH + rr]; rows or columns outside the
     // operand arrive as zeros (source size 0) ----
 #pragma unroll
-    for (int c = 0; c < CB; c++) {
+    for (int c = 0; c < CBK; c++) {
         const int col = c0 + c;
         const float* src = P.B + (size_t)min(col, P.ncols - 1) * P.ldb;
         const unsigned dst0 = (unsigned)__cvta_generic_to_shared(win + c * PITCH);
@@ -80,9 +81,9 @@ prod_windown_kernel(const WindowNParams P) {
         const bool row_ok = o < rows_out;
         // a row past the end of the matrix gets a row number that puts every term outside the matrix
         const int tj = row_ok ? tid : -(1 << 29);
-        float acc[CB];
+        float acc[CBK];
 #pragma unroll
-        for (int c = 0; c < CB; c++) {
+        for (int c = 0; c < CBK; c++) {
             acc[c] = 0.f;
             if (P.fc != 0.f && row_ok && c0 + c < P.ncols) acc[c] = __fmul_rn(P.C[(size_t)(c0 + c) * P.ldc + o], P.fc);
         }
@@ -118,7 +119,7 @@ prod_windown_kernel(const WindowNParams P) {
                     const float2 aa = make_float2(av, av);
                     const float* wp = win + pos[u];
 #pragma unroll
-                    for (int c = 0; c < CB; c += 2) {
+                    for (int c = 0; c < CBK; c += 2) {
                         const float2 x = make_float2(wp[c * PITCH], wp[(c + 1) * PITCH]);
                         if (EXACT) {
                             const float2 pr = __fmul2_rn(aa, x);
@@ -134,7 +135,7 @@ prod_windown_kernel(const WindowNParams P) {
         }
         if (row_ok) {
 #pragma unroll
-            for (int c = 0; c < CB; c++)
+            for (int c = 0; c < CBK; c++)
                 if (c0 + c < P.ncols) P.C[(size_t)(c0 + c) * P.ldc + o] = acc[c];
         }
     }
@@ -373,8 +374,8 @@ prod_windown_tma_kernel(const __grid_constant__ CUtensorMap mapA, const WindowTm
 }
 
 // Row tiles a block works through with one staged window (1, 2, 4 or 8) and the staged rows per column; 0 if the
-// kernel does not apply: row factor 1, 16-byte aligned B, at least 32 batch columns (8 per block), and a window of
-// at most 6400 rows.  Several tiles per block pay when the offsets span far more rows than a tile and the grid still
+// kernel does not apply: row factor 1, 16-byte aligned B, at least 32 batch columns (8 per block, 4 where the window
+// has more than 6400 rows), and a window of at most 12800 rows.  Several tiles per block pay when the offsets span far more rows than a tile and the grid still
 // fills the GPU.
 static int windown_shape(const cuvdia_plan* p, bool trans, const float* B, int ldb, int ncols, int* wrows_out) {
     using namespace pwn;
@@ -386,9 +387,9 @@ static int windown_shape(const cuvdia_plan* p, bool trans, const float* B, int l
         if (nt > 1 && (long long)T * nt > rows_out) break;
         // rows a block's outputs can touch, plus up to 3 for the 16-byte boundary the window starts on
         const long long wrows = std::min<long long>((long long)T * nt + span + 3, rows_b + 3);
-        if (wrows > 6400) break;
+        if (wrows > 12800) break;                               // 6400 rows x 8 columns, or 12800 x 4
         const long long blocks = ((rows_out + T * nt - 1) / (T * nt)) * ((ncols + CB - 1) / CB);
-        if (nt > 1 && (blocks < sm_count() || span < 4LL * T * nt)) break;
+        if (nt > 1 && (blocks < sm_count() || span < 4LL * T * nt || wrows > 6400)) break;
         best = nt;
         *wrows_out = (int)((wrows + 3) / 4 * 4);
     }
@@ -404,16 +405,16 @@ bool prod_windown_applicable(const cuvdia_plan* p, bool trans, const float* A, c
     return windown_shape(p, trans, B, ldb, ncols, &wrows) > 0;
 }
 
-template <bool TRANS, bool EXACT, int PITCH>
+template <bool TRANS, bool EXACT, int PITCH, int CBK>
 static int launch_windown_t(const WindowNParams& P, int rows_out, cudaStream_t st) {
     using namespace pwn;
-    const size_t smem = sizeof(float) * ((size_t)(CB - 1) * PITCH + (size_t)P.wrows);
+    const size_t smem = sizeof(float) * ((size_t)(CBK - 1) * PITCH + (size_t)P.wrows);
     static bool attr_done[64] = {false};
-    const int arc = allow_dynamic_smem(prod_windown_kernel<TRANS, EXACT, PITCH>, sizeof(float) * (size_t)CB * PITCH, attr_done);
+    const int arc = allow_dynamic_smem(prod_windown_kernel<TRANS, EXACT, PITCH, CBK>, sizeof(float) * (size_t)CBK * PITCH, attr_done);
     if (arc) return arc;
-    const int gx = (rows_out + T * P.tiles - 1) / (T * P.tiles), gy = (P.ncols + CB - 1) / CB;
+    const int gx = (rows_out + T * P.tiles - 1) / (T * P.tiles), gy = (P.ncols + CBK - 1) / CBK;
     if (gy > 65535) { set_last_error("too many batch columns"); return CUVDIA_ERR_UNSUPPORTED; }
-    prod_windown_kernel<TRANS, EXACT, PITCH><<<dim3(gx, gy), T, smem, st>>>(P);
+    prod_windown_kernel<TRANS, EXACT, PITCH, CBK><<<dim3(gx, gy), T, smem, st>>>(P);
     count_launch();
     return check_launch("prod_windown_kernel");
 }
@@ -490,15 +491,17 @@ int launch_prod_windown(const cuvdia_plan* p, const float* A, const float* B, in
     P.ldb = ldb; P.ldc = ldc; P.ncols = ncols; P.off_min = p->off_min; P.off_max = p->off_max; P.wrows = wrows;
     P.fa = fa; P.fc = fc; P.A = A; P.offs = p->d_offsets; P.B = B; P.C = C;
     const bool exact = mode == CUVDIA_MODE_EXACT;
-    // the pitch is a compile-time constant: the smallest of three that holds the window (4, 2 or 1 blocks per SM)
-#define GO(PV)                                                                                          \
+    // the pitch is a compile-time constant: the smallest of four that holds the window (4, 2 or 1 blocks per SM; the
+    // largest with 4 instead of 8 columns per block)
+#define GO(PV, CV)                                                                                      \
     do {                                                                                                \
-        if (trans) return exact ? launch_windown_t<true, true, PV>(P, p->w, st) : launch_windown_t<true, false, PV>(P, p->w, st); \
-        return exact ? launch_windown_t<false, true, PV>(P, p->h, st) : launch_windown_t<false, false, PV>(P, p->h, st);        \
+        if (trans) return exact ? launch_windown_t<true, true, PV, CV>(P, p->w, st) : launch_windown_t<true, false, PV, CV>(P, p->w, st); \
+        return exact ? launch_windown_t<false, true, PV, CV>(P, p->h, st) : launch_windown_t<false, false, PV, CV>(P, p->h, st);        \
     } while (0)
-    if (wrows <= 1600) GO(1600);
-    if (wrows <= 3200) GO(3200);
-    GO(6400);
+    if (wrows <= 1600) GO(1600, 8);
+    if (wrows <= 3200) GO(3200, 8);
+    if (wrows <= 6400) GO(6400, 8);
+    GO(12800, 4);
 #undef GO
 }
 
