@@ -729,9 +729,11 @@ def measure_single(args, cfg):
     mode = cb.MODE_FAST if args.mode == "fast" else cb.MODE_EXACT
     rng = np.random.Generator(np.random.PCG64(1000))
     case = args.case
-    if case == "cfg0":
+    if case in ("cfg0", "cfg0_t"):
+        # cfg0_t: the transposed product on config 0's matrix (not a BASELINE configuration)
         h = w = 4096; nb = 128; rf = 1
-        offs = np.sort(rng.choice(np.arange(-2047, 2048), 64, replace=False)).astype(np.int32); op = "prod_n"
+        offs = np.sort(rng.choice(np.arange(-2047, 2048), 64, replace=False)).astype(np.int32)
+        op = "prod_n" if case == "cfg0" else "prod_t"
     elif case == "cfg1":
         h, w, nb, rf = 16384, 4096, 512, 4
         offs = np.arange(-128, 128, dtype=np.int32); op = "prod_t"
