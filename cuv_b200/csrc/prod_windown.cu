@@ -427,8 +427,9 @@ static int windown_tma_shape(const cuvdia_plan* p, const float* A, const float* 
                              int* wrows_out) {
     using namespace pwn;
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    // (row numbers are compared as byte offsets in 32 bits inside the kernel: matrices of up to 2^29 rows and columns)
     if (p->rf != 1 || !al16(A) || !al16(B) || ldb % 4 != 0 || p->stride % 4 != 0 || ncols < 32 || p->nd > NDMAX ||
-        !tma_available())
+        p->h >= (1 << 29) || p->w >= (1 << 29) || !tma_available())
         return 0;
     const long long span = (long long)p->off_max - p->off_min;
     int best = 0;
