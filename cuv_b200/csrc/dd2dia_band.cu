@@ -1,9 +1,10 @@
-// densedense_to_dia for a banded pattern (consecutive ascending diagonals, row_fact 1).
+// densedense_to_dia for a banded pattern (consecutive ascending diagonals; row_fact 1, or a power of two up
+// to 32 - a "steep" band, the local receptive fields of a layer that shrinks by row_fact).
 //
-//   G[k][i] = factC*G[k][i] + factAB * sum_b A[i,b] * B[i+lo+k, b],   k = 0..nd-1
+//   G[k][i] = factC*G[k][i] + factAB * sum_b A[i,b] * B[i/rf+lo+k, b],   k = 0..nd-1
 //
 // is the product A*B^T restricted to a band, so it is computed as dense 128 x 128 tiles of A*B^T
-// that cover the band: block (ti, t, z) owns rows i0 = 128*ti of A, rows j0 = i0 + lo - rem + 128*t
+// that cover the band: block (ti, t, z) owns rows i0 = 128*ti of A, rows j0 = i0/rf + lo - rem + 128*t
 // of B and the z-th share of the batch.  Both operands are column-major, so a tile of 128 rows x 32
 // batch columns is one TMA box (cp.async.bulk.tensor, no multicast) and lands in shared memory as
 // [batch column][row]: exactly the layout an outer-product inner loop wants - per batch column a
@@ -65,6 +66,7 @@ __device__ __forceinline__ void dmbar_wait_short(unsigned long long* bar, unsign
 
 struct DdBandParams {
     int h, w, nd, lo, S, ncols;
+    int rf, rf_shift;   // row factor (a power of two) and its logarithm
     int rem;            // lo mod 4 (non-negative): keeps the TMA row coordinate of B 16-byte aligned
     int nsplit;
     int tile0, ntiles;  // this launch covers column tiles tile0 .. tile0 + gridDim.x - 1 of the ntiles of a row block
@@ -121,7 +123,7 @@ dd2dia_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
     // adjacent row blocks share most B tiles, so both operands come from HBM about once
     const int i0 = blockIdx.y * TI;
     const int tile = P.tile0 + (int)blockIdx.x;
-    const int j0 = i0 + P.lo - P.rem + tile * TJ;
+    const int j0 = (i0 >> P.rf_shift) + P.lo - P.rem + tile * TJ;
     const int z = blockIdx.z;
     const int nch_all = (P.ncols + KB - 1) / KB;
     const int ch0 = (int)((long long)nch_all * z / P.nsplit), ch1 = (int)((long long)nch_all * (z + 1) / P.nsplit);
@@ -132,7 +134,8 @@ dd2dia_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
     // rows ..63 x columns 64.. is not either when the band ends at or before the tile's main diagonal, and when it
     // ends 63 or more diagonals before it only the quadrant rows 64.. x columns ..63 is left.
     const int dlast = P.nd + P.rem - TJ * tile;                   // cells of this tile need jc - ir < dlast
-    const int skip = tile == 0 ? 1 : (tile == P.ntiles - 1 && dlast <= 1) ? (dlast <= -63 ? 3 : 2) : 0;
+    // (with a row factor the band crosses a tile at another slope: no quadrant is left out)
+    const int skip = P.rf != 1 ? 0 : tile == 0 ? 1 : (tile == P.ntiles - 1 && dlast <= 1) ? (dlast <= -63 ? 3 : 2) : 0;
 
     constexpr unsigned TX_BYTES = sizeof(float) * 2 * TILE_FLOATS;
     auto issue = [&](int c) {
@@ -202,7 +205,7 @@ dd2dia_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
 #pragma unroll
         for (int jj = 0; jj < 8; jj++) {
             const int j = j0 + 4 * cg + (jj & 3) + (jj >> 2) * 64;
-            const int k = j - i - P.lo;
+            const int k = j - (i >> P.rf_shift) - P.lo;
             if ((unsigned)k >= (unsigned)P.nd || (unsigned)j >= (unsigned)P.w) continue;
             const float v = (jj & 1) ? acc[ii][jj >> 1].y : acc[ii][jj >> 1].x;
             float* cell = out + (size_t)k * P.S + i;
@@ -219,9 +222,17 @@ dd2dia_band_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
 
 static inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+static int band_tiles(const cuvdia_plan* p);
+
+// Row factor 1, or a power of two up to 32 (a tile's first B row, i0 / rf, must stay a multiple of 4) when the dense
+// tiles are at least three tenths band: the staged-window kernel, which the steep band would otherwise take, runs at
+// a quarter of the FP32 rate but computes nothing beside the band.
 bool dd2dia_band_applicable(const cuvdia_plan* p, const float* A, int lda, const float* B, int ldb, int ncols) {
-    return p->is_band && p->rf == 1 && al16(A) && al16(B) && lda % 4 == 0 && ldb % 4 == 0 && ncols >= 1 &&
-           p->nd >= 16 && tma_available();
+    if (!(p->is_band && al16(A) && al16(B) && lda % 4 == 0 && ldb % 4 == 0 && ncols >= 1 && p->nd >= 16 && tma_available()))
+        return false;
+    if (p->rf == 1) return true;
+    if (!(p->rf == 2 || p->rf == 4 || p->rf == 8 || p->rf == 16 || p->rf == 32)) return false;
+    return 10LL * p->nd >= 3LL * db::TJ * band_tiles(p) && ncols >= 64;
 }
 
 // Column tiles per row block, and how a call may be cut in two launches so that the diagonals' array is finished
@@ -229,7 +240,8 @@ bool dd2dia_band_applicable(const cuvdia_plan* p, const float* A, int lda, const
 // 0 .. 128(T-1) - rem are complete (they are contiguous in memory: a band is stored in ascending order).
 static int band_tiles(const cuvdia_plan* p) {
     const int rem = ((p->band_lo % 4) + 4) % 4;
-    return (p->nd + db::TI - 1 + rem + db::TJ - 1) / db::TJ;
+    // the rows of B a block of 128 rows of A touches: rem + (0 .. 127) / rf + (0 .. nd-1)
+    return (p->nd + (db::TI - 1) / p->rf + rem + db::TJ - 1) / db::TJ;
 }
 
 // Finds a cut T (tiles 0..T-1, then T..gy-1) that needs no more waves of blocks than the uncut grid and finishes as
@@ -241,7 +253,7 @@ int dd2dia_band_cut(const cuvdia_plan* p, int ncols, int* first_diagonals, bool 
     const int gx = (p->h + db::TI - 1) / db::TI, gy = band_tiles(p);
     const long long slots = 2LL * sm_count();
     auto waves = [&](long long ctas) { return (ctas + slots - 1) / slots; };
-    if (gy < (force ? 3 : 4)) return 0;
+    if (gy < (force ? 3 : 4) || p->rf != 1) return 0;
     int best = 0, best_dist = 1 << 30;
     for (int T = 2; T < gy; T++) {
         if (!force && waves((long long)gx * T) + waves((long long)gx * (gy - T)) > waves((long long)gx * gy)) continue;
@@ -294,6 +306,8 @@ static int launch_dd2dia_band_tiles(cuvdia_plan* p, float* Cv, const float* A, i
     DdBandParams P;
     P.h = p->h; P.w = p->w; P.nd = p->nd; P.lo = p->band_lo; P.S = p->stride; P.ncols = ncols;
     P.rem = ((p->band_lo % 4) + 4) % 4;
+    P.rf = p->rf; P.rf_shift = 0;
+    while ((1 << P.rf_shift) < p->rf) P.rf_shift++;
     P.fa = fa; P.fc = fc; P.G = Cv; P.status = p->d_status;
     const int gx = (p->h + TI - 1) / TI;
     const int gy = band_tiles(p);                                // column tiles that cover the band of one row block

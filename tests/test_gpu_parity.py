@@ -437,6 +437,20 @@ def test_dd2dia_scattered_groups_outside_the_matrix(cb, h, w, ncols):
     dd_case(cb, rng, h, w, offs, 1, ncols, 1.0, 0.0, dist="uniform")
 
 
+@pytest.mark.parametrize("rf,h,w,lo,nd,ncols,fab,fc", [
+    (4, 2048, 512, -64, 128, 200, 1.0, 0.0),       # config 1's pattern at an eighth of the size: one and a bit tiles per row block
+    (2, 1024, 600, -50, 100, 96, 0.01, 0.9),       # row factor 2, both factors, batch not a multiple of the staged chunk
+    (8, 4096, 512, -31, 200, 64, -0.5, 1.0),       # row factor 8, odd first offset
+    (4, 1020, 300, 7, 64, 130, 1.0, 0.0),          # height not a multiple of the tile, band above the diagonal
+    (32, 4096, 128, -60, 120, 64, 1.0, 0.0),       # the largest row factor the tiles take
+])
+def test_dd2dia_steep_band(cb, rf, h, w, lo, nd, ncols, fab, fc):
+    """Bands with a row factor above 1 (cell (i, k) meets row i / rf + lo + k of the second operand) on the tiled kernel."""
+    rng = np.random.default_rng(h + 7 * nd + rf)
+    offs = np.arange(lo, lo + nd, dtype=np.int32)
+    dd_case(cb, rng, h, w, offs, rf, ncols, fab, fc, addend_scale=(fc != 0))
+
+
 def test_dd2dia_convolution_pattern(cb):
     """The weight gradient of a convolution-pattern matrix (runs of consecutive diagonals one image line apart,
     two input and two output maps): neighbouring runs share the staged window."""
