@@ -9,6 +9,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
+from oracle import host_oracle as ho
 from oracle import rbm_oracle
 
 UNITS, ND, B = 256, 16, 32
@@ -36,6 +37,16 @@ def _rank_main(rank, world, port, out_dir):
     rbm.allreduce_gradients(g, bias)
     np.save(os.path.join(out_dir, "g%d.npy" % rank), g.numpy())
     np.save(os.path.join(out_dir, "b%d.npy" % rank), bias.numpy())
+    # the same with the samples' uniform numbers drawn from the generator: a rank passes the global index of its first
+    # column and so draws the numbers the unsharded run draws for those columns
+    Uh = ho.uniform(UNITS, c1 - c0, seed=5, step=2, col0=c0, which=0)
+    Uv = ho.uniform(UNITS, c1 - c0, seed=5, step=2, col0=c0, which=1)
+    part = rbm_oracle.cd1_step(W, sl(V0), Uh, Uv, batch_global=B)
+    g = torch.from_numpy(part["G"].vals.copy())
+    bias = torch.from_numpy(np.concatenate([part["gc"], part["gb"]]))
+    rbm.allreduce_gradients(g, bias)
+    np.save(os.path.join(out_dir, "dg%d.npy" % rank), g.numpy())
+    np.save(os.path.join(out_dir, "ds%d.npy" % rank), part["V1"])
     dist.destroy_process_group()
 
 
@@ -50,6 +61,12 @@ def test_two_rank_allreduce_equals_unsharded_step(tmp_path):
     np.testing.assert_allclose(g0, full["G"].vals, rtol=0, atol=2e-6)
     b0 = np.load(tmp_path / "b0.npy")
     np.testing.assert_allclose(b0, np.concatenate([full["gc"], full["gb"]]), rtol=0, atol=2e-6)
+    # drawn samples: the shards' numbers are the unsharded run's, so the samples are its columns and the sums agree
+    Uh, Uv = ho.uniform(UNITS, B, seed=5, step=2, col0=0, which=0), ho.uniform(UNITS, B, seed=5, step=2, col0=0, which=1)
+    full = rbm_oracle.cd1_step(W, V0, Uh, Uv)
+    V1 = np.concatenate([np.load(tmp_path / ("ds%d.npy" % r)) for r in range(world)], axis=1)
+    assert np.array_equal(V1, full["V1"])
+    np.testing.assert_allclose(np.load(tmp_path / "dg0.npy"), full["G"].vals, rtol=0, atol=2e-6)
 
 
 def test_shard_columns():
