@@ -162,16 +162,19 @@ namespace pwn {
 constexpr int NDMAX = 1024;          // diagonals the per-block tables hold
 constexpr int SEG = 1024;            // window rows per segment: one bulk copy per column and segment
 constexpr unsigned SPIN_LIMIT = 1u << 26;
-template <int PITCH, int NSTA> __host__ __device__ constexpr size_t tma_smem_bytes() {
-    return sizeof(float) * ((size_t)CB * PITCH + (size_t)NSTA * U * T) + sizeof(int) * (NDMAX + 2 * (NDMAX / U)) +
-           8 * ((PITCH + SEG - 1) / SEG + 2 * NSTA) + 64;
+constexpr int CP = T + 8;            // transposed product: a staged diagonal holds 516 coefficients (one row of padding words)
+template <bool TRANS> __host__ __device__ constexpr int coef_stage() { return TRANS ? U * CP : U * T; }
+template <bool TRANS, int PITCH, int NSTA> __host__ __device__ constexpr size_t tma_smem_bytes() {
+    return sizeof(float) * ((size_t)CB * PITCH + (size_t)NSTA * coef_stage<TRANS>()) +
+           sizeof(int) * ((TRANS ? 2 : 1) * NDMAX + 2 * (NDMAX / U)) + 8 * ((PITCH + SEG - 1) / SEG + 2 * NSTA) + 64;
 }
 }  // namespace pwn
 
 struct WindowTmaParams {
-    int h, w, nd;
+    int h, w, nd, S;
     int ldb, ldc, ncols;
-    int off_min;
+    int off_min, off_max;
+    const float* A;         // the diagonals' values (the transposed product copies its coefficients itself)
     int nseg;               // window segments of 1024 rows
     int tiles;              // row tiles of 512 outputs a block works through with one staged window
     float fa, fc;
@@ -199,16 +202,24 @@ __device__ __forceinline__ void wn_tma_2d(void* dst, const CUtensorMap* map, int
         ::"r"(wn_smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(wn_smem_u32(bar)) : "memory");
 }
 
-template <bool EXACT, int PITCH, int NSTA, int MINB>
+// TRANS: C = A^T B.  The term of output o on diagonal k is A[k][o - off_k] * B[o - off_k]: the window position is the
+// thread's row MINUS the offset, and the coefficient sits at the same row of the diagonal as the B value, so a block's
+// coefficients of one diagonal are 512 consecutive values starting at row (tile's first output) - off_k.  That start is
+// on no particular boundary: the producer copies, per diagonal, the 516 values from the 16-byte boundary below it (one
+// bulk copy, clipped to the diagonal's storage) and a thread adds the diagonal's shift (0..3 values, one more broadcast
+// word per term) to its own index.
+template <bool TRANS, bool EXACT, int PITCH, int NSTA, int MINB>
 __global__ void __launch_bounds__(pwn::T + 32, MINB)
 prod_windown_tma_kernel(const __grid_constant__ CUtensorMap mapA, const WindowTmaParams P) {
     using namespace pwn;
     constexpr int NSEG_MAX = (PITCH + SEG - 1) / SEG;
+    constexpr int CSTAGE = coef_stage<TRANS>();
     extern __shared__ __align__(1024) float smem[];
     float* const win = smem;                                            // [CB][PITCH]
-    float* const coef = smem + CB * PITCH;                              // [NSTA][2 halves][U][256]
-    int* const s_p4 = reinterpret_cast<int*>(coef + NSTA * U * T);      // per diagonal: 4 * (window row of the block's first output)
-    int* const s_gmin = s_p4 + NDMAX;                                   // per group of U diagonals: smallest / largest of those rows
+    float* const coef = smem + CB * PITCH;                              // 'n': [NSTA][2 halves][U][256]; 't': [NSTA][U][CP]
+    int* const s_p4 = reinterpret_cast<int*>(coef + NSTA * CSTAGE);     // per diagonal: 4 * (window row of the block's first output)
+    int* const s_c4 = s_p4 + NDMAX;                                     // 't': per diagonal, 4 * (its coefficients' shift, 0..3)
+    int* const s_gmin = s_c4 + (TRANS ? NDMAX : 0);                     // per group of U diagonals: smallest / largest of those rows
     int* const s_gmax = s_gmin + NDMAX / U;
     unsigned long long* const wbar = reinterpret_cast<unsigned long long*>(s_gmax + NDMAX / U);   // [NSEG_MAX]
     unsigned long long* const full = wbar + NSEG_MAX;                   // [NSTA]
@@ -217,7 +228,9 @@ prod_windown_tma_kernel(const __grid_constant__ CUtensorMap mapA, const WindowTm
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int o0 = blockIdx.x * T * P.tiles;            // first output row of the block
     const int c0 = blockIdx.y * CB;
-    const int lo = (o0 + P.off_min) & ~3;               // first window row (may lie before the matrix), 16-byte boundary
+    // first window row (may lie before the matrix), on a 16-byte boundary
+    const int lo = (TRANS ? o0 - P.off_max : o0 + P.off_min) & ~3;
+    const int rows_b = TRANS ? P.h : P.w, rows_out = TRANS ? P.w : P.h;
     const int ngroups = (P.nd + U - 1) / U;
     const int nstages = ngroups * P.tiles;              // coefficient stages the block consumes, tile after tile
 
@@ -234,7 +247,11 @@ prod_windown_tma_kernel(const __grid_constant__ CUtensorMap mapA, const WindowTm
     // From here on the producer warp and the consumers go separate ways: the copies are under way while the consumers
     // build their tables (which need the offsets from global memory) and meet at a barrier of their own.
     if (warp != T / 32) {
-        for (int k = tid; k < ngroups * U; k += T) s_p4[k] = 4 * (o0 + (k < P.nd ? P.offs[k] : P.off_min) - lo);
+        for (int k = tid; k < ngroups * U; k += T) {
+            const int off = k < P.nd ? P.offs[k] : (TRANS ? P.off_max : P.off_min);
+            s_p4[k] = 4 * ((TRANS ? o0 - off : o0 + off) - lo);
+            if (TRANS) s_c4[k] = 4 * ((o0 - off) & 3);
+        }
         asm volatile("bar.sync 1, %0;" ::"n"(T) : "memory");
         for (int g = tid; g < ngroups; g += T) {
             int mn = s_p4[g * U], mx = mn;
@@ -249,13 +266,35 @@ prod_windown_tma_kernel(const __grid_constant__ CUtensorMap mapA, const WindowTm
         // ================= producer warp =================
         auto issue_coef = [&](int n) {                  // stage n: tile n / ngroups, diagonals U * (n % ngroups) ..
             const int s = n % NSTA;
-            if (lane == 0) {
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;"
-                             ::"r"(wn_smem_u32(&full[s])), "r"((unsigned)(sizeof(float) * U * T)) : "memory");
-                const int row = o0 + (n / ngroups) * T, dia = (n % ngroups) * U;
-                wn_tma_2d(coef + s * U * T, &mapA, row, dia, &full[s]);
-                wn_tma_2d(coef + s * U * T + U * 256, &mapA, row + 256, dia, &full[s]);
+            const int row = o0 + (n / ngroups) * T, dia = (n % ngroups) * U;
+            if (!TRANS) {
+                if (lane == 0) {
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;"
+                                 ::"r"(wn_smem_u32(&full[s])), "r"((unsigned)(sizeof(float) * U * T)) : "memory");
+                    wn_tma_2d(coef + s * CSTAGE, &mapA, row, dia, &full[s]);
+                    wn_tma_2d(coef + s * CSTAGE + U * 256, &mapA, row + 256, dia, &full[s]);
+                }
+                return;
             }
+            // lane u copies diagonal dia + u: the rows from the 16-byte boundary at or below (tile's first output - offset),
+            // 516 of them, clipped to the diagonal's storage (rows 0 .. S-1; those past the matrix are padding nobody adds)
+            int a = 0, b = 0, x4 = 0;
+            if (lane < U && dia + lane < P.nd) {
+                x4 = (row - P.offs[dia + lane]) & ~3;
+                a = max(x4, 0); b = min(x4 + T + 4, P.S);
+                if (b < a) b = a;
+            }
+            unsigned bytes = sizeof(float) * (unsigned)(b - a), total = bytes;
+#pragma unroll
+            for (int d = 16; d >= 1; d >>= 1) total += __shfl_xor_sync(0xffffffffu, total, d);
+            const unsigned bar = wn_smem_u32(&full[s]);
+            if (lane == 0)
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(total) : "memory");
+            __syncwarp();
+            if (bytes > 0)
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(wn_smem_u32(coef + s * CSTAGE + lane * CP + (a - x4))),
+                               "l"(P.A + (size_t)(dia + lane) * P.S + a), "r"(bytes), "r"(bar) : "memory");
         };
         // the first coefficient stage, then the window segment by segment, then the ring
         issue_coef(0);
@@ -263,7 +302,7 @@ prod_windown_tma_kernel(const __grid_constant__ CUtensorMap mapA, const WindowTm
         for (int sg = 0; sg < P.nseg; sg++) {
             // the segment's rows that lie inside the matrix: whole groups of four by bulk copy, up to three more by hand
             const int r0 = lo + sg * SEG;
-            const int v0 = max(r0, 0), v1 = min(r0 + SEG, P.w);
+            const int v0 = max(r0, 0), v1 = min(r0 + SEG, rows_b);
             const int n4 = v1 > v0 ? ((v1 - v0) & ~3) : 0, tail = v1 > v0 ? (v1 - v0) - n4 : 0;
             for (int t = lane; t < tail * ncol; t += 32) {
                 const int c = t / tail, row = v0 + n4 + t % tail;
@@ -309,17 +348,18 @@ prod_windown_tma_kernel(const __grid_constant__ CUtensorMap mapA, const WindowTm
 
     // ================= consumers =================
     const int half = tid >> 8, r = tid & 255;
-    const float* const cbase = coef + half * (U * 256) + r;           // this thread's coefficient of diagonal u: cbase[u * 256]
+    // this thread's coefficient of diagonal u: 'n' cbase[u * 256]; 't' cbase[u * CP + the diagonal's shift]
+    const float* const cbase = TRANS ? coef + tid : coef + half * (U * 256) + r;
     unsigned ready = 0;                                               // window segments this warp has seen complete
     int n = 0;                                                        // coefficient stage
     for (int rt = 0; rt < P.tiles; rt++) {
         const int ob = o0 + rt * T, o = ob + tid;
-        const bool row_ok = o < P.h;
+        const bool row_ok = o < rows_out;
         // byte offset of window row (rt * T + tid) in column 0; a term adds the diagonal's s_p4
         const unsigned tb = 4u * (unsigned)(rt * T + tid);
         // a term is inside the matrix iff 0 <= lo + window row < w, i.e. (byte offset - offset of matrix row 0) < 4w
         const unsigned v0 = 4u * (unsigned)(-lo);
-        const unsigned vlim = row_ok ? 4u * (unsigned)P.w : 0u;
+        const unsigned vlim = row_ok ? 4u * (unsigned)rows_b : 0u;
         const int wrow = rt * T + (tid & ~31);                        // the warp's first window row before the offset
         float acc[CB];
 #pragma unroll
@@ -338,14 +378,15 @@ prod_windown_tma_kernel(const __grid_constant__ CUtensorMap mapA, const WindowTm
             }
             const int s = n % NSTA;
             if (!wn_wait(&full[s], (n / NSTA) & 1, SPIN_LIMIT)) { *P.status = 8; return; }
-            const float* cs = cbase + s * (U * T);
+            const float* cs = cbase + s * CSTAGE;
             const int un = min(U, P.nd - g * U);
 #pragma unroll
             for (int u = 0; u < U; u++) {
                 if (u >= un) break;                                   // block-uniform: the last group may be partial
                 const unsigned addr = tb + (unsigned)s_p4[g * U + u];
                 const bool ok = (addr - v0) < vlim;
-                float av = cs[u * 256];
+                float av = TRANS ? *reinterpret_cast<const float*>(reinterpret_cast<const char*>(cs + u * CP) + s_c4[g * U + u])
+                                 : cs[u * 256];
                 if (P.fa != 1.f) av = __fmul_rn(P.fa, av);
                 const float2 aa = make_float2(av, av);
                 const float* wp = reinterpret_cast<const float*>(reinterpret_cast<const char*>(win) + addr);
@@ -396,12 +437,12 @@ static int windown_shape(const cuvdia_plan* p, bool trans, const float* B, int l
     return best;
 }
 
-static int windown_tma_shape(const cuvdia_plan* p, const float* A, const float* B, int ldb, int ncols, int* nseg_out,
-                             int* wrows_out);
+static int windown_tma_shape(const cuvdia_plan* p, bool trans, const float* A, const float* B, int ldb, int ncols,
+                             int* nseg_out, int* wrows_out);
 
 bool prod_windown_applicable(const cuvdia_plan* p, bool trans, const float* A, const float* B, int ldb, int ncols) {
     int wrows, nseg;
-    if (!trans && windown_tma_shape(p, A, B, ldb, ncols, &nseg, &wrows) > 0) return true;
+    if (windown_tma_shape(p, trans, A, B, ldb, ncols, &nseg, &wrows) > 0) return true;
     return windown_shape(p, trans, B, ldb, ncols, &wrows) > 0;
 }
 
@@ -419,12 +460,12 @@ static int launch_windown_t(const WindowNParams& P, int rows_out, cudaStream_t s
     return check_launch("prod_windown_kernel");
 }
 
-// The TMA-fed kernel serves the plain product when the diagonals' array and B allow TMA (16-byte aligned, pitches that
+// The TMA-fed kernel serves a product when the diagonals' array and B allow TMA (16-byte aligned, pitches that
 // are multiples of 4), there are at most 1024 diagonals and the rows a block can address fit its window: 5120 rows
-// (one block per SM, three coefficient stages) or 2304 (two blocks per SM, two stages).  Returns the row tiles per
+// (one block per SM, three coefficient stages) or 2176 (two blocks per SM, two stages).  Returns the row tiles per
 // block (0: does not apply) and the window segments.
-static int windown_tma_shape(const cuvdia_plan* p, const float* A, const float* B, int ldb, int ncols, int* nseg_out,
-                             int* wrows_out) {
+static int windown_tma_shape(const cuvdia_plan* p, bool trans, const float* A, const float* B, int ldb, int ncols,
+                             int* nseg_out, int* wrows_out) {
     using namespace pwn;
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
     // (row numbers are compared as byte offsets in 32 bits inside the kernel: matrices of up to 2^29 rows and columns)
@@ -434,10 +475,11 @@ static int windown_tma_shape(const cuvdia_plan* p, const float* A, const float* 
     const long long span = (long long)p->off_max - p->off_min;
     int best = 0;
     for (int nt = 1; nt <= 8; nt *= 2) {
-        if (nt > 1 && (long long)T * nt > p->h) break;
+        const long long rows_out = trans ? p->w : p->h;
+        if (nt > 1 && (long long)T * nt > rows_out) break;
         const long long wrows = (long long)T * nt + span + 3;       // every row the block's outputs can address
         if (wrows > 5120) break;
-        const long long blocks = (((long long)p->h + T * nt - 1) / (T * nt)) * ((ncols + CB - 1) / CB);
+        const long long blocks = ((rows_out + T * nt - 1) / (T * nt)) * ((ncols + CB - 1) / CB);
         if (nt > 1 && (blocks < sm_count() || span < 4LL * T * nt)) break;
         best = nt;
         *nseg_out = (int)((wrows + SEG - 1) / SEG);
@@ -446,43 +488,52 @@ static int windown_tma_shape(const cuvdia_plan* p, const float* A, const float* 
     return best;
 }
 
-template <bool EXACT, int PITCH, int NSTA, int MINB>
+template <bool TRANS, bool EXACT, int PITCH, int NSTA, int MINB>
 static int launch_windown_tma_t(const CUtensorMap& mapA, const WindowTmaParams& P, cudaStream_t st) {
     using namespace pwn;
-    constexpr size_t smem = tma_smem_bytes<PITCH, NSTA>();
+    constexpr size_t smem = tma_smem_bytes<TRANS, PITCH, NSTA>();
     static bool attr_done[64] = {false};
-    const int arc = allow_dynamic_smem(prod_windown_tma_kernel<EXACT, PITCH, NSTA, MINB>, smem, attr_done);
+    const int arc = allow_dynamic_smem(prod_windown_tma_kernel<TRANS, EXACT, PITCH, NSTA, MINB>, smem, attr_done);
     if (arc) return arc;
-    const int gx = (P.h + T * P.tiles - 1) / (T * P.tiles), gy = (P.ncols + CB - 1) / CB;
+    const int rows_out = TRANS ? P.w : P.h;
+    const int gx = (rows_out + T * P.tiles - 1) / (T * P.tiles), gy = (P.ncols + CB - 1) / CB;
     if (gy > 65535) { set_last_error("too many batch columns"); return CUVDIA_ERR_UNSUPPORTED; }
-    prod_windown_tma_kernel<EXACT, PITCH, NSTA, MINB><<<dim3(gx, gy), T + 32, smem, st>>>(mapA, P);
+    prod_windown_tma_kernel<TRANS, EXACT, PITCH, NSTA, MINB><<<dim3(gx, gy), T + 32, smem, st>>>(mapA, P);
     count_launch();
     return check_launch("prod_windown_tma_kernel");
 }
 
 static int launch_prod_windown_tma(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc,
-                                   int ncols, int tiles, int nseg, int wrows, float fa, float fc, int mode, cudaStream_t st) {
+                                   int ncols, bool trans, int tiles, int nseg, int wrows, float fa, float fc, int mode,
+                                   cudaStream_t st) {
     using namespace pwn;
     CUtensorMap mapA;
     int rc = make_map_2d(&mapA, A, p->h, p->nd, p->stride, 256, U);
     if (rc) return rc;
     WindowTmaParams P;
-    P.h = p->h; P.w = p->w; P.nd = p->nd; P.ldb = ldb; P.ldc = ldc; P.ncols = ncols; P.off_min = p->off_min;
+    P.h = p->h; P.w = p->w; P.nd = p->nd; P.S = p->stride; P.ldb = ldb; P.ldc = ldc; P.ncols = ncols;
+    P.off_min = p->off_min; P.off_max = p->off_max; P.A = A;
     P.nseg = nseg; P.tiles = tiles; P.fa = fa; P.fc = fc; P.offs = p->d_offsets; P.B = B; P.C = C; P.status = p->d_status;
     const bool exact = mode == CUVDIA_MODE_EXACT;
-    if (wrows <= 2304)
-        return exact ? launch_windown_tma_t<true, 2304, 2, 2>(mapA, P, st)
-                     : launch_windown_tma_t<false, 2304, 2, 2>(mapA, P, st);
-    return exact ? launch_windown_tma_t<true, 5120, 3, 1>(mapA, P, st)
-                 : launch_windown_tma_t<false, 5120, 3, 1>(mapA, P, st);
+#define GO(TR)                                                                              \
+    do {                                                                                    \
+        if (wrows <= 2176)                                                                  \
+            return exact ? launch_windown_tma_t<TR, true, 2176, 2, 2>(mapA, P, st)          \
+                         : launch_windown_tma_t<TR, false, 2176, 2, 2>(mapA, P, st);        \
+        return exact ? launch_windown_tma_t<TR, true, 5120, 3, 1>(mapA, P, st)              \
+                     : launch_windown_tma_t<TR, false, 5120, 3, 1>(mapA, P, st);            \
+    } while (0)
+    if (trans) GO(true);
+    GO(false);
+#undef GO
 }
 
 int launch_prod_windown(const cuvdia_plan* p, const float* A, const float* B, int ldb, float* C, int ldc, int ncols,
                         bool trans, float fa, float fc, int mode, cudaStream_t st) {
-    if (!trans) {
+    {
         int nseg = 0, wr = 0;
-        const int tiles = windown_tma_shape(p, A, B, ldb, ncols, &nseg, &wr);
-        if (tiles > 0) return launch_prod_windown_tma(p, A, B, ldb, C, ldc, ncols, tiles, nseg, wr, fa, fc, mode, st);
+        const int tiles = windown_tma_shape(p, trans, A, B, ldb, ncols, &nseg, &wr);
+        if (tiles > 0) return launch_prod_windown_tma(p, A, B, ldb, C, ldc, ncols, trans, tiles, nseg, wr, fa, fc, mode, st);
     }
     WindowNParams P;
     int wrows = 0;
