@@ -476,6 +476,17 @@ def fill_rnd_uniform(dst, seed, step=0, col0=0, which=0):
     return dst
 
 
+def rnd_binarize(act, seed, step=0, col0=0, which=0):
+    """act[i, j] = 1 if act[i, j] > u else 0, in place, u the uniform number :func:`fill_rnd_uniform` gives for the same
+    arguments (``rnd_binarize``, random/random.cu:86-91,139-156)."""
+    import ctypes
+    ld = _check_colmajor(act, "act")
+    d = _capi.Draw(int(seed), int(step), int(col0))
+    _capi.check(_capi.lib().cuvdia_rnd_binarize_f32(_ptr(act), ld, int(act.shape[0]), int(act.shape[1]), ctypes.byref(d),
+                                                    int(which), _stream()))
+    return act
+
+
 def bias_sigmoid_draw_sum(act, bias, sample, sum_dst, seed, step=0, col0=0, which=0, sum_of_sample=False, factNew=1.0,
                           factOld=0.0, store_act=True):
     """:func:`bias_sigmoid_sample_sum` with the uniform numbers drawn inside the pass (``rnd_binarize`` fused in,

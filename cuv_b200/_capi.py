@@ -40,6 +40,7 @@ SIGNATURES = {
     "cuvdia_bias_sigmoid_sample_sum_f32": (_i, [_vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _vp, _i, _f, _f, _i, _vp]),
     "cuvdia_rbm_cd1_step_f32": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "cuvdia_uniform_f32": (_i, [_vp, _i, _i, _i, _vp, _i, _vp]),
+    "cuvdia_rnd_binarize_f32": (_i, [_vp, _i, _i, _i, _vp, _i, _vp]),
     "cuvdia_bias_sigmoid_draw_sum_f32": (_i, [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _i, _f, _f, _i, _vp, _i, _vp]),
     "cuvdia_rbm_cd1_step_drawn_f32": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
     "cuvdia_rbm_cd1_step_drawn_allreduce_f32": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _vp]),

@@ -370,6 +370,15 @@ int cuvdia_uniform_f32(float* dst, int ld, int rows, int ncols, const cuvdia_dra
     return launch_uniform(dst, ld, rows, ncols, make_draw(draw, (unsigned)which), (cudaStream_t)stream);
 }
 
+int cuvdia_rnd_binarize_f32(float* act, int ld, int rows, int ncols, const cuvdia_draw* draw, int which, void* stream) {
+    CUVDIA_REQUIRE(act != nullptr && draw != nullptr);
+    CUVDIA_REQUIRE(rows > 0 && ncols >= 0 && ld >= rows);
+    CUVDIA_REQUIRE(which >= 0 && which < 65536);
+    CUVDIA_REQUIRE(draw->col0 >= 0 && draw->step < (1ull << 32));
+    if (ncols == 0) return CUVDIA_OK;
+    return launch_binarize(act, ld, rows, ncols, make_draw(draw, (unsigned)which), (cudaStream_t)stream);
+}
+
 int cuvdia_bias_sigmoid_draw_sum_f32(float* act, int ld, const float* bias, float* sample, int lds, int units, int ncols,
                                      float* sum_dst, int sum_of_sample, float factNew, float factOld, int store_act,
                                      const cuvdia_draw* draw, int which, void* stream) {

@@ -178,6 +178,8 @@ int launch_bias_sigmoid_sample_sum(float* act, int ld, const float* bias, const 
                                    int store_act, cudaStream_t st, const DrawParams* draw = nullptr);
 // dst[row, col] = the uniform number of (row, d.col0 + col) of draw d.which in step d.step
 int launch_uniform(float* dst, int ld, int rows, int ncols, const DrawParams& d, cudaStream_t st);
+// act[row, col] = act[row, col] > that number ? 1 : 0, in place
+int launch_binarize(float* act, int ld, int rows, int ncols, const DrawParams& d, cudaStream_t st);
 int launch_reduce_combine_add(float* dst, long long n_out, float fnew, float fold, int nsplit, const float* partial,
                               cudaStream_t st);
 int launch_axpby(float* dst, const float* x, const float* y, float a, float b, long long n, cudaStream_t st);

@@ -49,6 +49,29 @@ uniform_kernel(float* __restrict__ dst, int ld, int rows, int ncols, const DrawP
     }
 }
 
+// act <- act > u ? 1 : 0 in place, u drawn as above (rnd_binarize, random/random.cu:86-91,139-156).
+__global__ void __launch_bounds__(256)
+binarize_kernel(float* __restrict__ act, int ld, int rows, int ncols, const DrawParams d) {
+    const int groups = (rows + 3) / 4;
+    const long long total = (long long)groups * ncols;
+    for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total;
+         t += (long long)gridDim.x * blockDim.x) {
+        const int col = (int)(t / groups), q = (int)(t - (long long)col * groups);
+        const float4 u = draw4(d, q, d.col0 + col);
+        float* o = act + (size_t)col * ld + 4 * q;
+        const float v[4] = {u.x, u.y, u.z, u.w};
+        for (int e = 0; e < 4 && 4 * q + e < rows; e++) o[e] = o[e] > v[e] ? 1.f : 0.f;
+    }
+}
+
+int launch_binarize(float* act, int ld, int rows, int ncols, const DrawParams& d, cudaStream_t st) {
+    const long long total = (long long)((rows + 3) / 4) * ncols;
+    const int blocks = (int)std::max<long long>(1, std::min<long long>((total + 255) / 256, 16LL * sm_count()));
+    binarize_kernel<<<blocks, 256, 0, st>>>(act, ld, rows, ncols, d);
+    count_launch();
+    return check_launch("binarize_kernel");
+}
+
 int launch_uniform(float* dst, int ld, int rows, int ncols, const DrawParams& d, cudaStream_t st) {
     const long long total = (long long)((rows + 3) / 4) * ncols;
     const int blocks = (int)std::max<long long>(1, std::min<long long>((total + 255) / 256, 16LL * sm_count()));

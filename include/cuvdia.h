@@ -322,6 +322,11 @@ typedef struct cuvdia_draw {
 CUVDIA_API int cuvdia_uniform_f32(float* dst, int ld, int rows, int ncols, const cuvdia_draw* draw, int which,
                                   void* stream);
 
+/* act[row, col] = act[row, col] > u ? 1 : 0 in place, u = that uniform number (rnd_binarize,
+ * random/random.cu:86-91,139-156). */
+CUVDIA_API int cuvdia_rnd_binarize_f32(float* act, int ld, int rows, int ncols, const cuvdia_draw* draw, int which,
+                                       void* stream);
+
 /* cuvdia_bias_sigmoid_sample_sum_f32 with the uniform numbers drawn in the kernel instead of read from u:
  * bit for bit what that call gives on u = cuvdia_uniform_f32(draw, which) (rnd_binarize fused into the pass,
  * random/random.cu:139-156). */

@@ -15,6 +15,8 @@ int oracle_reduce(float* dst, const float* src, long n_contig, long n_strided, i
 int oracle_avg_diagonals(float* dst, const float* vals, const int* offsets, int nd, int h, int w, int stride, int rf);
 int oracle_reduce_typed(void* dst, int dst_type, const void* src, int src_type, long n_contig, long n_strided,
                         int over_strided, int rf, float factNew, float factOld);
+void oracle_uniform(float* dst, long ld, long rows, long ncols, unsigned long long seed, unsigned long long step,
+                    long long col0, int which);
 void oracle_learn_step_weight_decay(float* W, const float* dW, long n, float learnrate, float decay);
 void oracle_learn_step_weight_decay_momentum(float* W, float* M, const float* dW, long n, float lr, float mw, float l2,
                                              int device_formula);

@@ -417,6 +417,61 @@ static void test_given_up_wait_throws() {
     CHECK(thrown);
 }
 
+// fill_rnd_uniform and rnd_binarize (random/random.hpp:48-55): the device numbers are the host restatement's, a second
+// call draws other numbers, re-seeding starts over, and a binarised tensor is the comparison with those numbers.
+static void test_random() {
+    const int h = 37, w = 21;                        // 37 rows: the last group of four is ragged
+    tensor<float, dev_memory_space, column_major> U(h, w), U2(h, w);
+    initialize_mersenne_twister_seeds(99);
+    fill_rnd_uniform(U);
+    fill_rnd_uniform(U2);
+    std::vector<float> r0((size_t)h * w), r1((size_t)h * w);
+    oracle_uniform(r0.data(), h, h, w, 99, 0, 0, 0);
+    oracle_uniform(r1.data(), h, h, w, 99, 1, 0, 0);
+    int bad = 0, same = 0;
+    for (int j = 0; j < w; j++)
+        for (int i = 0; i < h; i++) {
+            const float a = U(i, j), b = U2(i, j);
+            bad += a != r0[(size_t)j * h + i] || b != r1[(size_t)j * h + i] || !(a >= 0.f && a < 1.f);
+            same += a == b;
+        }
+    CHECK(bad == 0);
+    CHECK(same < h * w / 100);
+    initialize_mersenne_twister_seeds(99);
+    tensor<float, dev_memory_space, column_major> P(h, w);
+    tensor<float, host_memory_space, column_major> Ph(h, w);
+    for (int j = 0; j < w; j++)
+        for (int i = 0; i < h; i++) Ph(i, j) = (float)((i * 7 + j * 13) % 11) / 10.f;     // 0 .. 1 in tenths
+    P = Ph;
+    rnd_binarize(P);                                  // draw 0 after the re-seed: compares with r0
+    bad = 0;
+    int ones = 0;
+    for (int j = 0; j < w; j++)
+        for (int i = 0; i < h; i++) {
+            const float want = (float)Ph(i, j) > r0[(size_t)j * h + i] ? 1.f : 0.f;
+            bad += (float)P(i, j) != want;
+            ones += want == 1.f;
+        }
+    CHECK(bad == 0);
+    CHECK(ones > h * w / 4 && ones < 3 * h * w / 4);
+    // a row-major tensor is drawn in memory order: its last dimension is the generator's row
+    tensor<float, dev_memory_space, row_major> R(w, h);
+    initialize_mersenne_twister_seeds(99);
+    fill_rnd_uniform(R);
+    bad = 0;
+    for (int j = 0; j < w; j++)
+        for (int i = 0; i < h; i++) bad += (float)R(j, i) != r0[(size_t)j * h + i];
+    CHECK(bad == 0);
+    tensor<float, dev_memory_space, column_major> v1(50);
+    initialize_mersenne_twister_seeds(3);
+    fill_rnd_uniform(v1);
+    std::vector<float> rv(50);
+    oracle_uniform(rv.data(), 50, 50, 1, 3, 0, 0, 0);
+    bad = 0;
+    for (int i = 0; i < 50; i++) bad += (float)v1(i) != rv[i];
+    CHECK(bad == 0);
+}
+
 int main() {
     try {
         initCUDA(0);
@@ -430,6 +485,7 @@ int main() {
         test_reduce_typed();
         test_reduce_3d();
         test_learn_step();
+        test_random();
         test_given_up_wait_throws();
         exitCUDA();
     } catch (const std::exception& e) {

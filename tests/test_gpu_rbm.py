@@ -352,6 +352,25 @@ def test_device_drawn_uniforms_equal_the_oracle(rows, ncols, ld_pad):
         assert (buf[rows:] == -1.0).all()
 
 
+@pytest.mark.parametrize("rows,ncols,ld_pad", [(1024, 33, 0), (1001, 7, 3), (6, 5, 0)])
+def test_rnd_binarize_equals_the_compare_with_the_oracles_numbers(rows, ncols, ld_pad):
+    """cuvdia_rnd_binarize_f32 (CUV's rnd_binarize): in place, 1 where the activation exceeds the generator's number
+    of that element and 0 elsewhere, rows beyond the matrix in a padded leading dimension untouched."""
+    import cuv_b200 as cb
+    rng = np.random.default_rng(rows * 31 + ncols)
+    act = np.asfortranarray(rng.random((rows, ncols), dtype=np.float32))
+    act[rng.random((rows, ncols)) < 0.05] = 0.0                       # 0 > u never holds, u = 0 included
+    act[rng.random((rows, ncols)) < 0.05] = 1.0                       # 1 > u always holds
+    buf = cb.colmajor_empty(rows + ld_pad, ncols)
+    buf.fill_(-7.0)
+    buf[:rows].copy_(cb.to_device(act))
+    cb.rnd_binarize(buf[:rows], seed=42, step=9, col0=12345, which=1)
+    u = ho.uniform(rows, ncols, seed=42, step=9, col0=12345, which=1)
+    assert_bits_equal(cb.to_host(buf[:rows]), (act > u).astype(np.float32), "binarised activation")
+    if ld_pad:
+        assert (buf[rows:] == -7.0).all()
+
+
 @pytest.mark.parametrize("units,nd,nb", [(1024, 64, 96), (1001, 37, 50)])
 def test_step_with_drawn_samples_equals_the_step_on_those_numbers(units, nd, nb):
     """The step that draws its uniform numbers inside the element-wise passes gives, bit for bit, the step that reads
