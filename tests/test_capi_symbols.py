@@ -53,6 +53,17 @@ def test_preconditions_checked_before_cuda(capi):
     assert L.cuvdia_prod_f32(None, None, None, 0, None, 0, 0, b"n", b"n", 1.0, 0.0, 0, None) == capi.ERR_INVALID
     assert L.cuvdia_reduce_f32(None, None, 1, 1, 0, 0, 1.0, 0.0, None) == capi.ERR_INVALID
     assert L.cuvdia_plan_destroy(None) == 0
+    # the entry points of the device-drawn uniform numbers: a draw descriptor is required and its fields are ranged
+    d = capi.Draw(1, 0, 0)
+    buf = ctypes.c_void_p(16)                            # never dereferenced: the checks come before any CUDA call
+    for fn in (L.cuvdia_uniform_f32, L.cuvdia_rnd_binarize_f32):
+        assert fn(buf, 8, 8, 1, None, 0, None) == capi.ERR_INVALID
+        assert fn(None, 8, 8, 1, ctypes.byref(d), 0, None) == capi.ERR_INVALID
+        assert fn(buf, 4, 8, 1, ctypes.byref(d), 0, None) == capi.ERR_INVALID          # ld < rows
+        assert fn(buf, 8, 8, 1, ctypes.byref(d), 65536, None) == capi.ERR_INVALID      # draw index of 16 bits
+        assert fn(buf, 8, 8, 1, ctypes.byref(capi.Draw(1, 1 << 32, 0)), 0, None) == capi.ERR_INVALID
+        assert fn(buf, 8, 8, 1, ctypes.byref(capi.Draw(1, 0, -1)), 0, None) == capi.ERR_INVALID
+        assert fn(buf, 8, 8, 0, ctypes.byref(d), 0, None) == 0                         # no columns: nothing to do
 
 
 def test_no_cpu_fallback(capi):
