@@ -176,6 +176,7 @@ struct WindowTmaParams {
     int off_min, off_max;
     const float* A;         // the diagonals' values (the transposed product copies its coefficients itself)
     int nseg;               // window segments of 1024 rows
+    int wrows;              // window rows a block's threads can address (a multiple of 4, at most the pitch)
     int tiles;              // row tiles of 512 outputs a block works through with one staged window
     float fa, fc;
     const int* offs; const float* B; float* C;
@@ -301,8 +302,9 @@ prod_windown_tma_kernel(const __grid_constant__ CUtensorMap mapA, const WindowTm
         const int ncol = min(CB, P.ncols - c0);
         for (int sg = 0; sg < P.nseg; sg++) {
             // the segment's rows that lie inside the matrix: whole groups of four by bulk copy, up to three more by hand
+            // (the last segment ends with the window: a column's copy must not run on into the next column's rows)
             const int r0 = lo + sg * SEG;
-            const int v0 = max(r0, 0), v1 = min(r0 + SEG, rows_b);
+            const int v0 = max(r0, 0), v1 = min(min(r0 + SEG, lo + P.wrows), rows_b);
             const int n4 = v1 > v0 ? ((v1 - v0) & ~3) : 0, tail = v1 > v0 ? (v1 - v0) - n4 : 0;
             for (int t = lane; t < tail * ncol; t += 32) {
                 const int c = t / tail, row = v0 + n4 + t % tail;
@@ -513,7 +515,7 @@ static int launch_prod_windown_tma(const cuvdia_plan* p, const float* A, const f
     WindowTmaParams P;
     P.h = p->h; P.w = p->w; P.nd = p->nd; P.S = p->stride; P.ldb = ldb; P.ldc = ldc; P.ncols = ncols;
     P.off_min = p->off_min; P.off_max = p->off_max; P.A = A;
-    P.nseg = nseg; P.tiles = tiles; P.fa = fa; P.fc = fc; P.offs = p->d_offsets; P.B = B; P.C = C; P.status = p->d_status;
+    P.nseg = nseg; P.wrows = (wrows + 3) & ~3; P.tiles = tiles; P.fa = fa; P.fc = fc; P.offs = p->d_offsets; P.B = B; P.C = C; P.status = p->d_status;
     const bool exact = mode == CUVDIA_MODE_EXACT;
 #define GO(TR)                                                                              \
     do {                                                                                    \

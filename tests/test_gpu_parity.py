@@ -132,6 +132,7 @@ def test_prod_steep_band_wide_batches(cb, trans, h, w, rf, lo, nd, ncols, fab, f
     (2200, 2200, 1100, None, 32, 1.0, 0.0),     # more than 1024 diagonals: the variant that fetches its coefficients
     (700, 5000, 64, None, 36, 2.0, 1.0),        # much wider than tall: most of the window lies beyond the outputs' rows
     (8192, 8192, 100, 3000, 36, 1.0, 0.0),      # offsets within +-3000: a window of 6500 rows, four columns per block
+    (4100, 4100, 48, 825, 40, 1.0, 0.0),        # a small window of 2107 / 2135 rows: its third segment is 59 / 87 rows long
 ])
 def test_prod_scattered_staged_window(cb, trans, h, w, nd, spread, ncols, fab, fc):
     """Scattered diagonals with row factor 1 on operands that allow TMA (16-byte aligned, leading dimensions that are
